@@ -1,0 +1,152 @@
+// ---------------------------------------------------------------------------------------------
+// Shared device code of every generated SGEMM translation unit (text-included by the generator,
+// so that the emitted .cu is one self-contained file that nvcc turns into one cubin).
+//
+// Problem: column-major NN FP32 GEMM   D = alpha * A * B + beta * C
+//   A is M x K, element (i,l) at a[i + l*lda]     B is K x N, element (l,j) at b[l + j*ldb]
+//   C, D are M x N, element (i,j) at [i + j*ldc] / [i + j*ldd]
+// (the kernel ABI and the math of the reference kernel: generator/generator.py:2603-2618 for the
+//  fifteen arguments, runner/generator_runner.cpp:16-33 for the arithmetic).
+// ---------------------------------------------------------------------------------------------
+#include <stdint.h>
+
+#ifndef OPT_WGM
+#define OPT_WGM 1
+#endif
+
+// Device status words written by a kernel that gave up on a bounded wait.
+//   status[0] = code (0 ok, 1 wait timed out, 2 aborted because another role timed out)
+//   status[1] = role/barrier tag   status[2] = tile index   status[3] = k-block / stage
+#define SGEMM_STATUS_WORDS 8
+#define SGEMM_STATUS_OK 0u
+#define SGEMM_STATUS_TIMEOUT 1u
+
+// ---------------------------------------------------------------------------------------------
+// Tile rasterisation ("wgm", the workgroup remap of generator/generator.py:1437-1464).
+// wgm <= 1: no remap, z = x + y*nx (M index fastest), as the reference when wgm is 1.
+// wgm  > 1: the linear id z walks groups of `wgm` tiles in M; inside a group the M index moves
+// fastest, then the N index; groups follow each other along M:
+//   x' = (z % wgm) + (z / wgm / ny) * wgm ,  y' = (z / wgm) % ny
+// which is the reference's formula when nx is a multiple of wgm.  The last, narrower group (nx not
+// a multiple of wgm) is walked with its own width so that every tile is visited exactly once.
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ __forceinline__ void sgemm_tile_raster(uint32_t z, uint32_t nx, uint32_t ny,
+                                                           uint32_t wgm, uint32_t &x, uint32_t &y) {
+    if (wgm <= 1) {
+        x = z % nx;
+        y = z / nx;
+        return;
+    }
+    const uint32_t group_tiles = wgm * ny;
+    const uint32_t g = z / group_tiles;
+    const uint32_t first_x = g * wgm;
+    const uint32_t width = (nx - first_x) < wgm ? (nx - first_x) : wgm;
+    const uint32_t r = z - g * group_tiles;
+    x = first_x + r % width;
+    y = r / width;
+}
+
+extern "C" __global__ void sgemm_tile_map(int32_t *xy, uint32_t nx, uint32_t ny) {
+    const uint32_t z = blockIdx.x * blockDim.x + threadIdx.x;
+    if (z >= nx * ny) return;
+    uint32_t x, y;
+    sgemm_tile_raster(z, nx, ny, OPT_WGM, x, y);
+    xy[2 * z] = (int32_t)x;
+    xy[2 * z + 1] = (int32_t)y;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Seeded inputs: splitmix64 finaliser over (element index, stream), top 24 bits -> [-1, 1).
+// Bit-identical to the host generator used by the tests, so that host and device fills agree.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float sgemm_uniform(uint64_t idx, uint64_t stream) {
+    uint64_t x = idx + 0x9E3779B97F4A7C15ull * (stream + 1ull);
+    x ^= x >> 30;
+    x *= 0xBF58476D1CE4E5B9ull;
+    x ^= x >> 27;
+    x *= 0x94D049BB133111EBull;
+    x ^= x >> 31;
+    return (float)(x >> 40) * 0x1p-23f - 1.0f;
+}
+
+extern "C" __global__ void sgemm_fill_uniform(float *dst, uint64_t count, uint64_t first_index,
+                                              uint64_t stream) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride)
+        dst[i] = sgemm_uniform(first_index + i, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Split pre-pass for the 3xTF32 path: lo = x - trunc_tf32(x).  The tensor core reads only the top
+// 19 bits of each FP32 word (sign, 8 exponent, 10 mantissa bits), so the raw FP32 operand already
+// acts as the "hi" term; the remainder is exact in FP32.  One launch covers A's and B's spans.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float sgemm_tf32_lo(float x) {
+    return x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+}
+
+extern "C" __global__ void sgemm_split_lo(const float *__restrict__ src_a, float *__restrict__ lo_a,
+                                          uint64_t count_a, const float *__restrict__ src_b,
+                                          float *__restrict__ lo_b, uint64_t count_b) {
+    // both spans are walked in float4 units; bases are 16-byte aligned (checked on the host)
+    const uint64_t va = count_a >> 2, vb = count_b >> 2;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (uint64_t i = tid; i < va + vb; i += stride) {
+        const bool is_a = i < va;
+        const float4 *s = is_a ? reinterpret_cast<const float4 *>(src_a) + i
+                               : reinterpret_cast<const float4 *>(src_b) + (i - va);
+        float4 *o = is_a ? reinterpret_cast<float4 *>(lo_a) + i
+                         : reinterpret_cast<float4 *>(lo_b) + (i - va);
+        float4 v = __ldg(s);
+        v.x = sgemm_tf32_lo(v.x);
+        v.y = sgemm_tf32_lo(v.y);
+        v.z = sgemm_tf32_lo(v.z);
+        v.w = sgemm_tf32_lo(v.w);
+        *o = v;
+    }
+    if (tid < (count_a & 3)) lo_a[(va << 2) + tid] = sgemm_tf32_lo(src_a[(va << 2) + tid]);
+    if (tid < (count_b & 3)) lo_b[(vb << 2) + tid] = sgemm_tf32_lo(src_b[(vb << 2) + tid]);
+}
+
+// K-major packing of A for the tensor path's alternative operand layout: writes
+//   hi_t[l + i*ldt] = a[i + l*lda]  and  lo_t[l + i*ldt] = lo(a[i + l*lda])   (32x32 smem transpose)
+extern "C" __global__ void sgemm_pack_a_kmajor(const float *__restrict__ a, uint32_t lda, uint32_t m,
+                                               uint32_t k, float *__restrict__ hi_t,
+                                               float *__restrict__ lo_t, uint32_t ldt) {
+    __shared__ float tile[32][33];
+    const uint32_t i0 = blockIdx.x * 32, l0 = blockIdx.y * 32;
+    for (uint32_t r = threadIdx.y; r < 32; r += blockDim.y) {
+        const uint32_t i = i0 + threadIdx.x, l = l0 + r;
+        tile[r][threadIdx.x] = (i < m && l < k) ? a[i + (uint64_t)l * lda] : 0.0f;
+    }
+    __syncthreads();
+    for (uint32_t r = threadIdx.y; r < 32; r += blockDim.y) {
+        const uint32_t i = i0 + r, l = l0 + threadIdx.x;
+        if (i < m && l < k) {
+            const float v = tile[threadIdx.x][r];
+            hi_t[l + (uint64_t)i * ldt] = v;
+            lo_t[l + (uint64_t)i * ldt] = sgemm_tf32_lo(v);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Deterministic split-K second pass: D = alpha * (ws[0] + ws[1] + ... in fixed order) + beta * C.
+// ws holds nsplit dense M x N partial products (leading dimension M).  nsplit = 0 gives
+// D = beta * C, which is also how K = 0 is served.
+// ---------------------------------------------------------------------------------------------
+extern "C" __global__ void sgemm_splitk_reduce(const float *__restrict__ ws, const float *c, float *d,
+                                               uint32_t m, uint32_t n, uint32_t ldc, uint32_t ldd,
+                                               float alpha, float beta, uint32_t nsplit) {
+    const uint64_t total = (uint64_t)m * n;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t e = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+        const uint32_t i = (uint32_t)(e % m), j = (uint32_t)(e / m);
+        float acc = 0.0f;
+        for (uint32_t s = 0; s < nsplit; ++s) acc += ws[(uint64_t)s * total + e];
+        float r = alpha * acc;
+        if (beta != 0.0f) r = fmaf(beta, c[i + (uint64_t)j * ldc], r);
+        d[i + (uint64_t)j * ldd] = r;
+    }
+}

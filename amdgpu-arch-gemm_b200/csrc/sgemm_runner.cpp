@@ -1,0 +1,853 @@
+// libsgemm_runner.so — CUDA-driver runner behind the C ABI of include/sgemm_runner.h.
+//
+// Replaces the host side of the reference's runner (runner/generator_runner.cpp:69-190: module load,
+// TOML -> config, kernel-argument packing, launch) for sm_100a cubins produced by generator.compile().
+// The CUDA driver is bound at run time with dlopen("libcuda.so.1"), so the library itself loads (and its
+// host-only entry points work) on a machine without a GPU; every device entry point then fails loudly.
+#include "sgemm_runner.h"
+#include "sgemm_toml.hpp"
+
+#include <cuda.h>
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <utility>
+#include <vector>
+
+#define SGEMM_API extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+// ------------------------------------------------------------------------------------ driver binding
+#define SGEMM_STR2(x) #x
+#define SGEMM_STR(x) SGEMM_STR2(x)
+#define DRIVER_FUNCTIONS(X)                                                                              \
+    X(cuInit) X(cuDeviceGet) X(cuDeviceGetCount) X(cuDeviceGetAttribute) X(cuDevicePrimaryCtxRetain)     \
+    X(cuDevicePrimaryCtxRelease) X(cuCtxPushCurrent) X(cuCtxPopCurrent) X(cuModuleLoad) X(cuModuleUnload) \
+    X(cuModuleGetFunction) X(cuFuncSetAttribute) X(cuLaunchKernel) X(cuTensorMapEncodeTiled)             \
+    X(cuMemAlloc) X(cuMemFree) X(cuMemcpyHtoDAsync) X(cuMemcpyDtoHAsync) X(cuMemcpyHtoD) X(cuMemcpyDtoH) \
+    X(cuMemsetD8) X(cuMemsetD32Async) X(cuStreamSynchronize) X(cuCtxSynchronize) X(cuEventCreate)        \
+    X(cuEventRecord) X(cuEventSynchronize) X(cuEventElapsedTime) X(cuEventDestroy) X(cuGetErrorString)   \
+    X(cuGetErrorName)
+
+struct Driver {
+#define DECL(name) decltype(&name) name##_ = nullptr;
+    DRIVER_FUNCTIONS(DECL)
+#undef DECL
+    bool ok = false;
+    std::string error;
+};
+
+Driver &driver() {
+    static Driver d;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *lib = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+        if (!lib) lib = dlopen("libcuda.so", RTLD_NOW | RTLD_GLOBAL);
+        if (!lib) {
+            const char *why = dlerror();  // one call: dlerror clears its message when read
+            d.error = std::string("cannot load the CUDA driver: ") + (why ? why : "libcuda.so.1 not found");
+            return;
+        }
+        // cuda.h renames some entry points with macros (cuMemAlloc -> cuMemAlloc_v2): SGEMM_STR expands them.
+#define LOAD(name)                                                                   \
+        d.name##_ = reinterpret_cast<decltype(&name)>(dlsym(lib, SGEMM_STR(name)));  \
+        if (!d.name##_) { d.error = std::string("CUDA driver lacks ") + SGEMM_STR(name); return; }
+        DRIVER_FUNCTIONS(LOAD)
+#undef LOAD
+        CUresult r = d.cuInit_(0);
+        if (r != CUDA_SUCCESS) {
+            d.error = "cuInit failed with code " + std::to_string((int)r);
+            return;
+        }
+        d.ok = true;
+    });
+    return d;
+}
+
+thread_local std::string g_open_error;
+
+constexpr int kStatusWords = 8;
+constexpr int kVariantSimt = 0, kVariantTensor = 1;
+
+struct TensorMapKey {
+    const void *base = nullptr;
+    uint64_t d0 = 0, d1 = 0, stride = 0;
+    uint32_t b0 = 0, b1 = 0;
+    bool operator==(const TensorMapKey &o) const {
+        return base == o.base && d0 == o.d0 && d1 == o.d1 && stride == o.stride && b0 == o.b0 && b1 == o.b1;
+    }
+};
+struct CachedMap {
+    TensorMapKey key;
+    alignas(64) CUtensorMap map;
+    bool valid = false;
+};
+
+}  // namespace
+
+struct sgemm_handle {
+    sgemm_config cfg{};
+    int device = 0;
+    CUdevice cu_device = 0;
+    CUcontext ctx = nullptr;
+    CUmodule module = nullptr;
+    CUfunction fn_main = nullptr, fn_simt = nullptr, fn_split_lo = nullptr, fn_pack_a = nullptr,
+               fn_reduce = nullptr, fn_fill = nullptr, fn_tile_map = nullptr;
+    int sm_count = 0;
+    uint32_t tile_m = 0, tile_n = 0;
+    CUdeviceptr status = 0;
+    // workspace: owned (grow on demand) or lent
+    CUdeviceptr ws_owned = 0;
+    size_t ws_owned_bytes = 0;
+    CUdeviceptr ws_lent = 0;
+    size_t ws_lent_bytes = 0;
+    // host-path staging
+    CUdeviceptr stage[4] = {0, 0, 0, 0};
+    size_t stage_bytes[4] = {0, 0, 0, 0};
+    // options and facts
+    int64_t force_variant = 0, split_k_opt = 0, simt_below_flops = (int64_t)1 << 27;
+    int64_t last_variant = 0, last_split_k = 1, last_grid = 0, launches = 0;
+    CachedMap maps[4];
+    // optional timing of the main GEMM kernel alone (events around it on the caller's stream)
+    bool profile = false;
+    std::vector<std::pair<CUevent, CUevent>> prof_events;
+    size_t prof_used = 0;
+    std::string error;
+};
+
+namespace {
+
+int fail(sgemm_handle *h, int code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (h) h->error = buf; else g_open_error = buf;
+    return code;
+}
+
+std::string cu_text(CUresult r) {
+    const char *name = nullptr, *text = nullptr;
+    Driver &d = driver();
+    if (d.ok) {
+        d.cuGetErrorName_(r, &name);
+        d.cuGetErrorString_(r, &text);
+    }
+    return std::string(name ? name : "CUDA_ERROR") + " (" + std::to_string((int)r) + "): " + (text ? text : "?");
+}
+
+#define CU_CHECK(h, call)                                                                         \
+    do {                                                                                          \
+        CUresult _r = (call);                                                                     \
+        if (_r != CUDA_SUCCESS) return fail(h, SGEMM_ERR_CUDA, "%s -> %s", #call, cu_text(_r).c_str()); \
+    } while (0)
+
+struct CtxGuard {
+    bool pushed = false;
+    explicit CtxGuard(sgemm_handle *h) {
+        if (h && h->ctx && driver().ok) pushed = driver().cuCtxPushCurrent_(h->ctx) == CUDA_SUCCESS;
+    }
+    ~CtxGuard() {
+        if (pushed) {
+            CUcontext c;
+            driver().cuCtxPopCurrent_(&c);
+        }
+    }
+};
+
+size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// ------------------------------------------------------------------------------------ launch plan
+struct Plan {
+    int variant = kVariantSimt;   // which kernel
+    uint32_t split_k = 1;
+    uint32_t tiles_m = 0, tiles_n = 0;
+    uint32_t grid_x = 0;
+    size_t lo_a_off = 0, lo_b_off = 0, hi_a_off = 0, partial_off = 0;  // byte offsets into the workspace
+    uint64_t span_a = 0, span_b = 0;                                    // floats walked by the split pre-pass
+    uint32_t ldt = 0;                                                   // K-major packed A: leading dimension
+    size_t ws_bytes = 0;
+};
+
+bool tensor_eligible(const sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_t n, uint32_t k,
+                     uint32_t lda, uint32_t ldb) {
+    (void)m; (void)n; (void)k;
+    if (h->cfg.variant != kVariantTensor) return false;
+    // TMA: 16-byte aligned bases and row pitches that are multiples of 16 bytes
+    if (((uintptr_t)a & 15) || ((uintptr_t)b & 15)) return false;
+    if ((ldb % 4) != 0) return false;
+    if (!h->cfg.a_kmajor && (lda % 4) != 0) return false;
+    return true;
+}
+
+uint32_t pick_split_k(const sgemm_handle *h, uint32_t tiles, uint32_t k, uint32_t bk) {
+    const uint32_t kb_total = (k + bk - 1) / bk;
+    uint32_t split = 1;
+    if (h->split_k_opt > 0) {
+        split = (uint32_t)h->split_k_opt;
+    } else if (tiles * 2 <= (uint32_t)h->sm_count && kb_total >= 16) {
+        // too few tiles to fill the device: cut K so that about one launch unit per SM exists, keeping at
+        // least 8 k-blocks per split so the partial-sum traffic stays small next to the operand traffic
+        split = std::min<uint32_t>({(uint32_t)h->sm_count / tiles, kb_total / 8, 32u});
+    }
+    split = std::max<uint32_t>(1, std::min(split, std::max<uint32_t>(kb_total, 1)));
+    // no empty splits: recompute from the per-split block count
+    const uint32_t per = (std::max<uint32_t>(kb_total, 1) + split - 1) / split;
+    return (std::max<uint32_t>(kb_total, 1) + per - 1) / per;
+}
+
+int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_t n, uint32_t k, uint32_t lda,
+              uint32_t ldb, Plan *p) {
+    const bool eligible = tensor_eligible(h, a, b, m, n, k, lda, ldb);
+    int variant;
+    if (h->force_variant == 1) {
+        if (!eligible)
+            return fail(h, SGEMM_ERR_UNSUPPORTED,
+                        "tensor variant forced but not usable: cubin variant %d, lda %u, ldb %u, bases %p %p "
+                        "(needs a tcgen05 cubin, 16-byte aligned A/B and lda, ldb multiples of 4)",
+                        h->cfg.variant, lda, ldb, a, b);
+        variant = kVariantTensor;
+    } else if (h->force_variant == 2) {
+        variant = kVariantSimt;
+    } else {
+        const double flops = 2.0 * m * n * k;
+        variant = (eligible && flops >= (double)h->simt_below_flops) ? kVariantTensor : kVariantSimt;
+    }
+    p->variant = variant;
+    size_t off = 0;
+    if (variant == kVariantTensor) {
+        p->tiles_m = (m + h->tile_m - 1) / h->tile_m;
+        p->tiles_n = (n + h->tile_n - 1) / h->tile_n;
+        p->split_k = pick_split_k(h, p->tiles_m * p->tiles_n, k, (uint32_t)h->cfg.depth_k);
+        const uint64_t units = (uint64_t)p->tiles_m * p->tiles_n * p->split_k;
+        p->grid_x = (uint32_t)std::min<uint64_t>(units, (uint64_t)h->sm_count);
+        p->span_b = (uint64_t)ldb * (n - 1) + k;
+        if (h->cfg.a_kmajor) {
+            p->ldt = (uint32_t)round_up(k, 4);
+            p->hi_a_off = off; off += round_up((size_t)p->ldt * m * 4, 256);
+            p->lo_a_off = off; off += round_up((size_t)p->ldt * m * 4, 256);
+            p->span_a = 0;
+        } else {
+            p->span_a = (uint64_t)lda * (k - 1) + m;
+            p->lo_a_off = off; off += round_up(p->span_a * 4, 256);
+        }
+        p->lo_b_off = off; off += round_up(p->span_b * 4, 256);
+    } else {
+        const bool own = h->cfg.variant == kVariantSimt;
+        const uint32_t tm = own ? h->tile_m : (uint32_t)h->cfg.fallback_tile[0];
+        const uint32_t tn = own ? h->tile_n : (uint32_t)h->cfg.fallback_tile[1];
+        const uint32_t bk = own ? (uint32_t)h->cfg.depth_k : (uint32_t)h->cfg.fallback_tile[2];
+        p->tiles_m = (m + tm - 1) / tm;
+        p->tiles_n = (n + tn - 1) / tn;
+        p->split_k = pick_split_k(h, p->tiles_m * p->tiles_n, k, bk);
+        p->grid_x = p->tiles_m * p->tiles_n;
+    }
+    if (p->split_k > 1) {
+        p->partial_off = off;
+        off += round_up((size_t)p->split_k * m * n * 4, 256);
+    }
+    p->ws_bytes = off;
+    return SGEMM_OK;
+}
+
+int ensure_workspace(sgemm_handle *h, size_t bytes, CUdeviceptr *ws) {
+    *ws = 0;
+    if (bytes == 0) return SGEMM_OK;
+    if (h->ws_lent) {
+        if (bytes > h->ws_lent_bytes)
+            return fail(h, SGEMM_ERR_WORKSPACE, "lent workspace holds %zu bytes, this call needs %zu",
+                        h->ws_lent_bytes, bytes);
+        *ws = h->ws_lent;
+        return SGEMM_OK;
+    }
+    if (bytes > h->ws_owned_bytes) {
+        Driver &d = driver();
+        if (h->ws_owned) {
+            CU_CHECK(h, d.cuCtxSynchronize_());  // kernels of earlier calls may still use the old block
+            d.cuMemFree_(h->ws_owned);
+            h->ws_owned = 0;
+            h->ws_owned_bytes = 0;
+        }
+        const size_t want = round_up(bytes, (size_t)1 << 20);
+        CUresult r = d.cuMemAlloc_(&h->ws_owned, want);
+        if (r != CUDA_SUCCESS)
+            return fail(h, SGEMM_ERR_WORKSPACE, "cuMemAlloc of %zu workspace bytes failed: %s", want, cu_text(r).c_str());
+        h->ws_owned_bytes = want;
+    }
+    *ws = h->ws_owned;
+    return SGEMM_OK;
+}
+
+int encode_map(sgemm_handle *h, int slot, const void *base, uint64_t d0, uint64_t d1, uint64_t stride_bytes,
+               uint32_t b0, uint32_t b1, const CUtensorMap **out) {
+    CachedMap &c = h->maps[slot];
+    TensorMapKey key{base, d0, d1, stride_bytes, b0, b1};
+    if (!(c.valid && c.key == key)) {
+        const cuuint64_t dims[2] = {d0, d1};
+        const cuuint64_t strides[1] = {stride_bytes};
+        const cuuint32_t box[2] = {b0, b1};
+        const cuuint32_t estr[2] = {1, 1};
+        CUresult r = driver().cuTensorMapEncodeTiled_(&c.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                                                      const_cast<void *>(base), dims, strides, box, estr,
+                                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return fail(h, SGEMM_ERR_CUDA, "cuTensorMapEncodeTiled(base %p, dims %llu x %llu, pitch %llu, box %u x %u) -> %s",
+                        base, (unsigned long long)d0, (unsigned long long)d1, (unsigned long long)stride_bytes,
+                        b0, b1, cu_text(r).c_str());
+        c.key = key;
+        c.valid = true;
+    }
+    *out = &c.map;
+    return SGEMM_OK;
+}
+
+int launch(sgemm_handle *h, CUfunction f, uint32_t gx, uint32_t gy, uint32_t gz, uint32_t bx, uint32_t by,
+           uint32_t smem, CUstream s, void **params) {
+    CU_CHECK(h, driver().cuLaunchKernel_(f, gx, gy, gz, bx, by, 1, smem, s, params, nullptr));
+    ++h->launches;
+    return SGEMM_OK;
+}
+
+// Launch the main GEMM kernel; with the "profile" option on, bracket it with an event pair so that its
+// duration can be read back separately from the pre-pass and the reduction (sgemm_get_info "profile_*").
+int launch_main(sgemm_handle *h, CUfunction f, uint32_t gx, uint32_t gz, uint32_t threads, uint32_t smem, CUstream s,
+                void **params) {
+    constexpr size_t kMaxPairs = 8192;
+    if (!h->profile || h->prof_used >= kMaxPairs) return launch(h, f, gx, 1, gz, threads, 1, smem, s, params);
+    Driver &d = driver();
+    if (h->prof_used == h->prof_events.size()) {
+        CUevent e0, e1;
+        CU_CHECK(h, d.cuEventCreate_(&e0, CU_EVENT_DEFAULT));
+        CU_CHECK(h, d.cuEventCreate_(&e1, CU_EVENT_DEFAULT));
+        h->prof_events.emplace_back(e0, e1);
+    }
+    auto &pair = h->prof_events[h->prof_used];
+    CU_CHECK(h, d.cuEventRecord_(pair.first, s));
+    int rc = launch(h, f, gx, 1, gz, threads, 1, smem, s, params);
+    if (rc) return rc;
+    CU_CHECK(h, d.cuEventRecord_(pair.second, s));
+    ++h->prof_used;
+    return SGEMM_OK;
+}
+
+int check_problem(sgemm_handle *h, const void *a, const void *b, const void *c, const void *d, float beta,
+                  uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd) {
+    if (!h) return SGEMM_ERR_INVALID_ARGUMENT;
+    if (m && n && !d) return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "D is NULL");
+    if (m && n && k && (!a || !b)) return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "A or B is NULL");
+    if (m && n && beta != 0.0f && !c) return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "C is NULL but beta != 0");
+    if (lda < std::max(m, 1u) || ldb < std::max(k, 1u) || ldd < std::max(m, 1u) || (beta != 0.0f && ldc < std::max(m, 1u)))
+        return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "leading dimension too small: lda %u ldb %u ldc %u ldd %u for M %u K %u",
+                    lda, ldb, ldc, ldd, m, k);
+    if ((uint64_t)m * n >= ((uint64_t)1 << 40)) return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "problem too large");
+    return SGEMM_OK;
+}
+
+int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float *dC, float *dD, float alpha,
+                  float beta, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb, uint32_t ldc,
+                  uint32_t ldd, CUstream stream) {
+    int rc = check_problem(h, dA, dB, dC, dD, beta, m, n, k, lda, ldb, ldc, ldd);
+    if (rc) return rc;
+    if (m == 0 || n == 0) return SGEMM_OK;
+    CUdeviceptr status = h->status;
+    if (k == 0) {  // D = beta * C: the reduction kernel with zero partial products
+        const float *ws0 = nullptr;
+        uint32_t zero = 0;
+        void *params[] = {&ws0, &dC, &dD, &m, &n, &ldc, &ldd, &alpha, &beta, &zero};
+        const uint32_t blocks = (uint32_t)std::min<uint64_t>(((uint64_t)m * n + 255) / 256, (uint64_t)h->sm_count * 8);
+        h->last_variant = 2; h->last_split_k = 1; h->last_grid = blocks;
+        return launch(h, h->fn_reduce, blocks, 1, 1, 256, 1, 0, stream, params);
+    }
+    Plan p;
+    rc = make_plan(h, dA, dB, m, n, k, lda, ldb, &p);
+    if (rc) return rc;
+    CUdeviceptr ws = 0;
+    rc = ensure_workspace(h, p.ws_bytes, &ws);
+    if (rc) return rc;
+    float *partial = p.split_k > 1 ? reinterpret_cast<float *>(ws + p.partial_off) : nullptr;
+    int32_t nwx = (int32_t)p.tiles_m, nwy = (int32_t)p.tiles_n;
+    uint32_t split = p.split_k;
+    uint32_t *status_ptr = reinterpret_cast<uint32_t *>(status);
+
+    if (p.variant == kVariantTensor) {
+        float *lo_a = reinterpret_cast<float *>(ws + p.lo_a_off);
+        float *lo_b = reinterpret_cast<float *>(ws + p.lo_b_off);
+        const uint32_t bk = (uint32_t)h->cfg.depth_k, bn = h->tile_n;
+        const CUtensorMap *ma_hi, *ma_lo, *mb_hi, *mb_lo;
+        const uint32_t blocks = (uint32_t)h->sm_count * 4;
+        if (h->cfg.a_kmajor) {
+            float *hi_t = reinterpret_cast<float *>(ws + p.hi_a_off);
+            void *pp[] = {&dA, &lda, &m, &k, &hi_t, &lo_a, &p.ldt};
+            rc = launch(h, h->fn_pack_a, (m + 31) / 32, (k + 31) / 32, 1, 32, 8, 0, stream, pp);
+            if (rc) return rc;
+            const float *na = nullptr;
+            uint64_t zero = 0;
+            void *ps[] = {&na, &na, &zero, &dB, &lo_b, &p.span_b};
+            rc = launch(h, h->fn_split_lo, blocks, 1, 1, 256, 1, 0, stream, ps);
+            if (rc) return rc;
+            if ((rc = encode_map(h, 0, hi_t, k, m, (uint64_t)p.ldt * 4, 32, 128, &ma_hi))) return rc;
+            if ((rc = encode_map(h, 1, lo_a, k, m, (uint64_t)p.ldt * 4, 32, 128, &ma_lo))) return rc;
+        } else {
+            void *ps[] = {&dA, &lo_a, &p.span_a, &dB, &lo_b, &p.span_b};
+            rc = launch(h, h->fn_split_lo, blocks, 1, 1, 256, 1, 0, stream, ps);
+            if (rc) return rc;
+            if ((rc = encode_map(h, 0, dA, m, k, (uint64_t)lda * 4, 32, bk, &ma_hi))) return rc;
+            if ((rc = encode_map(h, 1, lo_a, m, k, (uint64_t)lda * 4, 32, bk, &ma_lo))) return rc;
+        }
+        if ((rc = encode_map(h, 2, dB, k, n, (uint64_t)ldb * 4, 32, bn, &mb_hi))) return rc;
+        if ((rc = encode_map(h, 3, lo_b, k, n, (uint64_t)ldb * 4, 32, bn, &mb_lo))) return rc;
+        void *params[] = {&dA, &dB, &dC, &dD, &m, &n, &k, &lda, &ldb, &ldc, &ldd, &alpha, &beta, &nwx, &nwy,
+                          &partial, &status_ptr, &split,
+                          const_cast<CUtensorMap *>(ma_hi), const_cast<CUtensorMap *>(ma_lo),
+                          const_cast<CUtensorMap *>(mb_hi), const_cast<CUtensorMap *>(mb_lo)};
+        rc = launch_main(h, h->fn_main, p.grid_x, 1, (uint32_t)h->cfg.num_threads,
+                         (uint32_t)h->cfg.dynamic_smem_bytes, stream, params);
+        if (rc) return rc;
+    } else {
+        const bool own = h->cfg.variant == kVariantSimt;
+        CUfunction f = own ? h->fn_main : h->fn_simt;
+        const uint32_t threads = own ? (uint32_t)h->cfg.num_threads : (uint32_t)h->cfg.fallback_threads;
+        void *params[] = {&dA, &dB, &dC, &dD, &m, &n, &k, &lda, &ldb, &ldc, &ldd, &alpha, &beta, &nwx, &nwy,
+                          &partial, &status_ptr, &split};
+        rc = launch_main(h, f, p.grid_x, p.split_k, threads, 0, stream, params);
+        if (rc) return rc;
+    }
+    if (p.split_k > 1) {
+        const float *wsp = partial;
+        void *params[] = {&wsp, &dC, &dD, &m, &n, &ldc, &ldd, &alpha, &beta, &split};
+        const uint32_t blocks = (uint32_t)std::min<uint64_t>(((uint64_t)m * n + 255) / 256, (uint64_t)h->sm_count * 8);
+        rc = launch(h, h->fn_reduce, blocks, 1, 1, 256, 1, 0, stream, params);
+        if (rc) return rc;
+    }
+    h->last_variant = p.variant == kVariantTensor ? 1 : 2;
+    h->last_split_k = p.split_k;
+    h->last_grid = p.grid_x;
+    return SGEMM_OK;
+}
+
+int config_from_toml(const char *path, sgemm_config *c, std::string *err) {
+    sgemm_toml::Table t;
+    if (!sgemm_toml::parse_file(path, &t, err)) return SGEMM_ERR_TOML;
+    std::memset(c, 0, sizeof *c);
+    auto need_int = [&](const char *key, int32_t *dst) {
+        int64_t v;
+        if (!t.get_int(key, &v)) { *err = std::string("missing or non-integer key '") + key + "' in " + path; return false; }
+        *dst = (int32_t)v;
+        return true;
+    };
+    auto need_arr = [&](const char *key, int32_t *dst, size_t count) {
+        std::vector<int64_t> v;
+        if (!t.get_int_array(key, &v) || v.size() != count) {
+            *err = std::string("missing key or wrong length for integer array '") + key + "' in " + path;
+            return false;
+        }
+        for (size_t i = 0; i < count; ++i) dst[i] = (int32_t)v[i];
+        return true;
+    };
+    auto need_bool = [&](const char *key, int32_t *dst) {
+        bool v;
+        if (!t.get_bool(key, &v)) { *err = std::string("missing or non-boolean key '") + key + "' in " + path; return false; }
+        *dst = v ? 1 : 0;
+        return true;
+    };
+    // the keys the reference's runner reads (runner/generator_runner.cpp:103-122) are all required
+    if (!need_int("a_type", &c->a_type) || !need_int("b_type", &c->b_type) || !need_int("cd_type", &c->cd_type) ||
+        !need_int("scalar_type", &c->scalar_type) || !need_arr("mfma", c->mfma, 4) ||
+        !need_arr("wave_group", c->wave_group, 2) || !need_arr("wave_tiling", c->wave_tiling, 2) ||
+        !need_int("depth_k", &c->depth_k) || !need_bool("trans_a", &c->trans_a) || !need_bool("trans_b", &c->trans_b) ||
+        !need_int("wavefront_size", &c->wavefront_size) || !need_int("lds_usage_bytes", &c->lds_usage_bytes))
+        return SGEMM_ERR_TOML;
+    int64_t v;
+    c->vmem_stage = t.get_int("vmem_stage", &v) ? (int32_t)v : 1;
+    std::string s;
+    c->variant = (t.get_string("variant", &s) && s == "tcgen05_3xtf32") ? kVariantTensor : kVariantSimt;
+    c->num_threads = t.get_int("num_threads", &v) ? (int32_t)v : c->wave_group[0] * c->wave_group[1] * c->wavefront_size;
+    c->dynamic_smem_bytes = t.get_int("dynamic_smem_bytes", &v) ? (int32_t)v : 0;
+    c->stages = t.get_int("stages", &v) ? (int32_t)v : c->vmem_stage + 1;
+    c->a_kmajor = (t.get_string("a_major", &s) && s == "k") ? 1 : 0;
+    std::vector<int64_t> fb;
+    if (t.get_int_array("fallback_tile", &fb) && fb.size() == 3)
+        for (int i = 0; i < 3; ++i) c->fallback_tile[i] = (int32_t)fb[i];
+    c->fallback_threads = t.get_int("fallback_threads", &v) ? (int32_t)v : 0;
+    std::snprintf(c->entry, sizeof c->entry, "%s", t.get_string("entry", &s) ? s.c_str() : "generated_gemm");
+    std::snprintf(c->fallback_entry, sizeof c->fallback_entry, "%s", t.get_string("fallback_entry", &s) ? s.c_str() : "");
+    if (c->trans_a || c->trans_b) { *err = "transposed operands are not supported by these kernels"; return SGEMM_ERR_TOML; }
+    if (c->variant == kVariantTensor && (c->fallback_threads <= 0 || c->fallback_tile[0] <= 0 || !c->fallback_entry[0])) {
+        *err = "tensor-variant config lacks the fallback_* keys";
+        return SGEMM_ERR_TOML;
+    }
+    for (int i = 0; i < 2; ++i)
+        if (c->mfma[i] <= 0 || c->wave_group[i] <= 0 || c->wave_tiling[i] <= 0) { *err = "non-positive tiling value"; return SGEMM_ERR_TOML; }
+    if (c->depth_k <= 0 || c->num_threads <= 0) { *err = "non-positive depth_k or num_threads"; return SGEMM_ERR_TOML; }
+    return SGEMM_OK;
+}
+
+}  // namespace
+
+// =============================================================================================== ABI
+SGEMM_API const char *sgemm_strerror(int code) {
+    switch (code) {
+        case SGEMM_OK: return "ok";
+        case SGEMM_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case SGEMM_ERR_TOML: return "kernel config (TOML) unreadable or incomplete";
+        case SGEMM_ERR_NO_DRIVER: return "CUDA driver not available";
+        case SGEMM_ERR_CUDA: return "CUDA driver call failed";
+        case SGEMM_ERR_MODULE: return "cubin could not be loaded or lacks an entry point";
+        case SGEMM_ERR_UNSUPPORTED: return "request not supported by the loaded kernel";
+        case SGEMM_ERR_WORKSPACE: return "workspace too small or allocation failed";
+        case SGEMM_ERR_DEVICE_STATUS: return "a kernel gave up on a bounded wait";
+        default: return "unknown error";
+    }
+}
+
+SGEMM_API const char *sgemm_last_error(sgemm_handle *h) { return h ? h->error.c_str() : g_open_error.c_str(); }
+
+SGEMM_API int sgemm_device_count(void) {
+    Driver &d = driver();
+    if (!d.ok) return 0;
+    int n = 0;
+    return d.cuDeviceGetCount_(&n) == CUDA_SUCCESS ? n : 0;
+}
+
+SGEMM_API int sgemm_config_parse(const char *toml_path, sgemm_config *out) {
+    if (!toml_path || !out) return fail(nullptr, SGEMM_ERR_INVALID_ARGUMENT, "NULL argument");
+    std::string err;
+    int rc = config_from_toml(toml_path, out, &err);
+    if (rc) return fail(nullptr, rc, "%s", err.c_str());
+    return SGEMM_OK;
+}
+
+SGEMM_API int sgemm_config_tile(const sgemm_config *cfg, uint32_t *tile_m, uint32_t *tile_n) {
+    if (!cfg || !tile_m || !tile_n) return SGEMM_ERR_INVALID_ARGUMENT;
+    *tile_m = (uint32_t)(cfg->mfma[0] * cfg->wave_group[0] * cfg->wave_tiling[0]);
+    *tile_n = (uint32_t)(cfg->mfma[1] * cfg->wave_group[1] * cfg->wave_tiling[1]);
+    return SGEMM_OK;
+}
+
+SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int device, sgemm_handle **out) {
+    if (!cubin_path || !toml_path || !out) return fail(nullptr, SGEMM_ERR_INVALID_ARGUMENT, "NULL argument");
+    *out = nullptr;
+    sgemm_config cfg;
+    std::string err;
+    int rc = config_from_toml(toml_path, &cfg, &err);
+    if (rc) return fail(nullptr, rc, "%s", err.c_str());
+    FILE *probe = std::fopen(cubin_path, "rb");
+    if (!probe) return fail(nullptr, SGEMM_ERR_MODULE, "cannot open cubin '%s'", cubin_path);
+    std::fclose(probe);
+    Driver &d = driver();
+    if (!d.ok) return fail(nullptr, SGEMM_ERR_NO_DRIVER, "%s", d.error.c_str());
+    int count = 0;
+    if (d.cuDeviceGetCount_(&count) != CUDA_SUCCESS || device < 0 || device >= count)
+        return fail(nullptr, SGEMM_ERR_INVALID_ARGUMENT, "device %d not present (%d visible)", device, count);
+
+    sgemm_handle *h = new sgemm_handle();
+    h->cfg = cfg;
+    h->device = device;
+    sgemm_config_tile(&cfg, &h->tile_m, &h->tile_n);
+    auto bail = [&](int code) {
+        g_open_error = h->error;
+        sgemm_close(h);
+        return code;
+    };
+    CUresult r;
+    if ((r = d.cuDeviceGet_(&h->cu_device, device)) != CUDA_SUCCESS ||
+        (r = d.cuDevicePrimaryCtxRetain_(&h->ctx, h->cu_device)) != CUDA_SUCCESS) {
+        h->ctx = nullptr;
+        fail(h, SGEMM_ERR_CUDA, "cannot retain the primary context of device %d: %s", device, cu_text(r).c_str());
+        return bail(SGEMM_ERR_CUDA);
+    }
+    CtxGuard guard(h);
+    d.cuDeviceGetAttribute_(&h->sm_count, CU_DEVICE_ATTRIBUTE_MULTIPROCESSOR_COUNT, h->cu_device);
+    int cc_major = 0;
+    d.cuDeviceGetAttribute_(&cc_major, CU_DEVICE_ATTRIBUTE_COMPUTE_CAPABILITY_MAJOR, h->cu_device);
+    if ((r = d.cuModuleLoad_(&h->module, cubin_path)) != CUDA_SUCCESS) {
+        h->module = nullptr;
+        fail(h, SGEMM_ERR_MODULE, "cuModuleLoad('%s') on device %d (compute capability %d.x) -> %s", cubin_path,
+             device, cc_major, cu_text(r).c_str());
+        return bail(SGEMM_ERR_MODULE);
+    }
+    struct Want { CUfunction *f; const char *name; bool required; };
+    const Want wants[] = {
+        {&h->fn_main, cfg.entry, true},
+        {&h->fn_simt, cfg.fallback_entry, cfg.variant == kVariantTensor},
+        {&h->fn_split_lo, "sgemm_split_lo", true},
+        {&h->fn_pack_a, "sgemm_pack_a_kmajor", true},
+        {&h->fn_reduce, "sgemm_splitk_reduce", true},
+        {&h->fn_fill, "sgemm_fill_uniform", true},
+        {&h->fn_tile_map, "sgemm_tile_map", true},
+    };
+    for (const Want &w : wants) {
+        if (!w.required && !w.name[0]) continue;
+        if ((r = d.cuModuleGetFunction_(w.f, h->module, w.name)) != CUDA_SUCCESS) {
+            fail(h, SGEMM_ERR_MODULE, "entry point '%s' not found in '%s': %s", w.name, cubin_path, cu_text(r).c_str());
+            return bail(SGEMM_ERR_MODULE);
+        }
+    }
+    if (cfg.dynamic_smem_bytes > 0 &&
+        (r = d.cuFuncSetAttribute_(h->fn_main, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, cfg.dynamic_smem_bytes)) != CUDA_SUCCESS) {
+        fail(h, SGEMM_ERR_CUDA, "cannot opt in to %d bytes of dynamic shared memory: %s", cfg.dynamic_smem_bytes, cu_text(r).c_str());
+        return bail(SGEMM_ERR_CUDA);
+    }
+    if ((r = d.cuMemAlloc_(&h->status, kStatusWords * 4)) != CUDA_SUCCESS ||
+        (r = d.cuMemsetD8_(h->status, 0, kStatusWords * 4)) != CUDA_SUCCESS) {
+        fail(h, SGEMM_ERR_CUDA, "cannot allocate the status buffer: %s", cu_text(r).c_str());
+        return bail(SGEMM_ERR_CUDA);
+    }
+    *out = h;
+    return SGEMM_OK;
+}
+
+SGEMM_API int sgemm_close(sgemm_handle *h) {
+    if (!h) return SGEMM_ERR_INVALID_ARGUMENT;
+    Driver &d = driver();
+    if (d.ok && h->ctx) {
+        {
+            CtxGuard guard(h);
+            d.cuCtxSynchronize_();
+            for (auto &pr : h->prof_events) {
+                d.cuEventDestroy_(pr.first);
+                d.cuEventDestroy_(pr.second);
+            }
+            if (h->status) d.cuMemFree_(h->status);
+            if (h->ws_owned) d.cuMemFree_(h->ws_owned);
+            for (CUdeviceptr p : h->stage)
+                if (p) d.cuMemFree_(p);
+            if (h->module) d.cuModuleUnload_(h->module);
+        }
+        d.cuDevicePrimaryCtxRelease_(h->cu_device);
+    }
+    delete h;
+    return SGEMM_OK;
+}
+
+SGEMM_API int sgemm_launch(sgemm_handle *h, const float *dA, const float *dB, const float *dC, float *dD,
+                           float alpha, float beta, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb,
+                           uint32_t ldc, uint32_t ldd, void *stream) {
+    if (!h) return SGEMM_ERR_INVALID_ARGUMENT;
+    CtxGuard guard(h);
+    return launch_device(h, dA, dB, dC, dD, alpha, beta, m, n, k, lda, ldb, ldc, ldd, (CUstream)stream);
+}
+
+SGEMM_API int sgemm_run_host(sgemm_handle *h, const float *hA, const float *hB, const float *hC, float *hD,
+                             float alpha, float beta, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb,
+                             uint32_t ldc, uint32_t ldd) {
+    int rc = check_problem(h, hA, hB, hC, hD, beta, m, n, k, lda, ldb, ldc, ldd);
+    if (rc) return rc;
+    if (m == 0 || n == 0) return SGEMM_OK;
+    CtxGuard guard(h);
+    Driver &d = driver();
+    const bool use_c = beta != 0.0f;
+    const size_t bytes[4] = {k ? ((size_t)lda * (k - 1) + m) * 4 : 0, k ? ((size_t)ldb * (n - 1) + k) * 4 : 0,
+                             use_c ? ((size_t)ldc * (n - 1) + m) * 4 : 0, ((size_t)ldd * (n - 1) + m) * 4};
+    for (int i = 0; i < 4; ++i) {
+        if (bytes[i] > h->stage_bytes[i]) {
+            if (h->stage[i]) {
+                CU_CHECK(h, d.cuCtxSynchronize_());
+                d.cuMemFree_(h->stage[i]);
+                h->stage[i] = 0;
+                h->stage_bytes[i] = 0;
+            }
+            CUresult r = d.cuMemAlloc_(&h->stage[i], round_up(bytes[i], 256));
+            if (r != CUDA_SUCCESS)
+                return fail(h, SGEMM_ERR_CUDA, "cuMemAlloc of %zu staging bytes failed: %s", bytes[i], cu_text(r).c_str());
+            h->stage_bytes[i] = round_up(bytes[i], 256);
+        }
+    }
+    CUstream s = nullptr;
+    if (bytes[0]) CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[0], hA, bytes[0], s));
+    if (bytes[1]) CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[1], hB, bytes[1], s));
+    if (bytes[2]) CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[2], hC, bytes[2], s));
+    if (ldd != m)  // keep the caller's padding rows of D: the kernel writes only rows < M of each column
+        CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[3], hD, bytes[3], s));
+    rc = launch_device(h, reinterpret_cast<const float *>(h->stage[0]), reinterpret_cast<const float *>(h->stage[1]),
+                       use_c ? reinterpret_cast<const float *>(h->stage[2]) : nullptr,
+                       reinterpret_cast<float *>(h->stage[3]), alpha, beta, m, n, k, lda, ldb, ldc, ldd, s);
+    if (rc) return rc;
+    CU_CHECK(h, d.cuMemcpyDtoHAsync_(hD, h->stage[3], bytes[3], s));
+    CU_CHECK(h, d.cuStreamSynchronize_(s));
+    return SGEMM_OK;
+}
+
+SGEMM_API int sgemm_bench(sgemm_handle *h, const float *dA, const float *dB, const float *dC, float *dD, float alpha,
+                          float beta, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb, uint32_t ldc,
+                          uint32_t ldd, uint32_t warmup, uint32_t runs, void *stream, float *ms_mean) {
+    if (!h || !ms_mean || runs == 0) return SGEMM_ERR_INVALID_ARGUMENT;
+    CtxGuard guard(h);
+    Driver &d = driver();
+    CUstream s = (CUstream)stream;
+    int rc;
+    for (uint32_t i = 0; i < warmup; ++i)
+        if ((rc = launch_device(h, dA, dB, dC, dD, alpha, beta, m, n, k, lda, ldb, ldc, ldd, s))) return rc;
+    CU_CHECK(h, d.cuStreamSynchronize_(s));
+    CUevent e0, e1;
+    CU_CHECK(h, d.cuEventCreate_(&e0, CU_EVENT_DEFAULT));
+    CU_CHECK(h, d.cuEventCreate_(&e1, CU_EVENT_DEFAULT));
+    CU_CHECK(h, d.cuEventRecord_(e0, s));
+    for (uint32_t i = 0; i < runs; ++i)
+        if ((rc = launch_device(h, dA, dB, dC, dD, alpha, beta, m, n, k, lda, ldb, ldc, ldd, s))) return rc;
+    CU_CHECK(h, d.cuEventRecord_(e1, s));
+    CU_CHECK(h, d.cuEventSynchronize_(e1));
+    float ms = 0.f;
+    CU_CHECK(h, d.cuEventElapsedTime_(&ms, e0, e1));
+    d.cuEventDestroy_(e0);
+    d.cuEventDestroy_(e1);
+    *ms_mean = ms / (float)runs;
+    return SGEMM_OK;
+}
+
+SGEMM_API int sgemm_last_status(sgemm_handle *h, uint32_t status[8]) {
+    if (!h || !status) return SGEMM_ERR_INVALID_ARGUMENT;
+    CtxGuard guard(h);
+    Driver &d = driver();
+    CU_CHECK(h, d.cuCtxSynchronize_());
+    CU_CHECK(h, d.cuMemcpyDtoH_(status, h->status, kStatusWords * 4));
+    if (status[0] != 0) {
+        CU_CHECK(h, d.cuMemsetD8_(h->status, 0, kStatusWords * 4));
+        return fail(h, SGEMM_ERR_DEVICE_STATUS, "kernel gave up waiting: tag 0x%x tile %u k-block %u block %u parity %u",
+                    status[1], status[2], status[3], status[4], status[5]);
+    }
+    return SGEMM_OK;
+}
+
+SGEMM_API int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value) {
+    if (!h || !key) return SGEMM_ERR_INVALID_ARGUMENT;
+    const std::string k(key);
+    if (k == "force_variant" && value >= 0 && value <= 2) h->force_variant = value;
+    else if (k == "split_k" && value >= 0 && value <= 1024) h->split_k_opt = value;
+    else if (k == "simt_below_flops" && value >= 0) h->simt_below_flops = value;
+    else if (k == "profile" && (value == 0 || value == 1)) { h->profile = value != 0; h->prof_used = 0; }
+    else return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "unknown option or value out of range: %s = %lld", key, (long long)value);
+    return SGEMM_OK;
+}
+
+SGEMM_API int sgemm_get_info(sgemm_handle *h, const char *key, int64_t *value) {
+    if (!h || !key || !value) return SGEMM_ERR_INVALID_ARGUMENT;
+    const std::string k(key);
+    if (k == "variant") *value = h->cfg.variant;
+    else if (k == "last_variant") *value = h->last_variant;
+    else if (k == "last_split_k") *value = h->last_split_k;
+    else if (k == "last_grid") *value = h->last_grid;
+    else if (k == "launches") *value = h->launches;
+    else if (k == "tile_m") *value = h->tile_m;
+    else if (k == "tile_n") *value = h->tile_n;
+    else if (k == "sm_count") *value = h->sm_count;
+    else if (k == "workspace_bytes") *value = (int64_t)(h->ws_lent ? h->ws_lent_bytes : h->ws_owned_bytes);
+    else if (k == "profile_count") *value = (int64_t)h->prof_used;
+    else if (k == "profile_main_ns") {  // total device time of the bracketed main-kernel launches; resets the tally
+        CtxGuard guard(h);
+        Driver &d = driver();
+        double total_ms = 0.0;
+        for (size_t i = 0; i < h->prof_used; ++i) {
+            float ms = 0.f;
+            CU_CHECK(h, d.cuEventSynchronize_(h->prof_events[i].second));
+            CU_CHECK(h, d.cuEventElapsedTime_(&ms, h->prof_events[i].first, h->prof_events[i].second));
+            total_ms += ms;
+        }
+        h->prof_used = 0;
+        *value = (int64_t)(total_ms * 1e6);
+    }
+    else return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "unknown info key: %s", key);
+    return SGEMM_OK;
+}
+
+SGEMM_API int sgemm_workspace_bytes(sgemm_handle *h, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb,
+                                    size_t *bytes) {
+    if (!h || !bytes) return SGEMM_ERR_INVALID_ARGUMENT;
+    *bytes = 0;
+    if (m == 0 || n == 0 || k == 0) return SGEMM_OK;
+    Plan p;
+    // alignment of the real operands is unknown here; assume aligned bases (the common case)
+    int rc = make_plan(h, nullptr, nullptr, m, n, k, lda, ldb, &p);
+    if (rc) return rc;
+    *bytes = p.ws_bytes;
+    return SGEMM_OK;
+}
+
+SGEMM_API int sgemm_set_workspace(sgemm_handle *h, void *dptr, size_t bytes) {
+    if (!h) return SGEMM_ERR_INVALID_ARGUMENT;
+    if (dptr && ((uintptr_t)dptr & 255)) return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
+    h->ws_lent = (CUdeviceptr)(uintptr_t)dptr;
+    h->ws_lent_bytes = dptr ? bytes : 0;
+    for (CachedMap &c : h->maps) c.valid = false;
+    return SGEMM_OK;
+}
+
+SGEMM_API int sgemm_fill_uniform(sgemm_handle *h, float *dptr, uint64_t count, uint64_t first_index,
+                                 uint64_t stream_id, void *stream) {
+    if (!h || (!dptr && count)) return SGEMM_ERR_INVALID_ARGUMENT;
+    if (count == 0) return SGEMM_OK;
+    CtxGuard guard(h);
+    void *params[] = {&dptr, &count, &first_index, &stream_id};
+    const uint32_t blocks = (uint32_t)std::min<uint64_t>((count + 255) / 256, (uint64_t)h->sm_count * 16);
+    return launch(h, h->fn_fill, blocks, 1, 1, 256, 1, 0, (CUstream)stream, params);
+}
+
+SGEMM_API int sgemm_tile_map(sgemm_handle *h, int32_t *host_xy, uint32_t nx, uint32_t ny) {
+    if (!h || !host_xy || nx == 0 || ny == 0 || (uint64_t)nx * ny > (1u << 24)) return SGEMM_ERR_INVALID_ARGUMENT;
+    CtxGuard guard(h);
+    Driver &d = driver();
+    const size_t bytes = (size_t)nx * ny * 2 * sizeof(int32_t);
+    CUdeviceptr buf = 0;
+    CU_CHECK(h, d.cuMemAlloc_(&buf, bytes));
+    int32_t *dp = reinterpret_cast<int32_t *>(buf);
+    void *params[] = {&dp, &nx, &ny};
+    int rc = launch(h, h->fn_tile_map, (nx * ny + 255) / 256, 1, 1, 256, 1, 0, nullptr, params);
+    if (rc == SGEMM_OK) {
+        CUresult r = d.cuMemcpyDtoH_(host_xy, buf, bytes);
+        if (r != CUDA_SUCCESS) rc = fail(h, SGEMM_ERR_CUDA, "cuMemcpyDtoH -> %s", cu_text(r).c_str());
+    }
+    d.cuMemFree_(buf);
+    return rc;
+}
+
+SGEMM_API int sgemm_dev_alloc(sgemm_handle *h, size_t bytes, void **dptr) {
+    if (!h || !dptr) return SGEMM_ERR_INVALID_ARGUMENT;
+    CtxGuard guard(h);
+    CUdeviceptr p = 0;
+    CU_CHECK(h, driver().cuMemAlloc_(&p, bytes ? bytes : 1));
+    *dptr = reinterpret_cast<void *>(p);
+    return SGEMM_OK;
+}
+SGEMM_API int sgemm_dev_free(sgemm_handle *h, void *dptr) {
+    if (!h) return SGEMM_ERR_INVALID_ARGUMENT;
+    if (!dptr) return SGEMM_OK;
+    CtxGuard guard(h);
+    CU_CHECK(h, driver().cuMemFree_((CUdeviceptr)(uintptr_t)dptr));
+    return SGEMM_OK;
+}
+SGEMM_API int sgemm_dev_upload(sgemm_handle *h, void *dptr, const void *host, size_t bytes) {
+    if (!h || ((!dptr || !host) && bytes)) return SGEMM_ERR_INVALID_ARGUMENT;
+    if (!bytes) return SGEMM_OK;
+    CtxGuard guard(h);
+    CU_CHECK(h, driver().cuMemcpyHtoD_((CUdeviceptr)(uintptr_t)dptr, host, bytes));
+    return SGEMM_OK;
+}
+SGEMM_API int sgemm_dev_download(sgemm_handle *h, void *host, const void *dptr, size_t bytes) {
+    if (!h || ((!dptr || !host) && bytes)) return SGEMM_ERR_INVALID_ARGUMENT;
+    if (!bytes) return SGEMM_OK;
+    CtxGuard guard(h);
+    CU_CHECK(h, driver().cuMemcpyDtoH_(host, (CUdeviceptr)(uintptr_t)dptr, bytes));
+    return SGEMM_OK;
+}
+SGEMM_API int sgemm_dev_memset(sgemm_handle *h, void *dptr, int byte_value, size_t bytes) {
+    if (!h || (!dptr && bytes)) return SGEMM_ERR_INVALID_ARGUMENT;
+    if (!bytes) return SGEMM_OK;
+    CtxGuard guard(h);
+    CU_CHECK(h, driver().cuMemsetD8_((CUdeviceptr)(uintptr_t)dptr, (unsigned char)byte_value, bytes));
+    return SGEMM_OK;
+}
+SGEMM_API int sgemm_dev_sync(sgemm_handle *h) {
+    if (!h) return SGEMM_ERR_INVALID_ARGUMENT;
+    CtxGuard guard(h);
+    CU_CHECK(h, driver().cuCtxSynchronize_());
+    return SGEMM_OK;
+}

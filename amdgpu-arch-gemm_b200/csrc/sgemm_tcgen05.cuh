@@ -1,0 +1,385 @@
+// ---------------------------------------------------------------------------------------------
+// 3xTF32 split-precision SGEMM on the sm_100a tensor cores (tcgen05.mma, accumulators in TMEM).
+//
+//   A*B  ~=  A_lo*B_hi + A_hi*B_lo + A_hi*B_hi          (the lo*lo term is below FP32 rounding)
+//
+// hi is the raw FP32 operand (the tensor core reads only its top 19 bits), lo = x - trunc_tf32(x)
+// is written once per call by sgemm_split_lo.  All three products accumulate into one FP32 TMEM
+// accumulator, k ascending, so results do not depend on scheduling (bit-reproducible).
+//
+// Roles of the 192 threads of a CTA (persistent over output tiles, tile = blockIdx + i*gridDim):
+//   warp 0, one lane : TMA producer. Per k-block it fills one ring stage with four operand tiles
+//                      (A_hi, A_lo, B_hi, B_lo) and arms the stage's "full" mbarrier with the bytes.
+//   warp 1, one lane : MMA issuer. Waits "full", issues 3 * TC_BK/8 tcgen05.mma (K = 8 each) and
+//                      commits them to the stage's "empty" mbarrier; after the last k-block of a
+//                      tile it commits to the accumulator's "tmem_full" mbarrier. Warp 1 also owns
+//                      the TMEM allocation (two accumulator buffers, so the epilogue of tile i
+//                      overlaps the main loop of tile i+1).
+//   warps 2..5       : epilogue. Warp w reads TMEM lanes 32*(w%4)..+31 (= rows of the tile) with
+//                      tcgen05.ld, applies alpha/beta and stores straight to global memory: D is
+//                      column-major, so the 32 lanes of a warp write 128 contiguous bytes per column.
+//
+// Operand tiles in shared memory (128-byte swizzle, written by TMA, read by the tensor core):
+//   A (column-major, M contiguous => "MN-major" operand): per 32 rows of M one chunk of TC_BK rows
+//     of 128 bytes (row = one k, 32 consecutive m);   LBO = chunk stride, SBO = 8 rows = 1024 B;
+//     one K=8 MMA step advances the start address by 1024 B.
+//   B (K contiguous per column => "K-major" operand): per 32 k one sub-tile of BN rows of 128 bytes
+//     (row = one n, 32 consecutive k);                SBO = 8 rows = 1024 B;
+//     one K=8 MMA step advances the start address by 32 B inside the swizzle span.
+//   With TC_A_KMAJOR the A operand is read from K-major packed copies (sgemm_pack_a_kmajor) and
+//   uses B's layout.
+//
+// Every mbarrier wait is bounded: after TC_TIMEOUT_NS without progress the waiting role records a
+// status word, raises a CTA-wide abort flag and all roles leave their loops, release TMEM and
+// return; the host reads the status after synchronising.
+//
+// Generator-supplied macros: TC_BN (tile columns), TC_BK (k per stage, multiple of 32), TC_STAGES,
+// TC_A_KMAJOR (0/1), TC_TERMS (3 = 3xTF32, 1 = plain TF32 for bring-up), OPT_WGM.
+// ---------------------------------------------------------------------------------------------
+#ifndef TC_TERMS
+#define TC_TERMS 3
+#endif
+#ifndef TC_TIMEOUT_NS
+#define TC_TIMEOUT_NS 2000000000ull
+#endif
+
+#define TC_BM 128
+#define TC_THREADS 192
+#define TC_A_BYTES (TC_BM * TC_BK * 4)
+#define TC_B_BYTES (TC_BN * TC_BK * 4)
+#define TC_STAGE_BYTES (2 * TC_A_BYTES + 2 * TC_B_BYTES)
+#define TC_A_CHUNK_BYTES (TC_BK * 128)         // MN-major: 32 rows of M x TC_BK
+#define TC_A_SUB_BYTES (TC_BM * 128)           // K-major : TC_BM rows x 32 k
+#define TC_B_SUB_BYTES (TC_BN * 128)           // K-major : TC_BN rows x 32 k
+#define TC_TMEM_COLS_NEEDED (2 * TC_BN)
+#define TC_TMEM_COLS (TC_TMEM_COLS_NEEDED <= 32 ? 32 : TC_TMEM_COLS_NEEDED <= 64 ? 64 : \
+                      TC_TMEM_COLS_NEEDED <= 128 ? 128 : TC_TMEM_COLS_NEEDED <= 256 ? 256 : 512)
+#define TC_SMEM_BYTES (TC_STAGES * TC_STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/)
+
+static_assert(TC_BK % 32 == 0, "k per stage is a whole number of 128-byte swizzle spans");
+static_assert(TC_BN % 16 == 0 && TC_BN >= 16 && TC_BN <= 256, "UMMA N for M=128");
+static_assert(TC_SMEM_BYTES <= 232448, "shared memory budget of one CTA");
+
+struct alignas(64) TcTensorMap { uint64_t opaque[16]; };
+
+// --------------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t tc_smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ uint64_t tc_globaltimer() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void tc_mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void tc_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tc_mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t tc_mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+__device__ __forceinline__ void tc_tma_load_2d(uint32_t dst, const TcTensorMap *map, uint32_t bar,
+                                               int32_t x, int32_t y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_prefetch_map(const TcTensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ------------------------------------------------------------------------------ bounded waiting
+struct TcWait {
+    volatile uint32_t *abort_flag;  // shared memory, CTA-wide
+    uint32_t *status;               // global memory, SGEMM_STATUS_WORDS words
+};
+
+__device__ __noinline__ bool tc_wait_slow(const TcWait &w, uint32_t bar, uint32_t parity, uint32_t tag,
+                                          uint32_t tile, uint32_t kb) {
+    const uint64_t t0 = tc_globaltimer();
+    uint32_t spins = 0;
+    for (;;) {
+        if (tc_mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 31u) == 0u) {
+            if (*w.abort_flag) return false;
+            if (tc_globaltimer() - t0 > TC_TIMEOUT_NS) {
+                *w.abort_flag = 1u;
+                if (atomicCAS(w.status, SGEMM_STATUS_OK, SGEMM_STATUS_TIMEOUT) == SGEMM_STATUS_OK) {
+                    w.status[1] = tag;
+                    w.status[2] = tile;
+                    w.status[3] = kb;
+                    w.status[4] = blockIdx.x;
+                    w.status[5] = parity;
+                }
+                __threadfence();
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ bool tc_wait(const TcWait &w, uint32_t bar, uint32_t parity, uint32_t tag,
+                                        uint32_t tile, uint32_t kb) {
+    if (tc_mbar_try_wait(bar, parity)) return true;
+    return tc_wait_slow(w, bar, parity, tag, tile, kb);
+}
+
+// ---------------------------------------------------------------------------------- descriptors
+// 64-bit shared-memory matrix descriptor: start address [0,14) and the two byte offsets [16,30),
+// [32,46) in 16-byte units, descriptor version 1 at [46,48), swizzle mode at [61,64) (2 = 128 B).
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) |
+           ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// 32-bit instruction descriptor of kind::tf32: FP32 accumulate [4,6)=1, A/B format TF32 [7,10) and
+// [10,13) = 2, A/B major [15]/[16] (1 = MN-major), N>>3 at [17,23), M>>4 at [24,29).
+#define TC_IDESC ((1u << 4) | (2u << 7) | (2u << 10) | ((TC_A_KMAJOR ? 0u : 1u) << 15) | (0u << 16) | \
+                  ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24))
+
+// --------------------------------------------------------------------------------------- kernel
+extern "C" __global__ void __launch_bounds__(TC_THREADS, 1)
+generated_gemm(const float *a, const float *b, const float *c, float *d,
+               uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+               float alpha, float beta, int32_t num_wg_x, int32_t num_wg_y,
+               float *ws, uint32_t *status, uint32_t split_k,
+               const __grid_constant__ TcTensorMap map_a_hi, const __grid_constant__ TcTensorMap map_a_lo,
+               const __grid_constant__ TcTensorMap map_b_hi, const __grid_constant__ TcTensorMap map_b_lo) {
+    (void)a; (void)b; (void)lda; (void)ldb;
+    extern __shared__ uint8_t tc_smem_raw[];
+    const uint32_t smem_base = (tc_smem_u32(tc_smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = smem_base + TC_STAGES * TC_STAGE_BYTES;
+    // barrier block: full[S] | empty[S] | tmem_full[2] | tmem_empty[2] | tmem base (u32) | abort (u32)
+    const uint32_t bar_full = bar_base;
+    const uint32_t bar_empty = bar_base + 8 * TC_STAGES;
+    const uint32_t bar_tfull = bar_base + 16 * TC_STAGES;
+    const uint32_t bar_tempty = bar_tfull + 16;
+    uint8_t *generic_base = tc_smem_raw + (smem_base - tc_smem_u32(tc_smem_raw));
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(generic_base + TC_STAGES * TC_STAGE_BYTES + 16 * TC_STAGES + 32);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+    static_assert(16 * TC_STAGES + 32 + 8 <= 256, "barrier block size");
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const TcWait waiter{abort_flag, status};
+
+    const uint32_t tiles_mn = (uint32_t)num_wg_x * (uint32_t)num_wg_y;
+    const uint32_t num_tiles = tiles_mn * split_k;
+    const uint32_t kb_total = (k + TC_BK - 1) / TC_BK;
+    const uint32_t kb_per = (kb_total + split_k - 1) / split_k;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            tc_mbar_init(bar_full + 8 * s, 1);
+            tc_mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            tc_mbar_init(bar_tfull + 8 * i, 1);
+            tc_mbar_init(bar_tempty + 8 * i, 4);
+        }
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        tc_prefetch_map(&map_a_hi);
+        tc_prefetch_map(&map_a_lo);
+        tc_prefetch_map(&map_b_hi);
+        tc_prefetch_map(&map_b_lo);
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(tc_smem_u32(tmem_slot)), "r"((uint32_t)TC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool alive = true;
+            for (uint32_t tile = blockIdx.x; alive && tile < num_tiles; tile += gridDim.x) {
+                const uint32_t z = tile / tiles_mn;
+                uint32_t tx, ty;
+                sgemm_tile_raster(tile - z * tiles_mn, (uint32_t)num_wg_x, (uint32_t)num_wg_y, OPT_WGM, tx, ty);
+                const int32_t m0 = (int32_t)(tx * TC_BM), n0 = (int32_t)(ty * TC_BN);
+                const uint32_t kb_begin = min(kb_total, z * kb_per), kb_end = min(kb_total, kb_begin + kb_per);
+                for (uint32_t kb = kb_begin; kb < kb_end; ++kb) {
+                    if (!tc_wait(waiter, bar_empty + 8 * stage, phase ^ 1u, 0x100u + stage, tile, kb)) { alive = false; break; }
+                    const uint32_t full = bar_full + 8 * stage;
+                    const uint32_t sa_hi = smem_base + stage * TC_STAGE_BYTES;
+                    const uint32_t sa_lo = sa_hi + TC_A_BYTES;
+                    const uint32_t sb_hi = sa_lo + TC_A_BYTES;
+                    const uint32_t sb_lo = sb_hi + TC_B_BYTES;
+                    const int32_t k0 = (int32_t)(kb * TC_BK);
+                    tc_mbar_expect_tx(full, TC_STAGE_BYTES);
+#if TC_A_KMAJOR
+#pragma unroll
+                    for (int sub = 0; sub < TC_BK / 32; ++sub) {
+                        tc_tma_load_2d(sa_hi + sub * TC_A_SUB_BYTES, &map_a_hi, full, k0 + 32 * sub, m0);
+                        tc_tma_load_2d(sa_lo + sub * TC_A_SUB_BYTES, &map_a_lo, full, k0 + 32 * sub, m0);
+                    }
+#else
+#pragma unroll
+                    for (int ch = 0; ch < TC_BM / 32; ++ch) {
+                        tc_tma_load_2d(sa_hi + ch * TC_A_CHUNK_BYTES, &map_a_hi, full, m0 + 32 * ch, k0);
+                        tc_tma_load_2d(sa_lo + ch * TC_A_CHUNK_BYTES, &map_a_lo, full, m0 + 32 * ch, k0);
+                    }
+#endif
+#pragma unroll
+                    for (int sub = 0; sub < TC_BK / 32; ++sub) {
+                        tc_tma_load_2d(sb_hi + sub * TC_B_SUB_BYTES, &map_b_hi, full, k0 + 32 * sub, n0);
+                        tc_tma_load_2d(sb_lo + sub * TC_B_SUB_BYTES, &map_b_lo, full, k0 + 32 * sub, n0);
+                    }
+                    if (++stage == TC_STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, local = 0;
+            bool alive = true;
+            for (uint32_t tile = blockIdx.x; alive && tile < num_tiles; tile += gridDim.x, ++local) {
+                const uint32_t z = tile / tiles_mn;
+                const uint32_t kb_begin = min(kb_total, z * kb_per), kb_end = min(kb_total, kb_begin + kb_per);
+                const uint32_t buf = local & 1u, acc_phase = (local >> 1) & 1u;
+                if (!tc_wait(waiter, bar_tempty + 8 * buf, acc_phase ^ 1u, 0x200u + buf, tile, 0)) { alive = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * TC_BN;
+                if (kb_begin == kb_end) {  // empty K range: nothing to wait for, hand the buffer over
+                    tc_mbar_arrive(bar_tfull + 8 * buf);
+                    continue;
+                }
+                for (uint32_t kb = kb_begin; kb < kb_end; ++kb) {
+                    if (!tc_wait(waiter, bar_full + 8 * stage, phase, 0x300u + stage, tile, kb)) { alive = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa_hi = smem_base + stage * TC_STAGE_BYTES;
+                    const uint32_t sa_lo = sa_hi + TC_A_BYTES;
+                    const uint32_t sb_hi = sa_lo + TC_A_BYTES;
+                    const uint32_t sb_lo = sb_hi + TC_B_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < TC_BK / 8; ++kk) {
+#if TC_A_KMAJOR
+                        const uint32_t a_off = (kk / 4) * TC_A_SUB_BYTES + (kk % 4) * 32;
+                        const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, 16, 1024);
+                        const uint64_t da_lo = tc_smem_desc(sa_lo + a_off, 16, 1024);
+#else
+                        const uint32_t a_off = kk * 1024;
+                        const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, TC_A_CHUNK_BYTES, 1024);
+                        const uint64_t da_lo = tc_smem_desc(sa_lo + a_off, TC_A_CHUNK_BYTES, 1024);
+#endif
+                        const uint32_t b_off = (kk / 4) * TC_B_SUB_BYTES + (kk % 4) * 32;
+                        const uint64_t db_hi = tc_smem_desc(sb_hi + b_off, 16, 1024);
+                        const uint64_t db_lo = tc_smem_desc(sb_lo + b_off, 16, 1024);
+                        const uint32_t first = (kb == kb_begin && kk == 0) ? 0u : 1u;
+#if TC_TERMS == 3
+                        tc_mma_tf32(d_tmem, da_lo, db_hi, TC_IDESC, first);
+                        tc_mma_tf32(d_tmem, da_hi, db_lo, TC_IDESC, 1u);
+                        tc_mma_tf32(d_tmem, da_hi, db_hi, TC_IDESC, 1u);
+#else
+                        (void)da_lo; (void)db_lo;
+                        tc_mma_tf32(d_tmem, da_hi, db_hi, TC_IDESC, first);
+#endif
+                    }
+                    tc_commit(bar_empty + 8 * stage);
+                    if (++stage == TC_STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (alive) tc_commit(bar_tfull + 8 * buf);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------------------- epilogue
+        const uint32_t quarter = warp & 3u;  // TMEM lane quarter this warp may read
+        uint32_t local = 0;
+        bool alive = true;
+        for (uint32_t tile = blockIdx.x; alive && tile < num_tiles; tile += gridDim.x, ++local) {
+            const uint32_t z = tile / tiles_mn;
+            uint32_t tx, ty;
+            sgemm_tile_raster(tile - z * tiles_mn, (uint32_t)num_wg_x, (uint32_t)num_wg_y, OPT_WGM, tx, ty);
+            const uint32_t kb_begin = min(kb_total, z * kb_per), kb_end = min(kb_total, kb_begin + kb_per);
+            const bool empty_k = kb_begin == kb_end;
+            const uint32_t buf = local & 1u, acc_phase = (local >> 1) & 1u;
+            if (!tc_wait(waiter, bar_tfull + 8 * buf, acc_phase, 0x400u + buf, tile, 0)) { alive = false; break; }
+            tc_fence_after();
+            const uint32_t row = tx * TC_BM + quarter * 32 + lane;
+            const uint32_t col0 = ty * TC_BN;
+            const bool partial = split_k > 1;
+            float *out = partial ? ws + (uint64_t)z * m * n : d;
+            const uint32_t ldo = partial ? m : ldd;
+            const bool use_c = !partial && beta != 0.0f;
+#pragma unroll 1
+            for (int cc = 0; cc < TC_BN / 32; ++cc) {
+                uint32_t r[32];
+                tc_tmem_ld32(tmem_base + ((quarter * 32u) << 16) + buf * TC_BN + cc * 32, r);
+                tc_tmem_ld_wait();
+                if (row < m) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const uint32_t col = col0 + cc * 32 + j;
+                        if (col < n) {
+                            float v = empty_k ? 0.0f : __uint_as_float(r[j]);
+                            if (!partial) {
+                                v *= alpha;
+                                if (use_c) v = fmaf(beta, c[row + (uint64_t)col * ldc], v);
+                            }
+                            out[row + (uint64_t)col * ldo] = v;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tc_mbar_arrive(bar_tempty + 8 * buf);
+        }
+    }
+
+    // teardown: every thread gets here on both the normal and the abort path
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (*abort_flag) {
+            // give copies and MMAs that may still be in flight time to land before TMEM is released
+            const uint64_t t0 = tc_globaltimer();
+            while (tc_globaltimer() - t0 < 2000000ull) __nanosleep(1000);
+        }
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"((uint32_t)TC_TMEM_COLS) : "memory");
+    }
+}

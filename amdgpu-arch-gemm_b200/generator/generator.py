@@ -1,0 +1,474 @@
+"""Kernel generator for the sm_100a SGEMM backend.
+
+Drop-in for the reference's ``generator/generator.py`` on the generate -> compile leg of its
+pipeline: same public names, same positional signatures, same TOML contract — but ``gemm()`` emits
+CUDA C++ (hand-written tcgen05 / FFMA kernels specialised by ``#define``s) instead of GCN assembly and
+``compile()`` runs ``nvcc -gencode arch=compute_100a,code=sm_100a -cubin`` instead of ROCm clang++.
+
+Reference interface mirrored here (paths relative to the reference project):
+
+* ``DataType``                 generator/generator.py:816-824
+* ``GemmOptimizations``        generator/generator.py:827-854   (level, wgm, plr, gw, map_k_idx)
+* ``GemmSolutionConfig``       generator/generator.py:857-1055  (tile = mfma * wave_group * wave_tiling,
+                               shared-memory budget check raising ``RuntimeError``, ``to_dict``)
+* ``FunctionArgument``         generator/generator.py:94-101    (the 15-argument kernel ABI)
+* ``gemm``                     generator/generator.py:1056-2532 (returns the kernel source text)
+* ``compile``                  generator/generator.py:2534-2569 (source -> code object + TOML, returns rc)
+* CLI                          generator/generator.py:2571-2623
+
+How the reference's knobs are read on sm_100a
+---------------------------------------------
+``mfma = (M, N, B, K)`` is the MMA atom.  ``(128, N, 1, 8)`` selects the tensor-core variant
+(tcgen05 ``kind::tf32``, one CTA issues 128 x N x 8); ``(1, 1, 1, 1)`` selects the FFMA SIMT variant.
+The GCN shapes ``(16,16,1,4)`` / ``(32,32,1,2)`` of the reference's tuner are still accepted: they have
+no tensor-core counterpart for FP32 operands, so they map to the SIMT variant with the same block tile.
+``wave_group`` is the cluster shape for the tensor variant and the thread grid of a block for SIMT;
+``wave_tiling`` is atoms per CTA tile resp. the per-thread register tile.  ``tile_size`` keeps the
+reference's product rule, so a runner that only knows the legacy keys still derives the right grid.
+``depth_k`` is K per shared-memory stage, ``vmem_stage + 1`` the number of stages (the reference
+allocates ``vmem_stage + 1`` LDS buffers the same way).  ``lds_usage_bytes`` is the shared memory one
+CTA needs (dynamic for the tensor variant, static for SIMT) and is checked against the sm_100a limit.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import shutil
+import subprocess
+from enum import IntEnum
+from io import StringIO
+from pathlib import Path
+from typing import Dict, List, Optional, Tuple
+
+import tomli_w
+
+CSRC_DIR = Path(__file__).resolve().parent.parent / "csrc"
+
+DEFAULT_NVCC_PATH = os.environ.get("SGEMM_NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+SUPPORTED_ARCHS = ("sm_100a",)
+MAX_LDS_NUM_BYTES = 232448          # 227 KiB: dynamic shared memory one sm_100a CTA can opt in to
+MAX_STATIC_LDS_NUM_BYTES = 49152    # static shared memory limit (SIMT variant)
+MAX_TMEM_COLUMNS = 512
+
+VARIANT_TENSOR = "tcgen05_3xtf32"
+VARIANT_SIMT = "simt_ffma"
+KERNEL_ENTRY = "generated_gemm"     # the entry name the runner and the tuner hard-code
+SIMT_FALLBACK_ENTRY = "generated_gemm_simt"
+
+# The 15 arguments of the kernel ABI in order: (typename, name, bytes).
+KERNEL_ABI = (
+    ("global_buffer", "a", 8), ("global_buffer", "b", 8), ("global_buffer", "c", 8), ("global_buffer", "d", 8),
+    ("by_value", "m", 4), ("by_value", "n", 4), ("by_value", "k", 4),
+    ("by_value", "lda", 4), ("by_value", "ldb", 4), ("by_value", "ldc", 4), ("by_value", "ldd", 4),
+    ("by_value", "alpha", 4), ("by_value", "beta", 4),
+    ("by_value", "numWorkgroupX", 4), ("by_value", "numWorkgroupY", 4),
+)
+
+
+class FunctionArgument:
+    def __init__(self, typename: str, name: str, offset: Optional[int], num_bytes: int):
+        self.typename = typename
+        self.name = name
+        self.offset = offset
+        self.num_bytes = num_bytes
+        self.address_space = "global" if typename == "global_buffer" else None
+
+
+FunctionArgumentList = List[FunctionArgument]
+
+
+def default_arguments() -> FunctionArgumentList:
+    return [FunctionArgument(t, n, None, s) for (t, n, s) in KERNEL_ABI]
+
+
+class GpuContext:
+    """Holder for the emitted source (the reference's context accumulates GCN instructions; there is
+    no instruction DSL here, ``gemm`` writes the whole translation unit into ``content``)."""
+
+    def __init__(self):
+        self.content = StringIO()
+        self.instructions: list = []
+
+    def materialize(self) -> str:
+        return self.content.getvalue()
+
+
+def gpu_function(func):
+    def wrapper(context, *args, **kwargs):
+        if context is None:
+            context = GpuContext()
+        return func(context, *args, **kwargs)
+
+    return wrapper
+
+
+class DataType(IntEnum):
+    FP32 = 0
+
+
+def datatype_size(dtype: DataType) -> int:
+    if dtype == DataType.FP32:
+        return 4
+    raise RuntimeError(f"unrecognized type {dtype}")
+
+
+class GemmOptimizations:
+    """Optimisation knobs with the reference's names.
+
+    level      0 = plain schedule (SIMT: fragments read just in time), >=1 = prefetching schedule
+    wgm        tile rasterisation width (launch units are walked in groups of ``wgm`` tiles along M)
+    plr        SIMT: shared-memory fragment prefetch depth (0/1); ignored by the tensor variant
+    gw         epilogue strategy; both variants store straight from registers, accepted for parity
+    map_k_idx  per-tile K-start stagger; it would change the summation order per tile and with it
+               bit-reproducibility, so only 0 is implemented and other values are rejected by ``gemm``
+    """
+
+    def __init__(self, level: int, wgm: int | None = None, plr: int | None = None,
+                 gw: int | None = None, map_k_idx: int | None = None):
+        self.level = level
+        self.wgm = 1
+        self.plr = 0
+        self.gw = 0
+        self.map_k_idx = 0
+        self._setup_optimizations()
+        if wgm is not None:
+            self.wgm = wgm
+        if plr is not None:
+            self.plr = plr
+        if gw is not None:
+            self.gw = gw
+        if map_k_idx is not None:
+            self.map_k_idx = map_k_idx
+
+    def _setup_optimizations(self):
+        if self.level != 0:
+            self.plr = 1
+            self.gw = 1
+
+
+def _is_pow2(x: int) -> bool:
+    return x > 0 and (x & (x - 1)) == 0
+
+
+class GemmSolutionConfig:
+    def __init__(self, a_type: DataType, b_type: DataType, cd_type: DataType, scalar_type: DataType,
+                 mfma: Tuple[int, int, int, int], wave_group: Tuple[int, int], wave_tiling: Tuple[int, int],
+                 depth_k: int, trans_a: bool, trans_b: bool, vmem_stage: int = 1, *,
+                 a_major: str = "mn", terms: int = 3):
+        self.a_type = a_type
+        self.b_type = b_type
+        self.cd_type = cd_type
+        self.scalar_type = scalar_type
+        self.wave_group = tuple(wave_group)
+        self.trans_a = trans_a
+        self.trans_b = trans_b
+        self.mfma = tuple(mfma)
+        self.wave_tiling = tuple(wave_tiling)
+        self.depth_k = depth_k
+        self.vmem_stage = vmem_stage
+        self.wavefront_size = 32
+        self.name = None
+        self.a_major = a_major      # tensor variant: "mn" = TMA straight from column-major A, "k" = packed copy
+        self.terms = terms          # tensor variant: 3 = 3xTF32 (FP32-accurate), 1 = plain TF32 (bring-up only)
+
+        for t in (a_type, b_type, cd_type, scalar_type):
+            datatype_size(t)
+        if trans_a or trans_b:
+            raise RuntimeError("only the NN layout is implemented (column-major A and B, no transposes)")
+        if not all(_is_pow2(g) for g in self.wave_group):
+            raise RuntimeError(f"Invalid wave group: {wave_group}")
+        if len(self.mfma) != 4 or len(self.wave_group) != 2 or len(self.wave_tiling) != 2:
+            raise RuntimeError("mfma takes 4 ints, wave_group and wave_tiling 2 each")
+        if min(self.mfma + self.wave_group + self.wave_tiling) < 1 or depth_k < 1 or vmem_stage < 1:
+            raise RuntimeError("tiling parameters must be positive")
+
+        m0 = self.mfma[0]
+        if m0 == 128 and self.mfma[3] == 8:
+            self.variant = VARIANT_TENSOR
+            self._check_tensor()
+        elif self.mfma == (1, 1, 1, 1) or self.mfma in ((16, 16, 1, 4), (32, 32, 1, 2)):
+            self.variant = VARIANT_SIMT
+            self._check_simt()
+        else:
+            raise RuntimeError(f"unsupported MMA atom {self.mfma}: use (128, N, 1, 8) for tcgen05 tf32, "
+                               f"(1, 1, 1, 1) for FFMA, or a legacy (16,16,1,4)/(32,32,1,2) shape")
+
+        limit = MAX_LDS_NUM_BYTES if self.variant == VARIANT_TENSOR else MAX_STATIC_LDS_NUM_BYTES
+        if self.lds_usage_bytes > limit:
+            raise RuntimeError(f"LDS usage exceeds {limit}: {self.lds_usage_bytes}")
+
+    # ------------------------------------------------------------------ variant-specific checks
+    def _check_tensor(self):
+        if self.wave_group not in ((1, 1),):
+            raise RuntimeError(f"cluster shape {self.wave_group} is not implemented for the tensor variant")
+        if self.wave_tiling[0] != 1:
+            raise RuntimeError("the tensor variant holds one 128-row atom per CTA (wave_tiling[0] must be 1)")
+        bn = self.tile_size[1]
+        if bn % 16 or bn < 32 or bn > 256:
+            raise RuntimeError(f"tile N = {bn} must be a multiple of 16 in [32, 256] (UMMA N for M = 128)")
+        if bn % 32:
+            raise RuntimeError(f"tile N = {bn} must be a multiple of 32 (epilogue reads 32 TMEM columns at a time)")
+        if self.depth_k % 32:
+            raise RuntimeError(f"depth_k = {self.depth_k} must be a multiple of 32 (128-byte swizzle span of FP32)")
+        if 2 * bn > MAX_TMEM_COLUMNS:
+            raise RuntimeError("two accumulator buffers exceed the 512 TMEM columns")
+        if self.a_major not in ("mn", "k"):
+            raise RuntimeError("a_major is 'mn' or 'k'")
+        if self.terms not in (1, 3):
+            raise RuntimeError("terms is 3 (3xTF32) or 1 (plain TF32)")
+        if self.stages < 2:
+            raise RuntimeError("the TMA ring needs at least 2 stages")
+
+    def _check_simt(self):
+        bm, bn = self.tile_size
+        tm, tn = self.simt_thread_tile
+        if bm % tm or bn % tn:
+            raise RuntimeError(f"block tile {bm}x{bn} is not a multiple of the thread tile {tm}x{tn}")
+        threads = (bm // tm) * (bn // tn)
+        if threads < 1 or threads > 1024:
+            raise RuntimeError(f"a block of {threads} threads is not launchable")
+        if self.depth_k % 4:
+            raise RuntimeError("depth_k must be a multiple of 4 (16-byte loads along K)")
+        if tm * tn > 128:
+            raise RuntimeError(f"thread tile {tm}x{tn} does not fit the register file")
+
+    # ------------------------------------------------------------------------------- geometry
+    @property
+    def tile_size(self) -> Tuple[int, int]:
+        return (self.mfma[0] * self.wave_group[0] * self.wave_tiling[0],
+                self.mfma[1] * self.wave_group[1] * self.wave_tiling[1])
+
+    @property
+    def stages(self) -> int:
+        return self.vmem_stage + 1
+
+    @property
+    def simt_thread_tile(self) -> Tuple[int, int]:
+        """Per-thread register tile of the SIMT variant (multiples of 4 in both directions)."""
+        if self.mfma == (1, 1, 1, 1):
+            return self.wave_tiling
+        bm, bn = self.tile_size  # legacy MFMA shape: largest square thread tile that leaves >= 64 threads
+        for t in (8, 4):
+            if bm % t == 0 and bn % t == 0 and (bm // t) * (bn // t) >= 64:
+                return t, t
+        return 4, 4
+
+    @property
+    def num_workitems(self) -> int:
+        if self.variant == VARIANT_TENSOR:
+            return 192
+        bm, bn = self.tile_size
+        tm, tn = self.simt_thread_tile
+        return (bm // tm) * (bn // tn)
+
+    @property
+    def num_bytes_per_buffer_load(self) -> Tuple[int, int]:
+        """Bytes one global->shared transfer moves per operand: a 16-byte vector per thread for SIMT (the
+        reference's tuner keeps only configurations where this is (16, 16)), a whole TMA box for tcgen05."""
+        if self.variant == VARIANT_TENSOR:
+            return 32 * self.depth_k * 4, 32 * self.tile_size[1] * 4
+        return 16, 16
+
+    @property
+    def tmem_columns(self) -> int:
+        if self.variant != VARIANT_TENSOR:
+            return 0
+        need, cols = 2 * self.tile_size[1], 32
+        while cols < need:
+            cols *= 2
+        return cols
+
+    @property
+    def lds_usage_bytes(self) -> int:
+        bm, bn = self.tile_size
+        if self.variant == VARIANT_TENSOR:
+            stage = 2 * (128 * self.depth_k * 4) + 2 * (bn * self.depth_k * 4)   # A_hi, A_lo, B_hi, B_lo
+            return self.stages * stage + 1024 + 256                              # + alignment slack + barriers
+        return 2 * self.depth_k * (bm + bn + 4) * 4                              # double-buffered A and padded B
+
+    @property
+    def num_unrolled_iters(self) -> int:
+        return self.depth_k // max(self.mfma[3], 1)
+
+    def to_dict(self) -> Dict:
+        d = {
+            # ---- the reference's 14 keys (generator/generator.py:1001-1017), same order and types ----
+            "a_type": int(self.a_type),
+            "b_type": int(self.b_type),
+            "cd_type": int(self.cd_type),
+            "scalar_type": int(self.scalar_type),
+            "wave_group": list(self.wave_group),
+            "trans_a": self.trans_a,
+            "trans_b": self.trans_b,
+            "mfma": list(self.mfma),
+            "wave_tiling": list(self.wave_tiling),
+            "depth_k": self.depth_k,
+            "vmem_stage": self.vmem_stage,
+            "wavefront_size": self.wavefront_size,
+            "lds_usage_bytes": self.lds_usage_bytes,
+            "name": self.name if self.name else "",
+            # ---- sm_100a additions read by the CUDA runner ----
+            "variant": self.variant,
+            "block_tile": [self.tile_size[0], self.tile_size[1], self.depth_k],
+            "cluster": list(self.wave_group) if self.variant == VARIANT_TENSOR else [1, 1],
+            "stages": self.stages,
+            "num_threads": self.num_workitems,
+            "dynamic_smem_bytes": self.lds_usage_bytes if self.variant == VARIANT_TENSOR else 0,
+            "tmem_columns": self.tmem_columns,
+            "entry": KERNEL_ENTRY,
+        }
+        if self.variant == VARIANT_TENSOR:
+            fb = simt_fallback_config()
+            d.update({
+                "a_major": self.a_major,
+                "terms": self.terms,
+                "fallback_entry": SIMT_FALLBACK_ENTRY,
+                "fallback_tile": [fb.tile_size[0], fb.tile_size[1], fb.depth_k],
+                "fallback_threads": fb.num_workitems,
+            })
+        return d
+
+
+def simt_fallback_config() -> GemmSolutionConfig:
+    """The FFMA kernel compiled into every tensor-variant cubin for shapes TMA cannot describe
+    (leading dimensions that are not multiples of 4, unaligned bases) and for tiny problems."""
+    return GemmSolutionConfig(DataType.FP32, DataType.FP32, DataType.FP32, DataType.FP32,
+                              (1, 1, 1, 1), (16, 16), (8, 8), 16, False, False)
+
+
+# --------------------------------------------------------------------------------------------------
+# source emission
+# --------------------------------------------------------------------------------------------------
+def _read(name: str) -> str:
+    return (CSRC_DIR / name).read_text()
+
+
+def _defines(pairs) -> str:
+    return "".join(f"#define {k} {v}\n" for k, v in pairs)
+
+
+def _check_arguments(arguments: FunctionArgumentList):
+    got = [(a.typename, a.name, a.num_bytes) for a in arguments]
+    if got != list(KERNEL_ABI):
+        raise RuntimeError("kernel arguments must be the 15-entry SGEMM ABI "
+                           "(a, b, c, d, m, n, k, lda, ldb, ldc, ldd, alpha, beta, numWorkgroupX, numWorkgroupY)")
+    offset = 0
+    for a in arguments:  # natural alignment, as the reference's kernarg segment (generator.py:127-147)
+        offset = (offset + a.num_bytes - 1) // a.num_bytes * a.num_bytes
+        a.offset = offset
+        offset += a.num_bytes
+
+
+def _simt_defines(cfg: GemmSolutionConfig, opt: GemmOptimizations, entry: str):
+    bm, bn = cfg.tile_size
+    tm, tn = cfg.simt_thread_tile
+    return [("SIMT_ENTRY", entry), ("SIMT_BM", bm), ("SIMT_BN", bn), ("SIMT_BK", cfg.depth_k),
+            ("SIMT_TM", tm), ("SIMT_TN", tn), ("SIMT_PLR", 1 if opt.plr else 0)]
+
+
+@gpu_function
+def gemm(context: GpuContext, name: str, arch: str, config: GemmSolutionConfig, opt: GemmOptimizations,
+         arguments: FunctionArgumentList) -> str:
+    """Emit the CUDA translation unit for ``config``/``opt``; returns the source text.
+
+    ``name`` is recorded in the header only: the ``__global__`` entry is always ``generated_gemm``
+    because the runner and the tuner look it up under that name (runner/generator_runner.cpp:197,
+    tuner/sgemm_tuner.py:67).  Infeasible knob combinations raise ``RuntimeError`` — the tuner's skip
+    mechanism (tuner/sgemm_tuner.py:92)."""
+    _check_arguments(arguments)
+    if not _is_pow2(opt.wgm):
+        raise RuntimeError(f"wgm must be a power of two, got {opt.wgm}")
+    if opt.map_k_idx:
+        raise RuntimeError("map_k_idx != 0 (per-tile K stagger) is not offered: it changes the summation "
+                           "order per tile and would break run-to-run and tile-to-tile reproducibility")
+    if arch is not None and arch not in SUPPORTED_ARCHS:
+        raise RuntimeError(f"unsupported arch {arch!r}; this generator targets {SUPPORTED_ARCHS}")
+
+    out = StringIO()
+    out.write(f"// generated by generator.py: kernel '{name}', variant {config.variant}, "
+              f"tile {config.tile_size[0]}x{config.tile_size[1]}x{config.depth_k}, stages {config.stages}, "
+              f"wgm {opt.wgm}, plr {opt.plr}, gw {opt.gw}\n")
+    out.write(_defines([("OPT_WGM", opt.wgm)]))
+    out.write(_read("sgemm_common.cuh"))
+    if config.variant == VARIANT_SIMT:
+        out.write(_defines(_simt_defines(config, opt, KERNEL_ENTRY)))
+        out.write(_read("sgemm_simt.cuh"))
+    else:
+        out.write(_defines(_simt_defines(simt_fallback_config(), opt, SIMT_FALLBACK_ENTRY)))
+        out.write(_read("sgemm_simt.cuh"))
+        out.write(_defines([("TC_BN", config.tile_size[1]), ("TC_BK", config.depth_k),
+                            ("TC_STAGES", config.stages), ("TC_A_KMAJOR", 1 if config.a_major == "k" else 0),
+                            ("TC_TERMS", config.terms)]))
+        out.write(_read("sgemm_tcgen05.cuh"))
+    src = out.getvalue()
+    context.content.write(src)
+    return src
+
+
+def nvcc_command(src: str, out: str, extra: Optional[List[str]] = None) -> List[str]:
+    return [DEFAULT_NVCC_PATH, "-gencode", "arch=compute_100a,code=sm_100a", "-cubin", "-O3", "-std=c++17",
+            "-lineinfo", "-ccbin", os.environ.get("SGEMM_HOST_CXX", "g++"), *(extra or []), "-o", out, src]
+
+
+def compile(kern_name: str, kern_str: str, arch: str, output_folder: str, gemm_config: GemmSolutionConfig) -> int:
+    """Write ``<kern_name>.cu``, compile it to ``<kern_name>.cubin`` and write ``<kern_name>.toml``.
+    Returns nvcc's return code (0 = success); the TOML is written only for a kernel that compiled."""
+    os.makedirs(output_folder, exist_ok=True)
+    src = f"{output_folder}/{kern_name}.cu"
+    with open(src, "w") as f:
+        f.write(kern_str)
+    ret = subprocess.run(nvcc_command(src, f"{output_folder}/{kern_name}.cubin"),
+                         stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if ret.returncode:
+        print(ret.stdout)
+        return ret.returncode
+    with open(f"{output_folder}/{kern_name}.toml", "wb") as f:
+        tomli_w.dump(gemm_config.to_dict(), f)
+    return ret.returncode
+
+
+def tensor_config(bn: int = 256, bk: int = 32, stages: int = 2, **kw) -> GemmSolutionConfig:
+    """Shorthand for a tensor-variant configuration with tile 128 x bn x bk."""
+    return GemmSolutionConfig(DataType.FP32, DataType.FP32, DataType.FP32, DataType.FP32,
+                              (128, bn, 1, 8), (1, 1), (1, 1), bk, False, False, vmem_stage=stages - 1, **kw)
+
+
+def simt_config(bm: int = 128, bn: int = 128, bk: int = 16, tm: int = 8, tn: int = 8) -> GemmSolutionConfig:
+    return GemmSolutionConfig(DataType.FP32, DataType.FP32, DataType.FP32, DataType.FP32,
+                              (1, 1, 1, 1), (bm // tm, bn // tn), (tm, tn), bk, False, False)
+
+
+def build_kernel(output_folder: str, config: GemmSolutionConfig, opt: Optional[GemmOptimizations] = None,
+                 kern_name: str = KERNEL_ENTRY, arch: str = "sm_100a") -> Tuple[str, str]:
+    """generate + compile in one call; returns (cubin path, toml path) or raises RuntimeError."""
+    opt = opt or GemmOptimizations(1, wgm=8)
+    src = gemm(None, kern_name, arch, config, opt, default_arguments())
+    if compile(kern_name, src, arch, output_folder, config):
+        raise RuntimeError(f"nvcc failed for {kern_name} in {output_folder}")
+    return f"{output_folder}/{kern_name}.cubin", f"{output_folder}/{kern_name}.toml"
+
+
+def tile_raster(z: int, nx: int, ny: int, wgm: int) -> Tuple[int, int]:
+    """Host model of the kernels' launch-unit -> tile mapping (``sgemm_tile_raster`` in csrc/sgemm_common.cuh).
+    For ``nx`` a multiple of ``wgm`` this is the reference's workgroup remap (generator/generator.py:1437-1464,
+    checked by test/test_vm.py:735-740): x' = (z % wgm) + (z // wgm // ny) * wgm, y' = (z // wgm) % ny."""
+    if wgm <= 1:
+        return z % nx, z // nx
+    group = z // (wgm * ny)
+    first_x = group * wgm
+    width = min(wgm, nx - first_x)
+    r = z - group * wgm * ny
+    return first_x + r % width, r // width
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument(dest="output_folder", action="store", type=str, help="Output folder")
+    ap.add_argument("--arch", dest="arch", action="store", choices=list(SUPPORTED_ARCHS), default="sm_100a")
+    ap.add_argument("--variant", choices=["tensor", "simt"], default="tensor")
+    args = ap.parse_args()
+    gemm_config = tensor_config() if args.variant == "tensor" else simt_config()
+    opt = GemmOptimizations(1, wgm=8)
+    src_str = gemm(None, KERNEL_ENTRY, args.arch, gemm_config, opt, default_arguments())
+    raise SystemExit(compile(KERNEL_ENTRY, src_str, args.arch, args.output_folder, gemm_config))
+

@@ -1,0 +1,57 @@
+"""Named kernel configurations that are generated and compiled ahead of time (by ``build_all``) so that the
+tests, the smoke check and the benchmark find ready cubins; ``ensure`` compiles one on demand."""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Dict, Tuple
+
+from generator.generator import (GemmOptimizations, GemmSolutionConfig, DataType, build_kernel, simt_config,
+                                 tensor_config)
+
+GENERATED_DIR = Path(__file__).resolve().parent / "_generated"
+F = DataType.FP32
+
+
+def _legacy(mfma, wg, wt, dk):
+    return GemmSolutionConfig(F, F, F, F, mfma, wg, wt, dk, False, False)
+
+
+# name -> (config factory, optimisation knobs)
+REGISTRY = {
+    # tensor-core 3xTF32 kernels: tile 128 x BN x BK, S stages
+    "tc_128x256x32_s2": (lambda: tensor_config(256, 32, 2), dict(wgm=8)),
+    "tc_128x128x32_s3": (lambda: tensor_config(128, 32, 3), dict(wgm=8)),
+    "tc_128x64x32_s4": (lambda: tensor_config(64, 32, 4), dict(wgm=8)),
+    "tc_128x64x64_s2": (lambda: tensor_config(64, 64, 2), dict(wgm=4)),
+    # the same tile reading A from K-major packed copies, and a plain-TF32 build (bring-up aids)
+    "tc_128x128x32_s3_ak": (lambda: tensor_config(128, 32, 3, a_major="k"), dict(wgm=8)),
+    "tc_128x128x32_s3_1x": (lambda: tensor_config(128, 32, 3, terms=1), dict(wgm=8)),
+    # FFMA SIMT kernels
+    "simt_128x128x16": (lambda: simt_config(128, 128, 16, 8, 8), dict(wgm=8)),
+    "simt_64x64x16": (lambda: simt_config(64, 64, 16, 4, 4), dict(wgm=4)),
+    "simt_128x64x8_plr0": (lambda: simt_config(128, 64, 8, 8, 4), dict(wgm=1, plr=0)),
+    # configurations written the reference's way (GCN MFMA shapes): served by the SIMT kernel
+    "legacy_32x32x2_1wave": (lambda: _legacy((32, 32, 1, 2), (1, 1), (1, 1), 16), dict(wgm=1)),
+    "legacy_16x16x4_2x2x2x2": (lambda: _legacy((16, 16, 1, 4), (2, 2), (2, 2), 16), dict(wgm=4)),
+}
+
+DEFAULT_TENSOR = "tc_128x256x32_s2"
+DEFAULT_SIMT = "simt_128x128x16"
+
+
+def paths(name: str) -> Tuple[str, str]:
+    d = GENERATED_DIR / name
+    return str(d / "generated_gemm.cubin"), str(d / "generated_gemm.toml")
+
+
+def ensure(name: str, force: bool = False) -> Tuple[str, str]:
+    """Return (cubin, toml) of a registered kernel, generating and compiling it if it is not there."""
+    cubin, toml = paths(name)
+    if force or not (Path(cubin).exists() and Path(toml).exists()):
+        factory, opt_kwargs = REGISTRY[name]
+        build_kernel(str(GENERATED_DIR / name), factory(), GemmOptimizations(1, **opt_kwargs))
+    return cubin, toml
+
+
+def build_all(force: bool = True) -> Dict[str, Tuple[str, str]]:
+    return {name: ensure(name, force=force) for name in REGISTRY}

@@ -1,0 +1,48 @@
+"""Column-block sharding of one SGEMM over the GPUs of a box (one process per GPU).
+
+D's columns are independent, and in column-major storage ``B[:, n0:n1]``, ``C[:, n0:n1]`` and ``D[:, n0:n1]``
+are contiguous ranges ``[n0*ld, n1*ld)``: a shard is a pointer offset and each rank runs the unmodified
+single-GPU kernel on ``N' = n1 - n0`` columns with A replicated.  No collective sits on the compute path;
+``gather_columns`` is the optional all-gather of D, and ``max_over_ranks`` the timing reduction.
+"""
+from __future__ import annotations
+
+from typing import List, Tuple
+
+
+def shard_columns(n: int, world: int, rank: int, tile_n: int = 1) -> Tuple[int, int]:
+    """Columns [n0, n1) of rank ``rank``: whole tiles of ``tile_n`` columns, as even as possible, earlier
+    ranks take the extra tile; the last non-empty shard absorbs a ragged tail."""
+    if world < 1 or not (0 <= rank < world) or n < 0 or tile_n < 1:
+        raise ValueError("bad shard request")
+    tiles = (n + tile_n - 1) // tile_n
+    base, extra = divmod(tiles, world)
+    t0 = rank * base + min(rank, extra)
+    t1 = t0 + base + (1 if rank < extra else 0)
+    return min(t0 * tile_n, n), min(t1 * tile_n, n)
+
+
+def all_shards(n: int, world: int, tile_n: int = 1) -> List[Tuple[int, int]]:
+    return [shard_columns(n, world, r, tile_n) for r in range(world)]
+
+
+def gather_columns(dist, local_d, m: int, n: int, world: int, tile_n: int = 1):
+    """All-gather the column shards of D (flat column-major tensors) into the full M x N matrix on every rank.
+    Shards may differ in width, so each is padded to the widest one for the collective."""
+    import torch
+
+    shards = all_shards(n, world, tile_n)
+    widest = max(n1 - n0 for n0, n1 in shards)
+    padded = torch.zeros(m * widest, dtype=local_d.dtype, device=local_d.device)
+    padded[: local_d.numel()] = local_d
+    parts = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(parts, padded)
+    return torch.cat([parts[r][: m * (n1 - n0)] for r, (n0, n1) in enumerate(shards)])
+
+
+def max_over_ranks(dist, value: float, device="cpu") -> float:
+    import torch
+
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())

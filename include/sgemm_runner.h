@@ -1,0 +1,159 @@
+/*
+ * C ABI of libsgemm_runner.so — the drop-in boundary of the sm_100a SGEMM backend.
+ *
+ * The reference keeps the corresponding steps as internal C++ functions of its runner program
+ * (runner/generator_runner.cpp); each entry point below names the one it replaces.  A caller in
+ * any language binds these symbols (plain pointers and sizes, no C++ or torch types).
+ *
+ * Conventions
+ *   - every function returns 0 (SGEMM_OK) or a negative sgemm_error code; nothing throws or aborts;
+ *   - matrices are FP32, column-major, no transposes: A is M x K (lda >= M), B is K x N (ldb >= K),
+ *     C and D are M x N (ldc, ldd >= M);  D = alpha * A * B + beta * C;  C may be NULL when beta == 0;
+ *   - the caller owns A, B, C, D; the handle owns the loaded module, its kernels, a status buffer, the
+ *     tensor-map cache and (unless the caller lends one) the scratch workspace;
+ *   - one handle belongs to one device; a handle is not thread-safe, distinct handles are;
+ *   - sgemm_launch is asynchronous on the given stream (NULL = the default stream);
+ *   - there is no CPU path: every compute entry point fails with SGEMM_ERR_NO_DRIVER / SGEMM_ERR_CUDA
+ *     when no CUDA driver or device is present.
+ */
+#ifndef SGEMM_RUNNER_H
+#define SGEMM_RUNNER_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct sgemm_handle sgemm_handle;
+
+typedef enum sgemm_error {
+    SGEMM_OK = 0,
+    SGEMM_ERR_INVALID_ARGUMENT = -1, /* NULL handle/pointer, ld smaller than the rows it must hold, ... */
+    SGEMM_ERR_TOML = -2,             /* config file missing, unreadable, or a required key absent/ill-typed */
+    SGEMM_ERR_NO_DRIVER = -3,        /* libcuda.so.1 could not be loaded */
+    SGEMM_ERR_CUDA = -4,             /* a CUDA driver call failed; see sgemm_last_error */
+    SGEMM_ERR_MODULE = -5,           /* cubin missing / not loadable / entry point not found */
+    SGEMM_ERR_UNSUPPORTED = -6,      /* the loaded kernel cannot serve this request (e.g. forced variant) */
+    SGEMM_ERR_WORKSPACE = -7,        /* lent workspace too small, or allocation failed */
+    SGEMM_ERR_DEVICE_STATUS = -8     /* a kernel reported a bounded wait that ran out (sgemm_last_status) */
+} sgemm_error;
+
+/* Kernel configuration as read from the generator's TOML (generator/generator.py:1001-1017 writes it,
+ * runner/generator_runner.cpp:85-124 `AsmKernelConfig` / `getAsmKernelConfig` reads it there). */
+typedef struct sgemm_config {
+    int32_t a_type, b_type, cd_type, scalar_type;
+    int32_t mfma[4];
+    int32_t wave_group[2];
+    int32_t wave_tiling[2];
+    int32_t depth_k;
+    int32_t vmem_stage;
+    int32_t wavefront_size;
+    int32_t lds_usage_bytes;
+    int32_t trans_a, trans_b;
+    /* sm_100a additions (0 / empty when the file has only the legacy keys) */
+    int32_t variant;            /* 0 = SIMT FFMA, 1 = tcgen05 3xTF32 */
+    int32_t num_threads;
+    int32_t dynamic_smem_bytes;
+    int32_t stages;
+    int32_t a_kmajor;           /* tensor variant reads A from a K-major packed copy */
+    int32_t fallback_tile[3];
+    int32_t fallback_threads;
+    char entry[64];
+    char fallback_entry[64];
+} sgemm_config;
+
+/* Replaces getAsmKernelConfig (runner/generator_runner.cpp:100-124).  Host only, needs no GPU. */
+int sgemm_config_parse(const char *toml_path, sgemm_config *out);
+
+/* Tile of D one launch unit covers: mfma[i] * wave_group[i] * wave_tiling[i], the product rule of
+ * makeKernelArguments (runner/generator_runner.cpp:128-129).  Host only. */
+int sgemm_config_tile(const sgemm_config *cfg, uint32_t *tile_m, uint32_t *tile_n);
+
+/* Replaces prepareASMKernel + getAsmKernelConfig (runner/generator_runner.cpp:69-73, 193-197):
+ * loads the cubin with cuModuleLoad on `device` (its primary context) and resolves the entry points. */
+int sgemm_open(const char *cubin_path, const char *toml_path, int device, sgemm_handle **out);
+
+/* Replaces hipModuleUnload + the frees at the end of main (runner/generator_runner.cpp:318-322). */
+int sgemm_close(sgemm_handle *h);
+
+/* Replaces makeKernelArguments + launchASMKernel (runner/generator_runner.cpp:126-190) with device
+ * pointers.  Chooses the kernel variant and split-K factor (see sgemm_set_option), runs the 3xTF32
+ * split pre-pass and the split-K reduction when they apply.  May allocate or grow the handle-owned
+ * workspace (a synchronising cuMemAlloc) unless a workspace was lent with sgemm_set_workspace. */
+int sgemm_launch(sgemm_handle *h, const float *dA, const float *dB, const float *dC, float *dD,
+                 float alpha, float beta, uint32_t m, uint32_t n, uint32_t k,
+                 uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, void *stream);
+
+/* The same call with HOST buffers: uploads A, B (and C when beta != 0), launches, downloads D and
+ * synchronises — what the reference's main does around its kernel with hipMalloc / hipMemcpyHtoD /
+ * hipMemcpyDtoH (runner/generator_runner.cpp:236-242, 289-291).  Device staging buffers are cached in
+ * the handle.  Host buffers may be pageable or pinned. */
+int sgemm_run_host(sgemm_handle *h, const float *hA, const float *hB, const float *hC, float *hD,
+                   float alpha, float beta, uint32_t m, uint32_t n, uint32_t k,
+                   uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd);
+
+/* Replaces the timed loop of main (runner/generator_runner.cpp:270-280): `warmup` untimed launches, then
+ * `runs` back-to-back launches between two events on `stream`; *ms_mean = elapsed / runs. Synchronises. */
+int sgemm_bench(sgemm_handle *h, const float *dA, const float *dB, const float *dC, float *dD,
+                float alpha, float beta, uint32_t m, uint32_t n, uint32_t k,
+                uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                uint32_t warmup, uint32_t runs, void *stream, float *ms_mean);
+
+/* Device status words of the last kernels (synchronises the device).  status[0] == 0: no kernel gave up
+ * on a wait.  Otherwise status[0] = 1 (a bounded wait ran out), [1] = role/barrier tag, [2] = tile,
+ * [3] = k-block, [4] = block index, [5] = parity; the words are cleared by the call.  The reference has
+ * no counterpart (it ignores every hipError_t, runner/generator_runner.cpp:194-322). */
+int sgemm_last_status(sgemm_handle *h, uint32_t status[8]);
+
+/* Options: "force_variant" 0 auto, 1 tensor, 2 simt;  "split_k" 0 auto, n >= 1 fixed;
+ * "simt_below_flops" problems with 2*M*N*K below this use the SIMT kernel (auto mode);
+ * "profile" 1 brackets every main-GEMM-kernel launch with an event pair (read with "profile_main_ns"). */
+int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value);
+
+/* Facts: "variant" (of the cubin), "last_variant" (1 tensor / 2 simt), "last_split_k", "last_grid",
+ * "launches" (kernel launches issued so far), "tile_m", "tile_n", "sm_count", "workspace_bytes",
+ * "profile_count" (bracketed launches since the last read), "profile_main_ns" (their summed device time in
+ * nanoseconds; synchronises on them and resets the tally). */
+int sgemm_get_info(sgemm_handle *h, const char *key, int64_t *value);
+
+/* Scratch bytes sgemm_launch needs for this problem under the current options (0 = none). */
+int sgemm_workspace_bytes(sgemm_handle *h, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb,
+                          size_t *bytes);
+
+/* Lend device scratch (256-byte aligned) so that sgemm_launch never allocates; NULL returns to the
+ * handle-owned, grow-on-demand workspace. */
+int sgemm_set_workspace(sgemm_handle *h, void *dptr, size_t bytes);
+
+/* Seeded U[-1,1) fill on the device: element i gets the index-hash value of (first_index + i, stream_id).
+ * Replaces `randomize` (runner/Utils/BufferUtils.hpp:6-14), which is unseeded in the reference. */
+int sgemm_fill_uniform(sgemm_handle *h, float *dptr, uint64_t count, uint64_t first_index,
+                       uint64_t stream_id, void *stream);
+
+/* Tile rasterisation of the loaded kernel: xy[2*z], xy[2*z+1] = (tile x, tile y) of launch unit z for an
+ * nx x ny tile grid, computed on the device by the kernel's own mapping function (the workgroup remap of
+ * generator/generator.py:1437-1464). */
+int sgemm_tile_map(sgemm_handle *h, int32_t *host_xy, uint32_t nx, uint32_t ny);
+
+/* Plain device-memory helpers so that a caller without its own CUDA binding (the runner program, a
+ * ctypes harness) can stage buffers: hipMalloc / hipFree / hipMemcpy / hipMemset / hipDeviceSynchronize
+ * of runner/generator_runner.cpp:236-242, 267, 289, 319-322. */
+int sgemm_dev_alloc(sgemm_handle *h, size_t bytes, void **dptr);
+int sgemm_dev_free(sgemm_handle *h, void *dptr);
+int sgemm_dev_upload(sgemm_handle *h, void *dptr, const void *host, size_t bytes);
+int sgemm_dev_download(sgemm_handle *h, void *host, const void *dptr, size_t bytes);
+int sgemm_dev_memset(sgemm_handle *h, void *dptr, int byte_value, size_t bytes);
+int sgemm_dev_sync(sgemm_handle *h);
+
+/* Short text for an error code; detail of the last failure on a handle (NULL handle: last open error). */
+const char *sgemm_strerror(int code);
+const char *sgemm_last_error(sgemm_handle *h);
+
+/* Number of CUDA devices (<= 0: none or no driver). Host-side probe used by the runner program. */
+int sgemm_device_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SGEMM_RUNNER_H */

@@ -1,0 +1,123 @@
+"""Generator API: the reference's usage patterns (test/test_sgemm.py:4-44, tuner/sgemm_tuner.py:52-110) must
+work unchanged against this generator, with sm_100a meanings for the knobs."""
+import os
+import re
+import tomllib
+
+import pytest
+
+from generator import generator as g
+from generator.generator import (DataType, FunctionArgument, GemmOptimizations, GemmSolutionConfig, compile, gemm)
+
+ARGS = lambda: [
+    FunctionArgument("global_buffer", "a", None, 8), FunctionArgument("global_buffer", "b", None, 8),
+    FunctionArgument("global_buffer", "c", None, 8), FunctionArgument("global_buffer", "d", None, 8),
+    FunctionArgument("by_value", "m", None, 4), FunctionArgument("by_value", "n", None, 4),
+    FunctionArgument("by_value", "k", None, 4), FunctionArgument("by_value", "lda", None, 4),
+    FunctionArgument("by_value", "ldb", None, 4), FunctionArgument("by_value", "ldc", None, 4),
+    FunctionArgument("by_value", "ldd", None, 4), FunctionArgument("by_value", "alpha", None, 4),
+    FunctionArgument("by_value", "beta", None, 4), FunctionArgument("by_value", "numWorkgroupX", None, 4),
+    FunctionArgument("by_value", "numWorkgroupY", None, 4),
+]
+F = DataType.FP32
+
+
+def test_basic_sgemm_gen_reference_style():
+    # the reference's generation smoke test, verbatim in shape: a GCN-style config must still generate
+    cfg = g.GemmSolutionConfig(F, F, F, F, (16, 16, 1, 4), (2, 2), (2, 2), 16, False, False)
+    src = g.gemm(None, "gemm", "sm_100a", cfg, g.GemmOptimizations(1), ARGS())
+    assert len(src) and 'extern "C" __global__' in src and "generated_gemm" in src
+    assert cfg.tile_size == (64, 64) and cfg.variant == g.VARIANT_SIMT
+
+
+def test_tile_product_rule_and_properties():
+    cfg = g.tensor_config(256, 32, 2)
+    assert cfg.tile_size == (128, 256) and cfg.num_workitems == 192 and cfg.stages == 2
+    assert cfg.lds_usage_bytes == 2 * (2 * 128 * 32 * 4 + 2 * 256 * 32 * 4) + 1024 + 256
+    assert cfg.tmem_columns == 512
+    s = g.simt_config(128, 128, 16, 8, 8)
+    assert s.tile_size == (128, 128) and s.num_workitems == 256
+    assert s.lds_usage_bytes == 2 * 16 * (128 + 128 + 4) * 4
+    assert s.num_bytes_per_buffer_load == (16, 16)  # the tuner's vector-load filter (tuner/sgemm_tuner.py:102)
+
+
+@pytest.mark.parametrize("kwargs", [
+    dict(mfma=(128, 256, 1, 8), wg=(1, 1), wt=(1, 1), dk=32, vs=2),     # 3 stages of 96 KiB: over the smem budget
+    dict(mfma=(128, 512, 1, 8), wg=(1, 1), wt=(1, 1), dk=32, vs=1),     # N beyond the UMMA / TMEM limit
+    dict(mfma=(128, 128, 1, 8), wg=(1, 1), wt=(1, 1), dk=16, vs=1),     # k per stage below the swizzle span
+    dict(mfma=(128, 128, 1, 8), wg=(3, 1), wt=(1, 1), dk=32, vs=1),     # wave_group not a power of two
+    dict(mfma=(1, 1, 1, 1), wg=(16, 16), wt=(8, 8), dk=64, vs=1),       # SIMT static smem over 48 KiB
+    dict(mfma=(64, 64, 1, 8), wg=(1, 1), wt=(1, 1), dk=32, vs=1),       # no such atom
+])
+def test_infeasible_configs_raise_runtime_error(kwargs):
+    with pytest.raises(RuntimeError):  # the tuner's skip mechanism (tuner/sgemm_tuner.py:92)
+        GemmSolutionConfig(F, F, F, F, kwargs["mfma"], kwargs["wg"], kwargs["wt"], kwargs["dk"], False, False,
+                           vmem_stage=kwargs["vs"])
+
+
+def test_transposes_and_k_stagger_are_rejected():
+    with pytest.raises(RuntimeError):
+        GemmSolutionConfig(F, F, F, F, (1, 1, 1, 1), (16, 16), (8, 8), 16, True, False)
+    with pytest.raises(RuntimeError):
+        gemm(None, "k", "sm_100a", g.simt_config(), GemmOptimizations(1, map_k_idx=4), ARGS())
+    with pytest.raises(RuntimeError):
+        gemm(None, "k", "gfx90a", g.simt_config(), GemmOptimizations(1), ARGS())
+    with pytest.raises(RuntimeError):
+        gemm(None, "k", "sm_100a", g.simt_config(), GemmOptimizations(1), ARGS()[:-1])
+
+
+def test_optimization_defaults_follow_the_reference():
+    o0, o1 = GemmOptimizations(0), GemmOptimizations(1)
+    assert (o0.wgm, o0.plr, o0.gw, o0.map_k_idx) == (1, 0, 0, 0)
+    assert (o1.wgm, o1.plr, o1.gw, o1.map_k_idx) == (1, 1, 1, 0)
+    assert GemmOptimizations(1, wgm=4, plr=0).plr == 0
+
+
+def test_kernel_argument_offsets_match_the_76_byte_segment():
+    args = ARGS()
+    gemm(None, "k", "sm_100a", g.simt_config(), GemmOptimizations(1), args)
+    assert [a.offset for a in args] == [0, 8, 16, 24, 32, 36, 40, 44, 48, 52, 56, 60, 64, 68, 72]
+
+
+def test_emitted_source_knobs_and_no_cluster_multicast():
+    src = gemm(None, "k", "sm_100a", g.tensor_config(128, 32, 3), GemmOptimizations(1, wgm=4), ARGS())
+    assert "#define OPT_WGM 4" in src and "#define TC_BN 128" in src and "#define TC_STAGES 3" in src
+    assert "tcgen05.mma" in src and "cp.async.bulk.tensor" in src and "generated_gemm_simt" in src
+    assert "multicast" not in src
+    simt = gemm(None, "k", "sm_100a", g.simt_config(64, 64, 16, 4, 4), GemmOptimizations(0), ARGS())
+    assert "#define SIMT_PLR 0" in simt and "tcgen05" not in simt
+
+
+def test_compile_writes_cu_cubin_toml(tmp_path):
+    cfg = g.simt_config(64, 64, 16, 4, 4)
+    src = gemm(None, "generated_gemm", "sm_100a", cfg, GemmOptimizations(1), ARGS())
+    assert compile("generated_gemm", src, "sm_100a", str(tmp_path), cfg) == 0
+    for ext in ("cu", "cubin", "toml"):
+        assert (tmp_path / f"generated_gemm.{ext}").stat().st_size > 0
+    with open(tmp_path / "generated_gemm.toml", "rb") as f:
+        d = tomllib.load(f)
+    legacy = ["a_type", "b_type", "cd_type", "scalar_type", "wave_group", "trans_a", "trans_b", "mfma", "wave_tiling",
+              "depth_k", "vmem_stage", "wavefront_size", "lds_usage_bytes", "name"]
+    assert list(d)[:14] == legacy  # generator/generator.py:1001-1017, same order
+    assert d["mfma"] == [1, 1, 1, 1] and d["wave_group"] == [16, 16] and d["variant"] == "simt_ffma"
+    assert d["num_threads"] == 256 and d["entry"] == "generated_gemm"
+    # a kernel that does not compile returns non-zero and leaves no TOML behind
+    assert compile("broken", "this is not CUDA", "sm_100a", str(tmp_path), cfg) != 0
+    assert not (tmp_path / "broken.toml").exists()
+
+
+def test_reference_tuner_filters_work():
+    # tuner/sgemm_tuner.py:97-110 in miniature
+    cfg = g.tensor_config(128, 32, 3)
+    m, n, k = 1024, 1024, 1024
+    assert not ((m % cfg.tile_size[0]) or (n % cfg.tile_size[1]) or (k % cfg.depth_k))
+    assert cfg.num_bytes_per_buffer_load[0] % 16 == 0
+
+
+@pytest.mark.parametrize("nx,ny,wgm", [(8, 8, 4), (8, 8, 1), (7, 5, 4), (64, 32, 8), (3, 9, 8), (1, 1, 2)])
+def test_tile_raster_model(nx, ny, wgm):
+    seen = [g.tile_raster(z, nx, ny, wgm) for z in range(nx * ny)]
+    assert sorted(seen) == sorted((x, y) for x in range(nx) for y in range(ny))  # a permutation of the grid
+    if nx % wgm == 0 and wgm > 1:  # the reference's formula, test/test_vm.py:735-740
+        for z, (x, y) in enumerate(seen):
+            assert (x, y) == ((z % wgm) + (z // wgm // ny) * wgm, (z // wgm) % ny)

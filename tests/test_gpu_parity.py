@@ -1,0 +1,282 @@
+"""GPU parity: the CUDA kernels, called through the C ABI, against the CPU oracle and the golden vectors of
+the reference's own generator + VM.  Tolerance (FP32 GEMM): per element |D - D_ref| <= 1e-5 * sum_l |a_il||b_lj|
+(oracle.REL_TOL); split-free FP32 kernels and the 3xTF32 kernel are held to the same bound."""
+import numpy as np
+import pytest
+
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+TENSOR_KERNELS = ["tc_128x256x32_s2", "tc_128x128x32_s3", "tc_128x64x32_s4", "tc_128x64x64_s2", "tc_128x128x32_s3_ak"]
+SIMT_KERNELS = ["simt_128x128x16", "simt_64x64x16", "simt_128x64x8_plr0", "legacy_32x32x2_1wave", "legacy_16x16x4_2x2x2x2"]
+AUTO, TENSOR, SIMT = 0, 1, 2
+_runners = {}
+
+
+@pytest.fixture(scope="module")
+def runner_of(built):
+    from runner import api
+
+    def get(name):
+        if name not in _runners:
+            cubin, toml = built.ensure(name)
+            _runners[name] = api.SgemmRunner(cubin, toml, 0)
+        r = _runners[name]
+        r.set_option("force_variant", AUTO)
+        r.set_option("split_k", 0)
+        r.set_workspace(None, 0)
+        return r
+
+    yield get
+    for r in _runners.values():
+        assert r.last_status()[0] == 0  # no kernel ever gave up on a wait
+        r.close()
+    _runners.clear()
+
+
+def run(r, a, b, c, m, n, k, alpha=1.0, beta=0.0, force=AUTO, split_k=0, lda=0, ldb=0, ldc=0, ldd=0, d_init=None):
+    r.set_option("force_variant", force)
+    r.set_option("split_k", split_k)
+    d = np.zeros(max((ldd or m) * n, 1), dtype=np.float32) if d_init is None else d_init.copy()
+    r.run_host(a, b, c if beta != 0.0 else None, d, m, n, k, alpha=alpha, beta=beta, lda=lda, ldb=ldb, ldc=ldc, ldd=ldd)
+    return d[: (ldd or m) * n]
+
+
+def check(d, a, b, c, m, n, k, alpha, beta, lda=0, ldb=0, ldc=0, ldd=0):
+    ref = oracle.gemm(a, b, c, alpha, beta, m, n, k, lda=lda or None, ldb=ldb or None, ldc=ldc or None)
+    bound = abs(alpha) * oracle.abs_bound(a, b, m, n, k, lda=lda or None, ldb=ldb or None)
+    if beta != 0.0:
+        bound = bound + abs(beta) * np.abs(oracle.strip_ld(c, m, n, ldc or m)).astype(np.float64)
+    got = oracle.strip_ld(d, m, n, ldd or m)
+    ratio = oracle.worst_ratio(got, ref, bound)
+    assert ratio <= 1.0, f"worst |err| / (1e-5 * sum|a||b|) = {ratio}"
+    return ratio
+
+
+# ------------------------------------------------------------------------------------------- golden vectors
+GOLDEN = ["vm_16x16x64_arange", "vm_32x32x64_arange", "vm_64x48x64_mapk4_arange", "vm_64x48x64_3buf_arange",
+          "vm_64x64x32_wgm2_arange", "vm_32x32x32_seed0_mfma32_beta0", "vm_32x32x32_seed0_mfma32_beta1",
+          "vm_32x32x32_seed0_mfma16_beta0", "vm_32x32x32_seed0_mfma16_beta1"]
+
+
+@pytest.mark.parametrize("kernel", TENSOR_KERNELS + SIMT_KERNELS)
+@pytest.mark.parametrize("name", GOLDEN)
+def test_golden_vectors_of_the_reference_vm(runner_of, golden_dir, kernel, name):
+    z = np.load(golden_dir / f"{name}.npz")
+    m, n, k = (int(x) for x in z["mnk"])
+    a, b, c, d_vm = z["a"], z["b"], z["c"], z["d"]
+    alpha, beta = float(z["alpha"]), float(z["beta"])
+    r = runner_of(kernel)
+    d = run(r, a, b, c, m, n, k, alpha, beta, force=TENSOR if kernel in TENSOR_KERNELS else SIMT)
+    assert r.info("last_variant") == (TENSOR if kernel in TENSOR_KERNELS else SIMT)
+    bound = oracle.abs_bound(a, b, m, n, k) + abs(beta) * np.abs(c).astype(np.float64)
+    assert oracle.worst_ratio(d, d_vm, bound) <= 1.0
+    if "arange" in name:
+        assert np.allclose(d, d_vm, rtol=1e-5)  # the reference's acceptance rule, test/test_vm.py:536-537
+
+
+# ------------------------------------------------------------------------------- seeded shapes vs the oracle
+SHAPES = [(1, 1, 1), (8, 8, 8), (32, 32, 32), (33, 65, 129), (127, 257, 513), (128, 256, 32), (129, 255, 33),
+          (256, 512, 96), (1000, 1000, 1000), (1024, 1024, 1024), (130, 4, 2048), (4, 300, 77)]
+
+
+@pytest.mark.parametrize("kernel", ["tc_128x256x32_s2", "tc_128x128x32_s3", "tc_128x64x64_s2", "tc_128x128x32_s3_ak"])
+@pytest.mark.parametrize("mnk", SHAPES)
+@pytest.mark.parametrize("alpha,beta", [(1.0, 0.0), (0.5, -1.5)])
+def test_tensor_kernels_match_oracle(runner_of, kernel, mnk, alpha, beta):
+    m, n, k = mnk
+    lda, ldb = (m + 3) // 4 * 4, (k + 3) // 4 * 4   # TMA needs 16-byte row pitches; pad ragged shapes
+    a, b, c = oracle.make_inputs(m, n, k, seed=0, lda=lda, ldb=ldb)
+    r = runner_of(kernel)
+    d = run(r, a, b, c, m, n, k, alpha, beta, force=TENSOR, lda=lda, ldb=ldb)
+    assert r.info("last_variant") == TENSOR
+    check(d, a, b, c, m, n, k, alpha, beta, lda=lda, ldb=ldb)
+
+
+@pytest.mark.parametrize("kernel", SIMT_KERNELS)
+@pytest.mark.parametrize("mnk", SHAPES)
+@pytest.mark.parametrize("alpha,beta", [(1.0, 0.0), (0.5, -1.5)])
+def test_simt_kernels_match_oracle(runner_of, kernel, mnk, alpha, beta):
+    m, n, k = mnk
+    a, b, c = oracle.make_inputs(m, n, k, seed=0)
+    r = runner_of(kernel)
+    d = run(r, a, b, c, m, n, k, alpha, beta, force=SIMT)
+    assert r.info("last_variant") == SIMT
+    check(d, a, b, c, m, n, k, alpha, beta)
+
+
+def test_variant_selection(runner_of):
+    r = runner_of("tc_128x256x32_s2")
+    for (m, n, k), want in [((32, 32, 32), SIMT), ((127, 257, 513), SIMT), ((1000, 1000, 1000), TENSOR),
+                            ((1024, 1024, 1024), TENSOR)]:
+        a, b, c = oracle.make_inputs(m, n, k, seed=1)
+        d = run(r, a, b, c, m, n, k, 1.0, 0.0)
+        assert r.info("last_variant") == want, (m, n, k)
+        check(d, a, b, c, m, n, k, 1.0, 0.0)
+    # a forced tensor path on a shape TMA cannot describe is an error, not a silent fallback
+    from runner import api
+    a, b, c = oracle.make_inputs(127, 257, 513, seed=1)
+    with pytest.raises(api.SgemmError) as e:
+        run(r, a, b, c, 127, 257, 513, force=TENSOR)
+    assert e.value.code == -6
+    with pytest.raises(api.SgemmError) as e:  # lda smaller than M
+        r.run_host(a, b, None, np.zeros(127 * 257, np.float32), 127, 257, 513, lda=100)
+    assert e.value.code == -1
+
+
+# ------------------------------------------------------------------- BASELINE's skinny shapes, full oracle
+@pytest.mark.parametrize("mnk", [(8192, 8192, 256), (4096, 128, 16384)])
+def test_skinny_shapes_full_oracle(runner_of, mnk):
+    m, n, k = mnk
+    a, b, c = oracle.make_inputs(m, n, k, seed=0)
+    r = runner_of("tc_128x256x32_s2")
+    d = run(r, a, b, c, m, n, k, 1.0, 0.0)
+    assert r.info("last_variant") == TENSOR
+    if mnk == (4096, 128, 16384):
+        assert r.info("last_split_k") > 1   # 32 output tiles for 148 SMs: K must be cut
+    check(d, a, b, c, m, n, k, 1.0, 0.0)
+    d2 = run(r, a, b, c, m, n, k, 1.0, 0.0)
+    assert d.tobytes() == d2.tobytes()      # bit-reproducible, split-K included
+    ds = run(runner_of("simt_128x128x16"), a, b, c, m, n, k, 1.0, 0.0, force=SIMT)
+    check(ds, a, b, c, m, n, k, 1.0, 0.0)
+
+
+# ------------------------------------------------ 8192^3: column-sampled oracle + a checksum over every tile
+@pytest.mark.parametrize("kernel,force", [("tc_128x256x32_s2", TENSOR), ("simt_128x128x16", SIMT)])
+def test_8192_cubed_sampled_and_checksummed(runner_of, kernel, force):
+    m = n = k = 8192
+    a, b, c = oracle.make_inputs(m, n, k, seed=0)
+    r = runner_of(kernel)
+    d = run(r, a, b, c, m, n, k, 1.0, 0.0, force=force)
+    D = d.reshape(n, m)                                    # row j = column j of D
+    # (1) exact oracle on 96 sampled columns (every tile column of the 256-wide tiling is hit)
+    cols = np.unique(np.concatenate([np.arange(0, n, 128) + 7, np.array([0, 1, 255, 256, n - 1])]))
+    b_sub = np.ascontiguousarray(b.reshape(n, k)[cols]).reshape(-1)
+    ref = oracle.gemm(a, b_sub, None, 1.0, 0.0, m, len(cols), k)
+    bound = oracle.abs_bound(a, b_sub, m, len(cols), k)
+    assert oracle.worst_ratio(np.ascontiguousarray(D[cols]).reshape(-1), ref, bound) <= 1.0
+    # (2) linearity checksum over ALL of D: D @ 1 = A @ (B @ 1), in FP64, bounded by |A| @ (|B| @ 1) * 1e-5
+    A = a.reshape(k, m).astype(np.float64)
+    Bm = b.reshape(n, k).astype(np.float64)
+    rowsum = D.astype(np.float64).sum(axis=0)
+    want = Bm.sum(axis=0) @ A
+    slack = oracle.REL_TOL * (np.abs(Bm).sum(axis=0) @ np.abs(A))
+    assert np.all(np.abs(rowsum - want) <= slack)
+    colsum = D.astype(np.float64).sum(axis=1)
+    want_c = Bm @ A.sum(axis=1)
+    slack_c = oracle.REL_TOL * (np.abs(Bm) @ np.abs(A).sum(axis=1))
+    assert np.all(np.abs(colsum - want_c) <= slack_c)
+
+
+# ------------------------------------------------------------------------------ determinism and split-K
+@pytest.mark.parametrize("kernel,force", [("tc_128x128x32_s3", TENSOR), ("simt_64x64x16", SIMT)])
+def test_split_k_is_deterministic_and_in_tolerance(runner_of, kernel, force):
+    m, n, k = 200, 136, 4096
+    lda, ldb = 200, 4096
+    a, b, c = oracle.make_inputs(m, n, k, seed=7)
+    r = runner_of(kernel)
+    outs = {}
+    for split in (1, 3, 4, 16):
+        d1 = run(r, a, b, c, m, n, k, 2.0, 1.0, force=force, split_k=split)
+        assert r.info("last_split_k") <= split
+        d2 = run(r, a, b, c, m, n, k, 2.0, 1.0, force=force, split_k=split)
+        assert d1.tobytes() == d2.tobytes()
+        check(d1, a, b, c, m, n, k, 2.0, 1.0)
+        outs[split] = d1
+    assert r.info("last_split_k") > 1
+
+
+def test_split_k_beyond_the_k_blocks_is_clamped(runner_of):
+    m, n, k = 64, 64, 40
+    a, b, c = oracle.make_inputs(m, n, k, seed=2)
+    for kernel, force in (("tc_128x128x32_s3", TENSOR), ("simt_64x64x16", SIMT)):
+        r = runner_of(kernel)
+        d = run(r, a, b, c, m, n, k, 1.0, 0.0, force=force, split_k=64)
+        assert 1 <= r.info("last_split_k") <= 3
+        check(d, a, b, c, m, n, k, 1.0, 0.0)
+
+
+# -------------------------------------------------------------------------- leading dimensions, canaries
+@pytest.mark.parametrize("kernel,force", [("tc_128x256x32_s2", TENSOR), ("tc_128x128x32_s3_ak", TENSOR),
+                                          ("simt_128x128x16", SIMT)])
+def test_leading_dimensions_and_untouched_padding(runner_of, kernel, force):
+    m, n, k = 300, 270, 200
+    lda, ldb, ldc, ldd = 304, 208, 301, 303
+    a, b, c = oracle.make_inputs(m, n, k, seed=9, lda=lda, ldb=ldb, ldc=ldc)
+    canary = np.full(ldd * n, np.float32(-777.25))
+    r = runner_of(kernel)
+    d = run(r, a, b, c, m, n, k, 1.0, 1.0, force=force, lda=lda, ldb=ldb, ldc=ldc, ldd=ldd, d_init=canary)
+    check(d, a, b, c, m, n, k, 1.0, 1.0, lda=lda, ldb=ldb, ldc=ldc, ldd=ldd)
+    pad = d.reshape(n, ldd)[:, m:]
+    assert np.all(pad == np.float32(-777.25))   # rows >= M of every column keep the caller's bytes
+
+
+def test_degenerate_sizes(runner_of):
+    for kernel in ("tc_128x128x32_s3", "simt_64x64x16"):
+        r = runner_of(kernel)
+        c = oracle.fill_uniform(12, 5)
+        d = np.full(12, np.float32(9.0))
+        r.run_host(None, None, c, d, 4, 3, 0, alpha=1.0, beta=2.0, lda=4, ldb=1)   # K = 0: D = beta*C
+        assert np.array_equal(d, np.float32(2.0) * c)
+        r.run_host(None, None, None, d, 4, 3, 0, alpha=1.0, beta=0.0, lda=4, ldb=1)
+        assert np.all(d == 0.0)
+        r.run_host(None, None, None, d, 0, 3, 5, lda=1, ldb=5, ldc=1, ldd=1)        # M = 0: nothing to do
+        r.run_host(None, None, None, d, 4, 0, 5, lda=4, ldb=5)                      # N = 0
+
+
+def test_beta_zero_never_reads_c(runner_of):
+    m, n, k = 160, 96, 64
+    a, b, _ = oracle.make_inputs(m, n, k, seed=4)
+    for kernel, force in (("tc_128x128x32_s3", TENSOR), ("simt_64x64x16", SIMT)):
+        d = run(runner_of(kernel), a, b, None, m, n, k, 1.0, 0.0, force=force)   # C = NULL
+        check(d, a, b, None, m, n, k, 1.0, 0.0)
+
+
+# ------------------------------------------------------------------------------------ workspace handling
+def test_lent_workspace(runner_of):
+    from runner import api
+    m, n, k = 256, 256, 2048
+    a, b, c = oracle.make_inputs(m, n, k, seed=6)
+    r = runner_of("tc_128x128x32_s3")
+    base = run(r, a, b, c, m, n, k, 1.0, 0.0, force=TENSOR, split_k=4)
+    r.set_option("force_variant", TENSOR)
+    r.set_option("split_k", 4)
+    need = r.workspace_bytes(m, n, k)
+    assert need >= (m * k + k * n + 4 * m * n) * 4
+    ws = r.dev_alloc(need)
+    try:
+        r.set_workspace(ws, need)
+        lent = run(r, a, b, c, m, n, k, 1.0, 0.0, force=TENSOR, split_k=4)
+        assert lent.tobytes() == base.tobytes()
+        r.set_workspace(ws, need - 256)
+        with pytest.raises(api.SgemmError) as e:
+            run(r, a, b, c, m, n, k, 1.0, 0.0, force=TENSOR, split_k=4)
+        assert e.value.code == -7
+    finally:
+        r.set_workspace(None, 0)
+        r.sync()
+        r.dev_free(ws)
+
+
+# ------------------------------------------------------------------------------ helpers on the device
+def test_device_fill_equals_host_generator(runner_of):
+    r = runner_of("simt_64x64x16")
+    count = 1_000_003
+    p = r.dev_alloc(count * 4)
+    try:
+        r.fill_uniform(p, count, stream_id=3, first_index=12345)
+        got = np.empty(count, dtype=np.float32)
+        r.download(got, p)
+        assert got.tobytes() == oracle.fill_uniform(count, 3, first_index=12345).tobytes()
+    finally:
+        r.dev_free(p)
+
+
+@pytest.mark.parametrize("kernel", ["tc_128x256x32_s2", "simt_64x64x16", "legacy_32x32x2_1wave"])
+def test_tile_rasterisation_on_device_matches_the_model(runner_of, built, kernel):
+    from generator import generator as g
+    wgm = built.REGISTRY[kernel][1].get("wgm", 1)
+    r = runner_of(kernel)
+    for nx, ny in [(8, 8), (7, 5), (64, 32), (1, 9)]:
+        assert r.tile_map(nx, ny) == [g.tile_raster(z, nx, ny, wgm) for z in range(nx * ny)]

@@ -1,0 +1,45 @@
+"""The GeneratorRunner program: the reference's CLI `<code object> <toml> M N K warmup runs validate` and its
+stdout shape (runner/generator_runner.cpp:193-323), parsed the way the reference's tuner parses it."""
+import os
+import subprocess
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def run_cli(built, kernel, m, n, k, validate, env=None):
+    from runner import api
+    api.build_library()
+    cubin, toml = built.ensure(kernel)
+    e = dict(os.environ)
+    e.update(env or {})
+    return subprocess.run([str(api.RUNNER_PATH), cubin, toml, str(m), str(n), str(k), "2", "5", str(validate)],
+                          stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=e, timeout=600)
+
+
+@pytest.mark.parametrize("kernel", ["tc_128x256x32_s2", "simt_128x128x16"])
+def test_cli_stdout_contract_and_validation(built, kernel):
+    ret = run_cli(built, kernel, 512, 768, 640, 1)
+    assert ret.returncode == 0, ret.stdout + ret.stderr
+    lines = ret.stdout.split("\n")
+    assert lines[0].startswith("cpuGemm func: ") and lines[0].endswith(" ms")
+    assert lines[1].startswith("SIMT gemm: ") and lines[2].startswith("Gflops: ") and lines[3].startswith("GiB/s: ")
+    assert lines[4].startswith("ASM gemm: ") and lines[5].startswith("Gflops: ") and lines[6].startswith("GiB/s: ")
+    assert lines[7] == f"# of mismatches: 0/{512 * 768}"
+    ret = run_cli(built, kernel, 512, 768, 640, 0)
+    assert ret.returncode == 0
+    gflops = float(ret.stdout.split("\n")[-3].split(":")[-1])   # tuner/sgemm_tuner.py:115
+    assert gflops > 0
+    assert ("tcgen05" in ret.stderr) == kernel.startswith("tc_")
+
+
+def test_cli_argument_and_file_errors(built):
+    from runner import api
+    api.build_library()
+    cubin, toml = built.ensure("simt_128x128x16")
+    short = subprocess.run([str(api.RUNNER_PATH), cubin, toml, "64", "64"], capture_output=True, text=True)
+    assert short.returncode == 255      # the reference returns -1 for argc <= 8
+    bad = subprocess.run([str(api.RUNNER_PATH), cubin + ".missing", toml, "64", "64", "64", "1", "1", "0"],
+                         capture_output=True, text=True)
+    assert bad.returncode not in (0, 255) and "sgemm_open" in bad.stderr

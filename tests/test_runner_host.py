@@ -1,0 +1,100 @@
+"""Host-side behaviour of libsgemm_runner.so that needs no GPU: the library loads, exports every symbol the
+header declares, reads the generator's TOML, and refuses to compute without a CUDA device."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def header_symbols():
+    text = (ROOT / "include" / "sgemm_runner.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sgemm_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(built):
+    from runner import api
+    L = api.lib()
+    names = header_symbols()
+    assert len(names) >= 20 and set(names) == set(api.ABI)
+    for n in names:
+        assert getattr(L, n) is not None
+
+
+def test_strerror_is_total(built):
+    from runner import api
+    L = api.lib()
+    assert L.sgemm_strerror(0) == b"ok"
+    for code in range(-8, 0):
+        assert L.sgemm_strerror(code) not in (b"", b"unknown error")
+    assert L.sgemm_strerror(-99) == b"unknown error"
+
+
+def test_toml_reader_reads_generator_output(built):
+    from runner import api
+    for name in built.REGISTRY:
+        _, toml = built.ensure(name)
+        cfg = api.parse_config(toml)
+        factory, _ = built.REGISTRY[name]
+        py = factory()
+        assert api.config_tile(cfg) == py.tile_size
+        assert cfg.depth_k == py.depth_k and cfg.num_threads == py.num_workitems
+        assert cfg.lds_usage_bytes == py.lds_usage_bytes and cfg.vmem_stage == py.vmem_stage
+        assert cfg.variant == (1 if py.variant == "tcgen05_3xtf32" else 0)
+        assert cfg.entry == b"generated_gemm"
+
+
+def test_toml_reader_accepts_the_reference_files_shape(built, tmp_path):
+    from runner import api
+    # what the reference's compile() writes for its default config (multi-line arrays, trailing commas)
+    p = tmp_path / "ref.toml"
+    p.write_text('a_type = 0\nb_type = 0\ncd_type = 0\nscalar_type = 0\nwave_group = [\n    2,\n    2,\n]\n'
+                 'trans_a = false\ntrans_b = false\nmfma = [\n    32,\n    32,\n    1,\n    2,\n]\n'
+                 'wave_tiling = [ 4, 2 ]  # inline too\ndepth_k = 16\nvmem_stage = 1\nwavefront_size = 64\n'
+                 'lds_usage_bytes = 53_248\nname = ""\nunknown_key = "ignored"\n')
+    cfg = api.parse_config(str(p))
+    assert api.config_tile(cfg) == (256, 128) and cfg.num_threads == 256 and cfg.lds_usage_bytes == 53248
+    assert cfg.variant == 0 and cfg.stages == 2
+
+
+@pytest.mark.parametrize("text", ['a_type = 0\n', 'a_type = "x"\n', 'mfma = [1, 2\n', 'depth_k = 1.5\n', 'key value\n'])
+def test_toml_reader_reports_bad_files(built, tmp_path, text):
+    from runner import api
+    p = tmp_path / "bad.toml"
+    p.write_text(text)
+    with pytest.raises(api.SgemmError) as e:
+        api.parse_config(str(p))
+    assert e.value.code == -2
+    with pytest.raises(api.SgemmError):
+        api.parse_config(str(tmp_path / "missing.toml"))
+
+
+def test_open_fails_loudly_without_cubin_or_device(built, tmp_path):
+    from runner import api
+    _, toml = built.ensure(built.DEFAULT_SIMT)
+    with pytest.raises(api.SgemmError) as e:
+        api.SgemmRunner(str(tmp_path / "nope.cubin"), toml, 0)
+    assert e.value.code == -5
+    if api.device_count() == 0:  # no GPU here: the compute path must refuse, never fall back
+        cubin, _ = built.ensure(built.DEFAULT_SIMT)
+        with pytest.raises(api.SgemmError) as e:
+            api.SgemmRunner(cubin, toml, 0)
+        assert e.value.code in (-3, -1, -4)
+
+
+def test_shard_columns_cover_n_in_whole_tiles():
+    from runner.shard import all_shards, shard_columns
+    for n, world, tile in [(32768, 8, 256), (8192, 3, 256), (1000, 4, 128), (100, 8, 64), (0, 2, 16)]:
+        sh = all_shards(n, world, tile)
+        assert sh[0][0] == 0 and sh[-1][1] == n
+        for (a0, a1), (b0, b1) in zip(sh, sh[1:]):
+            assert a1 == b0 and a0 <= a1
+        for n0, n1 in sh:
+            assert n0 == n1 or (n0 % tile == 0 and (n1 % tile == 0 or n1 == n))  # non-empty shards: whole tiles
+        widths = [b - a for a, b in sh]
+        assert max(widths) - min(w for w in widths) <= tile or n < world * tile
+    with pytest.raises(ValueError):
+        shard_columns(10, 2, 2)
