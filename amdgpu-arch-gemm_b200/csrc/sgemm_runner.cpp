@@ -79,8 +79,10 @@ struct TensorMapKey {
     const void *base = nullptr;
     uint64_t d0 = 0, d1 = 0, stride = 0;
     uint32_t b0 = 0, b1 = 0;
+    int swizzle = 0;
     bool operator==(const TensorMapKey &o) const {
-        return base == o.base && d0 == o.d0 && d1 == o.d1 && stride == o.stride && b0 == o.b0 && b1 == o.b1;
+        return base == o.base && d0 == o.d0 && d1 == o.d1 && stride == o.stride && b0 == o.b0 && b1 == o.b1 &&
+               swizzle == o.swizzle;
     }
 };
 struct CachedMap {
@@ -285,10 +287,13 @@ int ensure_workspace(sgemm_handle *h, size_t bytes, CUdeviceptr *ws) {
     return SGEMM_OK;
 }
 
+// 2-D FP32 tensor map, dims {d0 (contiguous), d1}, box {b0, b1}.  `swizzle`: 128-byte swizzle of 16-byte units
+// for K-major operand tiles, of 32-byte units for the MN-major A tile (the only shared-memory layout the
+// tensor core accepts for 32-bit MN-major operands).
 int encode_map(sgemm_handle *h, int slot, const void *base, uint64_t d0, uint64_t d1, uint64_t stride_bytes,
-               uint32_t b0, uint32_t b1, const CUtensorMap **out) {
+               uint32_t b0, uint32_t b1, CUtensorMapSwizzle swizzle, const CUtensorMap **out) {
     CachedMap &c = h->maps[slot];
-    TensorMapKey key{base, d0, d1, stride_bytes, b0, b1};
+    TensorMapKey key{base, d0, d1, stride_bytes, b0, b1, (int)swizzle};
     if (!(c.valid && c.key == key)) {
         const cuuint64_t dims[2] = {d0, d1};
         const cuuint64_t strides[1] = {stride_bytes};
@@ -296,7 +301,7 @@ int encode_map(sgemm_handle *h, int slot, const void *base, uint64_t d0, uint64_
         const cuuint32_t estr[2] = {1, 1};
         CUresult r = driver().cuTensorMapEncodeTiled_(&c.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
                                                       const_cast<void *>(base), dims, strides, box, estr,
-                                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                      CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS)
@@ -394,17 +399,17 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
             void *ps[] = {&na, &na, &zero, &dB, &lo_b, &p.span_b};
             rc = launch(h, h->fn_split_lo, blocks, 1, 1, 256, 1, 0, stream, ps);
             if (rc) return rc;
-            if ((rc = encode_map(h, 0, hi_t, k, m, (uint64_t)p.ldt * 4, 32, 128, &ma_hi))) return rc;
-            if ((rc = encode_map(h, 1, lo_a, k, m, (uint64_t)p.ldt * 4, 32, 128, &ma_lo))) return rc;
+            if ((rc = encode_map(h, 0, hi_t, k, m, (uint64_t)p.ldt * 4, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B, &ma_hi))) return rc;
+            if ((rc = encode_map(h, 1, lo_a, k, m, (uint64_t)p.ldt * 4, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B, &ma_lo))) return rc;
         } else {
             void *ps[] = {&dA, &lo_a, &p.span_a, &dB, &lo_b, &p.span_b};
             rc = launch(h, h->fn_split_lo, blocks, 1, 1, 256, 1, 0, stream, ps);
             if (rc) return rc;
-            if ((rc = encode_map(h, 0, dA, m, k, (uint64_t)lda * 4, 32, bk, &ma_hi))) return rc;
-            if ((rc = encode_map(h, 1, lo_a, m, k, (uint64_t)lda * 4, 32, bk, &ma_lo))) return rc;
+            if ((rc = encode_map(h, 0, dA, m, k, (uint64_t)lda * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &ma_hi))) return rc;
+            if ((rc = encode_map(h, 1, lo_a, m, k, (uint64_t)lda * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &ma_lo))) return rc;
         }
-        if ((rc = encode_map(h, 2, dB, k, n, (uint64_t)ldb * 4, 32, bn, &mb_hi))) return rc;
-        if ((rc = encode_map(h, 3, lo_b, k, n, (uint64_t)ldb * 4, 32, bn, &mb_lo))) return rc;
+        if ((rc = encode_map(h, 2, dB, k, n, (uint64_t)ldb * 4, 32, bn, CU_TENSOR_MAP_SWIZZLE_128B, &mb_hi))) return rc;
+        if ((rc = encode_map(h, 3, lo_b, k, n, (uint64_t)ldb * 4, 32, bn, CU_TENSOR_MAP_SWIZZLE_128B, &mb_lo))) return rc;
         void *params[] = {&dA, &dB, &dC, &dD, &m, &n, &k, &lda, &ldb, &ldc, &ldd, &alpha, &beta, &nwx, &nwy,
                           &partial, &status_ptr, &split,
                           const_cast<CUtensorMap *>(ma_hi), const_cast<CUtensorMap *>(ma_lo),

@@ -21,8 +21,10 @@
 //
 // Operand tiles in shared memory (128-byte swizzle, written by TMA, read by the tensor core):
 //   A (column-major, M contiguous => "MN-major" operand): per 32 rows of M one chunk of TC_BK rows
-//     of 128 bytes (row = one k, 32 consecutive m);   LBO = chunk stride, SBO = 8 rows = 1024 B;
-//     one K=8 MMA step advances the start address by 1024 B.
+//     of 128 bytes (row = one k, 32 consecutive m).  32-bit MN-major operands must use the 128-byte
+//     swizzle with 32-byte atoms (descriptor layout 1; TMA mode SWIZZLE_128B_ATOM_32B), whose
+//     repeating unit is 4 rows: LBO = chunk stride (next 32 rows of M), SBO = 4 rows = 512 B (next
+//     4 k); one K=8 MMA step spans two units and advances the start address by 1024 B.
 //   B (K contiguous per column => "K-major" operand): per 32 k one sub-tile of BN rows of 128 bytes
 //     (row = one n, 32 consecutive k);                SBO = 8 rows = 1024 B;
 //     one K=8 MMA step advances the start address by 32 B inside the swizzle span.
@@ -161,10 +163,14 @@ __device__ __forceinline__ bool tc_wait(const TcWait &w, uint32_t bar, uint32_t 
 
 // ---------------------------------------------------------------------------------- descriptors
 // 64-bit shared-memory matrix descriptor: start address [0,14) and the two byte offsets [16,30),
-// [32,46) in 16-byte units, descriptor version 1 at [46,48), swizzle mode at [61,64) (2 = 128 B).
-__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// [32,46) in 16-byte units, descriptor version 1 at [46,48), swizzle mode at [61,64)
+// (2 = 128-byte swizzle of 16-byte units, 1 = 128-byte swizzle of 32-byte units).
+#define TC_LAYOUT_SW128 2ull
+#define TC_LAYOUT_SW128_32B 1ull
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                 uint64_t layout) {
     return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) |
-           ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
+           ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46) | (layout << 61);
 }
 // 32-bit instruction descriptor of kind::tf32: FP32 accumulate [4,6)=1, A/B format TF32 [7,10) and
 // [10,13) = 2, A/B major [15]/[16] (1 = MN-major), N>>3 at [17,23), M>>4 at [24,29).
@@ -297,16 +303,16 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                     for (int kk = 0; kk < TC_BK / 8; ++kk) {
 #if TC_A_KMAJOR
                         const uint32_t a_off = (kk / 4) * TC_A_SUB_BYTES + (kk % 4) * 32;
-                        const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, 16, 1024);
-                        const uint64_t da_lo = tc_smem_desc(sa_lo + a_off, 16, 1024);
+                        const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, 16, 1024, TC_LAYOUT_SW128);
+                        const uint64_t da_lo = tc_smem_desc(sa_lo + a_off, 16, 1024, TC_LAYOUT_SW128);
 #else
                         const uint32_t a_off = kk * 1024;
-                        const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, TC_A_CHUNK_BYTES, 1024);
-                        const uint64_t da_lo = tc_smem_desc(sa_lo + a_off, TC_A_CHUNK_BYTES, 1024);
+                        const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
+                        const uint64_t da_lo = tc_smem_desc(sa_lo + a_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
 #endif
                         const uint32_t b_off = (kk / 4) * TC_B_SUB_BYTES + (kk % 4) * 32;
-                        const uint64_t db_hi = tc_smem_desc(sb_hi + b_off, 16, 1024);
-                        const uint64_t db_lo = tc_smem_desc(sb_lo + b_off, 16, 1024);
+                        const uint64_t db_hi = tc_smem_desc(sb_hi + b_off, 16, 1024, TC_LAYOUT_SW128);
+                        const uint64_t db_lo = tc_smem_desc(sb_lo + b_off, 16, 1024, TC_LAYOUT_SW128);
                         const uint32_t first = (kb == kb_begin && kk == 0) ? 0u : 1u;
 #if TC_TERMS == 3
                         tc_mma_tf32(d_tmem, da_lo, db_hi, TC_IDESC, first);
