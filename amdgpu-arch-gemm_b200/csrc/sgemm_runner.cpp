@@ -228,8 +228,10 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
         p->tiles_m = (m + h->tile_m - 1) / h->tile_m;
         p->tiles_n = (n + h->tile_n - 1) / h->tile_n;
         p->split_k = pick_split_k(h, p->tiles_m * p->tiles_n, k, (uint32_t)h->cfg.depth_k);
+        // persistent grid: one CTA (or CTA pair) per SM (pair of SMs), never more launch units than tiles
         const uint64_t units = (uint64_t)p->tiles_m * p->tiles_n * p->split_k;
-        p->grid_x = (uint32_t)std::min<uint64_t>(units, (uint64_t)h->sm_count);
+        const uint32_t group = (uint32_t)std::max(1, h->cfg.wave_group[0]);
+        p->grid_x = group * (uint32_t)std::min<uint64_t>(units, (uint64_t)std::max(1, h->sm_count / (int)group));
         p->span_b = (uint64_t)ldb * (n - 1) + k;
         if (h->cfg.a_kmajor) {
             p->ldt = (uint32_t)round_up(k, 4);
@@ -386,7 +388,11 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
     if (p.variant == kVariantTensor) {
         float *lo_a = reinterpret_cast<float *>(ws + p.lo_a_off);
         float *lo_b = reinterpret_cast<float *>(ws + p.lo_b_off);
-        const uint32_t bk = (uint32_t)h->cfg.depth_k, bn = h->tile_n;
+        // a CTA pair (wave_group[0] = 2) stages half of the tile's columns of B per CTA
+        const uint32_t bk = (uint32_t)h->cfg.depth_k, bn = h->tile_n / (uint32_t)std::max(1, h->cfg.wave_group[0]);
+        // K-major tiles: rows of min(bk, 32) floats, 128-byte swizzle (64-byte for bk = 16)
+        const uint32_t kspan = std::min<uint32_t>(bk, 32);
+        const CUtensorMapSwizzle ksw = kspan == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
         const CUtensorMap *ma_hi, *ma_lo, *mb_hi, *mb_lo;
         const uint32_t blocks = (uint32_t)h->sm_count * 4;
         if (h->cfg.a_kmajor) {
@@ -399,8 +405,8 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
             void *ps[] = {&na, &na, &zero, &dB, &lo_b, &p.span_b};
             rc = launch(h, h->fn_split_lo, blocks, 1, 1, 256, 1, 0, stream, ps);
             if (rc) return rc;
-            if ((rc = encode_map(h, 0, hi_t, k, m, (uint64_t)p.ldt * 4, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B, &ma_hi))) return rc;
-            if ((rc = encode_map(h, 1, lo_a, k, m, (uint64_t)p.ldt * 4, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B, &ma_lo))) return rc;
+            if ((rc = encode_map(h, 0, hi_t, k, m, (uint64_t)p.ldt * 4, kspan, 128, ksw, &ma_hi))) return rc;
+            if ((rc = encode_map(h, 1, lo_a, k, m, (uint64_t)p.ldt * 4, kspan, 128, ksw, &ma_lo))) return rc;
         } else {
             void *ps[] = {&dA, &lo_a, &p.span_a, &dB, &lo_b, &p.span_b};
             rc = launch(h, h->fn_split_lo, blocks, 1, 1, 256, 1, 0, stream, ps);
@@ -408,8 +414,8 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
             if ((rc = encode_map(h, 0, dA, m, k, (uint64_t)lda * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &ma_hi))) return rc;
             if ((rc = encode_map(h, 1, lo_a, m, k, (uint64_t)lda * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &ma_lo))) return rc;
         }
-        if ((rc = encode_map(h, 2, dB, k, n, (uint64_t)ldb * 4, 32, bn, CU_TENSOR_MAP_SWIZZLE_128B, &mb_hi))) return rc;
-        if ((rc = encode_map(h, 3, lo_b, k, n, (uint64_t)ldb * 4, 32, bn, CU_TENSOR_MAP_SWIZZLE_128B, &mb_lo))) return rc;
+        if ((rc = encode_map(h, 2, dB, k, n, (uint64_t)ldb * 4, kspan, bn, ksw, &mb_hi))) return rc;
+        if ((rc = encode_map(h, 3, lo_b, k, n, (uint64_t)ldb * 4, kspan, bn, ksw, &mb_lo))) return rc;
         void *params[] = {&dA, &dB, &dC, &dD, &m, &n, &k, &lda, &ldb, &ldc, &ldd, &alpha, &beta, &nwx, &nwy,
                           &partial, &status_ptr, &split,
                           const_cast<CUtensorMap *>(ma_hi), const_cast<CUtensorMap *>(ma_lo),

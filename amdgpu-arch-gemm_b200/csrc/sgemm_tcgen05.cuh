@@ -28,15 +28,25 @@
 //   B (K contiguous per column => "K-major" operand): per 32 k one sub-tile of BN rows of 128 bytes
 //     (row = one n, 32 consecutive k);                SBO = 8 rows = 1024 B;
 //     one K=8 MMA step advances the start address by 32 B inside the swizzle span.
+//     TC_BK = 16 uses 64-byte rows with the 64-byte swizzle instead (SBO = 512 B).
 //   With TC_A_KMAJOR the A operand is read from K-major packed copies (sgemm_pack_a_kmajor) and
 //   uses B's layout.
+//
+// TC_CTA_GROUP = 2 pairs two CTAs (a 2x1 cluster, two neighbouring SMs) on one 256 x TC_BN tile with
+// tcgen05.mma.cta_group::2: CTA r of the pair loads rows 128r.. of the A tile and columns (TC_BN/2)r.. of
+// the B tile into its OWN shared memory (no cluster-wide copies), so per SM the B traffic halves and a
+// stage shrinks to 2*(128 + TC_BN/2)*TC_BK*4 bytes.  Only the leader (rank 0) issues MMAs; they read both
+// CTAs' shared memory and write both CTAs' TMEM (each CTA holds its 128 rows x TC_BN columns).  Barriers:
+//   full[s]      lives in the leader; both CTAs' TMA loads report their bytes to it
+//   empty[s]     one per CTA; the leader commits to its own and to the peer's copy (two plain commits)
+//   tmem_full[b] one per CTA, committed the same way;  tmem_empty[b] in the leader, 4 warps x 2 CTAs arrive
 //
 // Every mbarrier wait is bounded: after TC_TIMEOUT_NS without progress the waiting role records a
 // status word, raises a CTA-wide abort flag and all roles leave their loops, release TMEM and
 // return; the host reads the status after synchronising.
 //
-// Generator-supplied macros: TC_BN (tile columns), TC_BK (k per stage, multiple of 32), TC_STAGES,
-// TC_A_KMAJOR (0/1), TC_TERMS (3 = 3xTF32, 1 = plain TF32 for bring-up), OPT_WGM.
+// Generator-supplied macros: TC_BN (tile columns), TC_BK (k per stage: 16 or a multiple of 32), TC_STAGES,
+// TC_CTA_GROUP (1/2), TC_A_KMAJOR (0/1), TC_TERMS (3 = 3xTF32, 1 = plain TF32 for bring-up), OPT_WGM.
 // ---------------------------------------------------------------------------------------------
 #ifndef TC_TERMS
 #define TC_TERMS 3
@@ -45,21 +55,30 @@
 #define TC_TIMEOUT_NS 2000000000ull
 #endif
 
-#define TC_BM 128
+#ifndef TC_CTA_GROUP
+#define TC_CTA_GROUP 1
+#endif
+#define TC_BM 128                              // rows of A (and of the accumulator) per CTA
+#define TC_UMMA_M (TC_BM * TC_CTA_GROUP)       // rows of the launch unit's tile = UMMA M
+#define TC_BN_CTA (TC_BN / TC_CTA_GROUP)       // columns of B this CTA keeps in shared memory
 #define TC_THREADS 192
 #define TC_A_BYTES (TC_BM * TC_BK * 4)
-#define TC_B_BYTES (TC_BN * TC_BK * 4)
+#define TC_B_BYTES (TC_BN_CTA * TC_BK * 4)
 #define TC_STAGE_BYTES (2 * TC_A_BYTES + 2 * TC_B_BYTES)
+#define TC_KSPAN (TC_BK >= 32 ? 32 : TC_BK)    // k per swizzled row of a K-major tile (128-byte or 64-byte rows)
+#define TC_KROW_BYTES (TC_KSPAN * 4)
+#define TC_KSUBS (TC_BK / TC_KSPAN)            // K-major sub-tiles per stage
 #define TC_A_CHUNK_BYTES (TC_BK * 128)         // MN-major: 32 rows of M x TC_BK
-#define TC_A_SUB_BYTES (TC_BM * 128)           // K-major : TC_BM rows x 32 k
-#define TC_B_SUB_BYTES (TC_BN * 128)           // K-major : TC_BN rows x 32 k
+#define TC_A_SUB_BYTES (TC_BM * TC_KROW_BYTES) // K-major : TC_BM rows x TC_KSPAN k
+#define TC_B_SUB_BYTES (TC_BN_CTA * TC_KROW_BYTES) // K-major : TC_BN_CTA rows x TC_KSPAN k
 #define TC_TMEM_COLS_NEEDED (2 * TC_BN)
 #define TC_TMEM_COLS (TC_TMEM_COLS_NEEDED <= 32 ? 32 : TC_TMEM_COLS_NEEDED <= 64 ? 64 : \
                       TC_TMEM_COLS_NEEDED <= 128 ? 128 : TC_TMEM_COLS_NEEDED <= 256 ? 256 : 512)
 #define TC_SMEM_BYTES (TC_STAGES * TC_STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/)
 
-static_assert(TC_BK % 32 == 0, "k per stage is a whole number of 128-byte swizzle spans");
-static_assert(TC_BN % 16 == 0 && TC_BN >= 16 && TC_BN <= 256, "UMMA N for M=128");
+static_assert(TC_BK == 16 || TC_BK % 32 == 0, "k per stage: one 64-byte span or whole 128-byte swizzle spans");
+static_assert(TC_CTA_GROUP == 1 || TC_CTA_GROUP == 2, "one CTA or a CTA pair per tile");
+static_assert(TC_BN % (16 * TC_CTA_GROUP) == 0 && TC_BN >= 16 * TC_CTA_GROUP && TC_BN <= 256, "UMMA N");
 static_assert(TC_SMEM_BYTES <= 232448, "shared memory budget of one CTA");
 
 struct alignas(64) TcTensorMap { uint64_t opaque[16]; };
@@ -91,11 +110,32 @@ __device__ __forceinline__ uint32_t tc_mbar_try_wait(uint32_t bar, uint32_t pari
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
 }
+// TMA tile load into this CTA's shared memory.  In a CTA pair the completion bytes are reported to the
+// leader's mbarrier (`bar` is then a shared::cluster address), which the cta_group::2 form permits.
 __device__ __forceinline__ void tc_tma_load_2d(uint32_t dst, const TcTensorMap *map, uint32_t bar,
                                                int32_t x, int32_t y) {
+#if TC_CTA_GROUP == 2
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+#else
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+#endif
+}
+// shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t tc_map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void tc_mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tc_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tc_prefetch_map(const TcTensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
@@ -107,11 +147,23 @@ __device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, ui
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
+#if TC_CTA_GROUP == 2
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+#else
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+#endif
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// Arrive on `bar` once every MMA issued so far by this thread has completed.  In a CTA pair the same
+// barrier exists in both CTAs: the leader commits to its own copy and to the peer's (rank 1) copy.
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
+#if TC_CTA_GROUP == 2
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(tc_map_to_cta(bar, 1u)) : "memory");
+#else
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+#endif
 }
 __device__ __forceinline__ void tc_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -166,7 +218,11 @@ __device__ __forceinline__ bool tc_wait(const TcWait &w, uint32_t bar, uint32_t 
 // [32,46) in 16-byte units, descriptor version 1 at [46,48), swizzle mode at [61,64)
 // (2 = 128-byte swizzle of 16-byte units, 1 = 128-byte swizzle of 32-byte units).
 #define TC_LAYOUT_SW128 2ull
+#define TC_LAYOUT_SW64 4ull
 #define TC_LAYOUT_SW128_32B 1ull
+#define TC_LAYOUT_KMAJOR (TC_KSPAN == 32 ? TC_LAYOUT_SW128 : TC_LAYOUT_SW64)
+#define TC_KMAJOR_SBO (8 * TC_KROW_BYTES)      // 8 rows of a K-major tile
+#define TC_KMAJOR_OFF(kk, sub_bytes) (((kk) / (TC_KSPAN / 8)) * (sub_bytes) + ((kk) % (TC_KSPAN / 8)) * 32)
 __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
                                                  uint64_t layout) {
     return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) |
@@ -175,10 +231,15 @@ __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr, uint32_t lbo_byt
 // 32-bit instruction descriptor of kind::tf32: FP32 accumulate [4,6)=1, A/B format TF32 [7,10) and
 // [10,13) = 2, A/B major [15]/[16] (1 = MN-major), N>>3 at [17,23), M>>4 at [24,29).
 #define TC_IDESC ((1u << 4) | (2u << 7) | (2u << 10) | ((TC_A_KMAJOR ? 0u : 1u) << 15) | (0u << 16) | \
-                  ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24))
+                  ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_UMMA_M >> 4) << 24))
 
 // --------------------------------------------------------------------------------------- kernel
-extern "C" __global__ void __launch_bounds__(TC_THREADS, 1)
+#if TC_CTA_GROUP == 2
+#define TC_CLUSTER_ATTR __cluster_dims__(2, 1, 1)
+#else
+#define TC_CLUSTER_ATTR
+#endif
+extern "C" __global__ void TC_CLUSTER_ATTR __launch_bounds__(TC_THREADS, 1)
 generated_gemm(const float *a, const float *b, const float *c, float *d,
                uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
                float alpha, float beta, int32_t num_wg_x, int32_t num_wg_y,
@@ -201,6 +262,13 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const TcWait waiter{abort_flag, status};
+#if TC_CTA_GROUP == 2
+    uint32_t cta_rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cta_rank));
+#else
+    const uint32_t cta_rank = 0;
+#endif
+    const uint32_t unit0 = blockIdx.x / TC_CTA_GROUP, unit_stride = gridDim.x / TC_CTA_GROUP;
 
     const uint32_t tiles_mn = (uint32_t)num_wg_x * (uint32_t)num_wg_y;
     const uint32_t num_tiles = tiles_mn * split_k;
@@ -214,7 +282,7 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
         }
         for (int i = 0; i < 2; ++i) {
             tc_mbar_init(bar_tfull + 8 * i, 1);
-            tc_mbar_init(bar_tempty + 8 * i, 4);
+            tc_mbar_init(bar_tempty + 8 * i, 4 * TC_CTA_GROUP);
         }
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -225,12 +293,22 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
         tc_prefetch_map(&map_b_lo);
     }
     if (warp == 1) {
+#if TC_CTA_GROUP == 2
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(tc_smem_u32(tmem_slot)), "r"((uint32_t)TC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+#else
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(tc_smem_u32(tmem_slot)), "r"((uint32_t)TC_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+#endif
     }
     tc_fence_before();
+#if TC_CTA_GROUP == 2
+    tc_cluster_sync();   // the peer's barriers must be initialised before anything is signalled to them
+#else
     __syncthreads();
+#endif
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -239,26 +317,29 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool alive = true;
-            for (uint32_t tile = blockIdx.x; alive && tile < num_tiles; tile += gridDim.x) {
+            // in a CTA pair every load reports to the leader's "full" barrier
+            const uint32_t full_base = TC_CTA_GROUP == 2 ? tc_map_to_cta(bar_full, 0u) : bar_full;
+            for (uint32_t tile = unit0; alive && tile < num_tiles; tile += unit_stride) {
                 const uint32_t z = tile / tiles_mn;
                 uint32_t tx, ty;
                 sgemm_tile_raster(tile - z * tiles_mn, (uint32_t)num_wg_x, (uint32_t)num_wg_y, OPT_WGM, tx, ty);
-                const int32_t m0 = (int32_t)(tx * TC_BM), n0 = (int32_t)(ty * TC_BN);
+                const int32_t m0 = (int32_t)(tx * TC_UMMA_M + cta_rank * TC_BM);
+                const int32_t n0 = (int32_t)(ty * TC_BN + cta_rank * TC_BN_CTA);
                 const uint32_t kb_begin = min(kb_total, z * kb_per), kb_end = min(kb_total, kb_begin + kb_per);
                 for (uint32_t kb = kb_begin; kb < kb_end; ++kb) {
                     if (!tc_wait(waiter, bar_empty + 8 * stage, phase ^ 1u, 0x100u + stage, tile, kb)) { alive = false; break; }
-                    const uint32_t full = bar_full + 8 * stage;
+                    const uint32_t full = full_base + 8 * stage;
                     const uint32_t sa_hi = smem_base + stage * TC_STAGE_BYTES;
                     const uint32_t sa_lo = sa_hi + TC_A_BYTES;
                     const uint32_t sb_hi = sa_lo + TC_A_BYTES;
                     const uint32_t sb_lo = sb_hi + TC_B_BYTES;
                     const int32_t k0 = (int32_t)(kb * TC_BK);
-                    tc_mbar_expect_tx(full, TC_STAGE_BYTES);
+                    if (cta_rank == 0) tc_mbar_expect_tx(bar_full + 8 * stage, TC_CTA_GROUP * TC_STAGE_BYTES);
 #if TC_A_KMAJOR
 #pragma unroll
-                    for (int sub = 0; sub < TC_BK / 32; ++sub) {
-                        tc_tma_load_2d(sa_hi + sub * TC_A_SUB_BYTES, &map_a_hi, full, k0 + 32 * sub, m0);
-                        tc_tma_load_2d(sa_lo + sub * TC_A_SUB_BYTES, &map_a_lo, full, k0 + 32 * sub, m0);
+                    for (int sub = 0; sub < TC_KSUBS; ++sub) {
+                        tc_tma_load_2d(sa_hi + sub * TC_A_SUB_BYTES, &map_a_hi, full, k0 + TC_KSPAN * sub, m0);
+                        tc_tma_load_2d(sa_lo + sub * TC_A_SUB_BYTES, &map_a_lo, full, k0 + TC_KSPAN * sub, m0);
                     }
 #else
 #pragma unroll
@@ -268,9 +349,9 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                     }
 #endif
 #pragma unroll
-                    for (int sub = 0; sub < TC_BK / 32; ++sub) {
-                        tc_tma_load_2d(sb_hi + sub * TC_B_SUB_BYTES, &map_b_hi, full, k0 + 32 * sub, n0);
-                        tc_tma_load_2d(sb_lo + sub * TC_B_SUB_BYTES, &map_b_lo, full, k0 + 32 * sub, n0);
+                    for (int sub = 0; sub < TC_KSUBS; ++sub) {
+                        tc_tma_load_2d(sb_hi + sub * TC_B_SUB_BYTES, &map_b_hi, full, k0 + TC_KSPAN * sub, n0);
+                        tc_tma_load_2d(sb_lo + sub * TC_B_SUB_BYTES, &map_b_lo, full, k0 + TC_KSPAN * sub, n0);
                     }
                     if (++stage == TC_STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -278,10 +359,10 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
         }
     } else if (warp == 1) {
         // -------------------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
+        if (lane == 0 && cta_rank == 0) {
             uint32_t stage = 0, phase = 0, local = 0;
             bool alive = true;
-            for (uint32_t tile = blockIdx.x; alive && tile < num_tiles; tile += gridDim.x, ++local) {
+            for (uint32_t tile = unit0; alive && tile < num_tiles; tile += unit_stride, ++local) {
                 const uint32_t z = tile / tiles_mn;
                 const uint32_t kb_begin = min(kb_total, z * kb_per), kb_end = min(kb_total, kb_begin + kb_per);
                 const uint32_t buf = local & 1u, acc_phase = (local >> 1) & 1u;
@@ -290,6 +371,7 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                 const uint32_t d_tmem = tmem_base + buf * TC_BN;
                 if (kb_begin == kb_end) {  // empty K range: nothing to wait for, hand the buffer over
                     tc_mbar_arrive(bar_tfull + 8 * buf);
+                    if (TC_CTA_GROUP == 2) tc_mbar_arrive_cluster(tc_map_to_cta(bar_tfull + 8 * buf, 1u));
                     continue;
                 }
                 for (uint32_t kb = kb_begin; kb < kb_end; ++kb) {
@@ -302,17 +384,17 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
 #pragma unroll
                     for (int kk = 0; kk < TC_BK / 8; ++kk) {
 #if TC_A_KMAJOR
-                        const uint32_t a_off = (kk / 4) * TC_A_SUB_BYTES + (kk % 4) * 32;
-                        const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, 16, 1024, TC_LAYOUT_SW128);
-                        const uint64_t da_lo = tc_smem_desc(sa_lo + a_off, 16, 1024, TC_LAYOUT_SW128);
+                        const uint32_t a_off = TC_KMAJOR_OFF(kk, TC_A_SUB_BYTES);
+                        const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);
+                        const uint64_t da_lo = tc_smem_desc(sa_lo + a_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);
 #else
                         const uint32_t a_off = kk * 1024;
                         const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
                         const uint64_t da_lo = tc_smem_desc(sa_lo + a_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
 #endif
-                        const uint32_t b_off = (kk / 4) * TC_B_SUB_BYTES + (kk % 4) * 32;
-                        const uint64_t db_hi = tc_smem_desc(sb_hi + b_off, 16, 1024, TC_LAYOUT_SW128);
-                        const uint64_t db_lo = tc_smem_desc(sb_lo + b_off, 16, 1024, TC_LAYOUT_SW128);
+                        const uint32_t b_off = TC_KMAJOR_OFF(kk, TC_B_SUB_BYTES);
+                        const uint64_t db_hi = tc_smem_desc(sb_hi + b_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);
+                        const uint64_t db_lo = tc_smem_desc(sb_lo + b_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);
                         const uint32_t first = (kb == kb_begin && kk == 0) ? 0u : 1u;
 #if TC_TERMS == 3
                         tc_mma_tf32(d_tmem, da_lo, db_hi, TC_IDESC, first);
@@ -334,16 +416,19 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
         const uint32_t quarter = warp & 3u;  // TMEM lane quarter this warp may read
         uint32_t local = 0;
         bool alive = true;
-        for (uint32_t tile = blockIdx.x; alive && tile < num_tiles; tile += gridDim.x, ++local) {
+        // the accumulator buffer is handed back to the leader's MMA thread
+        const uint32_t tempty_base = TC_CTA_GROUP == 2 ? tc_map_to_cta(bar_tempty, 0u) : bar_tempty;
+        for (uint32_t tile = unit0; alive && tile < num_tiles; tile += unit_stride, ++local) {
             const uint32_t z = tile / tiles_mn;
             uint32_t tx, ty;
             sgemm_tile_raster(tile - z * tiles_mn, (uint32_t)num_wg_x, (uint32_t)num_wg_y, OPT_WGM, tx, ty);
             const uint32_t kb_begin = min(kb_total, z * kb_per), kb_end = min(kb_total, kb_begin + kb_per);
             const bool empty_k = kb_begin == kb_end;
             const uint32_t buf = local & 1u, acc_phase = (local >> 1) & 1u;
-            if (!tc_wait(waiter, bar_tfull + 8 * buf, acc_phase, 0x400u + buf, tile, 0)) { alive = false; break; }
+            alive = __all_sync(0xffffffffu, tc_wait(waiter, bar_tfull + 8 * buf, acc_phase, 0x400u + buf, tile, 0));
+            if (!alive) break;
             tc_fence_after();
-            const uint32_t row = tx * TC_BM + quarter * 32 + lane;
+            const uint32_t row = tx * TC_UMMA_M + cta_rank * TC_BM + quarter * 32 + lane;
             const uint32_t col0 = ty * TC_BN;
             const bool partial = split_k > 1;
             float *out = partial ? ws + (uint64_t)z * m * n : d;
@@ -371,13 +456,20 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) tc_mbar_arrive(bar_tempty + 8 * buf);
+            if (lane == 0) {
+                if (TC_CTA_GROUP == 2) tc_mbar_arrive_cluster(tempty_base + 8 * buf);
+                else tc_mbar_arrive(bar_tempty + 8 * buf);
+            }
         }
     }
 
     // teardown: every thread gets here on both the normal and the abort path
     tc_fence_before();
+#if TC_CTA_GROUP == 2
+    tc_cluster_sync();   // neither CTA may release TMEM or exit while the other can still reach into it
+#else
     __syncthreads();
+#endif
     if (warp == 1) {
         if (*abort_flag) {
             // give copies and MMAs that may still be in flight time to land before TMEM is released
@@ -385,7 +477,12 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
             while (tc_globaltimer() - t0 < 2000000ull) __nanosleep(1000);
         }
         tc_fence_after();
+#if TC_CTA_GROUP == 2
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"((uint32_t)TC_TMEM_COLS) : "memory");
+#else
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
                      ::"r"(tmem_base), "r"((uint32_t)TC_TMEM_COLS) : "memory");
+#endif
     }
 }

@@ -199,8 +199,9 @@ class GemmSolutionConfig:
 
     # ------------------------------------------------------------------ variant-specific checks
     def _check_tensor(self):
-        if self.wave_group not in ((1, 1),):
-            raise RuntimeError(f"cluster shape {self.wave_group} is not implemented for the tensor variant")
+        if self.wave_group not in ((1, 1), (2, 1)):
+            raise RuntimeError(f"cluster shape {self.wave_group} is not implemented for the tensor variant "
+                               f"(1x1: one CTA per tile, 2x1: a CTA pair on a 256-row tile)")
         if self.wave_tiling[0] != 1:
             raise RuntimeError("the tensor variant holds one 128-row atom per CTA (wave_tiling[0] must be 1)")
         bn = self.tile_size[1]
@@ -208,8 +209,11 @@ class GemmSolutionConfig:
             raise RuntimeError(f"tile N = {bn} must be a multiple of 16 in [32, 256] (UMMA N for M = 128)")
         if bn % 32:
             raise RuntimeError(f"tile N = {bn} must be a multiple of 32 (epilogue reads 32 TMEM columns at a time)")
-        if self.depth_k % 32:
-            raise RuntimeError(f"depth_k = {self.depth_k} must be a multiple of 32 (128-byte swizzle span of FP32)")
+        if self.wave_group[0] == 2 and bn % 64:
+            raise RuntimeError(f"tile N = {bn} must be a multiple of 64 for a CTA pair (each CTA stages N/2 columns)")
+        if self.depth_k != 16 and self.depth_k % 32:
+            raise RuntimeError(f"depth_k = {self.depth_k} must be 16 (one 64-byte swizzle span of FP32) or a "
+                               f"multiple of 32 (whole 128-byte spans)")
         if 2 * bn > MAX_TMEM_COLUMNS:
             raise RuntimeError("two accumulator buffers exceed the 512 TMEM columns")
         if self.a_major not in ("mn", "k"):
@@ -266,7 +270,7 @@ class GemmSolutionConfig:
         """Bytes one global->shared transfer moves per operand: a 16-byte vector per thread for SIMT (the
         reference's tuner keeps only configurations where this is (16, 16)), a whole TMA box for tcgen05."""
         if self.variant == VARIANT_TENSOR:
-            return 32 * self.depth_k * 4, 32 * self.tile_size[1] * 4
+            return 32 * self.depth_k * 4, min(self.depth_k, 32) * (self.tile_size[1] // self.wave_group[0]) * 4
         return 16, 16
 
     @property
@@ -282,7 +286,8 @@ class GemmSolutionConfig:
     def lds_usage_bytes(self) -> int:
         bm, bn = self.tile_size
         if self.variant == VARIANT_TENSOR:
-            stage = 2 * (128 * self.depth_k * 4) + 2 * (bn * self.depth_k * 4)   # A_hi, A_lo, B_hi, B_lo
+            bn_cta = bn // self.wave_group[0]                                    # a CTA pair splits B's columns
+            stage = 2 * (128 * self.depth_k * 4) + 2 * (bn_cta * self.depth_k * 4)  # A_hi, A_lo, B_hi, B_lo
             return self.stages * stage + 1024 + 256                              # + alignment slack + barriers
         return 2 * self.depth_k * (bm + bn + 4) * 4                              # double-buffered A and padded B
 
@@ -397,7 +402,8 @@ def gemm(context: GpuContext, name: str, arch: str, config: GemmSolutionConfig, 
         out.write(_defines(_simt_defines(simt_fallback_config(), opt, SIMT_FALLBACK_ENTRY)))
         out.write(_read("sgemm_simt.cuh"))
         out.write(_defines([("TC_BN", config.tile_size[1]), ("TC_BK", config.depth_k),
-                            ("TC_STAGES", config.stages), ("TC_A_KMAJOR", 1 if config.a_major == "k" else 0),
+                            ("TC_STAGES", config.stages), ("TC_CTA_GROUP", config.wave_group[0]),
+                            ("TC_A_KMAJOR", 1 if config.a_major == "k" else 0),
                             ("TC_TERMS", config.terms)]))
         out.write(_read("sgemm_tcgen05.cuh"))
     src = out.getvalue()
@@ -427,10 +433,10 @@ def compile(kern_name: str, kern_str: str, arch: str, output_folder: str, gemm_c
     return ret.returncode
 
 
-def tensor_config(bn: int = 256, bk: int = 32, stages: int = 2, **kw) -> GemmSolutionConfig:
-    """Shorthand for a tensor-variant configuration with tile 128 x bn x bk."""
+def tensor_config(bn: int = 256, bk: int = 32, stages: int = 2, cluster: int = 1, **kw) -> GemmSolutionConfig:
+    """Shorthand for a tensor-variant configuration with tile (128 * cluster) x bn x bk."""
     return GemmSolutionConfig(DataType.FP32, DataType.FP32, DataType.FP32, DataType.FP32,
-                              (128, bn, 1, 8), (1, 1), (1, 1), bk, False, False, vmem_stage=stages - 1, **kw)
+                              (128, bn, 1, 8), (cluster, 1), (1, 1), bk, False, False, vmem_stage=stages - 1, **kw)
 
 
 def simt_config(bm: int = 128, bn: int = 128, bk: int = 16, tm: int = 8, tn: int = 8) -> GemmSolutionConfig:

@@ -23,8 +23,15 @@ REGISTRY = {
     "tc_128x128x32_s3": (lambda: tensor_config(128, 32, 3), dict(wgm=8)),
     "tc_128x64x32_s4": (lambda: tensor_config(64, 32, 4), dict(wgm=8)),
     "tc_128x64x64_s2": (lambda: tensor_config(64, 64, 2), dict(wgm=4)),
+    "tc_128x256x16_s4": (lambda: tensor_config(256, 16, 4), dict(wgm=8)),
+    "tc_128x128x16_s7": (lambda: tensor_config(128, 16, 7), dict(wgm=8)),
+    # CTA pairs (cluster 2x1, tcgen05 cta_group::2): tile 256 x BN x BK
+    "tc2_256x256x32_s3": (lambda: tensor_config(256, 32, 3, cluster=2), dict(wgm=4)),
+    "tc2_256x256x16_s6": (lambda: tensor_config(256, 16, 6, cluster=2), dict(wgm=4)),
+    "tc2_256x128x32_s4": (lambda: tensor_config(128, 32, 4, cluster=2), dict(wgm=4)),
     # the same tile reading A from K-major packed copies, and a plain-TF32 build (bring-up aids)
     "tc_128x128x32_s3_ak": (lambda: tensor_config(128, 32, 3, a_major="k"), dict(wgm=8)),
+    "tc_128x128x16_s6_ak": (lambda: tensor_config(128, 16, 6, a_major="k"), dict(wgm=8)),
     "tc_128x128x32_s3_1x": (lambda: tensor_config(128, 32, 3, terms=1), dict(wgm=8)),
     # FFMA SIMT kernels
     "simt_128x128x16": (lambda: simt_config(128, 128, 16, 8, 8), dict(wgm=8)),
@@ -35,7 +42,7 @@ REGISTRY = {
     "legacy_16x16x4_2x2x2x2": (lambda: _legacy((16, 16, 1, 4), (2, 2), (2, 2), 16), dict(wgm=4)),
 }
 
-DEFAULT_TENSOR = "tc_128x256x32_s2"
+DEFAULT_TENSOR = "tc2_256x256x32_s3"
 DEFAULT_SIMT = "simt_128x128x16"
 
 

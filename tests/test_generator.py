@@ -44,7 +44,7 @@ def test_tile_product_rule_and_properties():
 @pytest.mark.parametrize("kwargs", [
     dict(mfma=(128, 256, 1, 8), wg=(1, 1), wt=(1, 1), dk=32, vs=2),     # 3 stages of 96 KiB: over the smem budget
     dict(mfma=(128, 512, 1, 8), wg=(1, 1), wt=(1, 1), dk=32, vs=1),     # N beyond the UMMA / TMEM limit
-    dict(mfma=(128, 128, 1, 8), wg=(1, 1), wt=(1, 1), dk=16, vs=1),     # k per stage below the swizzle span
+    dict(mfma=(128, 128, 1, 8), wg=(1, 1), wt=(1, 1), dk=48, vs=1),     # k per stage neither 16 nor whole 128-byte spans
     dict(mfma=(128, 128, 1, 8), wg=(3, 1), wt=(1, 1), dk=32, vs=1),     # wave_group not a power of two
     dict(mfma=(1, 1, 1, 1), wg=(16, 16), wt=(8, 8), dk=64, vs=1),       # SIMT static smem over 48 KiB
     dict(mfma=(64, 64, 1, 8), wg=(1, 1), wt=(1, 1), dk=32, vs=1),       # no such atom

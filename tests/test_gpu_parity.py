@@ -8,7 +8,9 @@ from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
-TENSOR_KERNELS = ["tc_128x256x32_s2", "tc_128x128x32_s3", "tc_128x64x32_s4", "tc_128x64x64_s2", "tc_128x128x32_s3_ak"]
+TENSOR_KERNELS = ["tc_128x256x32_s2", "tc_128x128x32_s3", "tc_128x64x32_s4", "tc_128x64x64_s2", "tc_128x128x32_s3_ak",
+                  "tc_128x256x16_s4", "tc_128x128x16_s7", "tc_128x128x16_s6_ak",
+                  "tc2_256x256x32_s3", "tc2_256x256x16_s6", "tc2_256x128x32_s4"]
 SIMT_KERNELS = ["simt_128x128x16", "simt_64x64x16", "simt_128x64x8_plr0", "legacy_32x32x2_1wave", "legacy_16x16x4_2x2x2x2"]
 AUTO, TENSOR, SIMT = 0, 1, 2
 _runners = {}
@@ -81,7 +83,8 @@ SHAPES = [(1, 1, 1), (8, 8, 8), (32, 32, 32), (33, 65, 129), (127, 257, 513), (1
           (256, 512, 96), (1000, 1000, 1000), (1024, 1024, 1024), (130, 4, 2048), (4, 300, 77)]
 
 
-@pytest.mark.parametrize("kernel", ["tc_128x256x32_s2", "tc_128x128x32_s3", "tc_128x64x64_s2", "tc_128x128x32_s3_ak"])
+@pytest.mark.parametrize("kernel", ["tc_128x256x32_s2", "tc_128x128x32_s3", "tc_128x64x64_s2", "tc_128x128x32_s3_ak",
+                                    "tc_128x256x16_s4", "tc_128x128x16_s6_ak", "tc2_256x256x32_s3", "tc2_256x128x32_s4"])
 @pytest.mark.parametrize("mnk", SHAPES)
 @pytest.mark.parametrize("alpha,beta", [(1.0, 0.0), (0.5, -1.5)])
 def test_tensor_kernels_match_oracle(runner_of, kernel, mnk, alpha, beta):
