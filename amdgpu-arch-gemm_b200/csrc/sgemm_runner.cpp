@@ -5,6 +5,7 @@
 // The CUDA driver is bound at run time with dlopen("libcuda.so.1"), so the library itself loads (and its
 // host-only entry points work) on a machine without a GPU; every device entry point then fails loudly.
 #include "sgemm_runner.h"
+#include "sgemm_internal.hpp"
 #include "sgemm_toml.hpp"
 
 #include <cuda.h>
@@ -516,6 +517,7 @@ SGEMM_API const char *sgemm_strerror(int code) {
         case SGEMM_ERR_UNSUPPORTED: return "request not supported by the loaded kernel";
         case SGEMM_ERR_WORKSPACE: return "workspace too small or allocation failed";
         case SGEMM_ERR_DEVICE_STATUS: return "a kernel gave up on a bounded wait";
+        case SGEMM_ERR_SCRATCH_LIMIT: return "problem needs more scratch than the allocation-free entry point has";
         default: return "unknown error";
     }
 }
@@ -862,3 +864,37 @@ SGEMM_API int sgemm_dev_sync(sgemm_handle *h) {
     CU_CHECK(h, driver().cuCtxSynchronize_());
     return SGEMM_OK;
 }
+
+// ------------------------------------------------------------------ seam used by sgemm_noalloc.cu
+namespace sgemm_internal {
+
+int handle_device(const sgemm_handle *h) { return h ? h->device : -1; }
+
+int set_error(sgemm_handle *h, int code, const char *message) { return fail(h, code, "%s", message); }
+
+int scratch_bytes(sgemm_handle *h, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb, size_t *bytes) {
+    return sgemm_workspace_bytes(h, m, n, k, lda, ldb, bytes);
+}
+
+int launch_with_scratch(sgemm_handle *h, void *scratch, size_t scratch_bytes, const float *dA, const float *dB,
+                        const float *dC, float *dD, float alpha, float beta, uint32_t m, uint32_t n, uint32_t k,
+                        uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, void *stream) {
+    if (!h) return SGEMM_ERR_INVALID_ARGUMENT;
+    // Borrow the lent-workspace slot for the duration of this call: with a lent block ensure_workspace never
+    // allocates, it only checks the size.  Tensor maps that point into a workspace are re-encoded whenever
+    // their base address changes, so switching blocks between calls is safe.
+    const CUdeviceptr saved_ptr = h->ws_lent;
+    const size_t saved_bytes = h->ws_lent_bytes;
+    h->ws_lent = (CUdeviceptr)(uintptr_t)scratch;
+    h->ws_lent_bytes = scratch_bytes;
+    int rc;
+    {
+        CtxGuard guard(h);
+        rc = launch_device(h, dA, dB, dC, dD, alpha, beta, m, n, k, lda, ldb, ldc, ldd, (CUstream)stream);
+    }
+    h->ws_lent = saved_ptr;
+    h->ws_lent_bytes = saved_bytes;
+    return rc;
+}
+
+}  // namespace sgemm_internal

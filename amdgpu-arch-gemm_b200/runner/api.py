@@ -52,6 +52,8 @@ ABI = {
     "sgemm_open": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(_vp)]),
     "sgemm_close": (ctypes.c_int, [_vp]),
     "sgemm_launch": (ctypes.c_int, _GEMM_ARGS + [_vp]),
+    "sgemm_launch_noalloc": (ctypes.c_int, _GEMM_ARGS + [_vp]),
+    "sgemm_noalloc_scratch_bytes": (ctypes.c_size_t, []),
     "sgemm_run_host": (ctypes.c_int, _GEMM_ARGS),
     "sgemm_bench": (ctypes.c_int, _GEMM_ARGS + [_u32, _u32, _vp, ctypes.POINTER(ctypes.c_float)]),
     "sgemm_last_status": (ctypes.c_int, [_vp, ctypes.POINTER(_u32 * 8)]),
@@ -174,6 +176,13 @@ class SgemmRunner:
         self._check(self._L.sgemm_launch(self._h, _ptr(a), _ptr(b), _ptr(c), _ptr(d), alpha, beta, m, n, k,
                                          lda, ldb, ldc, ldd, stream), "sgemm_launch")
 
+    def launch_noalloc(self, a, b, c, d, m, n, k, alpha=1.0, beta=0.0, lda=0, ldb=0, ldc=0, ldd=0, stream=0):
+        """``launch`` for callers that must not allocate device memory: the scratch comes from the library's
+        fixed array (``noalloc_scratch_bytes()``); larger problems raise ``SgemmError`` with code -9."""
+        lda, ldb, ldc, ldd = self._lds(m, n, k, lda, ldb, ldc, ldd)
+        self._check(self._L.sgemm_launch_noalloc(self._h, _ptr(a), _ptr(b), _ptr(c), _ptr(d), alpha, beta, m, n, k,
+                                                 lda, ldb, ldc, ldd, stream), "sgemm_launch_noalloc")
+
     def run_host(self, a, b, c, d, m, n, k, alpha=1.0, beta=0.0, lda=0, ldb=0, ldc=0, ldd=0):
         """The same with HOST buffers (upload, launch, download, synchronise)."""
         lda, ldb, ldc, ldd = self._lds(m, n, k, lda, ldb, ldc, ldd)
@@ -240,6 +249,10 @@ class SgemmRunner:
 
     def sync(self):
         self._check(self._L.sgemm_dev_sync(self._h), "sgemm_dev_sync")
+
+
+def noalloc_scratch_bytes() -> int:
+    return int(lib().sgemm_noalloc_scratch_bytes())
 
 
 def device_count() -> int:

@@ -37,7 +37,8 @@ typedef enum sgemm_error {
     SGEMM_ERR_MODULE = -5,           /* cubin missing / not loadable / entry point not found */
     SGEMM_ERR_UNSUPPORTED = -6,      /* the loaded kernel cannot serve this request (e.g. forced variant) */
     SGEMM_ERR_WORKSPACE = -7,        /* lent workspace too small, or allocation failed */
-    SGEMM_ERR_DEVICE_STATUS = -8     /* a kernel reported a bounded wait that ran out (sgemm_last_status) */
+    SGEMM_ERR_DEVICE_STATUS = -8,    /* a kernel reported a bounded wait that ran out (sgemm_last_status) */
+    SGEMM_ERR_SCRATCH_LIMIT = -9     /* problem needs more scratch than sgemm_launch_noalloc's fixed array holds */
 } sgemm_error;
 
 /* Kernel configuration as read from the generator's TOML (generator/generator.py:1001-1017 writes it,
@@ -85,6 +86,22 @@ int sgemm_close(sgemm_handle *h);
 int sgemm_launch(sgemm_handle *h, const float *dA, const float *dB, const float *dC, float *dD,
                  float alpha, float beta, uint32_t m, uint32_t n, uint32_t k,
                  uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, void *stream);
+
+/* No counterpart in the reference (its runner allocates freely with hipMalloc).  sgemm_launch for callers
+ * that cannot allocate device memory at call time: a serving loop with a frozen memory budget, a real-time path
+ * that cannot take a blocking driver call, or a process whose device memory belongs to another allocator.  Same arguments and
+ * results as sgemm_launch, but the scratch (3xTF32 lo copies, split-K partials) comes from a fixed array of
+ * SGEMM_NOALLOC_SCRATCH_BYTES that is part of the library image on every GPU that loads it; no cudaMalloc,
+ * cuMemAlloc or other allocating call is made.  Problems needing more scratch fail with
+ * SGEMM_ERR_SCRATCH_LIMIT before anything is launched (sgemm_workspace_bytes tells the need).  The first call
+ * on a device resolves the array's device address (one-time set-up; make it before any stream capture).  All
+ * calls on a device share the array: kernels of two such calls must not overlap in time on one GPU. */
+#define SGEMM_NOALLOC_SCRATCH_BYTES (32u << 20)
+int sgemm_launch_noalloc(sgemm_handle *h, const float *dA, const float *dB, const float *dC, float *dD,
+                         float alpha, float beta, uint32_t m, uint32_t n, uint32_t k,
+                         uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, void *stream);
+/* Size of that array in bytes (= SGEMM_NOALLOC_SCRATCH_BYTES of the library that was actually loaded). */
+size_t sgemm_noalloc_scratch_bytes(void);
 
 /* The same call with HOST buffers: uploads A, B (and C when beta != 0), launches, downloads D and
  * synchronises — what the reference's main does around its kernel with hipMalloc / hipMemcpyHtoD /

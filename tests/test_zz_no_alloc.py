@@ -1,0 +1,94 @@
+"""sgemm_launch_noalloc: the SGEMM entry point for callers that are not allowed to allocate device memory
+when they call (a serving loop whose memory budget is frozen, a real-time path that cannot take a blocking driver
+call, a process whose GPU memory is managed by somebody else's allocator).  Its scratch is a fixed array inside the library, so
+the things to check are: it computes what sgemm_launch computes, it keeps doing so when the array is reused by
+the next call (the array still holds the previous call's data), and it refuses problems that would not fit
+instead of allocating.  Collected last on purpose: a failure here cannot hide a failure elsewhere."""
+import numpy as np
+import pytest
+
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def runner(built):
+    from runner import api
+    cubin, toml = built.ensure(built.DEFAULT_TENSOR)
+    r = api.SgemmRunner(cubin, toml, 0)
+    yield r
+    assert r.last_status()[0] == 0
+    r.close()
+
+
+def device_inputs(r, m, n, k, seed):
+    a, b, c = oracle.make_inputs(m, n, k, seed=seed)
+    bufs = [r.dev_alloc(x.nbytes) for x in (a, b, c)] + [r.dev_alloc(m * n * 4)]
+    for p, x in zip(bufs, (a, b, c)):
+        r.upload(p, x)
+    return (a, b, c), bufs
+
+
+def fetch(r, dptr, count):
+    out = np.empty(count, dtype=np.float32)
+    r.sync()
+    r.download(out, dptr)
+    return out
+
+
+@pytest.mark.parametrize("force,split_k,mnk", [
+    (1, 4, (256, 320, 2048)),    # tensor path: lo copies of A and B + four split-K partial products in the scratch
+    (2, 8, (200, 136, 4096)),    # SIMT path: split-K partial products only
+    (0, 0, (512, 512, 512)),     # whatever the library picks on its own
+])
+def test_matches_the_allocating_entry_point_on_two_calls_in_a_row(runner, force, split_k, mnk):
+    from runner import api
+    m, n, k = mnk
+    r = runner
+    r.set_option("force_variant", force)
+    r.set_option("split_k", split_k)
+    assert 0 < r.workspace_bytes(m, n, k) <= api.noalloc_scratch_bytes()
+    (a, b, c), (pa, pb, pc, pd) = device_inputs(r, m, n, k, seed=21)
+    (a2, b2, c2), (qa, qb, qc, qd) = device_inputs(r, m, n, k, seed=22)
+    try:
+        # existing entry point (handle-owned, allocated workspace) as the reference
+        r.launch(pa, pb, pc, pd, m, n, k, alpha=1.0, beta=0.5)
+        want = fetch(r, pd, m * n)
+        r.launch(qa, qb, qc, qd, m, n, k, alpha=1.0, beta=0.5)
+        want2 = fetch(r, qd, m * n)
+        for p in (pd, qd):
+            r.memset(p, 0, m * n * 4)
+        owned_before = r.info("workspace_bytes")
+        # two allocation-free calls back to back: the second one finds the first one's data in the scratch
+        r.launch_noalloc(pa, pb, pc, pd, m, n, k, alpha=1.0, beta=0.5)
+        r.launch_noalloc(qa, qb, qc, qd, m, n, k, alpha=1.0, beta=0.5)
+        got, got2 = fetch(r, pd, m * n), fetch(r, qd, m * n)
+        assert r.info("workspace_bytes") == owned_before           # the handle's own workspace did not grow
+        for g, w, (x, y, z) in ((got, want, (a, b, c)), (got2, want2, (a2, b2, c2))):
+            bound = oracle.abs_bound(x, y, m, n, k) + 0.5 * np.abs(z).astype(np.float64)
+            assert oracle.worst_ratio(g, w, bound) <= 1.0           # the tolerance of the parity tests
+            assert g.tobytes() == w.tobytes()                       # and in fact the same bits: same kernels, same order
+        # and against the CPU oracle, so that both entry points being wrong together cannot pass
+        ref = oracle.gemm(a, b, c, 1.0, 0.5, m, n, k)
+        assert oracle.worst_ratio(got, ref, oracle.abs_bound(a, b, m, n, k) + 0.5 * np.abs(c).astype(np.float64)) <= 1.0
+    finally:
+        r.sync()
+        for p in (pa, pb, pc, pd, qa, qb, qc, qd):
+            r.dev_free(p)
+
+
+def test_refuses_problems_beyond_the_fixed_scratch(runner):
+    from runner import api
+    r = runner
+    m = n = k = 8192                        # needs 512 MiB of lo copies: far beyond the 32 MiB array
+    assert r.workspace_bytes(m, n, k) > api.noalloc_scratch_bytes()
+    dummy = r.dev_alloc(256)                # never dereferenced: the size check comes before any launch
+    try:
+        launches = r.info("launches")
+        with pytest.raises(api.SgemmError) as e:
+            r.launch_noalloc(dummy, dummy, None, dummy, m, n, k)
+        assert e.value.code == -9 and "scratch" in str(e.value)
+        assert r.info("launches") == launches
+    finally:
+        r.dev_free(dummy)
