@@ -26,7 +26,7 @@ REGISTRY = {
     "tc_128x256x16_s4": (lambda: tensor_config(256, 16, 4), dict(wgm=8)),
     "tc_128x128x16_s7": (lambda: tensor_config(128, 16, 7), dict(wgm=8)),
     # CTA pairs (cluster 2x1, tcgen05 cta_group::2): tile 256 x BN x BK
-    "tc2_256x256x32_s3": (lambda: tensor_config(256, 32, 3, cluster=2), dict(wgm=4)),
+    "tc2_256x256x32_s3": (lambda: tensor_config(256, 32, 3, cluster=2), dict(wgm=8)),
     "tc2_256x256x16_s6": (lambda: tensor_config(256, 16, 6, cluster=2), dict(wgm=4)),
     "tc2_256x128x32_s4": (lambda: tensor_config(128, 32, 4, cluster=2), dict(wgm=4)),
     # the same tile reading A from K-major packed copies, and a plain-TF32 build (bring-up aids)

@@ -101,6 +101,7 @@ def cpu_reference_tflops(oracle, budget_s: float = 12.0):
     """The reference's CPU GEMM (oracle restatement, all host threads) on a column block of the 8192^3 problem.
     Returns (tflops, columns used, seconds, threads)."""
     cols = 64
+    oracle.use_all_cores()
     a = oracle.fill_uniform(M * K, 0)
     while True:
         b = oracle.fill_uniform(K * cols, 1)

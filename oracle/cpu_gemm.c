@@ -45,6 +45,15 @@
 
 #define ORACLE_API __attribute__((visibility("default")))
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; the timed CPU baseline asks for all cores explicitly. */
+ORACLE_API void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 ORACLE_API int oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -67,6 +67,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_count_mismatches.restype = _u64
         L.oracle_worst_ratio.argtypes = [_f32p, _f32p, _f64p, _u64, ctypes.c_double]
         L.oracle_worst_ratio.restype = ctypes.c_double
+        L.oracle_set_num_threads.argtypes = [ctypes.c_int]
+        L.oracle_set_num_threads.restype = None
         L.oracle_num_threads.argtypes = []
         L.oracle_num_threads.restype = ctypes.c_int
         L.oracle_gflops.argtypes = [_u32, _u32, _u32, ctypes.c_double]
@@ -79,6 +81,13 @@ def lib() -> ctypes.CDLL:
 
 def num_threads() -> int:
     return int(lib().oracle_num_threads())
+
+
+def use_all_cores() -> int:
+    """Use every core this process may run on, whatever OMP_NUM_THREADS says (torchrun exports 1)."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().oracle_set_num_threads(n)
+    return num_threads()
 
 
 def _p32(x: np.ndarray):
