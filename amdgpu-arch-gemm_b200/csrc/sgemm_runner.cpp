@@ -239,11 +239,11 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
             p->hi_a_off = off; off += round_up((size_t)p->ldt * m * 4, 256);
             p->lo_a_off = off; off += round_up((size_t)p->ldt * m * 4, 256);
             p->span_a = 0;
-        } else {
+        } else if (!h->cfg.split_inkernel) {
             p->span_a = (uint64_t)lda * (k - 1) + m;
             p->lo_a_off = off; off += round_up(p->span_a * 4, 256);
         }
-        p->lo_b_off = off; off += round_up(p->span_b * 4, 256);
+        if (!h->cfg.split_inkernel) { p->lo_b_off = off; off += round_up(p->span_b * 4, 256); }
     } else {
         const bool own = h->cfg.variant == kVariantSimt;
         const uint32_t tm = own ? h->tile_m : (uint32_t)h->cfg.fallback_tile[0];
@@ -408,6 +408,10 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
             if (rc) return rc;
             if ((rc = encode_map(h, 0, hi_t, k, m, (uint64_t)p.ldt * 4, kspan, 128, ksw, &ma_hi))) return rc;
             if ((rc = encode_map(h, 1, lo_a, k, m, (uint64_t)p.ldt * 4, kspan, 128, ksw, &ma_lo))) return rc;
+        } else if (h->cfg.split_inkernel) {
+            // no pre-pass and no lo copies: the kernel's transform warps make the lo tiles; the lo map slots get the hi maps
+            if ((rc = encode_map(h, 0, dA, m, k, (uint64_t)lda * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &ma_hi))) return rc;
+            ma_lo = ma_hi;
         } else {
             void *ps[] = {&dA, &lo_a, &p.span_a, &dB, &lo_b, &p.span_b};
             rc = launch(h, h->fn_split_lo, blocks, 1, 1, 256, 1, 0, stream, ps);
@@ -416,7 +420,8 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
             if ((rc = encode_map(h, 1, lo_a, m, k, (uint64_t)lda * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &ma_lo))) return rc;
         }
         if ((rc = encode_map(h, 2, dB, k, n, (uint64_t)ldb * 4, kspan, bn, ksw, &mb_hi))) return rc;
-        if ((rc = encode_map(h, 3, lo_b, k, n, (uint64_t)ldb * 4, kspan, bn, ksw, &mb_lo))) return rc;
+        if (h->cfg.split_inkernel) mb_lo = mb_hi;
+        else if ((rc = encode_map(h, 3, lo_b, k, n, (uint64_t)ldb * 4, kspan, bn, ksw, &mb_lo))) return rc;
         void *params[] = {&dA, &dB, &dC, &dD, &m, &n, &k, &lda, &ldb, &ldc, &ldd, &alpha, &beta, &nwx, &nwy,
                           &partial, &status_ptr, &split,
                           const_cast<CUtensorMap *>(ma_hi), const_cast<CUtensorMap *>(ma_lo),
@@ -486,6 +491,7 @@ int config_from_toml(const char *path, sgemm_config *c, std::string *err) {
     c->dynamic_smem_bytes = t.get_int("dynamic_smem_bytes", &v) ? (int32_t)v : 0;
     c->stages = t.get_int("stages", &v) ? (int32_t)v : c->vmem_stage + 1;
     c->a_kmajor = (t.get_string("a_major", &s) && s == "k") ? 1 : 0;
+    c->split_inkernel = (t.get_string("split", &s) && s == "inkernel") ? 1 : 0;
     std::vector<int64_t> fb;
     if (t.get_int_array("fallback_tile", &fb) && fb.size() == 3)
         for (int i = 0; i < 3; ++i) c->fallback_tile[i] = (int32_t)fb[i];

@@ -15,9 +15,12 @@
 //                      tile it commits to the accumulator's "tmem_full" mbarrier. Warp 1 also owns
 //                      the TMEM allocation (two accumulator buffers, so the epilogue of tile i
 //                      overlaps the main loop of tile i+1).
-//   warps 2..5       : epilogue. Warp w reads TMEM lanes 32*(w%4)..+31 (= rows of the tile) with
-//                      tcgen05.ld, applies alpha/beta and stores straight to global memory: D is
-//                      column-major, so the 32 lanes of a warp write 128 contiguous bytes per column.
+//   warps 2..5 (..9) : epilogue, TC_EPI_WARPS = 4 or 8 warps. Warp w reads TMEM lanes 32*(w%4)..+31
+//                      (= rows of the tile) with tcgen05.ld, applies alpha/beta and stores straight to
+//                      global memory: D is column-major, so the 32 lanes of a warp write 128 contiguous
+//                      bytes per column.  With 8 warps the two warps of a lane quarter take half of the
+//                      tile's columns each, which doubles the loads/stores in flight (it matters when K
+//                      is small or C is read).
 //
 // Operand tiles in shared memory (128-byte swizzle, written by TMA, read by the tensor core):
 //   A (column-major, M contiguous => "MN-major" operand): per 32 rows of M one chunk of TC_BK rows
@@ -41,12 +44,19 @@
 //   empty[s]     one per CTA; the leader commits to its own and to the peer's copy (two plain commits)
 //   tmem_full[b] one per CTA, committed the same way;  tmem_empty[b] in the leader, 4 warps x 2 CTAs arrive
 //
+// TC_SPLIT_INKERNEL = 1 drops the pre-pass: TMA brings only the raw (hi) tiles, four extra "transform" warps
+// (warps 6..9) compute lo = x - trunc_tf32(x) from the landed tile into the stage's lo tile (element-wise,
+// so the swizzle does not matter), publish the writes to the tensor core's proxy with fence.proxy.async and
+// arrive on the stage's "ready" barrier, which the MMA issuer then waits on instead of "full".  In a CTA pair
+// "full" is then local to each CTA (each transforms what it loaded) and "ready" lives in the leader
+// (4 warps x 2 CTAs arrive).  Operand traffic from L2/HBM halves and no lo copies exist in global memory.
+//
 // Every mbarrier wait is bounded: after TC_TIMEOUT_NS without progress the waiting role records a
 // status word, raises a CTA-wide abort flag and all roles leave their loops, release TMEM and
 // return; the host reads the status after synchronising.
 //
 // Generator-supplied macros: TC_BN (tile columns), TC_BK (k per stage: 16 or a multiple of 32), TC_STAGES,
-// TC_CTA_GROUP (1/2), TC_A_KMAJOR (0/1), TC_TERMS (3 = 3xTF32, 1 = plain TF32 for bring-up), OPT_WGM.
+// TC_CTA_GROUP (1/2), TC_EPI_WARPS (4/8), TC_SPLIT_INKERNEL (0/1), TC_A_KMAJOR (0/1), TC_TERMS (3 = 3xTF32, 1 = plain TF32 for bring-up), OPT_WGM.
 // ---------------------------------------------------------------------------------------------
 #ifndef TC_TERMS
 #define TC_TERMS 3
@@ -61,7 +71,17 @@
 #define TC_BM 128                              // rows of A (and of the accumulator) per CTA
 #define TC_UMMA_M (TC_BM * TC_CTA_GROUP)       // rows of the launch unit's tile = UMMA M
 #define TC_BN_CTA (TC_BN / TC_CTA_GROUP)       // columns of B this CTA keeps in shared memory
-#define TC_THREADS 192
+#ifndef TC_SPLIT_INKERNEL
+#define TC_SPLIT_INKERNEL 0
+#endif
+#ifndef TC_EPI_WARPS
+#define TC_EPI_WARPS 4
+#endif
+#define TC_XFORM_WARPS (TC_SPLIT_INKERNEL ? 4 : 0)
+#define TC_THREADS (64 + 32 * TC_EPI_WARPS + 32 * TC_XFORM_WARPS)
+#define TC_EPI_COLS (TC_BN / (TC_EPI_WARPS / 4))   // accumulator columns one epilogue warp drains per tile
+static_assert(TC_EPI_WARPS == 4 || TC_EPI_WARPS == 8, "one or two epilogue warps per TMEM lane quarter");
+static_assert(TC_EPI_COLS % 32 == 0, "an epilogue warp drains whole 32-column chunks");
 #define TC_A_BYTES (TC_BM * TC_BK * 4)
 #define TC_B_BYTES (TC_BN_CTA * TC_BK * 4)
 #define TC_STAGE_BYTES (2 * TC_A_BYTES + 2 * TC_B_BYTES)
@@ -123,6 +143,13 @@ __device__ __forceinline__ void tc_tma_load_2d(uint32_t dst, const TcTensorMap *
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 #endif
+}
+// TMA tile load whose completion is reported to a barrier of this same CTA (any cluster shape).
+__device__ __forceinline__ void tc_tma_load_2d_local(uint32_t dst, const TcTensorMap *map, uint32_t bar,
+                                                     int32_t x, int32_t y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
 // shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster
 __device__ __forceinline__ uint32_t tc_map_to_cta(uint32_t addr, uint32_t rank) {
@@ -250,15 +277,16 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
     extern __shared__ uint8_t tc_smem_raw[];
     const uint32_t smem_base = (tc_smem_u32(tc_smem_raw) + 1023u) & ~1023u;
     const uint32_t bar_base = smem_base + TC_STAGES * TC_STAGE_BYTES;
-    // barrier block: full[S] | empty[S] | tmem_full[2] | tmem_empty[2] | tmem base (u32) | abort (u32)
+    // barrier block: full[S] | empty[S] | ready[S] | tmem_full[2] | tmem_empty[2] | tmem base (u32) | abort (u32)
     const uint32_t bar_full = bar_base;
     const uint32_t bar_empty = bar_base + 8 * TC_STAGES;
-    const uint32_t bar_tfull = bar_base + 16 * TC_STAGES;
+    const uint32_t bar_ready = bar_base + 16 * TC_STAGES;   // in-kernel split only
+    const uint32_t bar_tfull = bar_base + 24 * TC_STAGES;
     const uint32_t bar_tempty = bar_tfull + 16;
     uint8_t *generic_base = tc_smem_raw + (smem_base - tc_smem_u32(tc_smem_raw));
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(generic_base + TC_STAGES * TC_STAGE_BYTES + 16 * TC_STAGES + 32);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(generic_base + TC_STAGES * TC_STAGE_BYTES + 24 * TC_STAGES + 32);
     volatile uint32_t *abort_flag = tmem_slot + 1;
-    static_assert(16 * TC_STAGES + 32 + 8 <= 256, "barrier block size");
+    static_assert(24 * TC_STAGES + 32 + 8 <= 256, "barrier block size");
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const TcWait waiter{abort_flag, status};
@@ -279,10 +307,11 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
         for (int s = 0; s < TC_STAGES; ++s) {
             tc_mbar_init(bar_full + 8 * s, 1);
             tc_mbar_init(bar_empty + 8 * s, 1);
+            tc_mbar_init(bar_ready + 8 * s, (TC_XFORM_WARPS ? TC_XFORM_WARPS : 1) * TC_CTA_GROUP);
         }
         for (int i = 0; i < 2; ++i) {
             tc_mbar_init(bar_tfull + 8 * i, 1);
-            tc_mbar_init(bar_tempty + 8 * i, 4 * TC_CTA_GROUP);
+            tc_mbar_init(bar_tempty + 8 * i, TC_EPI_WARPS * TC_CTA_GROUP);
         }
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -334,6 +363,24 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                     const uint32_t sb_hi = sa_lo + TC_A_BYTES;
                     const uint32_t sb_lo = sb_hi + TC_B_BYTES;
                     const int32_t k0 = (int32_t)(kb * TC_BK);
+#if TC_SPLIT_INKERNEL
+                    // raw tiles only, reported to this CTA's own "full" barrier; the transform warps make the lo tiles
+                    (void)sa_lo; (void)sb_lo; (void)full;
+                    const uint32_t own_full = bar_full + 8 * stage;
+                    tc_mbar_expect_tx(own_full, TC_A_BYTES + TC_B_BYTES);
+#if TC_A_KMAJOR
+#pragma unroll
+                    for (int sub = 0; sub < TC_KSUBS; ++sub)
+                        tc_tma_load_2d_local(sa_hi + sub * TC_A_SUB_BYTES, &map_a_hi, own_full, k0 + TC_KSPAN * sub, m0);
+#else
+#pragma unroll
+                    for (int ch = 0; ch < TC_BM / 32; ++ch)
+                        tc_tma_load_2d_local(sa_hi + ch * TC_A_CHUNK_BYTES, &map_a_hi, own_full, m0 + 32 * ch, k0);
+#endif
+#pragma unroll
+                    for (int sub = 0; sub < TC_KSUBS; ++sub)
+                        tc_tma_load_2d_local(sb_hi + sub * TC_B_SUB_BYTES, &map_b_hi, own_full, k0 + TC_KSPAN * sub, n0);
+#else
                     if (cta_rank == 0) tc_mbar_expect_tx(bar_full + 8 * stage, TC_CTA_GROUP * TC_STAGE_BYTES);
 #if TC_A_KMAJOR
 #pragma unroll
@@ -353,6 +400,7 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                         tc_tma_load_2d(sb_hi + sub * TC_B_SUB_BYTES, &map_b_hi, full, k0 + TC_KSPAN * sub, n0);
                         tc_tma_load_2d(sb_lo + sub * TC_B_SUB_BYTES, &map_b_lo, full, k0 + TC_KSPAN * sub, n0);
                     }
+#endif  // TC_SPLIT_INKERNEL
                     if (++stage == TC_STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -375,7 +423,8 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                     continue;
                 }
                 for (uint32_t kb = kb_begin; kb < kb_end; ++kb) {
-                    if (!tc_wait(waiter, bar_full + 8 * stage, phase, 0x300u + stage, tile, kb)) { alive = false; break; }
+                    // operands of this stage are complete: TMA bytes landed (and, with the in-kernel split, lo tiles written)
+                    if (!tc_wait(waiter, (TC_SPLIT_INKERNEL ? bar_ready : bar_full) + 8 * stage, phase, 0x300u + stage, tile, kb)) { alive = false; break; }
                     tc_fence_after();
                     const uint32_t sa_hi = smem_base + stage * TC_STAGE_BYTES;
                     const uint32_t sa_lo = sa_hi + TC_A_BYTES;
@@ -411,9 +460,51 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                 if (alive) tc_commit(bar_tfull + 8 * buf);
             }
         }
+    } else if (warp >= 2 + TC_EPI_WARPS) {
+        // ------------------------------------------------------------------- transform (in-kernel split)
+#if TC_SPLIT_INKERNEL
+        const uint32_t t = threadIdx.x - 32 * (2 + TC_EPI_WARPS);   // 0 .. 32*TC_XFORM_WARPS-1
+        const uint32_t ready_base = TC_CTA_GROUP == 2 ? tc_map_to_cta(bar_ready, 0u) : bar_ready;
+        uint32_t stage = 0, phase = 0;
+        bool alive = true;
+        for (uint32_t tile = unit0; alive && tile < num_tiles; tile += unit_stride) {
+            const uint32_t z = tile / tiles_mn;
+            const uint32_t kb_begin = min(kb_total, z * kb_per), kb_end = min(kb_total, kb_begin + kb_per);
+            for (uint32_t kb = kb_begin; kb < kb_end; ++kb) {
+                alive = __all_sync(0xffffffffu, tc_wait(waiter, bar_full + 8 * stage, phase, 0x500u + stage, tile, kb));
+                if (!alive) break;
+                // [A_hi | A_lo | B_hi | B_lo]: lo = hi - trunc_tf32(hi), same offset in the neighbouring tile
+                const float4 *a_src = reinterpret_cast<const float4 *>(generic_base + stage * TC_STAGE_BYTES);
+                float4 *a_dst = reinterpret_cast<float4 *>(generic_base + stage * TC_STAGE_BYTES + TC_A_BYTES);
+                const float4 *b_src = reinterpret_cast<const float4 *>(generic_base + stage * TC_STAGE_BYTES + 2 * TC_A_BYTES);
+                float4 *b_dst = reinterpret_cast<float4 *>(generic_base + stage * TC_STAGE_BYTES + 2 * TC_A_BYTES + TC_B_BYTES);
+#pragma unroll 4
+                for (uint32_t i = t; i < TC_A_BYTES / 16; i += 32 * TC_XFORM_WARPS) {
+                    float4 v = a_src[i];
+                    v.x = sgemm_tf32_lo(v.x); v.y = sgemm_tf32_lo(v.y); v.z = sgemm_tf32_lo(v.z); v.w = sgemm_tf32_lo(v.w);
+                    a_dst[i] = v;
+                }
+#pragma unroll 4
+                for (uint32_t i = t; i < TC_B_BYTES / 16; i += 32 * TC_XFORM_WARPS) {
+                    float4 v = b_src[i];
+                    v.x = sgemm_tf32_lo(v.x); v.y = sgemm_tf32_lo(v.y); v.z = sgemm_tf32_lo(v.z); v.w = sgemm_tf32_lo(v.w);
+                    b_dst[i] = v;
+                }
+                // generic-proxy writes -> visible to the tensor core (async proxy), then hand the stage to the issuer
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    if (TC_CTA_GROUP == 2) tc_mbar_arrive_cluster(ready_base + 8 * stage);
+                    else tc_mbar_arrive(bar_ready + 8 * stage);
+                }
+                if (++stage == TC_STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+#endif
     } else {
         // ---------------------------------------------------------------------------- epilogue
         const uint32_t quarter = warp & 3u;  // TMEM lane quarter this warp may read
+        const uint32_t cbase = ((warp - 2u) >> 2) * TC_EPI_COLS;  // first accumulator column of this warp's share
         uint32_t local = 0;
         bool alive = true;
         // the accumulator buffer is handed back to the leader's MMA thread
@@ -425,29 +516,45 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
             const uint32_t kb_begin = min(kb_total, z * kb_per), kb_end = min(kb_total, kb_begin + kb_per);
             const bool empty_k = kb_begin == kb_end;
             const uint32_t buf = local & 1u, acc_phase = (local >> 1) & 1u;
-            alive = __all_sync(0xffffffffu, tc_wait(waiter, bar_tfull + 8 * buf, acc_phase, 0x400u + buf, tile, 0));
-            if (!alive) break;
-            tc_fence_after();
             const uint32_t row = tx * TC_UMMA_M + cta_rank * TC_BM + quarter * 32 + lane;
             const uint32_t col0 = ty * TC_BN;
             const bool partial = split_k > 1;
             float *out = partial ? ws + (uint64_t)z * m * n : d;
             const uint32_t ldo = partial ? m : ldd;
             const bool use_c = !partial && beta != 0.0f;
-#pragma unroll 1
-            for (int cc = 0; cc < TC_BN / 32; ++cc) {
+            // C is fetched one 32-column chunk ahead of its use, all 32 loads of a chunk in flight together; the
+            // first chunk is requested before the accumulator is even complete, so its latency hides behind the
+            // tile's main loop.  (C may be the same buffer as D: every element is read before this same thread
+            // overwrites it, and no other thread touches it.)
+            float cv[2][32];
+            auto fetch_c = [&](int cc, float (&dst)[32]) {
+                if (use_c && row < m) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const uint32_t col = col0 + cbase + cc * 32 + j;
+                        dst[j] = col < n ? c[row + (uint64_t)col * ldc] : 0.0f;
+                    }
+                }
+            };
+            fetch_c(0, cv[0]);
+            alive = __all_sync(0xffffffffu, tc_wait(waiter, bar_tfull + 8 * buf, acc_phase, 0x400u + buf, tile, 0));
+            if (!alive) break;
+            tc_fence_after();
+#pragma unroll
+            for (int cc = 0; cc < TC_EPI_COLS / 32; ++cc) {
                 uint32_t r[32];
-                tc_tmem_ld32(tmem_base + ((quarter * 32u) << 16) + buf * TC_BN + cc * 32, r);
+                tc_tmem_ld32(tmem_base + ((quarter * 32u) << 16) + buf * TC_BN + cbase + cc * 32, r);
+                if (cc + 1 < TC_EPI_COLS / 32) fetch_c(cc + 1, cv[(cc + 1) & 1]);
                 tc_tmem_ld_wait();
                 if (row < m) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const uint32_t col = col0 + cc * 32 + j;
+                        const uint32_t col = col0 + cbase + cc * 32 + j;
                         if (col < n) {
                             float v = empty_k ? 0.0f : __uint_as_float(r[j]);
                             if (!partial) {
                                 v *= alpha;
-                                if (use_c) v = fmaf(beta, c[row + (uint64_t)col * ldc], v);
+                                if (use_c) v = fmaf(beta, cv[cc & 1][j], v);
                             }
                             out[row + (uint64_t)col * ldo] = v;
                         }

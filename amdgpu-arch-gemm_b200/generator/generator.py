@@ -154,7 +154,8 @@ class GemmSolutionConfig:
     def __init__(self, a_type: DataType, b_type: DataType, cd_type: DataType, scalar_type: DataType,
                  mfma: Tuple[int, int, int, int], wave_group: Tuple[int, int], wave_tiling: Tuple[int, int],
                  depth_k: int, trans_a: bool, trans_b: bool, vmem_stage: int = 1, *,
-                 a_major: str = "mn", terms: int = 3):
+                 a_major: str = "mn", terms: int = 3, split: str = "prepass",
+                 epilogue_warps: Optional[int] = None):
         self.a_type = a_type
         self.b_type = b_type
         self.cd_type = cd_type
@@ -170,6 +171,12 @@ class GemmSolutionConfig:
         self.name = None
         self.a_major = a_major      # tensor variant: "mn" = TMA straight from column-major A, "k" = packed copy
         self.terms = terms          # tensor variant: 3 = 3xTF32 (FP32-accurate), 1 = plain TF32 (bring-up only)
+        # tensor variant: warps that drain the accumulator; 8 (two per TMEM lane quarter, half the columns each)
+        # keeps twice as many loads/stores in flight as 4 and is the default whenever tile N allows it
+        self.epilogue_warps = epilogue_warps
+        self.split = split          # tensor variant: where lo = x - trunc_tf32(x) is made: "prepass" (a kernel writes
+                                    # A_lo, B_lo to global memory once per call) or "inkernel" (transform warps make the
+                                    # lo tiles in shared memory from the TMA-landed raw tiles)
 
         for t in (a_type, b_type, cd_type, scalar_type):
             datatype_size(t)
@@ -220,6 +227,16 @@ class GemmSolutionConfig:
             raise RuntimeError("a_major is 'mn' or 'k'")
         if self.terms not in (1, 3):
             raise RuntimeError("terms is 3 (3xTF32) or 1 (plain TF32)")
+        if self.epilogue_warps is None:
+            self.epilogue_warps = 8 if bn % 64 == 0 else 4
+        if self.epilogue_warps not in (4, 8) or (self.epilogue_warps == 8 and bn % 64):
+            raise RuntimeError("epilogue_warps is 4, or 8 when tile N is a multiple of 64")
+        if self.split not in ("prepass", "inkernel"):
+            raise RuntimeError("split is 'prepass' or 'inkernel'")
+        if self.split == "inkernel" and self.a_major == "k":
+            raise RuntimeError("the K-major packed copy of A is made by a pre-pass; it excludes split='inkernel'")
+        if self.stages * 24 + 40 > 256:
+            raise RuntimeError(f"{self.stages} stages exceed the barrier block of the kernel")
         if self.stages < 2:
             raise RuntimeError("the TMA ring needs at least 2 stages")
 
@@ -260,7 +277,8 @@ class GemmSolutionConfig:
     @property
     def num_workitems(self) -> int:
         if self.variant == VARIANT_TENSOR:
-            return 192
+            # TMA warp + MMA warp + epilogue warps (+ four transform warps for the in-kernel split)
+            return 64 + 32 * self.epilogue_warps + (128 if self.split == "inkernel" else 0)
         bm, bn = self.tile_size
         tm, tn = self.simt_thread_tile
         return (bm // tm) * (bn // tn)
@@ -327,6 +345,8 @@ class GemmSolutionConfig:
             d.update({
                 "a_major": self.a_major,
                 "terms": self.terms,
+                "split": self.split,
+                "epilogue_warps": self.epilogue_warps,
                 "fallback_entry": SIMT_FALLBACK_ENTRY,
                 "fallback_tile": [fb.tile_size[0], fb.tile_size[1], fb.depth_k],
                 "fallback_threads": fb.num_workitems,
@@ -403,6 +423,8 @@ def gemm(context: GpuContext, name: str, arch: str, config: GemmSolutionConfig, 
         out.write(_read("sgemm_simt.cuh"))
         out.write(_defines([("TC_BN", config.tile_size[1]), ("TC_BK", config.depth_k),
                             ("TC_STAGES", config.stages), ("TC_CTA_GROUP", config.wave_group[0]),
+                            ("TC_SPLIT_INKERNEL", 1 if config.split == "inkernel" else 0),
+                            ("TC_EPI_WARPS", config.epilogue_warps),
                             ("TC_A_KMAJOR", 1 if config.a_major == "k" else 0),
                             ("TC_TERMS", config.terms)]))
         out.write(_read("sgemm_tcgen05.cuh"))

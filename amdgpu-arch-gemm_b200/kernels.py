@@ -22,6 +22,7 @@ REGISTRY = {
     "tc_128x256x32_s2": (lambda: tensor_config(256, 32, 2), dict(wgm=8)),
     "tc_128x128x32_s3": (lambda: tensor_config(128, 32, 3), dict(wgm=8)),
     "tc_128x64x32_s4": (lambda: tensor_config(64, 32, 4), dict(wgm=8)),
+    "tc2_256x256x32_s3_e4": (lambda: tensor_config(256, 32, 3, cluster=2, epilogue_warps=4), dict(wgm=8)),
     "tc_128x64x64_s2": (lambda: tensor_config(64, 64, 2), dict(wgm=4)),
     "tc_128x256x16_s4": (lambda: tensor_config(256, 16, 4), dict(wgm=8)),
     "tc_128x128x16_s7": (lambda: tensor_config(128, 16, 7), dict(wgm=8)),
@@ -29,6 +30,11 @@ REGISTRY = {
     "tc2_256x256x32_s3": (lambda: tensor_config(256, 32, 3, cluster=2), dict(wgm=8)),
     "tc2_256x256x16_s6": (lambda: tensor_config(256, 16, 6, cluster=2), dict(wgm=4)),
     "tc2_256x128x32_s4": (lambda: tensor_config(128, 32, 4, cluster=2), dict(wgm=4)),
+    # lo tiles made inside the kernel by transform warps (no pre-pass, no lo copies in global memory)
+    "tc2i_256x256x32_s3": (lambda: tensor_config(256, 32, 3, cluster=2, split="inkernel"), dict(wgm=8)),
+    "tc2i_256x256x16_s6": (lambda: tensor_config(256, 16, 6, cluster=2, split="inkernel"), dict(wgm=8)),
+    "tci_128x256x32_s2": (lambda: tensor_config(256, 32, 2, split="inkernel"), dict(wgm=8)),
+    "tci_128x128x32_s3": (lambda: tensor_config(128, 32, 3, split="inkernel"), dict(wgm=8)),
     # the same tile reading A from K-major packed copies, and a plain-TF32 build (bring-up aids)
     "tc_128x128x32_s3_ak": (lambda: tensor_config(128, 32, 3, a_major="k"), dict(wgm=8)),
     "tc_128x128x16_s6_ak": (lambda: tensor_config(128, 16, 6, a_major="k"), dict(wgm=8)),

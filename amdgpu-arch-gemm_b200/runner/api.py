@@ -33,7 +33,8 @@ class SgemmConfig(ctypes.Structure):
         ("depth_k", ctypes.c_int32), ("vmem_stage", ctypes.c_int32), ("wavefront_size", ctypes.c_int32),
         ("lds_usage_bytes", ctypes.c_int32), ("trans_a", ctypes.c_int32), ("trans_b", ctypes.c_int32),
         ("variant", ctypes.c_int32), ("num_threads", ctypes.c_int32), ("dynamic_smem_bytes", ctypes.c_int32),
-        ("stages", ctypes.c_int32), ("a_kmajor", ctypes.c_int32), ("fallback_tile", ctypes.c_int32 * 3),
+        ("stages", ctypes.c_int32), ("a_kmajor", ctypes.c_int32), ("split_inkernel", ctypes.c_int32),
+        ("fallback_tile", ctypes.c_int32 * 3),
         ("fallback_threads", ctypes.c_int32), ("entry", ctypes.c_char * 64), ("fallback_entry", ctypes.c_char * 64),
     ]
 

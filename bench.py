@@ -146,6 +146,11 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--kernel", default=None, help="registered kernel name (default: the tensor-core default)")
     ap.add_argument("--size", type=int, default=8192, help="M = N_per_gpu = K (profiling runs use a smaller case)")
+    ap.add_argument("--workload", choices=["c3", "c5"], default="c3",
+                    help="c3: M = K = N per GPU = --size, N grows with the GPU count (weak scaling, the default); "
+                         "c5: the fixed M = N = 32768, K = 8192 problem column-sharded over the GPUs (strong scaling)")
+    ap.add_argument("--allgather", action="store_true",
+                    help="also time the optional NCCL all-gather of D's column shards (reported apart from the GEMM)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -182,8 +187,13 @@ def main():
     r = api.SgemmRunner(cubin, toml, local_rank)
     tile_n = r.info("tile_n")
 
-    # weak scaling: N_total = N_PER_GPU * world columns, this rank owns [n0, n1)
-    n_total = N_PER_GPU * world
+    # c3, weak scaling: N_total = N_PER_GPU * world columns; c5, strong scaling: one fixed problem.
+    # Either way this rank owns the columns [n0, n1).
+    if args.workload == "c5":
+        M, K = 32768, 8192
+        n_total = 32768
+    else:
+        n_total = N_PER_GPU * world
     n0, n1 = shard_columns(n_total, world, rank, tile_n)
     n_local = n1 - n0
     a = torch.empty(M * K, dtype=torch.float32, device=dev)
@@ -232,9 +242,26 @@ def main():
     flops_step_all = 2.0 * M * n_total * K
     value = flops_step_all / (ms_step * 1e-3) * 1e-12
 
+    # ---- optional: all-gather of the column shards of D over NVLink (NCCL); never part of `value`
+    allgather = None
+    if args.allgather and world > 1:
+        from runner.shard import gather_columns
+        gather_columns(dist, d, M, n_total, world, tile_n)      # warm-up (NCCL channel set-up)
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        full_d = gather_columns(dist, d, M, n_total, world, tile_n)
+        g1.record()
+        barrier()
+        ag_ms = max_over_ranks(dist, g0.elapsed_time(g1), dev)
+        recv_bytes = (full_d.numel() - d.numel()) * 4
+        allgather = {"ms": ag_ms, "bytes_received_per_gpu": recv_bytes, "gb_per_s_per_gpu": recv_bytes / ag_ms * 1e-6,
+                     "full_d_elements": full_d.numel()}
+        del full_d
+
     # ---- end to end through the host-buffer entry point (pinned host memory, copies inside the timed region)
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and args.workload == "c3":   # (the c5 problem would need 6 GiB of pinned host memory per rank)
         ha = torch.empty(M * K, dtype=torch.float32).pin_memory()
         hb = torch.empty(K * n_local, dtype=torch.float32).pin_memory()
         hd = torch.empty(M * n_local, dtype=torch.float32).pin_memory()
@@ -261,20 +288,21 @@ def main():
         # ceiling for FP32-accurate flops is BF16 / 6 (sustained figure: the kernel is timed inside a long step).
         peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]) / 6.0
         achieved = (2.0 * M * n_local * K) / (main_ns / max(main_count, 1) * 1e-9) * 1e-12 if main_ns else None
-        traffic = NCU_TRAFFIC_BYTES.get(kernel) if M == 8192 else None
+        traffic = NCU_TRAFFIC_BYTES.get(kernel) if (M, n_local, K) == (8192, 8192, 8192) else None
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if args.workload == "c5" else "weak",
+            "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": f"column-major NN SGEMM M={M} N={n_total} K={K} (N={N_PER_GPU} per GPU), alpha=1, beta=0, "
+            "config": {"workload": f"column-major NN SGEMM M={M} N={n_total} K={K} (N={n_local} on rank 0), alpha=1, beta=0, "
                                    "seeded uniform[-1,1); 3xTF32 tcgen05 path", "kernel": kernel,
                        "parallelism": f"column-block shards x{world}, A replicated, no collective",
-                       "l2": "inputs (A + B = 512 MiB per GPU) exceed the 126 MB L2, no flush needed"},
+                       "l2": f"inputs (A + B = {(M * K + K * n_local) * 4 >> 20} MiB per GPU) exceed the 126 MB L2, no flush needed"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": (achieved / peak) if achieved else None, "traffic": traffic,
                          "kernel": "generated_gemm", "launches_timed": main_count,
                          "peak_source": f"{peak_src} bf16_tflops_sustained / 6 (TF32 = 1/2 BF16 rate, 3 MMAs per product)"},
-            "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "device_status": status[0],
+            "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "device_status": status[0], "allgather": allgather,
         }
         if world == 1 and not args.no_cpu_baseline:
             from oracle import oracle

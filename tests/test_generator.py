@@ -32,7 +32,8 @@ def test_basic_sgemm_gen_reference_style():
 
 def test_tile_product_rule_and_properties():
     cfg = g.tensor_config(256, 32, 2)
-    assert cfg.tile_size == (128, 256) and cfg.num_workitems == 192 and cfg.stages == 2
+    assert cfg.tile_size == (128, 256) and cfg.num_workitems == 64 + 32 * 8 and cfg.stages == 2
+    assert g.tensor_config(256, 32, 2, epilogue_warps=4).num_workitems == 192
     assert cfg.lds_usage_bytes == 2 * (2 * 128 * 32 * 4 + 2 * 256 * 32 * 4) + 1024 + 256
     assert cfg.tmem_columns == 512
     s = g.simt_config(128, 128, 16, 8, 8)

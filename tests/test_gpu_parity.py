@@ -10,7 +10,9 @@ pytestmark = pytest.mark.gpu
 
 TENSOR_KERNELS = ["tc_128x256x32_s2", "tc_128x128x32_s3", "tc_128x64x32_s4", "tc_128x64x64_s2", "tc_128x128x32_s3_ak",
                   "tc_128x256x16_s4", "tc_128x128x16_s7", "tc_128x128x16_s6_ak",
-                  "tc2_256x256x32_s3", "tc2_256x256x16_s6", "tc2_256x128x32_s4"]
+                  "tc2_256x256x32_s3", "tc2_256x256x16_s6", "tc2_256x128x32_s4",
+                  "tc2i_256x256x32_s3", "tc2i_256x256x16_s6", "tci_128x256x32_s2", "tci_128x128x32_s3",
+                  "tc2_256x256x32_s3_e4"]
 SIMT_KERNELS = ["simt_128x128x16", "simt_64x64x16", "simt_128x64x8_plr0", "legacy_32x32x2_1wave", "legacy_16x16x4_2x2x2x2"]
 AUTO, TENSOR, SIMT = 0, 1, 2
 _runners = {}
@@ -84,7 +86,8 @@ SHAPES = [(1, 1, 1), (8, 8, 8), (32, 32, 32), (33, 65, 129), (127, 257, 513), (1
 
 
 @pytest.mark.parametrize("kernel", ["tc_128x256x32_s2", "tc_128x128x32_s3", "tc_128x64x64_s2", "tc_128x128x32_s3_ak",
-                                    "tc_128x256x16_s4", "tc_128x128x16_s6_ak", "tc2_256x256x32_s3", "tc2_256x128x32_s4"])
+                                    "tc_128x256x16_s4", "tc_128x128x16_s6_ak", "tc2_256x256x32_s3", "tc2_256x128x32_s4",
+                                    "tc2i_256x256x32_s3", "tc2i_256x256x16_s6", "tci_128x256x32_s2"])
 @pytest.mark.parametrize("mnk", SHAPES)
 @pytest.mark.parametrize("alpha,beta", [(1.0, 0.0), (0.5, -1.5)])
 def test_tensor_kernels_match_oracle(runner_of, kernel, mnk, alpha, beta):
@@ -126,6 +129,36 @@ def test_variant_selection(runner_of):
     with pytest.raises(api.SgemmError) as e:  # lda smaller than M
         r.run_host(a, b, None, np.zeros(127 * 257, np.float32), 127, 257, 513, lda=100)
     assert e.value.code == -1
+
+
+def test_unaligned_base_pointers_take_the_simt_kernel(runner_of):
+    # TMA needs 16-byte aligned operand bases: a buffer that starts 4 bytes into an allocation is served by the
+    # FFMA kernel of the same cubin, and forcing the tensor path on it is refused.
+    from runner import api
+    m, n, k = 512, 512, 512
+    a, b, c = oracle.make_inputs(m, n, k, seed=3)
+    r = runner_of("tc2_256x256x32_s3")
+    pa, pb, pd = r.dev_alloc(a.nbytes + 16), r.dev_alloc(b.nbytes + 16), r.dev_alloc(m * n * 4)
+    try:
+        r.upload(pa + 4, a)
+        r.upload(pb, b)
+        r.launch(pa + 4, pb, None, pd, m, n, k)
+        assert r.info("last_variant") == SIMT
+        got = np.empty(m * n, np.float32)
+        r.sync()
+        r.download(got, pd)
+        check(got, a, b, None, m, n, k, 1.0, 0.0)
+        r.set_option("force_variant", TENSOR)
+        with pytest.raises(api.SgemmError) as e:
+            r.launch(pa + 4, pb, None, pd, m, n, k)
+        assert e.value.code == -6
+        r.set_option("force_variant", AUTO)
+        r.launch(pa, pb, None, pd, m, n, k)          # aligned: tensor path (A's content is shifted, only the variant matters)
+        assert r.info("last_variant") == TENSOR
+    finally:
+        r.sync()
+        for p in (pa, pb, pd):
+            r.dev_free(p)
 
 
 # ------------------------------------------------------------------- BASELINE's skinny shapes, full oracle
