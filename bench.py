@@ -38,8 +38,9 @@ METRIC = "sgemm_fp32_accurate_tflops_8192"
 UNIT = "TFLOP/s"
 
 # DRAM bytes one launch of the dominant kernel moved in an ncu capture (dram__bytes_read.sum +
-# dram__bytes_write.sum), keyed by kernel name; None until a capture exists.  Source: profiles/.
-NCU_TRAFFIC_BYTES = {}
+# dram__bytes_write.sum), keyed by kernel name, for the 8192^3 workload.
+# Source: profiles/bench_default_8192cubed_launches_and_dram.md (mean of two launches).
+NCU_TRAFFIC_BYTES = {"tc2_256x256x32_s3": 8.81e9}
 
 
 def measured_peaks():
