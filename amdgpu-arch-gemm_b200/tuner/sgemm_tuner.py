@@ -38,6 +38,7 @@ SUPPORTED_CLUSTERS = [(1, 1), (2, 1)]
 SUPPORTED_TILE_N = [128, 256]
 SUPPORTED_DEPTH_K = [16, 32, 64]
 SUPPORTED_STAGES = [2, 3, 4, 5, 6, 7]
+SUPPORTED_SPLIT = ["prepass", "inkernel"]   # where the 3xTF32 lo terms are made
 # FFMA variant: (thread grid, per-thread tile, k per stage)
 SUPPORTED_SIMT = [((16, 16), (8, 8), 16), ((16, 16), (8, 8), 8), ((16, 8), (8, 8), 16), ((16, 16), (4, 4), 16)]
 SUPPORTED_WGM = [1, 4, 8, 16]
@@ -57,12 +58,12 @@ def kernel_arguments():
 def candidates(include_simt: bool = True):
     """Yield (key, config factory, optimisation factory) for every point of the search space."""
     F = DataType.FP32
-    for cluster, bn, dk, stages, wgm in product(SUPPORTED_CLUSTERS, SUPPORTED_TILE_N, SUPPORTED_DEPTH_K,
-                                                SUPPORTED_STAGES, SUPPORTED_WGM):
-        key = f"tensor c{cluster[0]}x{cluster[1]} n{bn} k{dk} s{stages} wgm{wgm}"
+    for cluster, bn, dk, stages, split, wgm in product(SUPPORTED_CLUSTERS, SUPPORTED_TILE_N, SUPPORTED_DEPTH_K,
+                                                       SUPPORTED_STAGES, SUPPORTED_SPLIT, SUPPORTED_WGM):
+        key = f"tensor c{cluster[0]}x{cluster[1]} n{bn} k{dk} s{stages} {split} wgm{wgm}"
         yield (key,
-               lambda cluster=cluster, bn=bn, dk=dk, stages=stages: GemmSolutionConfig(
-                   F, F, F, F, (128, bn, 1, 8), cluster, (1, 1), dk, False, False, vmem_stage=stages - 1),
+               lambda cluster=cluster, bn=bn, dk=dk, stages=stages, split=split: GemmSolutionConfig(
+                   F, F, F, F, (128, bn, 1, 8), cluster, (1, 1), dk, False, False, vmem_stage=stages - 1, split=split),
                lambda wgm=wgm: GemmOptimizations(1, wgm=wgm))
     if include_simt:
         for (wg, wt, dk), wgm, plr in product(SUPPORTED_SIMT, SUPPORTED_WGM, SUPPORTED_PLR):
@@ -126,7 +127,7 @@ def tune(m: int, n: int, k: int, bench: str, output_folder: str, include_simt: b
             measured += 1
             rec = {"key": problem_key, "returncode": ret.returncode, "tile": list(config.tile_size), "depth_k": config.depth_k,
                    "stages": config.stages, "cluster": list(config.wave_group), "variant": config.variant, "wgm": opt.wgm,
-                   "plr": opt.plr}
+                   "plr": opt.plr, "split": getattr(config, "split", "")}
             if not ret.returncode:
                 rec["gflops"] = parse_gflops(ret.stdout.decode())
             else:
@@ -137,12 +138,13 @@ def tune(m: int, n: int, k: int, bench: str, output_folder: str, include_simt: b
             print(f"runner failed for {rec['key']} (exit {rec['returncode']})")
             continue
         print(f"Gflops: {rec['gflops']}, MT: {tuple(rec['tile'])}, DK: {rec['depth_k']}, wgm: {rec['wgm']}, plr: {rec['plr']}, "
-              f"stages: {rec['stages']}, cluster: {tuple(rec['cluster'])}, variant: {rec['variant']}")
+              f"stages: {rec['stages']}, cluster: {tuple(rec['cluster'])}, variant: {rec['variant']} {rec.get('split', '')}")
         if best is None or rec["gflops"] > best["gflops"]:
             best = rec
     if best is not None:
         print(f"Best: {best['gflops']} Gflops, MT: {tuple(best['tile'])}, DK: {best['depth_k']}, wgm: {best['wgm']}, "
-              f"plr: {best['plr']}, stages: {best['stages']}, cluster: {tuple(best['cluster'])}, variant: {best['variant']}")
+              f"plr: {best['plr']}, stages: {best['stages']}, cluster: {tuple(best['cluster'])}, variant: {best['variant']} "
+              f"{best.get('split', '')}")
     else:
         print("No valid configurations found.")
     return best

@@ -44,6 +44,7 @@ def test_tune_picks_best_and_resumes(tmp_path, monkeypatch, capsys):
     monkeypatch.setattr(t, "SUPPORTED_DEPTH_K", [32])
     monkeypatch.setattr(t, "SUPPORTED_STAGES", [2, 3, 4])     # 4 stages of 64 KiB do not fit: skipped by RuntimeError
     monkeypatch.setattr(t, "SUPPORTED_WGM", [4])
+    monkeypatch.setattr(t, "SUPPORTED_SPLIT", ["prepass"])
     out = tmp_path / "out"
     best = t.tune(512, 512, 512, runner, str(out), include_simt=False)
     assert best["gflops"] == 103 and best["stages"] == 3 and best["tile"] == [256, 256]
@@ -64,6 +65,7 @@ def test_runner_failure_is_recorded_not_fatal(tmp_path, monkeypatch, capsys):
     monkeypatch.setattr(t, "SUPPORTED_DEPTH_K", [32])
     monkeypatch.setattr(t, "SUPPORTED_STAGES", [3])
     monkeypatch.setattr(t, "SUPPORTED_WGM", [1])
+    monkeypatch.setattr(t, "SUPPORTED_SPLIT", ["inkernel"])
     best = t.tune(256, 256, 256, fake_runner(tmp_path, "echo boom >&2; exit 2\n"), str(tmp_path / "o"), include_simt=False)
     assert best is None
     assert "No valid configurations found." in capsys.readouterr().out
