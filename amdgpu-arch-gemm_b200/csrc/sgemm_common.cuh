@@ -141,12 +141,38 @@ extern "C" __global__ void sgemm_splitk_reduce(const float *__restrict__ ws, con
                                                float alpha, float beta, uint32_t nsplit) {
     const uint64_t total = (uint64_t)m * n;
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t e = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool use_c = beta != 0.0f;
+    // fast path: four consecutive rows of one column per thread, 16-byte loads and stores
+    const bool vec = (m % 4 == 0) && (ldd % 4 == 0) && ((reinterpret_cast<uintptr_t>(d) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(ws) & 15) == 0) &&
+                     (!use_c || ((ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0)));
+    if (vec) {
+        const uint32_t m4 = m / 4;
+        const uint64_t total4 = total / 4;
+        for (uint64_t e = tid; e < total4; e += stride) {
+            const uint32_t i = (uint32_t)(e % m4) * 4, j = (uint32_t)(e / m4);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t s = 0; s < nsplit; ++s) {
+                const float4 v = *reinterpret_cast<const float4 *>(ws + (uint64_t)s * total + e * 4);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            float4 r = make_float4(alpha * acc.x, alpha * acc.y, alpha * acc.z, alpha * acc.w);
+            if (use_c) {
+                const float4 cv = *reinterpret_cast<const float4 *>(c + i + (uint64_t)j * ldc);
+                r.x = fmaf(beta, cv.x, r.x); r.y = fmaf(beta, cv.y, r.y);
+                r.z = fmaf(beta, cv.z, r.z); r.w = fmaf(beta, cv.w, r.w);
+            }
+            *reinterpret_cast<float4 *>(d + i + (uint64_t)j * ldd) = r;
+        }
+        return;
+    }
+    for (uint64_t e = tid; e < total; e += stride) {
         const uint32_t i = (uint32_t)(e % m), j = (uint32_t)(e / m);
         float acc = 0.0f;
         for (uint32_t s = 0; s < nsplit; ++s) acc += ws[(uint64_t)s * total + e];
         float r = alpha * acc;
-        if (beta != 0.0f) r = fmaf(beta, c[i + (uint64_t)j * ldc], r);
+        if (use_c) r = fmaf(beta, c[i + (uint64_t)j * ldc], r);
         d[i + (uint64_t)j * ldd] = r;
     }
 }

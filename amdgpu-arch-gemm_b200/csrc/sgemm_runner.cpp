@@ -441,7 +441,9 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
     if (p.split_k > 1) {
         const float *wsp = partial;
         void *params[] = {&wsp, &dC, &dD, &m, &n, &ldc, &ldd, &alpha, &beta, &split};
-        const uint32_t blocks = (uint32_t)std::min<uint64_t>(((uint64_t)m * n + 255) / 256, (uint64_t)h->sm_count * 8);
+        // one thread per four rows on the kernel's vector path (M a multiple of 4), per element otherwise
+        const uint64_t items = (m % 4 == 0) ? (uint64_t)m * n / 4 : (uint64_t)m * n;
+        const uint32_t blocks = (uint32_t)std::min<uint64_t>((items + 255) / 256, (uint64_t)h->sm_count * 8);
         rc = launch(h, h->fn_reduce, blocks, 1, 1, 256, 1, 0, stream, params);
         if (rc) return rc;
     }
