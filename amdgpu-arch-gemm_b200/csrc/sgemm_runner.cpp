@@ -74,6 +74,7 @@ Driver &driver() {
 thread_local std::string g_open_error;
 
 constexpr int kStatusWords = 8;
+constexpr uint32_t kCounterWords = 1u << 18;   // 1 MiB of split-K arrival counters per handle
 constexpr int kVariantSimt = 0, kVariantTensor = 1;
 
 struct TensorMapKey {
@@ -105,6 +106,7 @@ struct sgemm_handle {
     int sm_count = 0;
     uint32_t tile_m = 0, tile_n = 0;
     CUdeviceptr status = 0;
+    CUdeviceptr counters = 0;   // split-K arrival counters of the tensor kernel, all zero between launches
     // workspace: owned (grow on demand) or lent
     CUdeviceptr ws_owned = 0;
     size_t ws_owned_bytes = 0;
@@ -115,6 +117,7 @@ struct sgemm_handle {
     size_t stage_bytes[4] = {0, 0, 0, 0};
     // options and facts
     int64_t force_variant = 0, split_k_opt = 0, simt_below_flops = (int64_t)1 << 27;
+    bool fuse_split_k = false;  // measured slower than the separate reduction kernel: off unless asked for
     int64_t last_variant = 0, last_split_k = 1, last_grid = 0, launches = 0;
     CachedMap maps[4];
     // optional timing of the main GEMM kernel alone (events around it on the caller's stream)
@@ -177,6 +180,7 @@ struct Plan {
     uint64_t span_a = 0, span_b = 0;                                    // floats walked by the split pre-pass
     uint32_t ldt = 0;                                                   // K-major packed A: leading dimension
     size_t ws_bytes = 0;
+    bool fused_reduce = false;   // tensor kernel sums the split-K partials itself (arrival counters)
 };
 
 bool tensor_eligible(const sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_t n, uint32_t k,
@@ -244,6 +248,10 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
             p->lo_a_off = off; off += round_up(p->span_a * 4, 256);
         }
         if (!h->cfg.split_inkernel) { p->lo_b_off = off; off += round_up(p->span_b * 4, 256); }
+        // epilogue warps per CTA = (threads - TMA warp - MMA warp - transform warps) / 32
+        const uint32_t epi_warps = ((uint32_t)h->cfg.num_threads - 64u - (h->cfg.split_inkernel ? 128u : 0u)) / 32u;
+        p->fused_reduce = p->split_k > 1 && h->fuse_split_k &&
+                          (uint64_t)p->tiles_m * p->tiles_n * group * epi_warps <= kCounterWords;
     } else {
         const bool own = h->cfg.variant == kVariantSimt;
         const uint32_t tm = own ? h->tile_m : (uint32_t)h->cfg.fallback_tile[0];
@@ -422,8 +430,9 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
         if ((rc = encode_map(h, 2, dB, k, n, (uint64_t)ldb * 4, kspan, bn, ksw, &mb_hi))) return rc;
         if (h->cfg.split_inkernel) mb_lo = mb_hi;
         else if ((rc = encode_map(h, 3, lo_b, k, n, (uint64_t)ldb * 4, kspan, bn, ksw, &mb_lo))) return rc;
+        uint32_t *counters = p.fused_reduce ? reinterpret_cast<uint32_t *>(h->counters) : nullptr;
         void *params[] = {&dA, &dB, &dC, &dD, &m, &n, &k, &lda, &ldb, &ldc, &ldd, &alpha, &beta, &nwx, &nwy,
-                          &partial, &status_ptr, &split,
+                          &partial, &status_ptr, &split, &counters,
                           const_cast<CUtensorMap *>(ma_hi), const_cast<CUtensorMap *>(ma_lo),
                           const_cast<CUtensorMap *>(mb_hi), const_cast<CUtensorMap *>(mb_lo)};
         rc = launch_main(h, h->fn_main, p.grid_x, 1, (uint32_t)h->cfg.num_threads,
@@ -433,12 +442,13 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
         const bool own = h->cfg.variant == kVariantSimt;
         CUfunction f = own ? h->fn_main : h->fn_simt;
         const uint32_t threads = own ? (uint32_t)h->cfg.num_threads : (uint32_t)h->cfg.fallback_threads;
+        uint32_t *counters = nullptr;
         void *params[] = {&dA, &dB, &dC, &dD, &m, &n, &k, &lda, &ldb, &ldc, &ldd, &alpha, &beta, &nwx, &nwy,
-                          &partial, &status_ptr, &split};
+                          &partial, &status_ptr, &split, &counters};
         rc = launch_main(h, f, p.grid_x, p.split_k, threads, 0, stream, params);
         if (rc) return rc;
     }
-    if (p.split_k > 1) {
+    if (p.split_k > 1 && !p.fused_reduce) {
         const float *wsp = partial;
         void *params[] = {&wsp, &dC, &dD, &m, &n, &ldc, &ldd, &alpha, &beta, &split};
         // one thread per four rows on the kernel's vector path (M a multiple of 4), per element otherwise
@@ -619,7 +629,9 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
         return bail(SGEMM_ERR_CUDA);
     }
     if ((r = d.cuMemAlloc_(&h->status, kStatusWords * 4)) != CUDA_SUCCESS ||
-        (r = d.cuMemsetD8_(h->status, 0, kStatusWords * 4)) != CUDA_SUCCESS) {
+        (r = d.cuMemsetD8_(h->status, 0, kStatusWords * 4)) != CUDA_SUCCESS ||
+        (r = d.cuMemAlloc_(&h->counters, (size_t)kCounterWords * 4)) != CUDA_SUCCESS ||
+        (r = d.cuMemsetD8_(h->counters, 0, (size_t)kCounterWords * 4)) != CUDA_SUCCESS) {
         fail(h, SGEMM_ERR_CUDA, "cannot allocate the status buffer: %s", cu_text(r).c_str());
         return bail(SGEMM_ERR_CUDA);
     }
@@ -639,6 +651,7 @@ SGEMM_API int sgemm_close(sgemm_handle *h) {
                 d.cuEventDestroy_(pr.second);
             }
             if (h->status) d.cuMemFree_(h->status);
+            if (h->counters) d.cuMemFree_(h->counters);
             if (h->ws_owned) d.cuMemFree_(h->ws_owned);
             for (CUdeviceptr p : h->stage)
                 if (p) d.cuMemFree_(p);
@@ -733,6 +746,8 @@ SGEMM_API int sgemm_last_status(sgemm_handle *h, uint32_t status[8]) {
     CU_CHECK(h, d.cuMemcpyDtoH_(status, h->status, kStatusWords * 4));
     if (status[0] != 0) {
         CU_CHECK(h, d.cuMemsetD8_(h->status, 0, kStatusWords * 4));
+        // a kernel that gave up may have left split-K arrival counters half-counted
+        CU_CHECK(h, d.cuMemsetD8_(h->counters, 0, (size_t)kCounterWords * 4));
         return fail(h, SGEMM_ERR_DEVICE_STATUS, "kernel gave up waiting: tag 0x%x tile %u k-block %u block %u parity %u",
                     status[1], status[2], status[3], status[4], status[5]);
     }
@@ -745,6 +760,7 @@ SGEMM_API int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value) 
     if (k == "force_variant" && value >= 0 && value <= 2) h->force_variant = value;
     else if (k == "split_k" && value >= 0 && value <= 1024) h->split_k_opt = value;
     else if (k == "simt_below_flops" && value >= 0) h->simt_below_flops = value;
+    else if (k == "fuse_split_k" && (value == 0 || value == 1)) h->fuse_split_k = value != 0;
     else if (k == "profile" && (value == 0 || value == 1)) { h->profile = value != 0; h->prof_used = 0; }
     else return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "unknown option or value out of range: %s = %lld", key, (long long)value);
     return SGEMM_OK;

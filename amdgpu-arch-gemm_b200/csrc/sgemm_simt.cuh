@@ -119,9 +119,10 @@ extern "C" __global__ void __launch_bounds__(SIMT_THREADS)
 SIMT_ENTRY(const float *__restrict__ a, const float *__restrict__ b, const float *c, float *d,
            uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
            float alpha, float beta, int32_t num_wg_x, int32_t num_wg_y,
-           float *ws, uint32_t *status, uint32_t split_k) {
+           float *ws, uint32_t *status, uint32_t split_k, uint32_t *counters) {
     __shared__ __align__(16) SimtSmem s;
     (void)status;
+    (void)counters;   // the SIMT variant always finishes split-K with sgemm_splitk_reduce
 
     uint32_t tile_x, tile_y;
     sgemm_tile_raster(blockIdx.x, (uint32_t)num_wg_x, (uint32_t)num_wg_y, OPT_WGM, tile_x, tile_y);

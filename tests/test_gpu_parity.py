@@ -29,6 +29,7 @@ def runner_of(built):
         r = _runners[name]
         r.set_option("force_variant", AUTO)
         r.set_option("split_k", 0)
+        r.set_option("fuse_split_k", 0)
         r.set_workspace(None, 0)
         return r
 
@@ -221,6 +222,28 @@ def test_split_k_is_deterministic_and_in_tolerance(runner_of, kernel, force):
         check(d1, a, b, c, m, n, k, 2.0, 1.0)
         outs[split] = d1
     assert r.info("last_split_k") > 1
+
+
+@pytest.mark.parametrize("kernel", ["tc2_256x256x32_s3", "tc_128x128x32_s3", "tc2i_256x256x32_s3", "tc2_256x256x32_s3_e4"])
+@pytest.mark.parametrize("mnk", [(1024, 1024, 1024), (300, 520, 4096), (4096, 128, 16384)])
+def test_fused_split_k_reduction_equals_the_separate_kernel(runner_of, kernel, mnk):
+    # the tensor kernel's own reduction (arrival counters, last warp sums in split order) and sgemm_splitk_reduce
+    # must agree to the bit, call after call (the counters have to come back to zero every time)
+    m, n, k = mnk
+    lda, ldb = (m + 3) // 4 * 4, k
+    a, b, c = oracle.make_inputs(m, n, k, seed=13, lda=lda)
+    r = runner_of(kernel)
+    outs = []
+    for fuse in (1, 0, 1, 1):
+        r.set_option("fuse_split_k", fuse)
+        launches = r.info("launches")
+        d = run(r, a, b, c, m, n, k, 1.5, -0.5, force=TENSOR, split_k=4, lda=lda)
+        assert r.info("last_split_k") == 4
+        prepass = 0 if kernel.startswith("tc2i") else 1
+        assert r.info("launches") - launches == prepass + 1 + (0 if fuse else 1)
+        outs.append(d)
+    check(outs[0], a, b, c, m, n, k, 1.5, -0.5, lda=lda)
+    assert all(o.tobytes() == outs[0].tobytes() for o in outs[1:])
 
 
 def test_split_k_beyond_the_k_blocks_is_clamped(runner_of):
