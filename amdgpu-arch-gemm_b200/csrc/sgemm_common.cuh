@@ -22,6 +22,19 @@
 #define SGEMM_STATUS_TIMEOUT 1u
 
 // ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  The runner launches every kernel with "programmatic stream
+// serialisation": a kernel's CTAs may become resident while the previous kernel of the stream is
+// still running.  sgemm_grid_dependency_wait() blocks until that previous kernel has completed and
+// its writes are visible; every kernel calls it before its first access to global memory (reads of
+// what the predecessor wrote, and writes to what the predecessor may still read).  Because each
+// kernel waits for its immediate predecessor, completion is transitive along the stream.
+// sgemm_launch_dependents() lets the next kernel's CTAs be scheduled early.  Both are no-ops for a
+// kernel launched the ordinary way.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void sgemm_grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void sgemm_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------------
 // Tile rasterisation ("wgm", the workgroup remap of generator/generator.py:1437-1464).
 // wgm <= 1: no remap, z = x + y*nx (M index fastest), as the reference when wgm is 1.
 // wgm  > 1: the linear id z walks groups of `wgm` tiles in M; inside a group the M index moves
@@ -47,6 +60,7 @@ __host__ __device__ __forceinline__ void sgemm_tile_raster(uint32_t z, uint32_t 
 }
 
 extern "C" __global__ void sgemm_tile_map(int32_t *xy, uint32_t nx, uint32_t ny) {
+    sgemm_grid_dependency_wait();
     const uint32_t z = blockIdx.x * blockDim.x + threadIdx.x;
     if (z >= nx * ny) return;
     uint32_t x, y;
@@ -71,6 +85,8 @@ __device__ __forceinline__ float sgemm_uniform(uint64_t idx, uint64_t stream) {
 
 extern "C" __global__ void sgemm_fill_uniform(float *dst, uint64_t count, uint64_t first_index,
                                               uint64_t stream) {
+    sgemm_launch_dependents();
+    sgemm_grid_dependency_wait();
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride)
         dst[i] = sgemm_uniform(first_index + i, stream);
@@ -88,6 +104,8 @@ __device__ __forceinline__ float sgemm_tf32_lo(float x) {
 extern "C" __global__ void sgemm_split_lo(const float *__restrict__ src_a, float *__restrict__ lo_a,
                                           uint64_t count_a, const float *__restrict__ src_b,
                                           float *__restrict__ lo_b, uint64_t count_b) {
+    sgemm_launch_dependents();   // the GEMM kernel may set itself up while this pass runs
+    sgemm_grid_dependency_wait();
     // both spans are walked in float4 units; bases are 16-byte aligned (checked on the host)
     const uint64_t va = count_a >> 2, vb = count_b >> 2;
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
@@ -115,6 +133,8 @@ extern "C" __global__ void sgemm_pack_a_kmajor(const float *__restrict__ a, uint
                                                uint32_t k, float *__restrict__ hi_t,
                                                float *__restrict__ lo_t, uint32_t ldt) {
     __shared__ float tile[32][33];
+    sgemm_launch_dependents();
+    sgemm_grid_dependency_wait();
     const uint32_t i0 = blockIdx.x * 32, l0 = blockIdx.y * 32;
     for (uint32_t r = threadIdx.y; r < 32; r += blockDim.y) {
         const uint32_t i = i0 + threadIdx.x, l = l0 + r;
@@ -139,6 +159,8 @@ extern "C" __global__ void sgemm_pack_a_kmajor(const float *__restrict__ a, uint
 extern "C" __global__ void sgemm_splitk_reduce(const float *__restrict__ ws, const float *c, float *d,
                                                uint32_t m, uint32_t n, uint32_t ldc, uint32_t ldd,
                                                float alpha, float beta, uint32_t nsplit) {
+    sgemm_launch_dependents();
+    sgemm_grid_dependency_wait();
     const uint64_t total = (uint64_t)m * n;
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;

@@ -30,7 +30,7 @@ namespace {
 #define DRIVER_FUNCTIONS(X)                                                                              \
     X(cuInit) X(cuDeviceGet) X(cuDeviceGetCount) X(cuDeviceGetAttribute) X(cuDevicePrimaryCtxRetain)     \
     X(cuDevicePrimaryCtxRelease) X(cuCtxPushCurrent) X(cuCtxPopCurrent) X(cuModuleLoad) X(cuModuleUnload) \
-    X(cuModuleGetFunction) X(cuFuncSetAttribute) X(cuLaunchKernel) X(cuTensorMapEncodeTiled)             \
+    X(cuModuleGetFunction) X(cuFuncSetAttribute) X(cuLaunchKernel) X(cuLaunchKernelEx) X(cuTensorMapEncodeTiled) \
     X(cuMemAlloc) X(cuMemFree) X(cuMemcpyHtoDAsync) X(cuMemcpyDtoHAsync) X(cuMemcpyHtoD) X(cuMemcpyDtoH) \
     X(cuMemsetD8) X(cuMemsetD32Async) X(cuStreamSynchronize) X(cuCtxSynchronize) X(cuEventCreate)        \
     X(cuEventRecord) X(cuEventSynchronize) X(cuEventElapsedTime) X(cuEventDestroy) X(cuGetErrorString)   \
@@ -117,6 +117,7 @@ struct sgemm_handle {
     size_t stage_bytes[4] = {0, 0, 0, 0};
     // options and facts
     int64_t force_variant = 0, split_k_opt = 0, simt_below_flops = (int64_t)1 << 27;
+    bool pdl = true;            // launch with programmatic stream serialisation (see launch())
     bool fuse_split_k = false;  // measured slower than the separate reduction kernel: off unless asked for
     int64_t last_variant = 0, last_split_k = 1, last_grid = 0, launches = 0;
     CachedMap maps[4];
@@ -328,7 +329,25 @@ int encode_map(sgemm_handle *h, int slot, const void *base, uint64_t d0, uint64_
 
 int launch(sgemm_handle *h, CUfunction f, uint32_t gx, uint32_t gy, uint32_t gz, uint32_t bx, uint32_t by,
            uint32_t smem, CUstream s, void **params) {
-    CU_CHECK(h, driver().cuLaunchKernel_(f, gx, gy, gz, bx, by, 1, smem, s, params, nullptr));
+    if (h->pdl) {
+        // programmatic dependent launch: the kernel may be scheduled while its predecessor in the stream is still
+        // running; every kernel of the cubin executes griddepcontrol.wait before it touches global memory, so
+        // only launch latency and per-CTA set-up overlap with the predecessor, never data.
+        CUlaunchAttribute attr;
+        attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+        attr.value.programmaticStreamSerializationAllowed = 1;
+        CUlaunchConfig cfg;
+        std::memset(&cfg, 0, sizeof cfg);
+        cfg.gridDimX = gx; cfg.gridDimY = gy; cfg.gridDimZ = gz;
+        cfg.blockDimX = bx; cfg.blockDimY = by; cfg.blockDimZ = 1;
+        cfg.sharedMemBytes = smem;
+        cfg.hStream = s;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        CU_CHECK(h, driver().cuLaunchKernelEx_(&cfg, f, params, nullptr));
+    } else {
+        CU_CHECK(h, driver().cuLaunchKernel_(f, gx, gy, gz, bx, by, 1, smem, s, params, nullptr));
+    }
     ++h->launches;
     return SGEMM_OK;
 }
@@ -761,6 +780,7 @@ SGEMM_API int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value) 
     else if (k == "split_k" && value >= 0 && value <= 1024) h->split_k_opt = value;
     else if (k == "simt_below_flops" && value >= 0) h->simt_below_flops = value;
     else if (k == "fuse_split_k" && (value == 0 || value == 1)) h->fuse_split_k = value != 0;
+    else if (k == "pdl" && (value == 0 || value == 1)) h->pdl = value != 0;
     else if (k == "profile" && (value == 0 || value == 1)) { h->profile = value != 0; h->prof_used = 0; }
     else return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "unknown option or value out of range: %s = %lld", key, (long long)value);
     return SGEMM_OK;

@@ -124,6 +124,8 @@ SIMT_ENTRY(const float *__restrict__ a, const float *__restrict__ b, const float
     (void)status;
     (void)counters;   // the SIMT variant always finishes split-K with sgemm_splitk_reduce
 
+    sgemm_launch_dependents();
+    sgemm_grid_dependency_wait();
     uint32_t tile_x, tile_y;
     sgemm_tile_raster(blockIdx.x, (uint32_t)num_wg_x, (uint32_t)num_wg_y, OPT_WGM, tile_x, tile_y);
     const uint32_t m0 = tile_x * SIMT_BM, n0 = tile_y * SIMT_BN;

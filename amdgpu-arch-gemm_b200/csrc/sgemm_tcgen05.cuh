@@ -346,6 +346,10 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
 #endif
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // set-up (barriers, TMEM, tensor-map prefetch) is done: let the next kernel of the stream get scheduled, and do not
+    // touch global memory before the previous one (the split pre-pass, or an earlier call's kernels) has completed
+    sgemm_launch_dependents();
+    sgemm_grid_dependency_wait();
 
     if (warp == 0) {
         // ------------------------------------------------------------------------ TMA producer

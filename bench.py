@@ -98,18 +98,20 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_reference_tflops(oracle, budget_s: float = 12.0):
+def cpu_reference_tflops(oracle, budget_s: float = 12.0, cols: int | None = None):
     """The reference's CPU GEMM (oracle restatement, all host threads) on a column block of the 8192^3 problem.
+    Without `cols` the block is grown until one product takes about `budget_s` / 3 seconds or more.
     Returns (tflops, columns used, seconds, threads)."""
-    cols = 64
     oracle.use_all_cores()
     a = oracle.fill_uniform(M * K, 0)
+    fixed = cols is not None
+    cols = cols or 64
     while True:
         b = oracle.fill_uniform(K * cols, 1)
         t0 = time.perf_counter()
         oracle.gemm(a, b, None, 1.0, 0.0, M, cols, K)
         dt = time.perf_counter() - t0
-        if dt >= budget_s / 3 or cols >= N_PER_GPU:
+        if fixed or dt >= budget_s / 3 or cols >= N_PER_GPU:
             break
         cols = min(N_PER_GPU, max(cols * 2, int(cols * (budget_s * 0.6) / max(dt, 1e-3)) // 64 * 64))
     return 2.0 * M * cols * K / dt * 1e-12, cols, dt, oracle.num_threads()
@@ -119,9 +121,14 @@ def run_reference(args, rank):
     if rank != 0:
         return
     from oracle import oracle
-    times, cols = [], 0
+    # one step = the CPU GEMM on a fixed column block of the problem, sized in a calibration pass so that the whole
+    # run (warm-up + steps) takes about two minutes at most, and at least 64 columns per step
+    _, c0, t0, threads = cpu_reference_tflops(oracle, cols=64)
+    per_step_s = min(8.0, max(0.2, 110.0 / max(args.warmup + args.steps, 1)))
+    cols = int(min(N_PER_GPU, max(64, (64 * per_step_s / max(t0, 1e-3)) // 64 * 64)))
+    times = []
     for i in range(args.warmup + args.steps):
-        tf, cols, dt, threads = cpu_reference_tflops(oracle, budget_s=8.0 if i >= args.warmup else 2.0)
+        tf, cols, dt, threads = cpu_reference_tflops(oracle, cols=cols)
         if i >= args.warmup:
             times.append((tf, dt))
     tf = statistics.mean(t for t, _ in times)

@@ -129,6 +129,8 @@ int sgemm_last_status(sgemm_handle *h, uint32_t status[8]);
  * "simt_below_flops" problems with 2*M*N*K below this use the SIMT kernel (auto mode);
  * "fuse_split_k" 1 lets the tensor kernel sum its split-K partials itself (arrival counters, the last warp of a
  * slice reduces), 0 (default) runs the separate reduction kernel — same bits either way, the separate kernel is faster;
+ * "pdl" 1 (default) launches every kernel with programmatic stream serialisation so that launch latency and per-CTA
+ * set-up overlap with the tail of the previous kernel (all kernels wait on the grid dependency before touching memory);
  * "profile" 1 brackets every main-GEMM-kernel launch with an event pair (read with "profile_main_ns"). */
 int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value);
 

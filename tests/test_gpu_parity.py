@@ -271,6 +271,16 @@ def test_leading_dimensions_and_untouched_padding(runner_of, kernel, force):
     assert np.all(pad == np.float32(-777.25))   # rows >= M of every column keep the caller's bytes
 
 
+@pytest.mark.parametrize("mnk", [(70001, 3, 5), (3, 70001, 5), (5, 7, 100003), (1, 65537, 1), (262147, 1, 2)])
+def test_extreme_aspect_ratios(runner_of, mnk):
+    # one dimension far beyond 65535 (the old grid-dimension limit) and the others tiny
+    m, n, k = mnk
+    a, b, c = oracle.make_inputs(m, n, k, seed=17)
+    for kernel in ("tc2_256x256x32_s3", "simt_128x128x16"):
+        d = run(runner_of(kernel), a, b, c, m, n, k, 1.0, 1.0)
+        check(d, a, b, c, m, n, k, 1.0, 1.0)
+
+
 def test_degenerate_sizes(runner_of):
     for kernel in ("tc_128x128x32_s3", "simt_64x64x16"):
         r = runner_of(kernel)
