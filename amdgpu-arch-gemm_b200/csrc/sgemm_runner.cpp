@@ -34,6 +34,7 @@ namespace {
     X(cuMemAlloc) X(cuMemFree) X(cuMemcpyHtoDAsync) X(cuMemcpyDtoHAsync) X(cuMemcpyHtoD) X(cuMemcpyDtoH) \
     X(cuMemsetD8) X(cuMemsetD32Async) X(cuStreamSynchronize) X(cuCtxSynchronize) X(cuEventCreate)        \
     X(cuEventRecord) X(cuEventSynchronize) X(cuEventElapsedTime) X(cuEventDestroy) X(cuGetErrorString)   \
+    X(cuStreamCreate) X(cuStreamDestroy) X(cuStreamWaitEvent)                                            \
     X(cuGetErrorName)
 
 struct Driver {
@@ -115,8 +116,13 @@ struct sgemm_handle {
     // host-path staging
     CUdeviceptr stage[4] = {0, 0, 0, 0};
     size_t stage_bytes[4] = {0, 0, 0, 0};
+    // host path, pipelined: upload / compute / download streams and the events that order column chunks across them
+    CUstream pipe_streams[3] = {nullptr, nullptr, nullptr};
+    std::vector<CUevent> pipe_events;
+    bool reuse_a_lo = false;    // set by the pipelined host path: A's lo copy of the previous chunk call is still valid
     // options and facts
     int64_t force_variant = 0, split_k_opt = 0, simt_below_flops = (int64_t)1 << 27;
+    bool pipeline_host = true;  // sgemm_run_host overlaps uploads, GEMM and downloads over column chunks
     bool pdl = true;            // launch with programmatic stream serialisation (see launch())
     bool fuse_split_k = false;  // measured slower than the separate reduction kernel: off unless asked for
     int64_t last_variant = 0, last_split_k = 1, last_grid = 0, launches = 0;
@@ -426,8 +432,10 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
         if (h->cfg.a_kmajor) {
             float *hi_t = reinterpret_cast<float *>(ws + p.hi_a_off);
             void *pp[] = {&dA, &lda, &m, &k, &hi_t, &lo_a, &p.ldt};
-            rc = launch(h, h->fn_pack_a, (m + 31) / 32, (k + 31) / 32, 1, 32, 8, 0, stream, pp);
-            if (rc) return rc;
+            if (!h->reuse_a_lo) {
+                rc = launch(h, h->fn_pack_a, (m + 31) / 32, (k + 31) / 32, 1, 32, 8, 0, stream, pp);
+                if (rc) return rc;
+            }
             const float *na = nullptr;
             uint64_t zero = 0;
             void *ps[] = {&na, &na, &zero, &dB, &lo_b, &p.span_b};
@@ -440,7 +448,8 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
             if ((rc = encode_map(h, 0, dA, m, k, (uint64_t)lda * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &ma_hi))) return rc;
             ma_lo = ma_hi;
         } else {
-            void *ps[] = {&dA, &lo_a, &p.span_a, &dB, &lo_b, &p.span_b};
+            uint64_t span_a = h->reuse_a_lo ? 0 : p.span_a;   // same A as the previous chunk of a pipelined host call
+            void *ps[] = {&dA, &lo_a, &span_a, &dB, &lo_b, &p.span_b};
             rc = launch(h, h->fn_split_lo, blocks, 1, 1, 256, 1, 0, stream, ps);
             if (rc) return rc;
             if ((rc = encode_map(h, 0, dA, m, k, (uint64_t)lda * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &ma_hi))) return rc;
@@ -674,6 +683,9 @@ SGEMM_API int sgemm_close(sgemm_handle *h) {
             if (h->ws_owned) d.cuMemFree_(h->ws_owned);
             for (CUdeviceptr p : h->stage)
                 if (p) d.cuMemFree_(p);
+            for (CUevent e : h->pipe_events) d.cuEventDestroy_(e);
+            for (CUstream st : h->pipe_streams)
+                if (st) d.cuStreamDestroy_(st);
             if (h->module) d.cuModuleUnload_(h->module);
         }
         d.cuDevicePrimaryCtxRelease_(h->cu_device);
@@ -714,6 +726,69 @@ SGEMM_API int sgemm_run_host(sgemm_handle *h, const float *hA, const float *hB, 
                 return fail(h, SGEMM_ERR_CUDA, "cuMemAlloc of %zu staging bytes failed: %s", bytes[i], cu_text(r).c_str());
             h->stage_bytes[i] = round_up(bytes[i], 256);
         }
+    }
+    // Large problems are pipelined over column chunks on three streams — upload of B (and C) chunk j+1, GEMM of
+    // chunk j and download of D chunk j-1 overlap — because the call is bound by the host link, not by the GPU.
+    // Columns of D are independent and every chunk runs the same kernel in the same k order, so the result is
+    // the one the single-launch path produces.
+    const uint32_t chunk_unit = std::max<uint32_t>(h->tile_n, 256);
+    if (h->pipeline_host && k > 0 && n >= 4 * chunk_unit && bytes[0] + bytes[1] + bytes[3] >= ((size_t)64 << 20)) {
+        const uint32_t nc = (uint32_t)round_up((n + 7) / 8, chunk_unit);
+        const uint32_t chunks = (n + nc - 1) / nc;
+        for (CUstream &st : h->pipe_streams)
+            if (!st) CU_CHECK(h, d.cuStreamCreate_(&st, CU_STREAM_NON_BLOCKING));
+        while (h->pipe_events.size() < 1 + 2 * (size_t)chunks) {
+            CUevent e;
+            CU_CHECK(h, d.cuEventCreate_(&e, CU_EVENT_DISABLE_TIMING));
+            h->pipe_events.push_back(e);
+        }
+        CUstream s_in = h->pipe_streams[0], s_cmp = h->pipe_streams[1], s_out = h->pipe_streams[2];
+        CUevent ev_a = h->pipe_events[0];
+        // every chunk uses the kernel variant and the split-K factor the whole problem would get, so that each
+        // element of D is summed in exactly the order of the single-launch path
+        Plan whole;
+        if ((rc = make_plan(h, reinterpret_cast<const void *>(h->stage[0]), reinterpret_cast<const void *>(h->stage[1]), m, n, k,
+                            lda, ldb, &whole)))
+            return rc;
+        const int64_t saved_variant = h->force_variant, saved_split = h->split_k_opt;
+        h->force_variant = whole.variant == kVariantTensor ? 1 : 2;
+        h->split_k_opt = whole.split_k;
+        CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[0], hA, bytes[0], s_in));
+        CU_CHECK(h, d.cuEventRecord_(ev_a, s_in));
+        CU_CHECK(h, d.cuStreamWaitEvent_(s_cmp, ev_a, 0));
+        rc = SGEMM_OK;
+        for (uint32_t j = 0; j < chunks && rc == SGEMM_OK; ++j) {
+            const uint32_t n0 = j * nc, nw = std::min(nc, n - n0);
+            CUevent ev_in = h->pipe_events[1 + 2 * j], ev_done = h->pipe_events[2 + 2 * j];
+            const size_t off_b = (size_t)n0 * ldb * 4, off_c = (size_t)n0 * ldc * 4, off_d = (size_t)n0 * ldd * 4;
+            const size_t by_b = ((size_t)ldb * (nw - 1) + k) * 4, by_c = ((size_t)ldc * (nw - 1) + m) * 4,
+                         by_d = ((size_t)ldd * (nw - 1) + m) * 4;
+            CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[1] + off_b, reinterpret_cast<const char *>(hB) + off_b, by_b, s_in));
+            if (use_c)
+                CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[2] + off_c, reinterpret_cast<const char *>(hC) + off_c, by_c, s_in));
+            if (ldd != m)
+                CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[3] + off_d, reinterpret_cast<const char *>(hD) + off_d, by_d, s_in));
+            CU_CHECK(h, d.cuEventRecord_(ev_in, s_in));
+            CU_CHECK(h, d.cuStreamWaitEvent_(s_cmp, ev_in, 0));
+            h->reuse_a_lo = j > 0;
+            rc = launch_device(h, reinterpret_cast<const float *>(h->stage[0]),
+                               reinterpret_cast<const float *>(h->stage[1] + off_b),
+                               use_c ? reinterpret_cast<const float *>(h->stage[2] + off_c) : nullptr,
+                               reinterpret_cast<float *>(h->stage[3] + off_d), alpha, beta, m, nw, k, lda, ldb, ldc, ldd, s_cmp);
+            h->reuse_a_lo = false;
+            if (rc) break;
+            CU_CHECK(h, d.cuEventRecord_(ev_done, s_cmp));
+            CU_CHECK(h, d.cuStreamWaitEvent_(s_out, ev_done, 0));
+            CU_CHECK(h, d.cuMemcpyDtoHAsync_(reinterpret_cast<char *>(hD) + off_d, h->stage[3] + off_d, by_d, s_out));
+        }
+        // drain all three streams on every path: nothing of this call may still be in flight when it returns
+        CUresult r1 = d.cuStreamSynchronize_(s_in), r2 = d.cuStreamSynchronize_(s_cmp), r3 = d.cuStreamSynchronize_(s_out);
+        h->force_variant = saved_variant;
+        h->split_k_opt = saved_split;
+        if (rc) return rc;
+        if (r1 != CUDA_SUCCESS || r2 != CUDA_SUCCESS || r3 != CUDA_SUCCESS)
+            return fail(h, SGEMM_ERR_CUDA, "pipelined host call failed: %s", cu_text(r1 != CUDA_SUCCESS ? r1 : r2 != CUDA_SUCCESS ? r2 : r3).c_str());
+        return SGEMM_OK;
     }
     CUstream s = nullptr;
     if (bytes[0]) CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[0], hA, bytes[0], s));
@@ -781,6 +856,7 @@ SGEMM_API int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value) 
     else if (k == "simt_below_flops" && value >= 0) h->simt_below_flops = value;
     else if (k == "fuse_split_k" && (value == 0 || value == 1)) h->fuse_split_k = value != 0;
     else if (k == "pdl" && (value == 0 || value == 1)) h->pdl = value != 0;
+    else if (k == "pipeline_host" && (value == 0 || value == 1)) h->pipeline_host = value != 0;
     else if (k == "profile" && (value == 0 || value == 1)) { h->profile = value != 0; h->prof_used = 0; }
     else return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "unknown option or value out of range: %s = %lld", key, (long long)value);
     return SGEMM_OK;

@@ -107,7 +107,9 @@ size_t sgemm_noalloc_scratch_bytes(void);
 /* The same call with HOST buffers: uploads A, B (and C when beta != 0), launches, downloads D and
  * synchronises — what the reference's main does around its kernel with hipMalloc / hipMemcpyHtoD /
  * hipMemcpyDtoH (runner/generator_runner.cpp:236-242, 289-291).  Device staging buffers are cached in
- * the handle.  Host buffers may be pageable or pinned. */
+ * the handle.  Host buffers may be pageable or pinned.  Large problems (>= 64 MiB of operands, N >= 4 tiles) are
+ * pipelined over column chunks on three internal streams so that uploads, GEMM and downloads overlap (this needs
+ * pinned host memory to take effect; option "pipeline_host" = 0 turns it off); results are the same either way. */
 int sgemm_run_host(sgemm_handle *h, const float *hA, const float *hB, const float *hC, float *hD,
                    float alpha, float beta, uint32_t m, uint32_t n, uint32_t k,
                    uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd);
@@ -131,6 +133,7 @@ int sgemm_last_status(sgemm_handle *h, uint32_t status[8]);
  * slice reduces), 0 (default) runs the separate reduction kernel — same bits either way, the separate kernel is faster;
  * "pdl" 1 (default) launches every kernel with programmatic stream serialisation so that launch latency and per-CTA
  * set-up overlap with the tail of the previous kernel (all kernels wait on the grid dependency before touching memory);
+ * "pipeline_host" 1 (default) lets sgemm_run_host overlap transfers and compute over column chunks;
  * "profile" 1 brackets every main-GEMM-kernel launch with an event pair (read with "profile_main_ns"). */
 int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value);
 

@@ -302,6 +302,28 @@ def test_beta_zero_never_reads_c(runner_of):
         check(d, a, b, None, m, n, k, 1.0, 0.0)
 
 
+# ------------------------------------------------------------------------------------ pipelined host path
+@pytest.mark.parametrize("kernel,force", [("tc2_256x256x32_s3", AUTO), ("tc_128x128x32_s3_ak", TENSOR), ("simt_128x128x16", SIMT)])
+@pytest.mark.parametrize("beta,ldd", [(0.0, 0), (0.75, 2052)])
+def test_pipelined_host_call_equals_the_single_launch(runner_of, kernel, force, beta, ldd):
+    # sgemm_run_host overlaps uploads, GEMM and downloads over column chunks for large problems; chunking must not
+    # change a single bit of D (same kernel, same split-K partition per element), padding rows included
+    m, n, k = 2048, 4096 + 96, 2048          # a ragged last chunk
+    a, b, c = oracle.make_inputs(m, n, k, seed=23)
+    canary = np.full((ldd or m) * n, np.float32(3.5))
+    r = runner_of(kernel)
+    outs = []
+    for pipelined in (1, 0):
+        r.set_option("pipeline_host", pipelined)
+        launches = r.info("launches")
+        outs.append(run(r, a, b, c, m, n, k, 1.0, beta, force=force, ldd=ldd, d_init=canary))
+        count = r.info("launches") - launches
+        assert (count > 3) == bool(pipelined)      # eight chunks against one launch chain
+    r.set_option("pipeline_host", 1)
+    assert outs[0].tobytes() == outs[1].tobytes()
+    check(outs[0], a, b, c, m, n, k, 1.0, beta, ldd=ldd)
+
+
 # ------------------------------------------------------------------------------------ workspace handling
 def test_lent_workspace(runner_of):
     from runner import api
