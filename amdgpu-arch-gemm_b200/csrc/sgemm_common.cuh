@@ -15,8 +15,8 @@
 #endif
 
 // Device status words written by a kernel that gave up on a bounded wait.
-//   status[0] = code (0 ok, 1 wait timed out, 2 aborted because another role timed out)
-//   status[1] = role/barrier tag   status[2] = tile index   status[3] = k-block / stage
+//   status[0] = code (0 ok, 1 a bounded wait ran out)   status[1] = role/barrier tag
+//   status[2] = tile index   status[3] = k-block   status[4] = block index   status[5] = parity waited for
 #define SGEMM_STATUS_WORDS 8
 #define SGEMM_STATUS_OK 0u
 #define SGEMM_STATUS_TIMEOUT 1u

@@ -32,7 +32,7 @@ namespace {
     X(cuDevicePrimaryCtxRelease) X(cuCtxPushCurrent) X(cuCtxPopCurrent) X(cuModuleLoad) X(cuModuleUnload) \
     X(cuModuleGetFunction) X(cuFuncSetAttribute) X(cuLaunchKernel) X(cuLaunchKernelEx) X(cuTensorMapEncodeTiled) \
     X(cuMemAlloc) X(cuMemFree) X(cuMemcpyHtoDAsync) X(cuMemcpyDtoHAsync) X(cuMemcpyHtoD) X(cuMemcpyDtoH) \
-    X(cuMemsetD8) X(cuMemsetD32Async) X(cuStreamSynchronize) X(cuCtxSynchronize) X(cuEventCreate)        \
+    X(cuMemsetD8) X(cuStreamSynchronize) X(cuCtxSynchronize) X(cuEventCreate)        \
     X(cuEventRecord) X(cuEventSynchronize) X(cuEventElapsedTime) X(cuEventDestroy) X(cuGetErrorString)   \
     X(cuStreamCreate) X(cuStreamDestroy) X(cuStreamWaitEvent)                                            \
     X(cuGetErrorName)
@@ -190,9 +190,7 @@ struct Plan {
     bool fused_reduce = false;   // tensor kernel sums the split-K partials itself (arrival counters)
 };
 
-bool tensor_eligible(const sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_t n, uint32_t k,
-                     uint32_t lda, uint32_t ldb) {
-    (void)m; (void)n; (void)k;
+bool tensor_eligible(const sgemm_handle *h, const void *a, const void *b, uint32_t lda, uint32_t ldb) {
     if (h->cfg.variant != kVariantTensor) return false;
     // TMA: 16-byte aligned bases and row pitches that are multiples of 16 bytes
     if (((uintptr_t)a & 15) || ((uintptr_t)b & 15)) return false;
@@ -219,7 +217,7 @@ uint32_t pick_split_k(const sgemm_handle *h, uint32_t tiles, uint32_t k, uint32_
 
 int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_t n, uint32_t k, uint32_t lda,
               uint32_t ldb, Plan *p) {
-    const bool eligible = tensor_eligible(h, a, b, m, n, k, lda, ldb);
+    const bool eligible = tensor_eligible(h, a, b, lda, ldb);
     int variant;
     if (h->force_variant == 1) {
         if (!eligible)

@@ -79,7 +79,7 @@ _lib: Optional[ctypes.CDLL] = None
 
 
 def build_library(force: bool = False) -> Path:
-    """Run the Makefile beside this file (g++; needs only <cuda.h>, not a GPU)."""
+    """Run the Makefile beside this file (g++ and nvcc; needs the CUDA toolkit headers, not a GPU)."""
     if force or not LIB_PATH.exists() or not RUNNER_PATH.exists():
         env = dict(os.environ)
         env.pop("CXX", None)

@@ -17,8 +17,8 @@ Cases
 * the 32x32x32 configuration with seeded uniform[-1,1) inputs (streams seed, seed+1, seed+2 of
   the index-hash generator in oracle/oracle.py), alpha = 1, beta in {0, 1}, for both single-wave
   32x32 tilings (mfma 32x32x2 with tiling 1x1, mfma 16x16x4 with tiling 2x2);
-* a 64x48x64 problem run over its whole 4x3 / 2x... workgroup grid with the workgroup-remap and
-  K-stagger knobs on, so the full D (not only one tile) is pinned.
+* multi-workgroup problems (64x48x64 over its 4x3 grid with the K-stagger and the three-buffer knobs, 64x64x32 over
+  its 4x4 grid with the workgroup remap) run workgroup by workgroup, so the full D (not only one tile) is pinned.
 """
 from __future__ import annotations
 
@@ -100,7 +100,7 @@ def run_reference_kernel(G, V, mfma, wave_tiling, depth_k, vmem_stage, opt_kwarg
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of the reference project")
     ap.add_argument("--seed", type=int, default=0)
     args = ap.parse_args()
     G, V = load_reference(args.reference)

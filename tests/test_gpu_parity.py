@@ -162,7 +162,7 @@ def test_unaligned_base_pointers_take_the_simt_kernel(runner_of):
             r.dev_free(p)
 
 
-# ------------------------------------------------------------------- BASELINE's skinny shapes, full oracle
+# ----------------------------------------------------------------- the skinny benchmark shapes, full oracle
 @pytest.mark.parametrize("mnk", [(8192, 8192, 256), (4096, 128, 16384)])
 def test_skinny_shapes_full_oracle(runner_of, mnk):
     m, n, k = mnk
