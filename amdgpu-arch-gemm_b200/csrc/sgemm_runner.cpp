@@ -195,7 +195,7 @@ bool tensor_eligible(const sgemm_handle *h, const void *a, const void *b, uint32
     // TMA: 16-byte aligned bases and row pitches that are multiples of 16 bytes
     if (((uintptr_t)a & 15) || ((uintptr_t)b & 15)) return false;
     if ((ldb % 4) != 0) return false;
-    if (!h->cfg.a_kmajor && (lda % 4) != 0) return false;
+    if ((!h->cfg.a_kmajor || h->cfg.trans_a) && (lda % 4) != 0) return false;   // a packed copy gets its own pitch
     return true;
 }
 
@@ -242,14 +242,16 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
         const uint64_t units = (uint64_t)p->tiles_m * p->tiles_n * p->split_k;
         const uint32_t group = (uint32_t)std::max(1, h->cfg.wave_group[0]);
         p->grid_x = group * (uint32_t)std::min<uint64_t>(units, (uint64_t)std::max(1, h->sm_count / (int)group));
-        p->span_b = (uint64_t)ldb * (n - 1) + k;
+        // floats between the first and the last element of an operand as stored (op(B) is K x N: stored K x N with
+        // pitch ldb, or, transposed, N x K with pitch ldb)
+        p->span_b = h->cfg.trans_b ? (uint64_t)ldb * (k - 1) + n : (uint64_t)ldb * (n - 1) + k;
         if (h->cfg.a_kmajor) {
             p->ldt = (uint32_t)round_up(k, 4);
             p->hi_a_off = off; off += round_up((size_t)p->ldt * m * 4, 256);
             p->lo_a_off = off; off += round_up((size_t)p->ldt * m * 4, 256);
             p->span_a = 0;
         } else if (!h->cfg.split_inkernel) {
-            p->span_a = (uint64_t)lda * (k - 1) + m;
+            p->span_a = h->cfg.trans_a ? (uint64_t)lda * (m - 1) + k : (uint64_t)lda * (k - 1) + m;
             p->lo_a_off = off; off += round_up(p->span_a * 4, 256);
         }
         if (!h->cfg.split_inkernel) { p->lo_b_off = off; off += round_up(p->span_b * 4, 256); }
@@ -384,9 +386,10 @@ int check_problem(sgemm_handle *h, const void *a, const void *b, const void *c, 
     if (m && n && !d) return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "D is NULL");
     if (m && n && k && (!a || !b)) return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "A or B is NULL");
     if (m && n && beta != 0.0f && !c) return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "C is NULL but beta != 0");
-    if (lda < std::max(m, 1u) || ldb < std::max(k, 1u) || ldd < std::max(m, 1u) || (beta != 0.0f && ldc < std::max(m, 1u)))
-        return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "leading dimension too small: lda %u ldb %u ldc %u ldd %u for M %u K %u",
-                    lda, ldb, ldc, ldd, m, k);
+    const uint32_t a_rows = h->cfg.trans_a ? k : m, b_rows = h->cfg.trans_b ? n : k;   // rows of A and B as stored
+    if (lda < std::max(a_rows, 1u) || ldb < std::max(b_rows, 1u) || ldd < std::max(m, 1u) || (beta != 0.0f && ldc < std::max(m, 1u)))
+        return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "leading dimension too small: lda %u ldb %u ldc %u ldd %u for M %u N %u K %u "
+                    "(trans_a %d, trans_b %d)", lda, ldb, ldc, ldd, m, n, k, h->cfg.trans_a, h->cfg.trans_b);
     if ((uint64_t)m * n >= ((uint64_t)1 << 40)) return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "problem too large");
     return SGEMM_OK;
 }
@@ -443,8 +446,18 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
             if ((rc = encode_map(h, 1, lo_a, k, m, (uint64_t)p.ldt * 4, kspan, 128, ksw, &ma_lo))) return rc;
         } else if (h->cfg.split_inkernel) {
             // no pre-pass and no lo copies: the kernel's transform warps make the lo tiles; the lo map slots get the hi maps
-            if ((rc = encode_map(h, 0, dA, m, k, (uint64_t)lda * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &ma_hi))) return rc;
+            if (h->cfg.trans_a) rc = encode_map(h, 0, dA, k, m, (uint64_t)lda * 4, kspan, 128, ksw, &ma_hi);
+            else rc = encode_map(h, 0, dA, m, k, (uint64_t)lda * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &ma_hi);
+            if (rc) return rc;
             ma_lo = ma_hi;
+        } else if (h->cfg.trans_a) {
+            // A is stored K-contiguous: it is the K-major operand as it lies, and so is its lo copy
+            uint64_t span_a = h->reuse_a_lo ? 0 : p.span_a;
+            void *ps[] = {&dA, &lo_a, &span_a, &dB, &lo_b, &p.span_b};
+            rc = launch(h, h->fn_split_lo, blocks, 1, 1, 256, 1, 0, stream, ps);
+            if (rc) return rc;
+            if ((rc = encode_map(h, 0, dA, k, m, (uint64_t)lda * 4, kspan, 128, ksw, &ma_hi))) return rc;
+            if ((rc = encode_map(h, 1, lo_a, k, m, (uint64_t)lda * 4, kspan, 128, ksw, &ma_lo))) return rc;
         } else {
             uint64_t span_a = h->reuse_a_lo ? 0 : p.span_a;   // same A as the previous chunk of a pipelined host call
             void *ps[] = {&dA, &lo_a, &span_a, &dB, &lo_b, &p.span_b};
@@ -453,9 +466,16 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
             if ((rc = encode_map(h, 0, dA, m, k, (uint64_t)lda * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &ma_hi))) return rc;
             if ((rc = encode_map(h, 1, lo_a, m, k, (uint64_t)lda * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &ma_lo))) return rc;
         }
-        if ((rc = encode_map(h, 2, dB, k, n, (uint64_t)ldb * 4, kspan, bn, ksw, &mb_hi))) return rc;
-        if (h->cfg.split_inkernel) mb_lo = mb_hi;
-        else if ((rc = encode_map(h, 3, lo_b, k, n, (uint64_t)ldb * 4, kspan, bn, ksw, &mb_lo))) return rc;
+        if (h->cfg.trans_b) {
+            // B is stored N-contiguous: an MN-major operand, staged in 32-column chunks like the untransposed A
+            if ((rc = encode_map(h, 2, dB, n, k, (uint64_t)ldb * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &mb_hi))) return rc;
+            if (h->cfg.split_inkernel) mb_lo = mb_hi;
+            else if ((rc = encode_map(h, 3, lo_b, n, k, (uint64_t)ldb * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &mb_lo))) return rc;
+        } else {
+            if ((rc = encode_map(h, 2, dB, k, n, (uint64_t)ldb * 4, kspan, bn, ksw, &mb_hi))) return rc;
+            if (h->cfg.split_inkernel) mb_lo = mb_hi;
+            else if ((rc = encode_map(h, 3, lo_b, k, n, (uint64_t)ldb * 4, kspan, bn, ksw, &mb_lo))) return rc;
+        }
         uint32_t *counters = p.fused_reduce ? reinterpret_cast<uint32_t *>(h->counters) : nullptr;
         void *params[] = {&dA, &dB, &dC, &dD, &m, &n, &k, &lda, &ldb, &ldc, &ldd, &alpha, &beta, &nwx, &nwy,
                           &partial, &status_ptr, &split, &counters,
@@ -536,7 +556,6 @@ int config_from_toml(const char *path, sgemm_config *c, std::string *err) {
     c->fallback_threads = t.get_int("fallback_threads", &v) ? (int32_t)v : 0;
     std::snprintf(c->entry, sizeof c->entry, "%s", t.get_string("entry", &s) ? s.c_str() : "generated_gemm");
     std::snprintf(c->fallback_entry, sizeof c->fallback_entry, "%s", t.get_string("fallback_entry", &s) ? s.c_str() : "");
-    if (c->trans_a || c->trans_b) { *err = "transposed operands are not supported by these kernels"; return SGEMM_ERR_TOML; }
     if (c->variant == kVariantTensor && (c->fallback_threads <= 0 || c->fallback_tile[0] <= 0 || !c->fallback_entry[0])) {
         *err = "tensor-variant config lacks the fallback_* keys";
         return SGEMM_ERR_TOML;
@@ -709,7 +728,9 @@ SGEMM_API int sgemm_run_host(sgemm_handle *h, const float *hA, const float *hB, 
     CtxGuard guard(h);
     Driver &d = driver();
     const bool use_c = beta != 0.0f;
-    const size_t bytes[4] = {k ? ((size_t)lda * (k - 1) + m) * 4 : 0, k ? ((size_t)ldb * (n - 1) + k) * 4 : 0,
+    const size_t a_floats = h->cfg.trans_a ? (size_t)lda * (m - 1) + k : (size_t)lda * (k - 1) + m;
+    const size_t b_floats = h->cfg.trans_b ? (size_t)ldb * (k - 1) + n : (size_t)ldb * (n - 1) + k;
+    const size_t bytes[4] = {k ? a_floats * 4 : 0, k ? b_floats * 4 : 0,
                              use_c ? ((size_t)ldc * (n - 1) + m) * 4 : 0, ((size_t)ldd * (n - 1) + m) * 4};
     for (int i = 0; i < 4; ++i) {
         if (bytes[i] > h->stage_bytes[i]) {
@@ -730,7 +751,8 @@ SGEMM_API int sgemm_run_host(sgemm_handle *h, const float *hA, const float *hB, 
     // Columns of D are independent and every chunk runs the same kernel in the same k order, so the result is
     // the one the single-launch path produces.
     const uint32_t chunk_unit = std::max<uint32_t>(h->tile_n, 256);
-    if (h->pipeline_host && k > 0 && n >= 4 * chunk_unit && bytes[0] + bytes[1] + bytes[3] >= ((size_t)64 << 20)) {
+    // (a transposed B keeps a column chunk of op(B) scattered over all of its rows: no contiguous chunk to upload)
+    if (h->pipeline_host && !h->cfg.trans_b && k > 0 && n >= 4 * chunk_unit && bytes[0] + bytes[1] + bytes[3] >= ((size_t)64 << 20)) {
         const uint32_t nc = (uint32_t)round_up((n + 7) / 8, chunk_unit);
         const uint32_t chunks = (n + nc - 1) / nc;
         for (CUstream &st : h->pipe_streams)

@@ -5,6 +5,8 @@
 // a SIMT_TM x SIMT_TN register tile made of 4x4 sub-blocks strided over the block tile, so that
 // shared-memory fragment reads are 16-byte and conflict-free.
 //
+// op(A), op(B): GEMM_TRANS_A / GEMM_TRANS_B select at compile time whether A (B) is stored transposed.
+//
 // Arbitrary M, N, K and leading dimensions: loads are 16-byte when base pointer and leading
 // dimension allow it and the whole vector is in range, guarded scalars otherwise (zero fill).
 //
@@ -29,76 +31,126 @@ static_assert(SIMT_TM % 4 == 0 && SIMT_TN % 4 == 0, "thread tile is built from 4
 static_assert(SIMT_BM % SIMT_TM == 0 && SIMT_BN % SIMT_TN == 0, "block tile / thread tile");
 static_assert(SIMT_BK % 4 == 0, "K step is loaded in 16-byte vectors");
 
+#ifndef GEMM_TRANS_A
+#define GEMM_TRANS_A 0   // 1: A is stored transposed (K x M column-major, element (i,l) at a[l + i*lda])
+#endif
+#ifndef GEMM_TRANS_B
+#define GEMM_TRANS_B 0   // 1: B is stored transposed (N x K column-major, element (l,j) at b[j + l*ldb])
+#endif
+
 struct SimtSmem {
-    float a[2][SIMT_BK][SIMT_BM];               // k-major rows of the A tile (M contiguous)
-    float b[2][SIMT_BK][SIMT_BN + SIMT_B_PAD];  // k-major rows of the B tile (transposed on store)
+    float a[2][SIMT_BK][SIMT_BM + SIMT_B_PAD];  // k-major rows of the A tile
+    float b[2][SIMT_BK][SIMT_BN + SIMT_B_PAD];  // k-major rows of the B tile
+};
+
+// Both operands end up in shared memory as [k][mn] rows.  An operand whose MN index is contiguous in global
+// memory (A not transposed, B transposed) is loaded in 16-byte vectors along MN and stored as is; an operand
+// whose K index is contiguous (B not transposed, A transposed) is loaded in vectors along K and transposed on
+// the store.  MN = rows of the tile, ld = leading dimension, mn0 / mn_end = tile origin / matrix extent.
+template <int TILE_MN>
+struct SimtLoader {
+    static constexpr int VEC = (TILE_MN * SIMT_BK / 4 + SIMT_THREADS - 1) / SIMT_THREADS;
+
+    __device__ static __forceinline__ void load_mn_contiguous(float4 (&r)[VEC], const float *__restrict__ p0, uint32_t mn_end,
+                                                              uint32_t ld, uint32_t mn0, uint32_t k0, uint32_t k_end, bool vec_ok) {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+            const uint32_t id = threadIdx.x + v * SIMT_THREADS;
+            const uint32_t i = mn0 + (id % (TILE_MN / 4)) * 4, l = k0 + id / (TILE_MN / 4);
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (id < TILE_MN * SIMT_BK / 4 && l < k_end) {
+                const float *p = p0 + i + (uint64_t)l * ld;
+                if (vec_ok && i + 3 < mn_end) {
+                    x = __ldg(reinterpret_cast<const float4 *>(p));
+                } else {
+                    if (i + 0 < mn_end) x.x = __ldg(p + 0);
+                    if (i + 1 < mn_end) x.y = __ldg(p + 1);
+                    if (i + 2 < mn_end) x.z = __ldg(p + 2);
+                    if (i + 3 < mn_end) x.w = __ldg(p + 3);
+                }
+            }
+            r[v] = x;
+        }
+    }
+
+    __device__ static __forceinline__ void load_k_contiguous(float4 (&r)[VEC], const float *__restrict__ p0, uint32_t mn_end,
+                                                             uint32_t ld, uint32_t mn0, uint32_t k0, uint32_t k_end, bool vec_ok) {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+            const uint32_t id = threadIdx.x + v * SIMT_THREADS;
+            const uint32_t l = k0 + (id % (SIMT_BK / 4)) * 4, j = mn0 + id / (SIMT_BK / 4);
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (id < TILE_MN * SIMT_BK / 4 && j < mn_end) {
+                const float *p = p0 + l + (uint64_t)j * ld;
+                if (vec_ok && l + 3 < k_end) {
+                    x = __ldg(reinterpret_cast<const float4 *>(p));
+                } else {
+                    if (l + 0 < k_end) x.x = __ldg(p + 0);
+                    if (l + 1 < k_end) x.y = __ldg(p + 1);
+                    if (l + 2 < k_end) x.z = __ldg(p + 2);
+                    if (l + 3 < k_end) x.w = __ldg(p + 3);
+                }
+            }
+            r[v] = x;
+        }
+    }
+
+    __device__ static __forceinline__ void store_mn_contiguous(float (*rows)[TILE_MN + SIMT_B_PAD], const float4 (&r)[VEC]) {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+            const uint32_t id = threadIdx.x + v * SIMT_THREADS;
+            if (id < TILE_MN * SIMT_BK / 4)
+                *reinterpret_cast<float4 *>(&rows[id / (TILE_MN / 4)][(id % (TILE_MN / 4)) * 4]) = r[v];
+        }
+    }
+
+    __device__ static __forceinline__ void store_k_contiguous(float (*rows)[TILE_MN + SIMT_B_PAD], const float4 (&r)[VEC]) {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+            const uint32_t id = threadIdx.x + v * SIMT_THREADS;
+            if (id < TILE_MN * SIMT_BK / 4) {
+                const uint32_t l = (id % (SIMT_BK / 4)) * 4, j = id / (SIMT_BK / 4);
+                rows[l + 0][j] = r[v].x;
+                rows[l + 1][j] = r[v].y;
+                rows[l + 2][j] = r[v].z;
+                rows[l + 3][j] = r[v].w;
+            }
+        }
+    }
 };
 
 __device__ __forceinline__ void simt_load_a(float4 (&ra)[SIMT_A_VEC], const float *__restrict__ a,
                                             uint32_t m, uint32_t lda, uint32_t m0, uint32_t k0,
                                             uint32_t k_end, bool vec_ok) {
-#pragma unroll
-    for (int v = 0; v < SIMT_A_VEC; ++v) {
-        const uint32_t id = threadIdx.x + v * SIMT_THREADS;
-        const uint32_t i = m0 + (id % (SIMT_BM / 4)) * 4, l = k0 + id / (SIMT_BM / 4);
-        float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (id < SIMT_BM * SIMT_BK / 4 && l < k_end) {
-            const float *p = a + i + (uint64_t)l * lda;
-            if (vec_ok && i + 3 < m) {
-                r = __ldg(reinterpret_cast<const float4 *>(p));
-            } else {
-                if (i + 0 < m) r.x = __ldg(p + 0);
-                if (i + 1 < m) r.y = __ldg(p + 1);
-                if (i + 2 < m) r.z = __ldg(p + 2);
-                if (i + 3 < m) r.w = __ldg(p + 3);
-            }
-        }
-        ra[v] = r;
-    }
+#if GEMM_TRANS_A
+    SimtLoader<SIMT_BM>::load_k_contiguous(ra, a, m, lda, m0, k0, k_end, vec_ok);
+#else
+    SimtLoader<SIMT_BM>::load_mn_contiguous(ra, a, m, lda, m0, k0, k_end, vec_ok);
+#endif
 }
 
 __device__ __forceinline__ void simt_load_b(float4 (&rb)[SIMT_B_VEC], const float *__restrict__ b,
                                             uint32_t n, uint32_t ldb, uint32_t n0, uint32_t k0,
                                             uint32_t k_end, bool vec_ok) {
-#pragma unroll
-    for (int v = 0; v < SIMT_B_VEC; ++v) {
-        const uint32_t id = threadIdx.x + v * SIMT_THREADS;
-        const uint32_t l = k0 + (id % (SIMT_BK / 4)) * 4, j = n0 + id / (SIMT_BK / 4);
-        float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (id < SIMT_BN * SIMT_BK / 4 && j < n) {
-            const float *p = b + l + (uint64_t)j * ldb;
-            if (vec_ok && l + 3 < k_end) {
-                r = __ldg(reinterpret_cast<const float4 *>(p));
-            } else {
-                if (l + 0 < k_end) r.x = __ldg(p + 0);
-                if (l + 1 < k_end) r.y = __ldg(p + 1);
-                if (l + 2 < k_end) r.z = __ldg(p + 2);
-                if (l + 3 < k_end) r.w = __ldg(p + 3);
-            }
-        }
-        rb[v] = r;
-    }
+#if GEMM_TRANS_B
+    SimtLoader<SIMT_BN>::load_mn_contiguous(rb, b, n, ldb, n0, k0, k_end, vec_ok);
+#else
+    SimtLoader<SIMT_BN>::load_k_contiguous(rb, b, n, ldb, n0, k0, k_end, vec_ok);
+#endif
 }
 
 __device__ __forceinline__ void simt_store_tiles(SimtSmem &s, int buf, const float4 (&ra)[SIMT_A_VEC],
                                                  const float4 (&rb)[SIMT_B_VEC]) {
-#pragma unroll
-    for (int v = 0; v < SIMT_A_VEC; ++v) {
-        const uint32_t id = threadIdx.x + v * SIMT_THREADS;
-        if (id < SIMT_BM * SIMT_BK / 4)
-            *reinterpret_cast<float4 *>(&s.a[buf][id / (SIMT_BM / 4)][(id % (SIMT_BM / 4)) * 4]) = ra[v];
-    }
-#pragma unroll
-    for (int v = 0; v < SIMT_B_VEC; ++v) {
-        const uint32_t id = threadIdx.x + v * SIMT_THREADS;
-        if (id < SIMT_BN * SIMT_BK / 4) {
-            const uint32_t l = (id % (SIMT_BK / 4)) * 4, j = id / (SIMT_BK / 4);
-            s.b[buf][l + 0][j] = rb[v].x;
-            s.b[buf][l + 1][j] = rb[v].y;
-            s.b[buf][l + 2][j] = rb[v].z;
-            s.b[buf][l + 3][j] = rb[v].w;
-        }
-    }
+#if GEMM_TRANS_A
+    SimtLoader<SIMT_BM>::store_k_contiguous(s.a[buf], ra);
+#else
+    SimtLoader<SIMT_BM>::store_mn_contiguous(s.a[buf], ra);
+#endif
+#if GEMM_TRANS_B
+    SimtLoader<SIMT_BN>::store_mn_contiguous(s.b[buf], rb);
+#else
+    SimtLoader<SIMT_BN>::store_k_contiguous(s.b[buf], rb);
+#endif
 }
 
 __device__ __forceinline__ void simt_read_frag(const SimtSmem &s, int buf, int kk, uint32_t tx,

@@ -32,8 +32,9 @@
 //     (row = one n, 32 consecutive k);                SBO = 8 rows = 1024 B;
 //     one K=8 MMA step advances the start address by 32 B inside the swizzle span.
 //     TC_BK = 16 uses 64-byte rows with the 64-byte swizzle instead (SBO = 512 B).
-//   With TC_A_KMAJOR the A operand is read from K-major packed copies (sgemm_pack_a_kmajor) and
-//   uses B's layout.
+//   With TC_A_KMAJOR the A operand is K-major — the caller's A is stored transposed (K contiguous), or
+//   packed copies made by sgemm_pack_a_kmajor are read — and uses B's layout.  With TC_B_MNMAJOR the
+//   caller's B is stored transposed (N contiguous) and uses A's MN-major layout (32-column chunks).
 //
 // TC_CTA_GROUP = 2 pairs two CTAs (a 2x1 cluster, two neighbouring SMs) on one 256 x TC_BN tile with
 // tcgen05.mma.cta_group::2: CTA r of the pair loads rows 128r.. of the A tile and columns (TC_BN/2)r.. of
@@ -74,6 +75,9 @@
 #ifndef TC_CTA_GROUP
 #define TC_CTA_GROUP 1
 #endif
+#ifndef TC_B_MNMAJOR
+#define TC_B_MNMAJOR 0   // 1: B is stored N-contiguous (the caller's B is transposed), read as an MN-major operand
+#endif
 #define TC_BM 128                              // rows of A (and of the accumulator) per CTA
 #define TC_UMMA_M (TC_BM * TC_CTA_GROUP)       // rows of the launch unit's tile = UMMA M
 #define TC_BN_CTA (TC_BN / TC_CTA_GROUP)       // columns of B this CTA keeps in shared memory
@@ -104,6 +108,7 @@ static_assert(TC_EPI_COLS % 32 == 0, "an epilogue warp drains whole 32-column ch
 
 static_assert(TC_BK == 16 || TC_BK % 32 == 0, "k per stage: one 64-byte span or whole 128-byte swizzle spans");
 static_assert(TC_CTA_GROUP == 1 || TC_CTA_GROUP == 2, "one CTA or a CTA pair per tile");
+static_assert(!TC_B_MNMAJOR || (TC_BN / TC_CTA_GROUP) % 32 == 0, "MN-major B is staged in 32-column chunks");
 static_assert(TC_BN % (16 * TC_CTA_GROUP) == 0 && TC_BN >= 16 * TC_CTA_GROUP && TC_BN <= 256, "UMMA N");
 static_assert(TC_SMEM_BYTES <= 232448, "shared memory budget of one CTA");
 
@@ -263,7 +268,7 @@ __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr, uint32_t lbo_byt
 }
 // 32-bit instruction descriptor of kind::tf32: FP32 accumulate [4,6)=1, A/B format TF32 [7,10) and
 // [10,13) = 2, A/B major [15]/[16] (1 = MN-major), N>>3 at [17,23), M>>4 at [24,29).
-#define TC_IDESC ((1u << 4) | (2u << 7) | (2u << 10) | ((TC_A_KMAJOR ? 0u : 1u) << 15) | (0u << 16) | \
+#define TC_IDESC ((1u << 4) | (2u << 7) | (2u << 10) | ((TC_A_KMAJOR ? 0u : 1u) << 15) | ((TC_B_MNMAJOR ? 1u : 0u) << 16) | \
                   ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_UMMA_M >> 4) << 24))
 
 // --------------------------------------------------------------------------------------- kernel
@@ -387,9 +392,15 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                     for (int ch = 0; ch < TC_BM / 32; ++ch)
                         tc_tma_load_2d_local(sa_hi + ch * TC_A_CHUNK_BYTES, &map_a_hi, own_full, m0 + 32 * ch, k0);
 #endif
+#if TC_B_MNMAJOR
+#pragma unroll
+                    for (int ch = 0; ch < TC_BN_CTA / 32; ++ch)
+                        tc_tma_load_2d_local(sb_hi + ch * TC_A_CHUNK_BYTES, &map_b_hi, own_full, n0 + 32 * ch, k0);
+#else
 #pragma unroll
                     for (int sub = 0; sub < TC_KSUBS; ++sub)
                         tc_tma_load_2d_local(sb_hi + sub * TC_B_SUB_BYTES, &map_b_hi, own_full, k0 + TC_KSPAN * sub, n0);
+#endif
 #else
                     if (cta_rank == 0) tc_mbar_expect_tx(bar_full + 8 * stage, TC_CTA_GROUP * TC_STAGE_BYTES);
 #if TC_A_KMAJOR
@@ -405,11 +416,19 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                         tc_tma_load_2d(sa_lo + ch * TC_A_CHUNK_BYTES, &map_a_lo, full, m0 + 32 * ch, k0);
                     }
 #endif
+#if TC_B_MNMAJOR
+#pragma unroll
+                    for (int ch = 0; ch < TC_BN_CTA / 32; ++ch) {
+                        tc_tma_load_2d(sb_hi + ch * TC_A_CHUNK_BYTES, &map_b_hi, full, n0 + 32 * ch, k0);
+                        tc_tma_load_2d(sb_lo + ch * TC_A_CHUNK_BYTES, &map_b_lo, full, n0 + 32 * ch, k0);
+                    }
+#else
 #pragma unroll
                     for (int sub = 0; sub < TC_KSUBS; ++sub) {
                         tc_tma_load_2d(sb_hi + sub * TC_B_SUB_BYTES, &map_b_hi, full, k0 + TC_KSPAN * sub, n0);
                         tc_tma_load_2d(sb_lo + sub * TC_B_SUB_BYTES, &map_b_lo, full, k0 + TC_KSPAN * sub, n0);
                     }
+#endif
 #endif  // TC_SPLIT_INKERNEL
                     if (++stage == TC_STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -451,9 +470,15 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                         const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
                         const uint64_t da_lo = tc_smem_desc(sa_lo + a_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
 #endif
+#if TC_B_MNMAJOR
+                        const uint32_t b_off = kk * 1024;
+                        const uint64_t db_hi = tc_smem_desc(sb_hi + b_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
+                        const uint64_t db_lo = tc_smem_desc(sb_lo + b_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
+#else
                         const uint32_t b_off = TC_KMAJOR_OFF(kk, TC_B_SUB_BYTES);
                         const uint64_t db_hi = tc_smem_desc(sb_hi + b_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);
                         const uint64_t db_lo = tc_smem_desc(sb_lo + b_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);
+#endif
                         const uint32_t first = (kb == kb_begin && kk == 0) ? 0u : 1u;
 #if TC_TERMS == 3
                         tc_mma_tf32(d_tmem, da_lo, db_hi, TC_IDESC, first);

@@ -180,8 +180,7 @@ class GemmSolutionConfig:
 
         for t in (a_type, b_type, cd_type, scalar_type):
             datatype_size(t)
-        if trans_a or trans_b:
-            raise RuntimeError("only the NN layout is implemented (column-major A and B, no transposes)")
+        self.trans_a, self.trans_b = bool(trans_a), bool(trans_b)
         if not all(_is_pow2(g) for g in self.wave_group):
             raise RuntimeError(f"Invalid wave group: {wave_group}")
         if len(self.mfma) != 4 or len(self.wave_group) != 2 or len(self.wave_tiling) != 2:
@@ -233,6 +232,10 @@ class GemmSolutionConfig:
             raise RuntimeError("epilogue_warps is 4, or 8 when tile N is a multiple of 64")
         if self.split not in ("prepass", "inkernel"):
             raise RuntimeError("split is 'prepass' or 'inkernel'")
+        if self.trans_a and self.a_major == "k":
+            raise RuntimeError("a transposed A is K-major already: a_major='k' (packed copy) does not apply")
+        if self.trans_b and (bn // self.wave_group[0]) % 32:
+            raise RuntimeError("a transposed B is staged in 32-column chunks: tile N per CTA must be a multiple of 32")
         if self.split == "inkernel" and self.a_major == "k":
             raise RuntimeError("the K-major packed copy of A is made by a pre-pass; it excludes split='inkernel'")
         if self.stages * 24 + 40 > 256:
@@ -307,7 +310,7 @@ class GemmSolutionConfig:
             bn_cta = bn // self.wave_group[0]                                    # a CTA pair splits B's columns
             stage = 2 * (128 * self.depth_k * 4) + 2 * (bn_cta * self.depth_k * 4)  # A_hi, A_lo, B_hi, B_lo
             return self.stages * stage + 1024 + 256                              # + alignment slack + barriers
-        return 2 * self.depth_k * (bm + bn + 4) * 4                              # double-buffered A and padded B
+        return 2 * self.depth_k * (bm + 4 + bn + 4) * 4                          # double-buffered, padded A and B
 
     @property
     def num_unrolled_iters(self) -> int:
@@ -341,7 +344,7 @@ class GemmSolutionConfig:
             "entry": KERNEL_ENTRY,
         }
         if self.variant == VARIANT_TENSOR:
-            fb = simt_fallback_config()
+            fb = simt_fallback_config(self.trans_a, self.trans_b)
             d.update({
                 "a_major": self.a_major,
                 "terms": self.terms,
@@ -354,11 +357,11 @@ class GemmSolutionConfig:
         return d
 
 
-def simt_fallback_config() -> GemmSolutionConfig:
+def simt_fallback_config(trans_a: bool = False, trans_b: bool = False) -> GemmSolutionConfig:
     """The FFMA kernel compiled into every tensor-variant cubin for shapes TMA cannot describe
     (leading dimensions that are not multiples of 4, unaligned bases) and for tiny problems."""
     return GemmSolutionConfig(DataType.FP32, DataType.FP32, DataType.FP32, DataType.FP32,
-                              (1, 1, 1, 1), (16, 16), (8, 8), 16, False, False)
+                              (1, 1, 1, 1), (16, 16), (8, 8), 16, trans_a, trans_b)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -391,6 +394,10 @@ def _simt_defines(cfg: GemmSolutionConfig, opt: GemmOptimizations, entry: str):
             ("SIMT_TM", tm), ("SIMT_TN", tn), ("SIMT_PLR", 1 if opt.plr else 0)]
 
 
+def _trans_defines(cfg: GemmSolutionConfig):
+    return [("GEMM_TRANS_A", 1 if cfg.trans_a else 0), ("GEMM_TRANS_B", 1 if cfg.trans_b else 0)]
+
+
 @gpu_function
 def gemm(context: GpuContext, name: str, arch: str, config: GemmSolutionConfig, opt: GemmOptimizations,
          arguments: FunctionArgumentList) -> str:
@@ -413,19 +420,20 @@ def gemm(context: GpuContext, name: str, arch: str, config: GemmSolutionConfig, 
     out.write(f"// generated by generator.py: kernel '{name}', variant {config.variant}, "
               f"tile {config.tile_size[0]}x{config.tile_size[1]}x{config.depth_k}, stages {config.stages}, "
               f"wgm {opt.wgm}, plr {opt.plr}, gw {opt.gw}\n")
-    out.write(_defines([("OPT_WGM", opt.wgm)]))
+    out.write(_defines([("OPT_WGM", opt.wgm)] + _trans_defines(config)))
     out.write(_read("sgemm_common.cuh"))
     if config.variant == VARIANT_SIMT:
         out.write(_defines(_simt_defines(config, opt, KERNEL_ENTRY)))
         out.write(_read("sgemm_simt.cuh"))
     else:
-        out.write(_defines(_simt_defines(simt_fallback_config(), opt, SIMT_FALLBACK_ENTRY)))
+        out.write(_defines(_simt_defines(simt_fallback_config(config.trans_a, config.trans_b), opt, SIMT_FALLBACK_ENTRY)))
         out.write(_read("sgemm_simt.cuh"))
         out.write(_defines([("TC_BN", config.tile_size[1]), ("TC_BK", config.depth_k),
                             ("TC_STAGES", config.stages), ("TC_CTA_GROUP", config.wave_group[0]),
                             ("TC_SPLIT_INKERNEL", 1 if config.split == "inkernel" else 0),
                             ("TC_EPI_WARPS", config.epilogue_warps),
-                            ("TC_A_KMAJOR", 1 if config.a_major == "k" else 0),
+                            ("TC_A_KMAJOR", 1 if (config.a_major == "k" or config.trans_a) else 0),
+                            ("TC_B_MNMAJOR", 1 if config.trans_b else 0),
                             ("TC_TERMS", config.terms)]))
         out.write(_read("sgemm_tcgen05.cuh"))
     src = out.getvalue()
@@ -455,15 +463,17 @@ def compile(kern_name: str, kern_str: str, arch: str, output_folder: str, gemm_c
     return ret.returncode
 
 
-def tensor_config(bn: int = 256, bk: int = 32, stages: int = 2, cluster: int = 1, **kw) -> GemmSolutionConfig:
+def tensor_config(bn: int = 256, bk: int = 32, stages: int = 2, cluster: int = 1, trans_a: bool = False,
+                  trans_b: bool = False, **kw) -> GemmSolutionConfig:
     """Shorthand for a tensor-variant configuration with tile (128 * cluster) x bn x bk."""
     return GemmSolutionConfig(DataType.FP32, DataType.FP32, DataType.FP32, DataType.FP32,
-                              (128, bn, 1, 8), (cluster, 1), (1, 1), bk, False, False, vmem_stage=stages - 1, **kw)
+                              (128, bn, 1, 8), (cluster, 1), (1, 1), bk, trans_a, trans_b, vmem_stage=stages - 1, **kw)
 
 
-def simt_config(bm: int = 128, bn: int = 128, bk: int = 16, tm: int = 8, tn: int = 8) -> GemmSolutionConfig:
+def simt_config(bm: int = 128, bn: int = 128, bk: int = 16, tm: int = 8, tn: int = 8, trans_a: bool = False,
+                trans_b: bool = False) -> GemmSolutionConfig:
     return GemmSolutionConfig(DataType.FP32, DataType.FP32, DataType.FP32, DataType.FP32,
-                              (1, 1, 1, 1), (bm // tm, bn // tn), (tm, tn), bk, False, False)
+                              (1, 1, 1, 1), (bm // tm, bn // tn), (tm, tn), bk, trans_a, trans_b)
 
 
 def build_kernel(output_folder: str, config: GemmSolutionConfig, opt: Optional[GemmOptimizations] = None,

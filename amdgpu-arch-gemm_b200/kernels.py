@@ -39,6 +39,15 @@ REGISTRY = {
     "tc_128x128x32_s3_ak": (lambda: tensor_config(128, 32, 3, a_major="k"), dict(wgm=8)),
     "tc_128x128x16_s6_ak": (lambda: tensor_config(128, 16, 6, a_major="k"), dict(wgm=8)),
     "tc_128x128x32_s3_1x": (lambda: tensor_config(128, 32, 3, terms=1), dict(wgm=8)),
+    # transposed operands (TN: A stored K x M, NT: B stored N x K, TT: both)
+    "tc2_256x256x32_s3_tn": (lambda: tensor_config(256, 32, 3, cluster=2, trans_a=True), dict(wgm=8)),
+    "tc2_256x256x32_s3_nt": (lambda: tensor_config(256, 32, 3, cluster=2, trans_b=True), dict(wgm=8)),
+    "tc2_256x256x32_s3_tt": (lambda: tensor_config(256, 32, 3, cluster=2, trans_a=True, trans_b=True), dict(wgm=8)),
+    "tc_128x128x32_s3_tt": (lambda: tensor_config(128, 32, 3, trans_a=True, trans_b=True), dict(wgm=8)),
+    "tc2i_256x256x32_s3_tt": (lambda: tensor_config(256, 32, 3, cluster=2, split="inkernel", trans_a=True, trans_b=True), dict(wgm=8)),
+    "simt_128x128x16_tn": (lambda: simt_config(128, 128, 16, 8, 8, trans_a=True), dict(wgm=8)),
+    "simt_128x128x16_nt": (lambda: simt_config(128, 128, 16, 8, 8, trans_b=True), dict(wgm=8)),
+    "simt_64x64x16_tt": (lambda: simt_config(64, 64, 16, 4, 4, trans_a=True, trans_b=True), dict(wgm=4)),
     # FFMA SIMT kernels
     "simt_128x128x16": (lambda: simt_config(128, 128, 16, 8, 8), dict(wgm=8)),
     "simt_64x64x16": (lambda: simt_config(64, 64, 16, 4, 4), dict(wgm=4)),

@@ -7,8 +7,9 @@
  *
  * Conventions
  *   - every function returns 0 (SGEMM_OK) or a negative sgemm_error code; nothing throws or aborts;
- *   - matrices are FP32, column-major, no transposes: A is M x K (lda >= M), B is K x N (ldb >= K),
- *     C and D are M x N (ldc, ldd >= M);  D = alpha * A * B + beta * C;  C may be NULL when beta == 0;
+ *   - matrices are FP32, column-major: A is M x K (lda >= M), B is K x N (ldb >= K), C and D are M x N
+ *     (ldc, ldd >= M);  D = alpha * A * B + beta * C;  C may be NULL when beta == 0.  A cubin generated with
+ *     trans_a (trans_b) expects A stored as K x M with lda >= K (B stored as N x K with ldb >= N) instead;
  *   - the caller owns A, B, C, D; the handle owns the loaded module, its kernels, a status buffer, the
  *     tensor-map cache and (unless the caller lends one) the scratch workspace;
  *   - one handle belongs to one device; a handle is not thread-safe, distinct handles are;

@@ -38,7 +38,7 @@ def test_tile_product_rule_and_properties():
     assert cfg.tmem_columns == 512
     s = g.simt_config(128, 128, 16, 8, 8)
     assert s.tile_size == (128, 128) and s.num_workitems == 256
-    assert s.lds_usage_bytes == 2 * 16 * (128 + 128 + 4) * 4
+    assert s.lds_usage_bytes == 2 * 16 * (128 + 4 + 128 + 4) * 4
     assert s.num_bytes_per_buffer_load == (16, 16)  # the tuner's vector-load filter (tuner/sgemm_tuner.py:102)
 
 
@@ -56,9 +56,21 @@ def test_infeasible_configs_raise_runtime_error(kwargs):
                            vmem_stage=kwargs["vs"])
 
 
-def test_transposes_and_k_stagger_are_rejected():
-    with pytest.raises(RuntimeError):
-        GemmSolutionConfig(F, F, F, F, (1, 1, 1, 1), (16, 16), (8, 8), 16, True, False)
+def test_transposes_select_operand_layouts():
+    # trans_a / trans_b exist in the reference's config and TOML (generator/generator.py:868-869, 1008-1009) but only NN
+    # is implemented there; here they pick the operand layout at generation time
+    cfg = g.tensor_config(256, 32, 3, cluster=2, trans_a=True, trans_b=True)
+    src = gemm(None, "k", "sm_100a", cfg, GemmOptimizations(1), ARGS())
+    assert "#define GEMM_TRANS_A 1" in src and "#define GEMM_TRANS_B 1" in src
+    assert "#define TC_A_KMAJOR 1" in src and "#define TC_B_MNMAJOR 1" in src
+    assert cfg.to_dict()["trans_a"] is True and cfg.to_dict()["trans_b"] is True
+    nn = gemm(None, "k", "sm_100a", g.tensor_config(256, 32, 3, cluster=2), GemmOptimizations(1), ARGS())
+    assert "#define GEMM_TRANS_A 0" in nn and "#define TC_A_KMAJOR 0" in nn and "#define TC_B_MNMAJOR 0" in nn
+    with pytest.raises(RuntimeError):   # a transposed A is K-major already; the packed-copy knob does not apply
+        g.tensor_config(128, 32, 3, trans_a=True, a_major="k")
+
+
+def test_k_stagger_and_foreign_archs_are_rejected():
     with pytest.raises(RuntimeError):
         gemm(None, "k", "sm_100a", g.simt_config(), GemmOptimizations(1, map_k_idx=4), ARGS())
     with pytest.raises(RuntimeError):

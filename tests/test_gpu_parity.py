@@ -13,6 +13,7 @@ TENSOR_KERNELS = ["tc_128x256x32_s2", "tc_128x128x32_s3", "tc_128x64x32_s4", "tc
                   "tc2_256x256x32_s3", "tc2_256x256x16_s6", "tc2_256x128x32_s4",
                   "tc2i_256x256x32_s3", "tc2i_256x256x16_s6", "tci_128x256x32_s2", "tci_128x128x32_s3",
                   "tc2_256x256x32_s3_e4"]
+# (kernels built for transposed operands have their own tests below)
 SIMT_KERNELS = ["simt_128x128x16", "simt_64x64x16", "simt_128x64x8_plr0", "legacy_32x32x2_1wave", "legacy_16x16x4_2x2x2x2"]
 AUTO, TENSOR, SIMT = 0, 1, 2
 _runners = {}
@@ -300,6 +301,56 @@ def test_beta_zero_never_reads_c(runner_of):
     for kernel, force in (("tc_128x128x32_s3", TENSOR), ("simt_64x64x16", SIMT)):
         d = run(runner_of(kernel), a, b, None, m, n, k, 1.0, 0.0, force=force)   # C = NULL
         check(d, a, b, None, m, n, k, 1.0, 0.0)
+
+
+# ------------------------------------------------------------------------------------------ transposes
+def stored(flat, rows, cols, transposed, ld=0):
+    """Column-major rows x cols matrix (flat) as the kernel expects it: as is, or stored transposed (cols x rows
+    column-major), optionally with a padded leading dimension."""
+    mat = flat.reshape(cols, rows)                    # numpy row = one column of the matrix
+    if transposed:
+        mat = np.ascontiguousarray(mat.T)             # rows x cols array = cols-contiguous storage
+    inner = mat.shape[1]
+    ld = ld or inner
+    out = np.zeros(mat.shape[0] * ld, dtype=np.float32)
+    out.reshape(mat.shape[0], ld)[:, :inner] = mat
+    return out, ld
+
+
+@pytest.mark.parametrize("kernel,ta,tb", [
+    ("tc2_256x256x32_s3_tn", True, False), ("tc2_256x256x32_s3_nt", False, True), ("tc2_256x256x32_s3_tt", True, True),
+    ("tc_128x128x32_s3_tt", True, True), ("tc2i_256x256x32_s3_tt", True, True),
+    ("simt_128x128x16_tn", True, False), ("simt_128x128x16_nt", False, True), ("simt_64x64x16_tt", True, True)])
+@pytest.mark.parametrize("mnk", [(32, 32, 32), (129, 255, 33), (300, 520, 1000), (1024, 768, 512), (4, 300, 77)])
+@pytest.mark.parametrize("padded", [False, True])
+def test_transposed_operands(runner_of, kernel, ta, tb, mnk, padded):
+    m, n, k = mnk
+    a, b, c = oracle.make_inputs(m, n, k, seed=31)
+    a_rows, b_rows = (k if ta else m), (n if tb else k)           # contiguous extent of A and B as stored
+    pad = lambda x: (x + 3) // 4 * 4 + (8 if padded else 0)
+    tensor = kernel.startswith("tc")
+    sa, lda = stored(a, m, k, ta, pad(a_rows) if (tensor or padded) else 0)
+    sb, ldb = stored(b, k, n, tb, pad(b_rows) if (tensor or padded) else 0)
+    r = runner_of(kernel)
+    d = run(r, sa, sb, c, m, n, k, 1.25, 0.5, force=TENSOR if tensor else SIMT, lda=lda, ldb=ldb)
+    assert r.info("last_variant") == (TENSOR if tensor else SIMT)
+    check(d, a, b, c, m, n, k, 1.25, 0.5)      # against the NN oracle on the logical matrices
+    if tensor:                                  # the FFMA kernel inside the same cubin follows the same flags
+        d2 = run(r, sa, sb, c, m, n, k, 1.25, 0.5, force=SIMT, lda=lda, ldb=ldb)
+        check(d2, a, b, c, m, n, k, 1.25, 0.5)
+
+
+def test_transposed_leading_dimension_checks(runner_of):
+    from runner import api
+    m, n, k = 64, 96, 128
+    a, b, c = oracle.make_inputs(m, n, k, seed=1)
+    r = runner_of("tc2_256x256x32_s3_tt")
+    with pytest.raises(api.SgemmError) as e:       # A is stored K x M: lda must cover K, not M
+        r.run_host(a, b, None, np.zeros(m * n, np.float32), m, n, k, lda=m, ldb=n)
+    assert e.value.code == -1
+    with pytest.raises(api.SgemmError) as e:       # B is stored N x K: ldb must cover N
+        r.run_host(a, b, None, np.zeros(m * n, np.float32), m, n, k, lda=k, ldb=64)
+    assert e.value.code == -1
 
 
 # ------------------------------------------------------------------------------------ pipelined host path
