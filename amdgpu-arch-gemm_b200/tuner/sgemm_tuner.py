@@ -40,7 +40,9 @@ SUPPORTED_DEPTH_K = [16, 32, 64]
 SUPPORTED_STAGES = [2, 3, 4, 5, 6, 7]
 SUPPORTED_SPLIT = ["prepass", "inkernel"]   # where the 3xTF32 lo terms are made
 # FFMA variant: (thread grid, per-thread tile, k per stage)
-SUPPORTED_SIMT = [((16, 16), (8, 8), 16), ((16, 16), (8, 8), 8), ((16, 8), (8, 8), 16), ((16, 16), (4, 4), 16)]
+SUPPORTED_SIMT = [((16, 16), (8, 8), 16), ((16, 16), (8, 8), 8), ((16, 8), (8, 8), 16), ((8, 16), (8, 8), 16),
+                  ((16, 16), (8, 4), 16), ((16, 16), (4, 8), 16), ((32, 8), (4, 8), 16), ((16, 16), (4, 4), 16),
+                  ((16, 8), (8, 8), 8), ((32, 16), (4, 8), 16)]
 SUPPORTED_WGM = [1, 4, 8, 16]
 SUPPORTED_PLR = [0, 1]
 VERBOSE = False
@@ -55,11 +57,12 @@ def kernel_arguments():
     return [FunctionArgument(t, n, None, s) for t, n, s in names]
 
 
-def candidates(include_simt: bool = True):
+def candidates(include_simt: bool = True, include_tensor: bool = True):
     """Yield (key, config factory, optimisation factory) for every point of the search space."""
     F = DataType.FP32
-    for cluster, bn, dk, stages, split, wgm in product(SUPPORTED_CLUSTERS, SUPPORTED_TILE_N, SUPPORTED_DEPTH_K,
-                                                       SUPPORTED_STAGES, SUPPORTED_SPLIT, SUPPORTED_WGM):
+    tensor_space = product(SUPPORTED_CLUSTERS, SUPPORTED_TILE_N, SUPPORTED_DEPTH_K, SUPPORTED_STAGES, SUPPORTED_SPLIT,
+                           SUPPORTED_WGM) if include_tensor else ()
+    for cluster, bn, dk, stages, split, wgm in tensor_space:
         key = f"tensor c{cluster[0]}x{cluster[1]} n{bn} k{dk} s{stages} {split} wgm{wgm}"
         yield (key,
                lambda cluster=cluster, bn=bn, dk=dk, stages=stages, split=split: GemmSolutionConfig(
@@ -91,13 +94,13 @@ def load_done(path: Path):
 
 
 def tune(m: int, n: int, k: int, bench: str, output_folder: str, include_simt: bool = True, allow_ragged: bool = False,
-         limit: int | None = None):
+         limit: int | None = None, include_tensor: bool = True):
     os.makedirs(output_folder, exist_ok=True)
     log_path = Path(output_folder) / "tuner_results.jsonl"
     done = load_done(log_path)
     best = None
     measured = 0
-    for key, make_config, make_opt in candidates(include_simt):
+    for key, make_config, make_opt in candidates(include_simt, include_tensor):
         problem_key = f"{m}x{n}x{k} {key}"
         if problem_key in done:
             rec = done[problem_key]
@@ -158,8 +161,9 @@ if __name__ == "__main__":
     ap.add_argument("--bench", dest="bench", type=str, required=True, action="store")
     ap.add_argument("--output-folder", dest="output_folder", type=str, required=True, action="store")
     ap.add_argument("--no-simt", action="store_true", help="search the tensor-core variant only")
+    ap.add_argument("--no-tensor", action="store_true", help="search the FFMA variant only")
     ap.add_argument("--allow-ragged", action="store_true", help="keep tilings that do not divide M, N, K")
     ap.add_argument("--limit", type=int, default=None, help="stop after this many new measurements")
     args = ap.parse_args()
     tune(args.m, args.n, args.k, args.bench, args.output_folder, include_simt=not args.no_simt,
-         allow_ragged=args.allow_ragged, limit=args.limit)
+         allow_ragged=args.allow_ragged, limit=args.limit, include_tensor=not args.no_tensor)
