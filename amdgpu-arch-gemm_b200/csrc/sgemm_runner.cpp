@@ -103,7 +103,7 @@ struct sgemm_handle {
     CUcontext ctx = nullptr;
     CUmodule module = nullptr;
     CUfunction fn_main = nullptr, fn_simt = nullptr, fn_split_lo = nullptr, fn_pack_a = nullptr,
-               fn_reduce = nullptr, fn_fill = nullptr, fn_tile_map = nullptr;
+               fn_reduce = nullptr, fn_fill = nullptr, fn_tile_map = nullptr, fn_wait_selftest = nullptr;
     int sm_count = 0;
     uint32_t tile_m = 0, tile_n = 0;
     CUdeviceptr status = 0;
@@ -660,9 +660,10 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
         {&h->fn_reduce, "sgemm_splitk_reduce", true},
         {&h->fn_fill, "sgemm_fill_uniform", true},
         {&h->fn_tile_map, "sgemm_tile_map", true},
+        {&h->fn_wait_selftest, "sgemm_wait_selftest", cfg.variant == kVariantTensor},
     };
     for (const Want &w : wants) {
-        if (!w.required && !w.name[0]) continue;
+        if (!w.required) continue;   // entry points that only one variant's cubin contains stay NULL in the other's handle
         if ((r = d.cuModuleGetFunction_(w.f, h->module, w.name)) != CUDA_SUCCESS) {
             fail(h, SGEMM_ERR_MODULE, "entry point '%s' not found in '%s': %s", w.name, cubin_path, cu_text(r).c_str());
             return bail(SGEMM_ERR_MODULE);
@@ -866,6 +867,17 @@ SGEMM_API int sgemm_last_status(sgemm_handle *h, uint32_t status[8]) {
                     status[1], status[2], status[3], status[4], status[5]);
     }
     return SGEMM_OK;
+}
+
+SGEMM_API int sgemm_wait_selftest(sgemm_handle *h, uint32_t timeout_ms, uint32_t tag) {
+    if (!h || timeout_ms == 0 || timeout_ms > 1000) return SGEMM_ERR_INVALID_ARGUMENT;
+    if (!h->fn_wait_selftest)
+        return fail(h, SGEMM_ERR_UNSUPPORTED, "the loaded cubin has no tensor-core kernel, hence no bounded waits to test");
+    CtxGuard guard(h);
+    uint32_t *status_ptr = reinterpret_cast<uint32_t *>(h->status);
+    uint64_t timeout_ns = (uint64_t)timeout_ms * 1000000ull;
+    void *params[] = {&status_ptr, &timeout_ns, &tag};
+    return launch(h, h->fn_wait_selftest, 1, 1, 1, 64, 1, 0, nullptr, params);
 }
 
 SGEMM_API int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value) {

@@ -220,6 +220,7 @@ __device__ __forceinline__ void tc_tmem_ld_wait() { asm volatile("tcgen05.wait::
 struct TcWait {
     volatile uint32_t *abort_flag;  // shared memory, CTA-wide
     uint32_t *status;               // global memory, SGEMM_STATUS_WORDS words
+    uint64_t timeout_ns;            // how long one wait may go without the barrier completing
 };
 
 __device__ __noinline__ bool tc_wait_slow(const TcWait &w, uint32_t bar, uint32_t parity, uint32_t tag,
@@ -230,7 +231,7 @@ __device__ __noinline__ bool tc_wait_slow(const TcWait &w, uint32_t bar, uint32_
         if (tc_mbar_try_wait(bar, parity)) return true;
         if ((++spins & 31u) == 0u) {
             if (*w.abort_flag) return false;
-            if (tc_globaltimer() - t0 > TC_TIMEOUT_NS) {
+            if (tc_globaltimer() - t0 > w.timeout_ns) {
                 *w.abort_flag = 1u;
                 if (atomicCAS(w.status, SGEMM_STATUS_OK, SGEMM_STATUS_TIMEOUT) == SGEMM_STATUS_OK) {
                     w.status[1] = tag;
@@ -300,7 +301,7 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
     static_assert(24 * TC_STAGES + 32 + 8 <= 256, "barrier block size");
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const TcWait waiter{abort_flag, status};
+    const TcWait waiter{abort_flag, status, TC_TIMEOUT_NS};
 #if TC_CTA_GROUP == 2
     uint32_t cta_rank;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cta_rank));
@@ -669,4 +670,27 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                      ::"r"(tmem_base), "r"((uint32_t)TC_TMEM_COLS) : "memory");
 #endif
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Self-test of the bounded wait: one CTA initialises an mbarrier that nothing will ever arrive on and
+// waits on it with the kernel's own wait routine and a short limit.  The wait must run out, record the
+// status words and return, the kernel must end normally and the context must stay usable — this is the
+// failure path of generated_gemm exercised without a hung pipeline behind it.
+// ---------------------------------------------------------------------------------------------
+extern "C" __global__ void sgemm_wait_selftest(uint32_t *status, uint64_t timeout_ns, uint32_t tag) {
+    __shared__ __align__(8) uint64_t barrier_storage;
+    __shared__ uint32_t abort_flag;
+    sgemm_grid_dependency_wait();
+    if (threadIdx.x == 0) {
+        tc_mbar_init(tc_smem_u32(&barrier_storage), 1);
+        abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const TcWait waiter{&abort_flag, status, timeout_ns};
+    // every thread waits; the first whose limit runs out reports, the others leave through the abort flag
+    const bool completed = tc_wait(waiter, tc_smem_u32(&barrier_storage), 0u, tag, 0u, threadIdx.x);
+    if (completed && threadIdx.x == 0) status[6] = 0xBAD0BAD0u;   // cannot happen: nobody arrives
+    __syncthreads();
 }

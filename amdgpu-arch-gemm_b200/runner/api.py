@@ -58,6 +58,7 @@ ABI = {
     "sgemm_run_host": (ctypes.c_int, _GEMM_ARGS),
     "sgemm_bench": (ctypes.c_int, _GEMM_ARGS + [_u32, _u32, _vp, ctypes.POINTER(ctypes.c_float)]),
     "sgemm_last_status": (ctypes.c_int, [_vp, ctypes.POINTER(_u32 * 8)]),
+    "sgemm_wait_selftest": (ctypes.c_int, [_vp, _u32, _u32]),
     "sgemm_set_option": (ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.c_int64]),
     "sgemm_get_info": (ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.POINTER(ctypes.c_int64)]),
     "sgemm_workspace_bytes": (ctypes.c_int, [_vp, _u32, _u32, _u32, _u32, _u32, ctypes.POINTER(ctypes.c_size_t)]),
@@ -202,6 +203,10 @@ class SgemmRunner:
         st = (_u32 * 8)()
         self._check(self._L.sgemm_last_status(self._h, ctypes.byref(st)), "sgemm_last_status")
         return list(st)
+
+    def wait_selftest(self, timeout_ms: int = 20, tag: int = 0x7E57):
+        """Launch the bounded-wait self-test kernel (see ``sgemm_wait_selftest``); read the outcome with ``last_status``."""
+        self._check(self._L.sgemm_wait_selftest(self._h, timeout_ms, tag), "sgemm_wait_selftest")
 
     # ------------------------------------------------------------------------- options and facts
     def set_option(self, key: str, value: int):

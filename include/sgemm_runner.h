@@ -128,6 +128,13 @@ int sgemm_bench(sgemm_handle *h, const float *dA, const float *dB, const float *
  * no counterpart (it ignores every hipError_t, runner/generator_runner.cpp:194-322). */
 int sgemm_last_status(sgemm_handle *h, uint32_t status[8]);
 
+/* Failure-detection self-test (no counterpart in the reference, which never inspects an error): launches a
+ * one-block kernel that waits, with the GEMM kernel's own bounded-wait routine and a limit of `timeout_ms`
+ * (1..1000), on a barrier nothing arrives on.  The wait runs out, the kernel records the status words and ends
+ * normally; the following sgemm_last_status must return SGEMM_ERR_DEVICE_STATUS with status[1] == tag, and the
+ * handle must keep working.  Tensor-variant cubins only. */
+int sgemm_wait_selftest(sgemm_handle *h, uint32_t timeout_ms, uint32_t tag);
+
 /* Options: "force_variant" 0 auto, 1 tensor, 2 simt;  "split_k" 0 auto, n >= 1 fixed;
  * "simt_below_flops" problems with 2*M*N*K below this use the SIMT kernel (auto mode);
  * "fuse_split_k" 1 lets the tensor kernel sum its split-K partials itself (arrival counters, the last warp of a

@@ -401,6 +401,33 @@ def test_lent_workspace(runner_of):
         r.dev_free(ws)
 
 
+# ------------------------------------------------------------------------------------ failure detection
+def test_bounded_wait_runs_out_reports_and_leaves_the_context_usable(built):
+    # A wait whose barrier nothing completes must give up after its limit, record the status words and return:
+    # the host sees SGEMM_ERR_DEVICE_STATUS with the tag, the status is cleared by the read, and the same handle
+    # computes correctly afterwards.  (The waiting kernel is a one-block self-test around the GEMM kernel's own
+    # wait routine; no pipeline is left hanging behind it.)
+    from runner import api
+    cubin, toml = built.ensure("tc2_256x256x32_s3")
+    with api.SgemmRunner(cubin, toml, 0) as r:
+        assert r.last_status()[0] == 0
+        r.wait_selftest(timeout_ms=20, tag=0x51DE)
+        with pytest.raises(api.SgemmError) as e:
+            r.last_status()
+        assert e.value.code == -8 and "0x51de" in str(e.value)
+        assert r.last_status()[0] == 0                       # cleared by the failing read
+        m, n, k = 300, 260, 520
+        a, b, c = oracle.make_inputs(m, n, k, seed=5, lda=300, ldb=520)
+        d = run(r, a, b, c, m, n, k, 1.0, 1.0, force=TENSOR, split_k=2)
+        check(d, a, b, c, m, n, k, 1.0, 1.0)
+        assert r.last_status()[0] == 0
+    cubin, toml = built.ensure("simt_128x128x16")
+    with api.SgemmRunner(cubin, toml, 0) as r:               # an FFMA-only cubin has no bounded waits
+        with pytest.raises(api.SgemmError) as e:
+            r.wait_selftest()
+        assert e.value.code == -6
+
+
 # ------------------------------------------------------------------------------ helpers on the device
 def test_device_fill_equals_host_generator(runner_of):
     r = runner_of("simt_64x64x16")
