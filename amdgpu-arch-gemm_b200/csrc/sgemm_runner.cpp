@@ -122,6 +122,8 @@ struct sgemm_handle {
     bool reuse_a_lo = false;    // set by the pipelined host path: A's lo copy of the previous chunk call is still valid
     // options and facts
     int64_t force_variant = 0, split_k_opt = 0, simt_below_flops = (int64_t)1 << 27;
+    bool wave_sync = true;      // tensor kernel: soft alignment of the persistent CTAs at tile boundaries
+    uint32_t wave_sync_base = 0;   // value of the alignment counter before the next launch (it only ever counts up)
     bool pipeline_host = true;  // sgemm_run_host overlaps uploads, GEMM and downloads over column chunks
     bool pdl = true;            // launch with programmatic stream serialisation (see launch())
     bool fuse_split_k = false;  // measured slower than the separate reduction kernel: off unless asked for
@@ -477,8 +479,12 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
             else if ((rc = encode_map(h, 3, lo_b, k, n, (uint64_t)ldb * 4, kspan, bn, ksw, &mb_lo))) return rc;
         }
         uint32_t *counters = p.fused_reduce ? reinterpret_cast<uint32_t *>(h->counters) : nullptr;
+        // the alignment counter is the word behind the split-K counters; every launch unit adds one per tile
+        uint32_t *wave_sync = h->wave_sync ? reinterpret_cast<uint32_t *>(h->counters) + kCounterWords : nullptr;
+        uint32_t wave_base = h->wave_sync_base;
+        if (wave_sync) h->wave_sync_base += p.tiles_m * p.tiles_n * p.split_k;
         void *params[] = {&dA, &dB, &dC, &dD, &m, &n, &k, &lda, &ldb, &ldc, &ldd, &alpha, &beta, &nwx, &nwy,
-                          &partial, &status_ptr, &split, &counters,
+                          &partial, &status_ptr, &split, &counters, &wave_sync, &wave_base,
                           const_cast<CUtensorMap *>(ma_hi), const_cast<CUtensorMap *>(ma_lo),
                           const_cast<CUtensorMap *>(mb_hi), const_cast<CUtensorMap *>(mb_lo)};
         rc = launch_main(h, h->fn_main, p.grid_x, 1, (uint32_t)h->cfg.num_threads,
@@ -488,9 +494,10 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
         const bool own = h->cfg.variant == kVariantSimt;
         CUfunction f = own ? h->fn_main : h->fn_simt;
         const uint32_t threads = own ? (uint32_t)h->cfg.num_threads : (uint32_t)h->cfg.fallback_threads;
-        uint32_t *counters = nullptr;
+        uint32_t *counters = nullptr, *wave_sync = nullptr;
+        uint32_t wave_base = 0;
         void *params[] = {&dA, &dB, &dC, &dD, &m, &n, &k, &lda, &ldb, &ldc, &ldd, &alpha, &beta, &nwx, &nwy,
-                          &partial, &status_ptr, &split, &counters};
+                          &partial, &status_ptr, &split, &counters, &wave_sync, &wave_base};
         rc = launch_main(h, f, p.grid_x, p.split_k, threads, 0, stream, params);
         if (rc) return rc;
     }
@@ -676,8 +683,8 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
     }
     if ((r = d.cuMemAlloc_(&h->status, kStatusWords * 4)) != CUDA_SUCCESS ||
         (r = d.cuMemsetD8_(h->status, 0, kStatusWords * 4)) != CUDA_SUCCESS ||
-        (r = d.cuMemAlloc_(&h->counters, (size_t)kCounterWords * 4)) != CUDA_SUCCESS ||
-        (r = d.cuMemsetD8_(h->counters, 0, (size_t)kCounterWords * 4)) != CUDA_SUCCESS) {
+        (r = d.cuMemAlloc_(&h->counters, (size_t)(kCounterWords + 64) * 4)) != CUDA_SUCCESS ||
+        (r = d.cuMemsetD8_(h->counters, 0, (size_t)(kCounterWords + 64) * 4)) != CUDA_SUCCESS) {
         fail(h, SGEMM_ERR_CUDA, "cannot allocate the status buffer: %s", cu_text(r).c_str());
         return bail(SGEMM_ERR_CUDA);
     }
@@ -861,8 +868,9 @@ SGEMM_API int sgemm_last_status(sgemm_handle *h, uint32_t status[8]) {
     CU_CHECK(h, d.cuMemcpyDtoH_(status, h->status, kStatusWords * 4));
     if (status[0] != 0) {
         CU_CHECK(h, d.cuMemsetD8_(h->status, 0, kStatusWords * 4));
-        // a kernel that gave up may have left split-K arrival counters half-counted
-        CU_CHECK(h, d.cuMemsetD8_(h->counters, 0, (size_t)kCounterWords * 4));
+        // a kernel that gave up may have left split-K arrival counters and the alignment counter half-counted
+        CU_CHECK(h, d.cuMemsetD8_(h->counters, 0, (size_t)(kCounterWords + 64) * 4));
+        h->wave_sync_base = 0;
         return fail(h, SGEMM_ERR_DEVICE_STATUS, "kernel gave up waiting: tag 0x%x tile %u k-block %u block %u parity %u",
                     status[1], status[2], status[3], status[4], status[5]);
     }
@@ -889,6 +897,7 @@ SGEMM_API int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value) 
     else if (k == "fuse_split_k" && (value == 0 || value == 1)) h->fuse_split_k = value != 0;
     else if (k == "pdl" && (value == 0 || value == 1)) h->pdl = value != 0;
     else if (k == "pipeline_host" && (value == 0 || value == 1)) h->pipeline_host = value != 0;
+    else if (k == "wave_sync" && (value == 0 || value == 1)) h->wave_sync = value != 0;
     else if (k == "profile" && (value == 0 || value == 1)) { h->profile = value != 0; h->prof_used = 0; }
     else return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "unknown option or value out of range: %s = %lld", key, (long long)value);
     return SGEMM_OK;

@@ -71,6 +71,9 @@
 #ifndef TC_TIMEOUT_NS
 #define TC_TIMEOUT_NS 2000000000ull
 #endif
+#ifndef TC_WAVE_SYNC_NS
+#define TC_WAVE_SYNC_NS 100000ull   // longest a unit waits for the others at a tile boundary (soft, see the producer)
+#endif
 
 #ifndef TC_CTA_GROUP
 #define TC_CTA_GROUP 1
@@ -283,6 +286,7 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
                float alpha, float beta, int32_t num_wg_x, int32_t num_wg_y,
                float *ws, uint32_t *status, uint32_t split_k, uint32_t *counters,
+               uint32_t *wave_sync, uint32_t wave_sync_base,
                const __grid_constant__ TcTensorMap map_a_hi, const __grid_constant__ TcTensorMap map_a_lo,
                const __grid_constant__ TcTensorMap map_b_hi, const __grid_constant__ TcTensorMap map_b_lo) {
     (void)a; (void)b; (void)lda; (void)ldb;
@@ -364,7 +368,23 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
             bool alive = true;
             // in a CTA pair every load reports to the leader's "full" barrier
             const uint32_t full_base = TC_CTA_GROUP == 2 ? tc_map_to_cta(bar_full, 0u) : bar_full;
-            for (uint32_t tile = unit0; alive && tile < num_tiles; tile += unit_stride) {
+            uint32_t round = 0;
+            for (uint32_t tile = unit0; alive && tile < num_tiles; tile += unit_stride, ++round) {
+                // Soft wave alignment: launch units that run side by side share operand panels through L2 only
+                // while they stream K at about the same place, and units that fall behind fall further behind.
+                // At every tile boundary the leader counts itself in and waits — for TC_WAVE_SYNC_NS at most, then
+                // it simply goes on — until all units of this round have begun it.  Never an error, never a deadlock:
+                // a unit that is not resident only costs the others the bounded wait.
+                if (wave_sync != nullptr && cta_rank == 0) {
+                    atomicAdd(wave_sync, 1u);
+                    if (round > 0) {
+                        const uint32_t target = wave_sync_base + min(num_tiles, (round + 1u) * unit_stride);
+                        const uint64_t t0 = tc_globaltimer();
+                        while ((int32_t)(*reinterpret_cast<volatile uint32_t *>(wave_sync) - target) < 0 &&
+                               tc_globaltimer() - t0 < TC_WAVE_SYNC_NS) {
+                        }
+                    }
+                }
                 const uint32_t z = tile / tiles_mn;
                 uint32_t tx, ty;
                 sgemm_tile_raster(tile - z * tiles_mn, (uint32_t)num_wg_x, (uint32_t)num_wg_y, OPT_WGM, tx, ty);

@@ -141,6 +141,8 @@ int sgemm_wait_selftest(sgemm_handle *h, uint32_t timeout_ms, uint32_t tag);
  * slice reduces), 0 (default) runs the separate reduction kernel — same bits either way, the separate kernel is faster;
  * "pdl" 1 (default) launches every kernel with programmatic stream serialisation so that launch latency and per-CTA
  * set-up overlap with the tail of the previous kernel (all kernels wait on the grid dependency before touching memory);
+ * "wave_sync" 1 (default) lets the persistent CTAs of the tensor kernel wait briefly for each other at tile
+ * boundaries so that they keep sharing operand panels in L2 (a bounded, soft wait: performance only);
  * "pipeline_host" 1 (default) lets sgemm_run_host overlap transfers and compute over column chunks;
  * "profile" 1 brackets every main-GEMM-kernel launch with an event pair (read with "profile_main_ns"). */
 int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value);
