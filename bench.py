@@ -39,8 +39,8 @@ UNIT = "TFLOP/s"
 
 # DRAM bytes one launch of the dominant kernel moved in an ncu capture (dram__bytes_read.sum +
 # dram__bytes_write.sum), keyed by kernel name, for the 8192^3 workload.
-# Source: profiles/bench_default_8192cubed_launches_and_dram.md (mean of two launches).
-NCU_TRAFFIC_BYTES = {"tc2_256x256x32_s3": 8.81e9}
+# Source: profiles/bench_default_8192cubed_launches_and_dram.md (three launches, identical to three digits).
+NCU_TRAFFIC_BYTES = {"tc2_256x256x32_s3": 4.83e9}
 
 
 def measured_peaks():
