@@ -98,3 +98,13 @@ def test_shard_columns_cover_n_in_whole_tiles():
         assert max(widths) - min(w for w in widths) <= tile or n < world * tile
     with pytest.raises(ValueError):
         shard_columns(10, 2, 2)
+
+
+def test_kernel_recommendation_names_registered_kernels(built):
+    cases = {(8192, 8192, 8192): "tc2_256x256x32_s3", (32, 32, 32): "simt_128x128x16", (4096, 128, 16384): "tci_128x128x32_s3",
+             (8192, 8192, 256): "tc2i_256x256x32_s3", (32768, 4096, 8192): "tc2_256x256x32_s3"}
+    for shape, want in cases.items():
+        got = built.recommend(*shape)
+        assert got in built.REGISTRY and got == want, (shape, got)
+    for shape in [(1024, 1024, 1024), (300, 5000, 700), (1, 1, 1), (65536, 64, 64)]:
+        assert built.recommend(*shape) in built.REGISTRY
