@@ -8,7 +8,8 @@
 // std::random_device, beta comes from SGEMM_BETA (default 1, the reference's hard-coded value), and the
 // time of the single CPU validation run is reported as measured rather than divided by `runs`.
 //
-// Extra diagnostics go to stderr so the stdout contract stays intact.
+// Extra diagnostics go to stderr so the stdout contract stays intact; with SGEMM_JSON=<path> the measured block is
+// also written to that file as one JSON object (shape, variant, split-K, ms, TFLOP/s, GiB/s figure, mismatches).
 #include "sgemm_runner.h"
 
 #include <chrono>
@@ -155,6 +156,18 @@ int main(int argc, char **argv) {
             }
         }
         std::cout << "# of mismatches: " << mismatches << "/" << nc << '\n';
+    }
+    if (const char *json_path = std::getenv("SGEMM_JSON")) {
+        if (FILE *f = std::fopen(json_path, "w")) {
+            std::fprintf(f, "{\"m\": %u, \"n\": %u, \"k\": %u, \"alpha\": %g, \"beta\": %g, \"seed\": %llu, \"warmup\": %u, "
+                            "\"runs\": %u, \"variant\": \"%s\", \"split_k\": %lld, \"ms\": %.6f, \"tflops\": %.4f, "
+                            "\"gib_per_s\": %.3f, \"validated\": %s, \"mismatches\": %zu}\n",
+                         m, n, k, alpha, beta, (unsigned long long)seed, warmup, runs, variant == 1 ? "tcgen05_3xtf32" : "simt_ffma",
+                         (long long)split, ms, gflops(m, n, k, ms) * 1e-3, mem_bw(m, n, k, ms), validate ? "true" : "false", mismatches);
+            std::fclose(f);
+        } else {
+            std::fprintf(stderr, "GeneratorRunner: cannot write %s\n", json_path);
+        }
     }
     sgemm_dev_free(h, da);
     sgemm_dev_free(h, db);
