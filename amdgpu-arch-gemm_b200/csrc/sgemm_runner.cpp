@@ -75,7 +75,7 @@ Driver &driver() {
 thread_local std::string g_open_error;
 
 constexpr int kStatusWords = 8;
-constexpr uint32_t kCounterWords = 1u << 18;   // 1 MiB of split-K arrival counters per handle
+constexpr uint32_t kCounterWords = 64;
 constexpr int kVariantSimt = 0, kVariantTensor = 1;
 
 struct TensorMapKey {
@@ -96,6 +96,16 @@ struct CachedMap {
 
 }  // namespace
 
+// What the host has to know about one tcgen05 kernel of the cubin.
+struct TensorKernel {
+    CUfunction fn = nullptr;
+    uint32_t tile_m = 0, tile_n = 0, bk = 0;   // tile of one launch unit, k per stage
+    uint32_t group = 1;                         // CTAs per launch unit (2 = CTA pair)
+    uint32_t threads = 0, smem = 0;
+    bool split_inkernel = false;                // lo tiles made in the kernel: no pre-pass, no lo copies
+    bool a_packed = false;                      // A is read from K-major packed copies made by a pre-pass
+};
+
 struct sgemm_handle {
     sgemm_config cfg{};
     int device = 0;
@@ -106,8 +116,9 @@ struct sgemm_handle {
                fn_reduce = nullptr, fn_fill = nullptr, fn_tile_map = nullptr, fn_wait_selftest = nullptr;
     int sm_count = 0;
     uint32_t tile_m = 0, tile_n = 0;
+    TensorKernel tk_main, tk_skinny;   // tk_skinny.fn == NULL: the cubin has no companion kernel
     CUdeviceptr status = 0;
-    CUdeviceptr counters = 0;   // split-K arrival counters of the tensor kernel, all zero between launches
+    CUdeviceptr counters = 0;   // device words shared by all launches of the handle: [0] = wave-alignment counter
     // workspace: owned (grow on demand) or lent
     CUdeviceptr ws_owned = 0;
     size_t ws_owned_bytes = 0;
@@ -122,11 +133,11 @@ struct sgemm_handle {
     bool reuse_a_lo = false;    // set by the pipelined host path: A's lo copy of the previous chunk call is still valid
     // options and facts
     int64_t force_variant = 0, split_k_opt = 0, simt_below_flops = (int64_t)1 << 27;
+    int64_t skinny_below_intensity = 200;   // flop per byte of A and B below which the companion kernel is used
     bool wave_sync = true;      // tensor kernel: soft alignment of the persistent CTAs at tile boundaries
     uint32_t wave_sync_base = 0;   // value of the alignment counter before the next launch (it only ever counts up)
     bool pipeline_host = true;  // sgemm_run_host overlaps uploads, GEMM and downloads over column chunks
     bool pdl = true;            // launch with programmatic stream serialisation (see launch())
-    bool fuse_split_k = false;  // measured slower than the separate reduction kernel: off unless asked for
     int64_t last_variant = 0, last_split_k = 1, last_grid = 0, launches = 0;
     CachedMap maps[4];
     // optional timing of the main GEMM kernel alone (events around it on the caller's stream)
@@ -189,7 +200,7 @@ struct Plan {
     uint64_t span_a = 0, span_b = 0;                                    // floats walked by the split pre-pass
     uint32_t ldt = 0;                                                   // K-major packed A: leading dimension
     size_t ws_bytes = 0;
-    bool fused_reduce = false;   // tensor kernel sums the split-K partials itself (arrival counters)
+    const TensorKernel *tk = nullptr;   // the tcgen05 kernel chosen (tensor variant only)
 };
 
 bool tensor_eligible(const sgemm_handle *h, const void *a, const void *b, uint32_t lda, uint32_t ldb) {
@@ -221,7 +232,14 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
               uint32_t ldb, Plan *p) {
     const bool eligible = tensor_eligible(h, a, b, lda, ldb);
     int variant;
-    if (h->force_variant == 1) {
+    const TensorKernel *tk = &h->tk_main;
+    if (h->force_variant == 3) {
+        if (!eligible || !h->tk_skinny.fn)
+            return fail(h, SGEMM_ERR_UNSUPPORTED, "companion tensor kernel forced but %s",
+                        h->tk_skinny.fn ? "the operands are not TMA-eligible" : "the cubin has none");
+        variant = kVariantTensor;
+        tk = &h->tk_skinny;
+    } else if (h->force_variant == 1) {
         if (!eligible)
             return fail(h, SGEMM_ERR_UNSUPPORTED,
                         "tensor variant forced but not usable: cubin variant %d, lda %u, ldb %u, bases %p %p "
@@ -233,34 +251,36 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
     } else {
         const double flops = 2.0 * m * n * k;
         variant = (eligible && flops >= (double)h->simt_below_flops) ? kVariantTensor : kVariantSimt;
+        // few flops per byte of A and B (a skinny M or N with a long K): the pre-pass, which reads both operands and
+        // writes and re-reads their lo copies, would cost as much as the GEMM; the companion kernel (small tiles,
+        // lo terms made in the kernel) has neither pre-pass nor copies
+        const double intensity = flops / (4.0 * ((double)m * k + (double)k * n));
+        if (variant == kVariantTensor && h->tk_skinny.fn && intensity < (double)h->skinny_below_intensity) tk = &h->tk_skinny;
     }
     p->variant = variant;
+    p->tk = variant == kVariantTensor ? tk : nullptr;
     size_t off = 0;
     if (variant == kVariantTensor) {
-        p->tiles_m = (m + h->tile_m - 1) / h->tile_m;
-        p->tiles_n = (n + h->tile_n - 1) / h->tile_n;
-        p->split_k = pick_split_k(h, p->tiles_m * p->tiles_n, k, (uint32_t)h->cfg.depth_k);
+        p->tiles_m = (m + tk->tile_m - 1) / tk->tile_m;
+        p->tiles_n = (n + tk->tile_n - 1) / tk->tile_n;
+        p->split_k = pick_split_k(h, p->tiles_m * p->tiles_n, k, tk->bk);
         // persistent grid: one CTA (or CTA pair) per SM (pair of SMs), never more launch units than tiles
         const uint64_t units = (uint64_t)p->tiles_m * p->tiles_n * p->split_k;
-        const uint32_t group = (uint32_t)std::max(1, h->cfg.wave_group[0]);
+        const uint32_t group = tk->group;
         p->grid_x = group * (uint32_t)std::min<uint64_t>(units, (uint64_t)std::max(1, h->sm_count / (int)group));
         // floats between the first and the last element of an operand as stored (op(B) is K x N: stored K x N with
         // pitch ldb, or, transposed, N x K with pitch ldb)
         p->span_b = h->cfg.trans_b ? (uint64_t)ldb * (k - 1) + n : (uint64_t)ldb * (n - 1) + k;
-        if (h->cfg.a_kmajor) {
+        if (tk->a_packed) {
             p->ldt = (uint32_t)round_up(k, 4);
             p->hi_a_off = off; off += round_up((size_t)p->ldt * m * 4, 256);
             p->lo_a_off = off; off += round_up((size_t)p->ldt * m * 4, 256);
             p->span_a = 0;
-        } else if (!h->cfg.split_inkernel) {
+        } else if (!tk->split_inkernel) {
             p->span_a = h->cfg.trans_a ? (uint64_t)lda * (m - 1) + k : (uint64_t)lda * (k - 1) + m;
             p->lo_a_off = off; off += round_up(p->span_a * 4, 256);
         }
-        if (!h->cfg.split_inkernel) { p->lo_b_off = off; off += round_up(p->span_b * 4, 256); }
-        // epilogue warps per CTA = (threads - TMA warp - MMA warp - transform warps) / 32
-        const uint32_t epi_warps = ((uint32_t)h->cfg.num_threads - 64u - (h->cfg.split_inkernel ? 128u : 0u)) / 32u;
-        p->fused_reduce = p->split_k > 1 && h->fuse_split_k &&
-                          (uint64_t)p->tiles_m * p->tiles_n * group * epi_warps <= kCounterWords;
+        if (!tk->split_inkernel) { p->lo_b_off = off; off += round_up(p->span_b * 4, 256); }
     } else {
         const bool own = h->cfg.variant == kVariantSimt;
         const uint32_t tm = own ? h->tile_m : (uint32_t)h->cfg.fallback_tile[0];
@@ -423,16 +443,17 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
     uint32_t *status_ptr = reinterpret_cast<uint32_t *>(status);
 
     if (p.variant == kVariantTensor) {
+        const TensorKernel &tk = *p.tk;
         float *lo_a = reinterpret_cast<float *>(ws + p.lo_a_off);
         float *lo_b = reinterpret_cast<float *>(ws + p.lo_b_off);
-        // a CTA pair (wave_group[0] = 2) stages half of the tile's columns of B per CTA
-        const uint32_t bk = (uint32_t)h->cfg.depth_k, bn = h->tile_n / (uint32_t)std::max(1, h->cfg.wave_group[0]);
+        // a CTA pair stages half of the tile's columns of B per CTA
+        const uint32_t bk = tk.bk, bn = tk.tile_n / tk.group;
         // K-major tiles: rows of min(bk, 32) floats, 128-byte swizzle (64-byte for bk = 16)
         const uint32_t kspan = std::min<uint32_t>(bk, 32);
         const CUtensorMapSwizzle ksw = kspan == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
         const CUtensorMap *ma_hi, *ma_lo, *mb_hi, *mb_lo;
         const uint32_t blocks = (uint32_t)h->sm_count * 4;
-        if (h->cfg.a_kmajor) {
+        if (tk.a_packed) {
             float *hi_t = reinterpret_cast<float *>(ws + p.hi_a_off);
             void *pp[] = {&dA, &lda, &m, &k, &hi_t, &lo_a, &p.ldt};
             if (!h->reuse_a_lo) {
@@ -446,7 +467,7 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
             if (rc) return rc;
             if ((rc = encode_map(h, 0, hi_t, k, m, (uint64_t)p.ldt * 4, kspan, 128, ksw, &ma_hi))) return rc;
             if ((rc = encode_map(h, 1, lo_a, k, m, (uint64_t)p.ldt * 4, kspan, 128, ksw, &ma_lo))) return rc;
-        } else if (h->cfg.split_inkernel) {
+        } else if (tk.split_inkernel) {
             // no pre-pass and no lo copies: the kernel's transform warps make the lo tiles; the lo map slots get the hi maps
             if (h->cfg.trans_a) rc = encode_map(h, 0, dA, k, m, (uint64_t)lda * 4, kspan, 128, ksw, &ma_hi);
             else rc = encode_map(h, 0, dA, m, k, (uint64_t)lda * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &ma_hi);
@@ -471,37 +492,35 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
         if (h->cfg.trans_b) {
             // B is stored N-contiguous: an MN-major operand, staged in 32-column chunks like the untransposed A
             if ((rc = encode_map(h, 2, dB, n, k, (uint64_t)ldb * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &mb_hi))) return rc;
-            if (h->cfg.split_inkernel) mb_lo = mb_hi;
+            if (tk.split_inkernel) mb_lo = mb_hi;
             else if ((rc = encode_map(h, 3, lo_b, n, k, (uint64_t)ldb * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &mb_lo))) return rc;
         } else {
             if ((rc = encode_map(h, 2, dB, k, n, (uint64_t)ldb * 4, kspan, bn, ksw, &mb_hi))) return rc;
-            if (h->cfg.split_inkernel) mb_lo = mb_hi;
+            if (tk.split_inkernel) mb_lo = mb_hi;
             else if ((rc = encode_map(h, 3, lo_b, k, n, (uint64_t)ldb * 4, kspan, bn, ksw, &mb_lo))) return rc;
         }
-        uint32_t *counters = p.fused_reduce ? reinterpret_cast<uint32_t *>(h->counters) : nullptr;
-        // the alignment counter is the word behind the split-K counters; every launch unit adds one per tile
-        uint32_t *wave_sync = h->wave_sync ? reinterpret_cast<uint32_t *>(h->counters) + kCounterWords : nullptr;
+        // the alignment counter only ever counts up: every launch unit adds one per tile
+        uint32_t *wave_sync = h->wave_sync ? reinterpret_cast<uint32_t *>(h->counters) : nullptr;
         uint32_t wave_base = h->wave_sync_base;
         if (wave_sync) h->wave_sync_base += p.tiles_m * p.tiles_n * p.split_k;
         void *params[] = {&dA, &dB, &dC, &dD, &m, &n, &k, &lda, &ldb, &ldc, &ldd, &alpha, &beta, &nwx, &nwy,
-                          &partial, &status_ptr, &split, &counters, &wave_sync, &wave_base,
+                          &partial, &status_ptr, &split, &wave_sync, &wave_base,
                           const_cast<CUtensorMap *>(ma_hi), const_cast<CUtensorMap *>(ma_lo),
                           const_cast<CUtensorMap *>(mb_hi), const_cast<CUtensorMap *>(mb_lo)};
-        rc = launch_main(h, h->fn_main, p.grid_x, 1, (uint32_t)h->cfg.num_threads,
-                         (uint32_t)h->cfg.dynamic_smem_bytes, stream, params);
+        rc = launch_main(h, tk.fn, p.grid_x, 1, tk.threads, tk.smem, stream, params);
         if (rc) return rc;
     } else {
         const bool own = h->cfg.variant == kVariantSimt;
         CUfunction f = own ? h->fn_main : h->fn_simt;
         const uint32_t threads = own ? (uint32_t)h->cfg.num_threads : (uint32_t)h->cfg.fallback_threads;
-        uint32_t *counters = nullptr, *wave_sync = nullptr;
+        uint32_t *wave_sync = nullptr;
         uint32_t wave_base = 0;
         void *params[] = {&dA, &dB, &dC, &dD, &m, &n, &k, &lda, &ldb, &ldc, &ldd, &alpha, &beta, &nwx, &nwy,
-                          &partial, &status_ptr, &split, &counters, &wave_sync, &wave_base};
+                          &partial, &status_ptr, &split, &wave_sync, &wave_base};
         rc = launch_main(h, f, p.grid_x, p.split_k, threads, 0, stream, params);
         if (rc) return rc;
     }
-    if (p.split_k > 1 && !p.fused_reduce) {
+    if (p.split_k > 1) {
         const float *wsp = partial;
         void *params[] = {&wsp, &dC, &dD, &m, &n, &ldc, &ldd, &alpha, &beta, &split};
         // one thread per four rows on the kernel's vector path (M a multiple of 4), per element otherwise
@@ -510,7 +529,7 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
         rc = launch(h, h->fn_reduce, blocks, 1, 1, 256, 1, 0, stream, params);
         if (rc) return rc;
     }
-    h->last_variant = p.variant == kVariantTensor ? 1 : 2;
+    h->last_variant = p.variant != kVariantTensor ? 2 : (p.tk == &h->tk_skinny ? 3 : 1);
     h->last_split_k = p.split_k;
     h->last_grid = p.grid_x;
     return SGEMM_OK;
@@ -561,6 +580,12 @@ int config_from_toml(const char *path, sgemm_config *c, std::string *err) {
     if (t.get_int_array("fallback_tile", &fb) && fb.size() == 3)
         for (int i = 0; i < 3; ++i) c->fallback_tile[i] = (int32_t)fb[i];
     c->fallback_threads = t.get_int("fallback_threads", &v) ? (int32_t)v : 0;
+    std::vector<int64_t> sk;
+    if (t.get_int_array("skinny_tile", &sk) && sk.size() == 3)
+        for (int i = 0; i < 3; ++i) c->skinny_tile[i] = (int32_t)sk[i];
+    c->skinny_threads = t.get_int("skinny_threads", &v) ? (int32_t)v : 0;
+    c->skinny_smem_bytes = t.get_int("skinny_smem_bytes", &v) ? (int32_t)v : 0;
+    std::snprintf(c->skinny_entry, sizeof c->skinny_entry, "%s", t.get_string("skinny_entry", &s) ? s.c_str() : "");
     std::snprintf(c->entry, sizeof c->entry, "%s", t.get_string("entry", &s) ? s.c_str() : "generated_gemm");
     std::snprintf(c->fallback_entry, sizeof c->fallback_entry, "%s", t.get_string("fallback_entry", &s) ? s.c_str() : "");
     if (c->variant == kVariantTensor && (c->fallback_threads <= 0 || c->fallback_tile[0] <= 0 || !c->fallback_entry[0])) {
@@ -676,6 +701,23 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
             return bail(SGEMM_ERR_MODULE);
         }
     }
+    h->tk_main.fn = h->fn_main;
+    h->tk_main.tile_m = h->tile_m; h->tk_main.tile_n = h->tile_n; h->tk_main.bk = (uint32_t)cfg.depth_k;
+    h->tk_main.group = (uint32_t)std::max(1, cfg.wave_group[0]);
+    h->tk_main.threads = (uint32_t)cfg.num_threads; h->tk_main.smem = (uint32_t)cfg.dynamic_smem_bytes;
+    h->tk_main.split_inkernel = cfg.split_inkernel != 0; h->tk_main.a_packed = cfg.a_kmajor != 0;
+    if (cfg.variant == kVariantTensor && cfg.skinny_entry[0] && cfg.skinny_threads > 0 && cfg.skinny_tile[0] > 0) {
+        // companion kernel for low-intensity shapes: one CTA per 128-row tile, lo tiles made in the kernel
+        if ((r = d.cuModuleGetFunction_(&h->tk_skinny.fn, h->module, cfg.skinny_entry)) != CUDA_SUCCESS ||
+            (r = d.cuFuncSetAttribute_(h->tk_skinny.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, cfg.skinny_smem_bytes)) != CUDA_SUCCESS) {
+            fail(h, SGEMM_ERR_MODULE, "companion entry point '%s' unusable in '%s': %s", cfg.skinny_entry, cubin_path, cu_text(r).c_str());
+            return bail(SGEMM_ERR_MODULE);
+        }
+        h->tk_skinny.tile_m = (uint32_t)cfg.skinny_tile[0]; h->tk_skinny.tile_n = (uint32_t)cfg.skinny_tile[1];
+        h->tk_skinny.bk = (uint32_t)cfg.skinny_tile[2];
+        h->tk_skinny.group = 1; h->tk_skinny.threads = (uint32_t)cfg.skinny_threads; h->tk_skinny.smem = (uint32_t)cfg.skinny_smem_bytes;
+        h->tk_skinny.split_inkernel = true; h->tk_skinny.a_packed = false;
+    }
     if (cfg.dynamic_smem_bytes > 0 &&
         (r = d.cuFuncSetAttribute_(h->fn_main, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, cfg.dynamic_smem_bytes)) != CUDA_SUCCESS) {
         fail(h, SGEMM_ERR_CUDA, "cannot opt in to %d bytes of dynamic shared memory: %s", cfg.dynamic_smem_bytes, cu_text(r).c_str());
@@ -683,8 +725,8 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
     }
     if ((r = d.cuMemAlloc_(&h->status, kStatusWords * 4)) != CUDA_SUCCESS ||
         (r = d.cuMemsetD8_(h->status, 0, kStatusWords * 4)) != CUDA_SUCCESS ||
-        (r = d.cuMemAlloc_(&h->counters, (size_t)(kCounterWords + 64) * 4)) != CUDA_SUCCESS ||
-        (r = d.cuMemsetD8_(h->counters, 0, (size_t)(kCounterWords + 64) * 4)) != CUDA_SUCCESS) {
+        (r = d.cuMemAlloc_(&h->counters, (size_t)kCounterWords * 4)) != CUDA_SUCCESS ||
+        (r = d.cuMemsetD8_(h->counters, 0, (size_t)kCounterWords * 4)) != CUDA_SUCCESS) {
         fail(h, SGEMM_ERR_CUDA, "cannot allocate the status buffer: %s", cu_text(r).c_str());
         return bail(SGEMM_ERR_CUDA);
     }
@@ -779,7 +821,7 @@ SGEMM_API int sgemm_run_host(sgemm_handle *h, const float *hA, const float *hB, 
                             lda, ldb, &whole)))
             return rc;
         const int64_t saved_variant = h->force_variant, saved_split = h->split_k_opt;
-        h->force_variant = whole.variant == kVariantTensor ? 1 : 2;
+        h->force_variant = whole.variant != kVariantTensor ? 2 : (whole.tk == &h->tk_skinny ? 3 : 1);
         h->split_k_opt = whole.split_k;
         CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[0], hA, bytes[0], s_in));
         CU_CHECK(h, d.cuEventRecord_(ev_a, s_in));
@@ -868,8 +910,8 @@ SGEMM_API int sgemm_last_status(sgemm_handle *h, uint32_t status[8]) {
     CU_CHECK(h, d.cuMemcpyDtoH_(status, h->status, kStatusWords * 4));
     if (status[0] != 0) {
         CU_CHECK(h, d.cuMemsetD8_(h->status, 0, kStatusWords * 4));
-        // a kernel that gave up may have left split-K arrival counters and the alignment counter half-counted
-        CU_CHECK(h, d.cuMemsetD8_(h->counters, 0, (size_t)(kCounterWords + 64) * 4));
+        // a kernel that gave up may have left the alignment counter half-counted
+        CU_CHECK(h, d.cuMemsetD8_(h->counters, 0, (size_t)kCounterWords * 4));
         h->wave_sync_base = 0;
         return fail(h, SGEMM_ERR_DEVICE_STATUS, "kernel gave up waiting: tag 0x%x tile %u k-block %u block %u parity %u",
                     status[1], status[2], status[3], status[4], status[5]);
@@ -891,10 +933,10 @@ SGEMM_API int sgemm_wait_selftest(sgemm_handle *h, uint32_t timeout_ms, uint32_t
 SGEMM_API int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value) {
     if (!h || !key) return SGEMM_ERR_INVALID_ARGUMENT;
     const std::string k(key);
-    if (k == "force_variant" && value >= 0 && value <= 2) h->force_variant = value;
+    if (k == "force_variant" && value >= 0 && value <= 3) h->force_variant = value;
+    else if (k == "skinny_below_intensity" && value >= 0) h->skinny_below_intensity = value;
     else if (k == "split_k" && value >= 0 && value <= 1024) h->split_k_opt = value;
     else if (k == "simt_below_flops" && value >= 0) h->simt_below_flops = value;
-    else if (k == "fuse_split_k" && (value == 0 || value == 1)) h->fuse_split_k = value != 0;
     else if (k == "pdl" && (value == 0 || value == 1)) h->pdl = value != 0;
     else if (k == "pipeline_host" && (value == 0 || value == 1)) h->pipeline_host = value != 0;
     else if (k == "wave_sync" && (value == 0 || value == 1)) h->wave_sync = value != 0;

@@ -171,11 +171,10 @@ extern "C" __global__ void __launch_bounds__(SIMT_THREADS)
 SIMT_ENTRY(const float *__restrict__ a, const float *__restrict__ b, const float *c, float *d,
            uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
            float alpha, float beta, int32_t num_wg_x, int32_t num_wg_y,
-           float *ws, uint32_t *status, uint32_t split_k, uint32_t *counters,
+           float *ws, uint32_t *status, uint32_t split_k,
            uint32_t *wave_sync, uint32_t wave_sync_base) {
     __shared__ __align__(16) SimtSmem s;
     (void)status;
-    (void)counters;   // the SIMT variant always finishes split-K with sgemm_splitk_reduce
     (void)wave_sync; (void)wave_sync_base;   // one tile per block: nothing to align
 
     sgemm_launch_dependents();

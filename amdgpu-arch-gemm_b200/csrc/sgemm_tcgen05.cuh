@@ -53,10 +53,7 @@
 // (4 warps x 2 CTAs arrive).  Operand traffic from L2/HBM halves and no lo copies exist in global memory.
 //
 // Split-K (split_k > 1): every launch unit covers one K range of one tile and stores its raw partial to the
-// workspace.  With an arrival-counter array (`counters`, all zero between launches) the reduction is fused: each
-// epilogue warp bumps the counter of its (tile, CTA, warp) slice after publishing its partial; the warp that
-// arrives last re-reads all partials of the slice in split order, applies alpha/beta and writes D, then zeroes
-// the counter.  Without counters the host runs sgemm_splitk_reduce afterwards.  Both give identical bits.
+// workspace; the host runs sgemm_splitk_reduce afterwards (fixed summation order, no atomics).
 //
 // Every mbarrier wait is bounded: after TC_TIMEOUT_NS without progress the waiting role records a
 // status word, raises a CTA-wide abort flag and all roles leave their loops, release TMEM and
@@ -285,7 +282,7 @@ extern "C" __global__ void TC_CLUSTER_ATTR __launch_bounds__(TC_THREADS, 1)
 generated_gemm(const float *a, const float *b, const float *c, float *d,
                uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
                float alpha, float beta, int32_t num_wg_x, int32_t num_wg_y,
-               float *ws, uint32_t *status, uint32_t split_k, uint32_t *counters,
+               float *ws, uint32_t *status, uint32_t split_k,
                uint32_t *wave_sync, uint32_t wave_sync_base,
                const __grid_constant__ TcTensorMap map_a_hi, const __grid_constant__ TcTensorMap map_a_lo,
                const __grid_constant__ TcTensorMap map_b_hi, const __grid_constant__ TcTensorMap map_b_lo) {
@@ -582,9 +579,6 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
             // first chunk is requested before the accumulator is even complete, so its latency hides behind the
             // tile's main loop.  (C may be the same buffer as D: every element is read before this same thread
             // overwrites it, and no other thread touches it.)
-            // split-K with arrival counters: the warp that finds every other split's slice already stored sums the
-            // partials itself (fixed order s = 0, 1, ...: the result does not depend on which split arrives last)
-            const bool fused = partial && counters != nullptr;
             float cv[2][32];
             auto fetch_c = [&](int cc, float (&dst)[32]) {
                 if (use_c && row < m) {
@@ -626,45 +620,6 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                 if (TC_CTA_GROUP == 2) tc_mbar_arrive_cluster(tempty_base + 8 * buf);
                 else tc_mbar_arrive(bar_tempty + 8 * buf);
             }
-            if (fused) {
-                // publish this slice's partial, then count arrivals for (tile, CTA of the pair, epilogue warp)
-                __threadfence();
-                __syncwarp();
-                const uint32_t slot = (((tile - z * tiles_mn) * TC_CTA_GROUP + cta_rank) * TC_EPI_WARPS) + (warp - 2u);
-                uint32_t arrived = 0;
-                if (lane == 0) arrived = atomicAdd(counters + slot, 1u);
-                arrived = __shfl_sync(0xffffffffu, arrived, 0);
-                if (arrived == split_k - 1u) {
-                    __threadfence();
-                    const uint64_t plane = (uint64_t)m * n;
-                    if (row < m) {
-#pragma unroll 1
-                        for (int cc = 0; cc < TC_EPI_COLS / 32; ++cc) {
-                            float acc[32];
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) acc[j] = 0.0f;
-                            for (uint32_t sp = 0; sp < split_k; ++sp) {
-#pragma unroll
-                                for (int j = 0; j < 32; ++j) {
-                                    const uint32_t col = col0 + cbase + cc * 32 + j;
-                                    if (col < n) acc[j] += __ldcg(ws + sp * plane + row + (uint64_t)col * m);
-                                }
-                            }
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const uint32_t col = col0 + cbase + cc * 32 + j;
-                                if (col < n) {
-                                    float v = alpha * acc[j];
-                                    if (beta != 0.0f) v = fmaf(beta, c[row + (uint64_t)col * ldc], v);
-                                    d[row + (uint64_t)col * ldd] = v;
-                                }
-                            }
-                        }
-                    }
-                    __syncwarp();
-                    if (lane == 0) counters[slot] = 0u;   // leave the counters as they were found: all zero
-                }
-            }
         }
     }
 
@@ -691,6 +646,8 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
 #endif
     }
 }
+
+// ==== end of the per-kernel section (the generator instantiates everything above once per tcgen05 kernel) ====
 
 // ---------------------------------------------------------------------------------------------
 // Self-test of the bounded wait: one CTA initialises an mbarrier that nothing will ever arrive on and

@@ -33,6 +33,7 @@ from __future__ import annotations
 
 import argparse
 import os
+import re
 import shutil
 import subprocess
 from enum import IntEnum
@@ -54,6 +55,7 @@ VARIANT_TENSOR = "tcgen05_3xtf32"
 VARIANT_SIMT = "simt_ffma"
 KERNEL_ENTRY = "generated_gemm"     # the entry name the runner and the tuner hard-code
 SIMT_FALLBACK_ENTRY = "generated_gemm_simt"
+SKINNY_ENTRY = "generated_gemm_skinny"   # companion tcgen05 kernel for low-intensity shapes (tensor cubins)
 
 # The 15 arguments of the kernel ABI in order: (typename, name, bytes).
 KERNEL_ABI = (
@@ -155,7 +157,7 @@ class GemmSolutionConfig:
                  mfma: Tuple[int, int, int, int], wave_group: Tuple[int, int], wave_tiling: Tuple[int, int],
                  depth_k: int, trans_a: bool, trans_b: bool, vmem_stage: int = 1, *,
                  a_major: str = "mn", terms: int = 3, split: str = "prepass",
-                 epilogue_warps: Optional[int] = None):
+                 epilogue_warps: Optional[int] = None, companion: bool = True):
         self.a_type = a_type
         self.b_type = b_type
         self.cd_type = cd_type
@@ -174,6 +176,10 @@ class GemmSolutionConfig:
         # tensor variant: warps that drain the accumulator; 8 (two per TMEM lane quarter, half the columns each)
         # keeps twice as many loads/stores in flight as 4 and is the default whenever tile N allows it
         self.epilogue_warps = epilogue_warps
+        # tensor variant: also emit the companion kernel (128 x 128 x 32, one CTA per tile, lo terms made in the kernel)
+        # that the runner uses for problems of low arithmetic intensity, where a pre-pass over the operands would
+        # cost as much as the GEMM itself
+        self.companion = companion
         self.split = split          # tensor variant: where lo = x - trunc_tf32(x) is made: "prepass" (a kernel writes
                                     # A_lo, B_lo to global memory once per call) or "inkernel" (transform warps make the
                                     # lo tiles in shared memory from the TMA-landed raw tiles)
@@ -316,6 +322,14 @@ class GemmSolutionConfig:
     def num_unrolled_iters(self) -> int:
         return self.depth_k // max(self.mfma[3], 1)
 
+    def companion_config(self) -> Optional["GemmSolutionConfig"]:
+        """Configuration of the companion kernel emitted next to a tensor-variant kernel (None: no companion)."""
+        if self.variant != VARIANT_TENSOR or not self.companion:
+            return None
+        return GemmSolutionConfig(self.a_type, self.b_type, self.cd_type, self.scalar_type, (128, 128, 1, 8), (1, 1), (1, 1),
+                                  32, self.trans_a, self.trans_b, vmem_stage=2, split="inkernel", terms=self.terms,
+                                  companion=False)
+
     def to_dict(self) -> Dict:
         d = {
             # ---- the reference's 14 keys (generator/generator.py:1001-1017), same order and types ----
@@ -354,6 +368,14 @@ class GemmSolutionConfig:
                 "fallback_tile": [fb.tile_size[0], fb.tile_size[1], fb.depth_k],
                 "fallback_threads": fb.num_workitems,
             })
+            sk = self.companion_config()
+            if sk is not None:
+                d.update({
+                    "skinny_entry": SKINNY_ENTRY,
+                    "skinny_tile": [sk.tile_size[0], sk.tile_size[1], sk.depth_k],
+                    "skinny_threads": sk.num_workitems,
+                    "skinny_smem_bytes": sk.lds_usage_bytes,
+                })
         return d
 
 
@@ -394,6 +416,14 @@ def _simt_defines(cfg: GemmSolutionConfig, opt: GemmOptimizations, entry: str):
             ("SIMT_TM", tm), ("SIMT_TN", tn), ("SIMT_PLR", 1 if opt.plr else 0)]
 
 
+def _tensor_defines(config: GemmSolutionConfig):
+    return [("TC_BN", config.tile_size[1]), ("TC_BK", config.depth_k), ("TC_STAGES", config.stages),
+            ("TC_CTA_GROUP", config.wave_group[0]), ("TC_SPLIT_INKERNEL", 1 if config.split == "inkernel" else 0),
+            ("TC_EPI_WARPS", config.epilogue_warps),
+            ("TC_A_KMAJOR", 1 if (config.a_major == "k" or config.trans_a) else 0),
+            ("TC_B_MNMAJOR", 1 if config.trans_b else 0), ("TC_TERMS", config.terms)]
+
+
 def _trans_defines(cfg: GemmSolutionConfig):
     return [("GEMM_TRANS_A", 1 if cfg.trans_a else 0), ("GEMM_TRANS_B", 1 if cfg.trans_b else 0)]
 
@@ -428,14 +458,21 @@ def gemm(context: GpuContext, name: str, arch: str, config: GemmSolutionConfig, 
     else:
         out.write(_defines(_simt_defines(simt_fallback_config(config.trans_a, config.trans_b), opt, SIMT_FALLBACK_ENTRY)))
         out.write(_read("sgemm_simt.cuh"))
-        out.write(_defines([("TC_BN", config.tile_size[1]), ("TC_BK", config.depth_k),
-                            ("TC_STAGES", config.stages), ("TC_CTA_GROUP", config.wave_group[0]),
-                            ("TC_SPLIT_INKERNEL", 1 if config.split == "inkernel" else 0),
-                            ("TC_EPI_WARPS", config.epilogue_warps),
-                            ("TC_A_KMAJOR", 1 if (config.a_major == "k" or config.trans_a) else 0),
-                            ("TC_B_MNMAJOR", 1 if config.trans_b else 0),
-                            ("TC_TERMS", config.terms)]))
-        out.write(_read("sgemm_tcgen05.cuh"))
+        template = _read("sgemm_tcgen05.cuh")
+        out.write(_defines(_tensor_defines(config)))
+        out.write(template)
+        companion = config.companion_config()
+        if companion is not None:
+            # second instance of the per-kernel part of the template under its own names: macros TC_* -> TCS_*,
+            # functions tc_* -> tcs_*, types Tc* -> Tcs*, entry generated_gemm -> generated_gemm_skinny
+            body = template.split("// ==== end of the per-kernel section")[0]
+            body = re.sub(r"\bTC_", "TCS_", body)
+            body = re.sub(r"\btc_", "tcs_", body)
+            body = re.sub(r"\bTc(?=[A-Z])", "Tcs", body)
+            body = re.sub(r"\b%s\b" % KERNEL_ENTRY, SKINNY_ENTRY, body)
+            out.write("\n// ---- companion kernel for low-intensity shapes: 128 x 128 x 32, one CTA per tile, in-kernel split ----\n")
+            out.write(_defines([(k.replace("TC_", "TCS_", 1), v) for k, v in _tensor_defines(companion)]))
+            out.write(body)
     src = out.getvalue()
     context.content.write(src)
     return src

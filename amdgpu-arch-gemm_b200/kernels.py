@@ -85,19 +85,17 @@ def recommend(m: int, n: int, k: int) -> str:
     A handle serves one cubin, so choosing between configurations is the caller's (or the tuner's) job, as in the
     reference where the tuner picks one configuration per problem size.  The rules condense the sweeps recorded in
     the design notes:
-      * large, compute-bound problems: CTA pairs on 256 x 256 tiles with the split pre-pass;
-      * low arithmetic intensity (a skinny dimension: the operands are read about once): the in-kernel split, whose
-        operand traffic is half and which needs no lo copies; 128-wide tiles when a dimension is below one pair tile;
+      * tiny problems: the FFMA kernel (launch-latency bound either way, and no pre-pass);
+      * few flops per byte of A and B (a skinny M or N with a long K): small tiles with the in-kernel split — the
+        default cubin switches to its companion kernel of this kind by itself, so it is returned here as well;
       * fewer than one wave of 256 x 256 tiles: 128 x 128 tiles so that more SMs get work;
-      * tiny problems: the FFMA kernel (launch-latency bound either way, and no pre-pass).
+      * everything else: CTA pairs on 256 x 256 tiles with the split pre-pass.
     """
     flops = 2.0 * m * n * k
     if flops < 2 ** 27:
         return DEFAULT_SIMT
-    intensity = flops / (4.0 * (m * k + k * n + m * n))          # flop per byte of compulsory traffic
-    pair_tiles = -(-m // 256) * -(-n // 256)
-    if intensity < 200.0:
-        return "tci_128x128x32_s3" if min(m, n) < 256 else "tc2i_256x256x32_s3"
-    if pair_tiles < 74:
+    if flops / (4.0 * (m * k + k * n)) < 200.0:
+        return DEFAULT_TENSOR if min(m, n) < 256 else "tc2i_256x256x32_s3"
+    if -(-m // 256) * -(-n // 256) < 37:
         return "tc_128x128x32_s3"
     return DEFAULT_TENSOR

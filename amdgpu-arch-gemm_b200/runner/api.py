@@ -36,6 +36,8 @@ class SgemmConfig(ctypes.Structure):
         ("stages", ctypes.c_int32), ("a_kmajor", ctypes.c_int32), ("split_inkernel", ctypes.c_int32),
         ("fallback_tile", ctypes.c_int32 * 3),
         ("fallback_threads", ctypes.c_int32), ("entry", ctypes.c_char * 64), ("fallback_entry", ctypes.c_char * 64),
+        ("skinny_tile", ctypes.c_int32 * 3), ("skinny_threads", ctypes.c_int32), ("skinny_smem_bytes", ctypes.c_int32),
+        ("skinny_entry", ctypes.c_char * 64),
     ]
 
 
@@ -134,7 +136,7 @@ def _ptr(x) -> int:
 class SgemmRunner:
     """One loaded kernel on one device (wraps ``sgemm_handle``)."""
 
-    AUTO, TENSOR, SIMT = 0, 1, 2
+    AUTO, TENSOR, SIMT, TENSOR_SKINNY = 0, 1, 2, 3
 
     def __init__(self, cubin_path: str, toml_path: str, device: int = 0):
         self._L = lib()

@@ -65,6 +65,11 @@ typedef struct sgemm_config {
     int32_t fallback_threads;
     char entry[64];
     char fallback_entry[64];
+    /* companion tcgen05 kernel for low-intensity shapes (tensor-variant cubins; empty entry: none) */
+    int32_t skinny_tile[3];
+    int32_t skinny_threads;
+    int32_t skinny_smem_bytes;
+    char skinny_entry[64];
 } sgemm_config;
 
 /* Replaces getAsmKernelConfig (runner/generator_runner.cpp:100-124).  Host only, needs no GPU. */
@@ -135,10 +140,10 @@ int sgemm_last_status(sgemm_handle *h, uint32_t status[8]);
  * handle must keep working.  Tensor-variant cubins only. */
 int sgemm_wait_selftest(sgemm_handle *h, uint32_t timeout_ms, uint32_t tag);
 
-/* Options: "force_variant" 0 auto, 1 tensor, 2 simt;  "split_k" 0 auto, n >= 1 fixed;
+/* Options: "force_variant" 0 auto, 1 tensor (main kernel), 2 simt, 3 tensor (companion kernel for skinny shapes);
+ * "skinny_below_intensity": in auto mode problems with fewer flop per byte of A and B than this (default 200: a
+ * skinny M or N with a long K) run on the companion kernel (128 x 128 tiles, lo terms made in the kernel, no pre-pass);  "split_k" 0 auto, n >= 1 fixed;
  * "simt_below_flops" problems with 2*M*N*K below this use the SIMT kernel (auto mode);
- * "fuse_split_k" 1 lets the tensor kernel sum its split-K partials itself (arrival counters, the last warp of a
- * slice reduces), 0 (default) runs the separate reduction kernel — same bits either way, the separate kernel is faster;
  * "pdl" 1 (default) launches every kernel with programmatic stream serialisation so that launch latency and per-CTA
  * set-up overlap with the tail of the previous kernel (all kernels wait on the grid dependency before touching memory);
  * "wave_sync" 1 (default) lets the persistent CTAs of the tensor kernel wait briefly for each other at tile
@@ -147,7 +152,7 @@ int sgemm_wait_selftest(sgemm_handle *h, uint32_t timeout_ms, uint32_t tag);
  * "profile" 1 brackets every main-GEMM-kernel launch with an event pair (read with "profile_main_ns"). */
 int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value);
 
-/* Facts: "variant" (of the cubin), "last_variant" (1 tensor / 2 simt), "last_split_k", "last_grid",
+/* Facts: "variant" (of the cubin), "last_variant" (1 tensor main / 2 simt / 3 tensor companion), "last_split_k", "last_grid",
  * "launches" (kernel launches issued so far), "tile_m", "tile_n", "sm_count", "workspace_bytes",
  * "profile_count" (bracketed launches since the last read), "profile_main_ns" (their summed device time in
  * nanoseconds; synchronises on them and resets the tally). */

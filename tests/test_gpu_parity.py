@@ -15,7 +15,7 @@ TENSOR_KERNELS = ["tc_128x256x32_s2", "tc_128x128x32_s3", "tc_128x64x32_s4", "tc
                   "tc2_256x256x32_s3_e4"]
 # (kernels built for transposed operands have their own tests below)
 SIMT_KERNELS = ["simt_128x128x16", "simt_64x64x16", "simt_128x64x8_plr0", "legacy_32x32x2_1wave", "legacy_16x16x4_2x2x2x2"]
-AUTO, TENSOR, SIMT = 0, 1, 2
+AUTO, TENSOR, SIMT, SKINNY = 0, 1, 2, 3
 _runners = {}
 
 
@@ -30,7 +30,7 @@ def runner_of(built):
         r = _runners[name]
         r.set_option("force_variant", AUTO)
         r.set_option("split_k", 0)
-        r.set_option("fuse_split_k", 0)
+        r.set_option("skinny_below_intensity", 0)   # parity tests pick kernels explicitly
         r.set_workspace(None, 0)
         return r
 
@@ -58,6 +58,19 @@ def check(d, a, b, c, m, n, k, alpha, beta, lda=0, ldb=0, ldc=0, ldd=0):
     ratio = oracle.worst_ratio(got, ref, bound)
     assert ratio <= 1.0, f"worst |err| / (1e-5 * sum|a||b|) = {ratio}"
     return ratio
+
+
+def stored(flat, rows, cols, transposed, ld=0):
+    """Column-major rows x cols matrix (flat) as the kernel expects it: as is, or stored transposed (cols x rows
+    column-major), optionally with a padded leading dimension."""
+    mat = flat.reshape(cols, rows)                    # numpy row = one column of the matrix
+    if transposed:
+        mat = np.ascontiguousarray(mat.T)             # rows x cols array = cols-contiguous storage
+    inner = mat.shape[1]
+    ld = ld or inner
+    out = np.zeros(mat.shape[0] * ld, dtype=np.float32)
+    out.reshape(mat.shape[0], ld)[:, :inner] = mat
+    return out, ld
 
 
 # ------------------------------------------------------------------------------------------- golden vectors
@@ -112,6 +125,40 @@ def test_simt_kernels_match_oracle(runner_of, kernel, mnk, alpha, beta):
     d = run(r, a, b, c, m, n, k, alpha, beta, force=SIMT)
     assert r.info("last_variant") == SIMT
     check(d, a, b, c, m, n, k, alpha, beta)
+
+
+@pytest.mark.parametrize("kernel,ta,tb", [("tc2_256x256x32_s3", False, False), ("tc_128x256x32_s2", False, False),
+                                          ("tc2_256x256x32_s3_tt", True, True)])
+@pytest.mark.parametrize("mnk", SHAPES + [(4096, 128, 2048)])
+def test_companion_kernel_matches_oracle(runner_of, kernel, ta, tb, mnk):
+    # every tensor-variant cubin carries a second tcgen05 kernel (128 x 128 x 32 tiles, lo terms made in the kernel)
+    # for low-intensity shapes; forced here on all shapes
+    m, n, k = mnk
+    a, b, c = oracle.make_inputs(m, n, k, seed=41)
+    pad = lambda x: (x + 3) // 4 * 4
+    sa, lda = stored(a, m, k, ta, pad(k if ta else m))
+    sb, ldb = stored(b, k, n, tb, pad(n if tb else k))
+    r = runner_of(kernel)
+    launches = r.info("launches")
+    d = run(r, sa, sb, c, m, n, k, 0.5, 2.0, force=SKINNY, lda=lda, ldb=ldb)
+    assert r.info("last_variant") == SKINNY
+    assert r.info("launches") - launches == (1 if r.info("last_split_k") == 1 else 2)   # no pre-pass
+    check(d, a, b, c, m, n, k, 0.5, 2.0)
+
+
+def test_low_intensity_shapes_take_the_companion_kernel(runner_of):
+    r = runner_of("tc2_256x256x32_s3")
+    r.set_option("skinny_below_intensity", 200)          # the library's default: flop per byte of A and B
+    for (m, n, k), want in [((4096, 128, 4096), SKINNY), ((64, 4096, 8192), SKINNY), ((2048, 2048, 2048), TENSOR),
+                            ((4096, 4096, 256), TENSOR)]:
+        a, b, c = oracle.make_inputs(m, n, k, seed=2)
+        d = run(r, a, b, c, m, n, k, 1.0, 0.0)
+        assert r.info("last_variant") == want, (m, n, k)
+        check(d, a, b, c, m, n, k, 1.0, 0.0)
+    from runner import api
+    with pytest.raises(api.SgemmError) as e:             # an FFMA-only cubin has no companion to force
+        run(runner_of("simt_128x128x16"), a, b, c, m, n, k, force=SKINNY)
+    assert e.value.code == -6
 
 
 def test_variant_selection(runner_of):
@@ -225,28 +272,6 @@ def test_split_k_is_deterministic_and_in_tolerance(runner_of, kernel, force):
     assert r.info("last_split_k") > 1
 
 
-@pytest.mark.parametrize("kernel", ["tc2_256x256x32_s3", "tc_128x128x32_s3", "tc2i_256x256x32_s3", "tc2_256x256x32_s3_e4"])
-@pytest.mark.parametrize("mnk", [(1024, 1024, 1024), (300, 520, 4096), (4096, 128, 16384)])
-def test_fused_split_k_reduction_equals_the_separate_kernel(runner_of, kernel, mnk):
-    # the tensor kernel's own reduction (arrival counters, last warp sums in split order) and sgemm_splitk_reduce
-    # must agree to the bit, call after call (the counters have to come back to zero every time)
-    m, n, k = mnk
-    lda, ldb = (m + 3) // 4 * 4, k
-    a, b, c = oracle.make_inputs(m, n, k, seed=13, lda=lda)
-    r = runner_of(kernel)
-    outs = []
-    for fuse in (1, 0, 1, 1):
-        r.set_option("fuse_split_k", fuse)
-        launches = r.info("launches")
-        d = run(r, a, b, c, m, n, k, 1.5, -0.5, force=TENSOR, split_k=4, lda=lda)
-        assert r.info("last_split_k") == 4
-        prepass = 0 if kernel.startswith("tc2i") else 1
-        assert r.info("launches") - launches == prepass + 1 + (0 if fuse else 1)
-        outs.append(d)
-    check(outs[0], a, b, c, m, n, k, 1.5, -0.5, lda=lda)
-    assert all(o.tobytes() == outs[0].tobytes() for o in outs[1:])
-
-
 def test_split_k_beyond_the_k_blocks_is_clamped(runner_of):
     m, n, k = 64, 64, 40
     a, b, c = oracle.make_inputs(m, n, k, seed=2)
@@ -304,19 +329,6 @@ def test_beta_zero_never_reads_c(runner_of):
 
 
 # ------------------------------------------------------------------------------------------ transposes
-def stored(flat, rows, cols, transposed, ld=0):
-    """Column-major rows x cols matrix (flat) as the kernel expects it: as is, or stored transposed (cols x rows
-    column-major), optionally with a padded leading dimension."""
-    mat = flat.reshape(cols, rows)                    # numpy row = one column of the matrix
-    if transposed:
-        mat = np.ascontiguousarray(mat.T)             # rows x cols array = cols-contiguous storage
-    inner = mat.shape[1]
-    ld = ld or inner
-    out = np.zeros(mat.shape[0] * ld, dtype=np.float32)
-    out.reshape(mat.shape[0], ld)[:, :inner] = mat
-    return out, ld
-
-
 @pytest.mark.parametrize("kernel,ta,tb", [
     ("tc2_256x256x32_s3_tn", True, False), ("tc2_256x256x32_s3_nt", False, True), ("tc2_256x256x32_s3_tt", True, True),
     ("tc_128x128x32_s3_tt", True, True), ("tc2i_256x256x32_s3_tt", True, True),
