@@ -75,8 +75,15 @@ def ensure(name: str, force: bool = False) -> Tuple[str, str]:
     return cubin, toml
 
 
-def build_all(force: bool = True) -> Dict[str, Tuple[str, str]]:
-    return {name: ensure(name, force=force) for name in REGISTRY}
+def build_all(force: bool = True, jobs: int = 0) -> Dict[str, Tuple[str, str]]:
+    """Generate and compile every registered kernel (nvcc runs as a subprocess, so threads give real parallelism)."""
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+
+    jobs = jobs or min(8, os.cpu_count() or 1)
+    with ThreadPoolExecutor(max_workers=jobs) as pool:
+        results = list(pool.map(lambda name: ensure(name, force=force), REGISTRY))
+    return dict(zip(REGISTRY, results))
 
 
 def recommend(m: int, n: int, k: int) -> str:
