@@ -136,8 +136,11 @@ int main(int argc, char **argv) {
     sgemm_get_info(h, "last_variant", &variant);
     sgemm_get_info(h, "last_split_k", &split);
     sgemm_get_info(h, "launches", &info);
+    // 1 = the cubin's main tensor kernel, 3 = its companion for problems with few flops per input byte, 2 = SIMT
+    const char *variant_text = variant == 1 ? "tcgen05 3xTF32" : variant == 3 ? "tcgen05 3xTF32 (companion)" : "SIMT FFMA";
+    const char *variant_key = variant == 1 ? "tcgen05_3xtf32" : variant == 3 ? "tcgen05_3xtf32_companion" : "simt_ffma";
     std::fprintf(stderr, "measured kernel: %s, split_k %lld, %.3f TFLOPS, %lld launches in total\n",
-                 variant == 1 ? "tcgen05 3xTF32" : "SIMT FFMA", (long long)split, gflops(m, n, k, ms) * 1e-3, (long long)info);
+                 variant_text, (long long)split, gflops(m, n, k, ms) * 1e-3, (long long)info);
     std::cout << "ASM gemm: " << ms << " ms\n"
               << "Gflops: " << gflops(m, n, k, ms) << '\n'
               << "GiB/s: " << mem_bw(m, n, k, ms) << '\n';
@@ -162,7 +165,7 @@ int main(int argc, char **argv) {
             std::fprintf(f, "{\"m\": %u, \"n\": %u, \"k\": %u, \"alpha\": %g, \"beta\": %g, \"seed\": %llu, \"warmup\": %u, "
                             "\"runs\": %u, \"variant\": \"%s\", \"split_k\": %lld, \"ms\": %.6f, \"tflops\": %.4f, "
                             "\"gib_per_s\": %.3f, \"validated\": %s, \"mismatches\": %zu}\n",
-                         m, n, k, alpha, beta, (unsigned long long)seed, warmup, runs, variant == 1 ? "tcgen05_3xtf32" : "simt_ffma",
+                         m, n, k, alpha, beta, (unsigned long long)seed, warmup, runs, variant_key,
                          (long long)split, ms, gflops(m, n, k, ms) * 1e-3, mem_bw(m, n, k, ms), validate ? "true" : "false", mismatches);
             std::fclose(f);
         } else {

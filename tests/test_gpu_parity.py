@@ -328,6 +328,38 @@ def test_beta_zero_never_reads_c(runner_of):
         check(d, a, b, None, m, n, k, 1.0, 0.0)
 
 
+# ------------------------------------------------------------------------- seeded random sweep of the API
+def test_random_shapes_layouts_and_options(runner_of):
+    # 80 seeded cases: random sizes (ragged on purpose), leading-dimension padding, alpha/beta, kernel and variant;
+    # every one against the oracle, a few also for run-to-run bit equality
+    rng = np.random.default_rng(20240607)
+    pool = ["tc2_256x256x32_s3", "tc_128x256x32_s2", "tc_128x128x16_s7", "tc2i_256x256x32_s3", "tc2_256x256x32_s3_tt",
+            "tc2_256x256x32_s3_tn", "simt_128x128x16", "simt_64x64x16_tt", "legacy_32x32x2_1wave"]
+    for case in range(80):
+        kernel = pool[int(rng.integers(len(pool)))]
+        ta, tb = kernel.endswith(("_tt", "_tn")), kernel.endswith(("_tt", "_nt"))
+        m, n, k = (int(rng.integers(1, 700)) for _ in range(3))
+        if case % 7 == 0:
+            k = int(rng.integers(2000, 6000))               # long K: split-K territory
+        alpha = float(rng.choice([1.0, -0.5, 2.25]))
+        beta = float(rng.choice([0.0, 0.0, 1.0, -1.75]))
+        tensor_cubin = kernel.startswith("tc")
+        pad4 = lambda x: (x + 3) // 4 * 4
+        extra = int(rng.choice([0, 0, 4, 12]))
+        a, b, c = oracle.make_inputs(m, n, k, seed=1000 + case)
+        sa, lda = stored(a, m, k, ta, (pad4(k if ta else m) + extra) if tensor_cubin else 0)
+        sb, ldb = stored(b, k, n, tb, (pad4(n if tb else k) + extra) if tensor_cubin else 0)
+        ldd = m + int(rng.choice([0, 0, 3]))
+        force = int(rng.choice([AUTO, TENSOR, SIMT, SKINNY])) if tensor_cubin else SIMT
+        split = int(rng.choice([0, 0, 1, 3]))
+        r = runner_of(kernel)
+        d = run(r, sa, sb, c, m, n, k, alpha, beta, force=force, split_k=split, lda=lda, ldb=ldb, ldd=ldd)
+        check(d, a, b, c, m, n, k, alpha, beta, ldd=ldd)
+        if case % 5 == 0:
+            d2 = run(r, sa, sb, c, m, n, k, alpha, beta, force=force, split_k=split, lda=lda, ldb=ldb, ldd=ldd)
+            assert d.tobytes() == d2.tobytes(), (case, kernel, m, n, k)
+
+
 # ------------------------------------------------------------------------------------------ transposes
 @pytest.mark.parametrize("kernel,ta,tb", [
     ("tc2_256x256x32_s3_tn", True, False), ("tc2_256x256x32_s3_nt", False, True), ("tc2_256x256x32_s3_tt", True, True),

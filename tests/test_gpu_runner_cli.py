@@ -32,7 +32,7 @@ def test_cli_stdout_contract_and_validation(built, kernel):
         ret = run_cli(built, kernel, 512, 768, 640, 0, env={"SGEMM_JSON": f"{tmp}/r.json", "SGEMM_BETA": "0", "SGEMM_SEED": "7"})
         rec = json.load(open(f"{tmp}/r.json"))
     assert (rec["m"], rec["n"], rec["k"], rec["beta"], rec["seed"], rec["validated"]) == (512, 768, 640, 0, 7, False)
-    assert rec["tflops"] > 0 and rec["variant"] == ("tcgen05_3xtf32" if kernel.startswith("tc") else "simt_ffma")
+    assert rec["tflops"] > 0 and rec["variant"].startswith("tcgen05_3xtf32" if kernel.startswith("tc") else "simt_ffma")
     assert ret.returncode == 0
     gflops = float(ret.stdout.split("\n")[-3].split(":")[-1])   # tuner/sgemm_tuner.py:115
     assert gflops > 0
