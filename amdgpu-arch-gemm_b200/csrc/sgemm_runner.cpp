@@ -104,6 +104,7 @@ struct TensorKernel {
     uint32_t threads = 0, smem = 0;
     bool split_inkernel = false;                // lo tiles made in the kernel: no pre-pass, no lo copies
     bool a_packed = false;                      // A is read from K-major packed copies made by a pre-pass
+    uint32_t acc_chain = 0;                     // k per accumulation chain the kernel was generated for (0: no register path)
 };
 
 struct sgemm_handle {
@@ -117,6 +118,7 @@ struct sgemm_handle {
     int sm_count = 0;
     uint32_t tile_m = 0, tile_n = 0;
     TensorKernel tk_main, tk_skinny;   // tk_skinny.fn == NULL: the cubin has no companion kernel
+    TensorKernel tk_wholek;            // twin of tk_main with whole-K accumulation (fn == NULL: none)
     CUdeviceptr status = 0;
     CUdeviceptr counters = 0;   // device words shared by all launches of the handle: [0] = wave-alignment counter
     // workspace: owned (grow on demand) or lent
@@ -138,7 +140,8 @@ struct sgemm_handle {
     uint32_t wave_sync_base = 0;   // value of the alignment counter before the next launch (it only ever counts up)
     bool pipeline_host = true;  // sgemm_run_host overlaps uploads, GEMM and downloads over column chunks
     bool pdl = true;            // launch with programmatic stream serialisation (see launch())
-    int64_t last_variant = 0, last_split_k = 1, last_grid = 0, launches = 0;
+    int64_t acc_chain_opt = -1;   // -1: as generated, 0: whole K in one chain, else k per chain
+    int64_t last_variant = 0, last_split_k = 1, last_grid = 0, launches = 0, last_acc_chain = 0;
     CachedMap maps[4];
     // optional timing of the main GEMM kernel alone (events around it on the caller's stream)
     bool profile = false;
@@ -201,6 +204,7 @@ struct Plan {
     uint32_t ldt = 0;                                                   // K-major packed A: leading dimension
     size_t ws_bytes = 0;
     const TensorKernel *tk = nullptr;   // the tcgen05 kernel chosen (tensor variant only)
+    uint32_t acc_chain = 0;             // k per tensor-core accumulation chain (0: all of K in one chain)
 };
 
 bool tensor_eligible(const sgemm_handle *h, const void *a, const void *b, uint32_t lda, uint32_t ldb) {
@@ -258,6 +262,20 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
         if (variant == kVariantTensor && h->tk_skinny.fn && intensity < (double)h->skinny_below_intensity) tk = &h->tk_skinny;
     }
     p->variant = variant;
+    if (variant == kVariantTensor) {
+        // accumulation chain: the kernel's own unless the caller chose one
+        uint32_t chain = h->acc_chain_opt < 0 ? tk->acc_chain : (uint32_t)h->acc_chain_opt;
+        if (chain && (!tk->acc_chain || chain % tk->bk))
+            return fail(h, SGEMM_ERR_UNSUPPORTED, "acc_chain %u: %s", chain,
+                        tk->acc_chain ? "not a multiple of the kernel's k-block" : "this kernel was generated without chunked accumulation");
+        // a tile with one accumulation chunk (no chunking, or K up to two chains: the first chunks are double length)
+        // does not need the running sum: the main kernel's whole-K twin writes it out straight from TMEM
+        if (tk == &h->tk_main && h->tk_wholek.fn && (chain == 0 || k <= 2 * chain)) {
+            tk = &h->tk_wholek;
+            chain = 0;
+        }
+        p->acc_chain = chain;
+    }
     p->tk = variant == kVariantTensor ? tk : nullptr;
     size_t off = 0;
     if (variant == kVariantTensor) {
@@ -503,8 +521,10 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
         uint32_t *wave_sync = h->wave_sync ? reinterpret_cast<uint32_t *>(h->counters) : nullptr;
         uint32_t wave_base = h->wave_sync_base;
         if (wave_sync) h->wave_sync_base += p.tiles_m * p.tiles_n * p.split_k;
+        uint32_t acc_chunk = p.acc_chain / tk.bk;
+        h->last_acc_chain = p.acc_chain;
         void *params[] = {&dA, &dB, &dC, &dD, &m, &n, &k, &lda, &ldb, &ldc, &ldd, &alpha, &beta, &nwx, &nwy,
-                          &partial, &status_ptr, &split, &wave_sync, &wave_base,
+                          &partial, &status_ptr, &split, &wave_sync, &wave_base, &acc_chunk,
                           const_cast<CUtensorMap *>(ma_hi), const_cast<CUtensorMap *>(ma_lo),
                           const_cast<CUtensorMap *>(mb_hi), const_cast<CUtensorMap *>(mb_lo)};
         rc = launch_main(h, tk.fn, p.grid_x, 1, tk.threads, tk.smem, stream, params);
@@ -530,6 +550,7 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
         if (rc) return rc;
     }
     h->last_variant = p.variant != kVariantTensor ? 2 : (p.tk == &h->tk_skinny ? 3 : 1);
+    if (p.variant != kVariantTensor) h->last_acc_chain = 0;
     h->last_split_k = p.split_k;
     h->last_grid = p.grid_x;
     return SGEMM_OK;
@@ -586,6 +607,9 @@ int config_from_toml(const char *path, sgemm_config *c, std::string *err) {
     c->skinny_threads = t.get_int("skinny_threads", &v) ? (int32_t)v : 0;
     c->skinny_smem_bytes = t.get_int("skinny_smem_bytes", &v) ? (int32_t)v : 0;
     std::snprintf(c->skinny_entry, sizeof c->skinny_entry, "%s", t.get_string("skinny_entry", &s) ? s.c_str() : "");
+    c->acc_chain = t.get_int("acc_chain", &v) ? (int32_t)v : 0;
+    std::snprintf(c->wholek_entry, sizeof c->wholek_entry, "%s", t.get_string("wholek_entry", &s) ? s.c_str() : "");
+    c->skinny_acc_chain = t.get_int("skinny_acc_chain", &v) ? (int32_t)v : 0;
     std::snprintf(c->entry, sizeof c->entry, "%s", t.get_string("entry", &s) ? s.c_str() : "generated_gemm");
     std::snprintf(c->fallback_entry, sizeof c->fallback_entry, "%s", t.get_string("fallback_entry", &s) ? s.c_str() : "");
     if (c->variant == kVariantTensor && (c->fallback_threads <= 0 || c->fallback_tile[0] <= 0 || !c->fallback_entry[0])) {
@@ -706,6 +730,16 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
     h->tk_main.group = (uint32_t)std::max(1, cfg.wave_group[0]);
     h->tk_main.threads = (uint32_t)cfg.num_threads; h->tk_main.smem = (uint32_t)cfg.dynamic_smem_bytes;
     h->tk_main.split_inkernel = cfg.split_inkernel != 0; h->tk_main.a_packed = cfg.a_kmajor != 0;
+    h->tk_main.acc_chain = (uint32_t)std::max(cfg.acc_chain, 0);
+    if (cfg.variant == kVariantTensor && cfg.wholek_entry[0]) {
+        h->tk_wholek = h->tk_main;
+        h->tk_wholek.acc_chain = 0;
+        if ((r = d.cuModuleGetFunction_(&h->tk_wholek.fn, h->module, cfg.wholek_entry)) != CUDA_SUCCESS ||
+            (r = d.cuFuncSetAttribute_(h->tk_wholek.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)h->tk_main.smem)) != CUDA_SUCCESS) {
+            fail(h, SGEMM_ERR_MODULE, "whole-K entry point '%s' unusable in '%s': %s", cfg.wholek_entry, cubin_path, cu_text(r).c_str());
+            return bail(SGEMM_ERR_MODULE);
+        }
+    }
     if (cfg.variant == kVariantTensor && cfg.skinny_entry[0] && cfg.skinny_threads > 0 && cfg.skinny_tile[0] > 0) {
         // companion kernel for low-intensity shapes: one CTA per 128-row tile, lo tiles made in the kernel
         if ((r = d.cuModuleGetFunction_(&h->tk_skinny.fn, h->module, cfg.skinny_entry)) != CUDA_SUCCESS ||
@@ -717,6 +751,7 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
         h->tk_skinny.bk = (uint32_t)cfg.skinny_tile[2];
         h->tk_skinny.group = 1; h->tk_skinny.threads = (uint32_t)cfg.skinny_threads; h->tk_skinny.smem = (uint32_t)cfg.skinny_smem_bytes;
         h->tk_skinny.split_inkernel = true; h->tk_skinny.a_packed = false;
+        h->tk_skinny.acc_chain = (uint32_t)std::max(cfg.skinny_acc_chain, 0);
     }
     if (cfg.dynamic_smem_bytes > 0 &&
         (r = d.cuFuncSetAttribute_(h->fn_main, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, cfg.dynamic_smem_bytes)) != CUDA_SUCCESS) {
@@ -941,6 +976,7 @@ SGEMM_API int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value) 
     else if (k == "pipeline_host" && (value == 0 || value == 1)) h->pipeline_host = value != 0;
     else if (k == "wave_sync" && (value == 0 || value == 1)) h->wave_sync = value != 0;
     else if (k == "profile" && (value == 0 || value == 1)) { h->profile = value != 0; h->prof_used = 0; }
+    else if (k == "acc_chain" && value >= -1 && value <= (1 << 20)) h->acc_chain_opt = value;
     else return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "unknown option or value out of range: %s = %lld", key, (long long)value);
     return SGEMM_OK;
 }
@@ -951,6 +987,9 @@ SGEMM_API int sgemm_get_info(sgemm_handle *h, const char *key, int64_t *value) {
     if (k == "variant") *value = h->cfg.variant;
     else if (k == "last_variant") *value = h->last_variant;
     else if (k == "last_split_k") *value = h->last_split_k;
+    else if (k == "last_acc_chain") *value = h->last_acc_chain;
+    else if (k == "acc_chain") *value = h->tk_main.acc_chain;
+    else if (k == "skinny_acc_chain") *value = h->tk_skinny.acc_chain;
     else if (k == "last_grid") *value = h->last_grid;
     else if (k == "launches") *value = h->launches;
     else if (k == "tile_m") *value = h->tile_m;

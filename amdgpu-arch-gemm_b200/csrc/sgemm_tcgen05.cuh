@@ -7,7 +7,8 @@
 // is written once per call by sgemm_split_lo.  All three products accumulate into one FP32 TMEM
 // accumulator, k ascending, so results do not depend on scheduling (bit-reproducible).
 //
-// Roles of the 192 threads of a CTA (persistent over output tiles, tile = blockIdx + i*gridDim):
+// Roles of the warps of a CTA (persistent over output tiles, tile = blockIdx + i*gridDim).  Roles are laid out in
+// groups of four warps, the unit in which registers can be handed from one role to another (setmaxnreg):
 //   warp 0, one lane : TMA producer. Per k-block it fills one ring stage with four operand tiles
 //                      (A_hi, A_lo, B_hi, B_lo) and arms the stage's "full" mbarrier with the bytes.
 //   warp 1, one lane : MMA issuer. Waits "full", issues 3 * TC_BK/8 tcgen05.mma (K = 8 each) and
@@ -15,12 +16,21 @@
 //                      tile it commits to the accumulator's "tmem_full" mbarrier. Warp 1 also owns
 //                      the TMEM allocation (two accumulator buffers, so the epilogue of tile i
 //                      overlaps the main loop of tile i+1).
-//   warps 2..5 (..9) : epilogue, TC_EPI_WARPS = 4 or 8 warps. Warp w reads TMEM lanes 32*(w%4)..+31
+//   warps 2, 3       : no work (they complete the first group of four).
+//   warps 4..7 (..11): epilogue, TC_EPI_WARPS = 4 or 8 warps. Warp w reads TMEM lanes 32*(w%4)..+31
 //                      (= rows of the tile) with tcgen05.ld, applies alpha/beta and stores straight to
 //                      global memory: D is column-major, so the 32 lanes of a warp write 128 contiguous
 //                      bytes per column.  With 8 warps the two warps of a lane quarter take half of the
 //                      tile's columns each, which doubles the loads/stores in flight (it matters when K
 //                      is small or C is read).
+//   4 more warps     : (TC_SPLIT_INKERNEL) transform warps that write the lo tiles in shared memory.
+//
+// Chunked accumulation (kernels generated with TC_ACC_CHUNK > 0, launched with acc_chunk > 0).  The tensor core adds products into its accumulator with truncation
+// (toward zero, two guard bits), so an unbroken chain of MMAs drifts toward zero in proportion to its length.  The
+// issuer therefore starts a fresh accumulator, in the other TMEM buffer, every acc_chunk k-blocks, and the
+// epilogue warps add the finished chunks, in chunk order and with round-to-nearest FP32 adds, to a running sum in
+// registers; the epilogue proper then runs from registers.  The running sum needs TC_EPI_COLS registers per
+// epilogue thread; with 8 epilogue warps the first warp group gives registers up and the epilogue groups take them.
 //
 // Operand tiles in shared memory (128-byte swizzle, written by TMA, read by the tensor core):
 //   A (column-major, M contiguous => "MN-major" operand): per 32 rows of M one chunk of TC_BK rows
@@ -72,6 +82,10 @@
 #define TC_WAVE_SYNC_NS 100000ull   // longest a unit waits for the others at a tile boundary (soft, see the producer)
 #endif
 
+#ifndef TC_ACC_CHUNK
+#define TC_ACC_CHUNK 0   // != 0: the kernel can cut the accumulation into chains of `acc_chunk` k-blocks (a kernel argument) and add the
+                         // chains up in FP32 registers; the value is the generator's default chain, in k-blocks
+#endif
 #ifndef TC_CTA_GROUP
 #define TC_CTA_GROUP 1
 #endif
@@ -88,9 +102,24 @@
 #define TC_EPI_WARPS 4
 #endif
 #define TC_XFORM_WARPS (TC_SPLIT_INKERNEL ? 4 : 0)
-#define TC_THREADS (64 + 32 * TC_EPI_WARPS + 32 * TC_XFORM_WARPS)
+#define TC_THREADS (128 + 32 * TC_EPI_WARPS + 32 * TC_XFORM_WARPS)
+#define TC_FIRST_EPI_WARP 4u
+#ifndef TC_CW
+#define TC_CW 16  // columns of C per fetch in the epilogue that runs from registers (three buffers of this size)
+#endif
 #define TC_EPI_COLS (TC_BN / (TC_EPI_WARPS / 4))   // accumulator columns one epilogue warp drains per tile
 static_assert(TC_EPI_WARPS == 4 || TC_EPI_WARPS == 8, "one or two epilogue warps per TMEM lane quarter");
+// Registers.  A scheduler partition owns 512 registers per lane and runs TC_THREADS/128 warps of this CTA, one of
+// each group of four.  With 8 epilogue warps and a running sum (chunked accumulation) an even share is too small for
+// the epilogue threads, so the other groups shrink to TC_REGS_SMALL and the two epilogue groups grow to TC_REGS_EPI.
+#define TC_WARPS_PER_PARTITION (TC_THREADS / 128)
+#define TC_REGS_LAUNCH ((512 / TC_WARPS_PER_PARTITION) / 8 * 8)           // what __launch_bounds__ lets ptxas use
+#define TC_REG_HANDOVER (TC_ACC_CHUNK > 0 && TC_EPI_WARPS == 8)
+#define TC_REGS_SMALL 40
+#define TC_REGS_EPI (((TC_WARPS_PER_PARTITION * TC_REGS_LAUNCH - (TC_WARPS_PER_PARTITION - 2) * TC_REGS_SMALL) / 2) / 8 * 8)
+static_assert(!TC_REG_HANDOVER || (2 * TC_REGS_EPI + (TC_WARPS_PER_PARTITION - 2) * TC_REGS_SMALL <= TC_WARPS_PER_PARTITION * TC_REGS_LAUNCH &&
+                                   TC_REGS_EPI <= 232 && TC_REGS_EPI > TC_REGS_LAUNCH && TC_REGS_SMALL < TC_REGS_LAUNCH),
+              "the register hand-over must not ask for more than the launch allocated");
 static_assert(TC_EPI_COLS % 32 == 0, "an epilogue warp drains whole 32-column chunks");
 #define TC_A_BYTES (TC_BM * TC_BK * 4)
 #define TC_B_BYTES (TC_BN_CTA * TC_BK * 4)
@@ -214,6 +243,14 @@ __device__ __forceinline__ void tc_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) 
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tc_tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tc_tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ------------------------------------------------------------------------------ bounded waiting
@@ -223,7 +260,7 @@ struct TcWait {
     uint64_t timeout_ns;            // how long one wait may go without the barrier completing
 };
 
-__device__ __noinline__ bool tc_wait_slow(const TcWait &w, uint32_t bar, uint32_t parity, uint32_t tag,
+__device__ __forceinline__ bool tc_wait_slow(const TcWait &w, uint32_t bar, uint32_t parity, uint32_t tag,
                                           uint32_t tile, uint32_t kb) {
     const uint64_t t0 = tc_globaltimer();
     uint32_t spins = 0;
@@ -250,6 +287,17 @@ __device__ __forceinline__ bool tc_wait(const TcWait &w, uint32_t bar, uint32_t 
                                         uint32_t tile, uint32_t kb) {
     if (tc_mbar_try_wait(bar, parity)) return true;
     return tc_wait_slow(w, bar, parity, tag, tile, kb);
+}
+
+// ------------------------------------------------------------------------- chunked accumulation
+// A launch unit's k-blocks are cut into accumulation chunks of `chunk` k-blocks, except that the first two chunks of
+// a tile are twice as long: while the epilogue warps write the previous tile out (and read C) they drain nothing,
+// and the issuer can run ahead by the two accumulator buffers only — two long chunks cover that time.
+__device__ __forceinline__ uint32_t tc_chunk_span(uint32_t blocks_done, uint32_t chunk) {
+    return blocks_done < 4u * chunk ? 2u * chunk : chunk;
+}
+__device__ __forceinline__ uint32_t tc_chunk_count(uint32_t blocks, uint32_t chunk) {
+    return blocks <= 4u * chunk ? (blocks + 2u * chunk - 1u) / (2u * chunk) : 2u + (blocks - 4u * chunk + chunk - 1u) / chunk;
 }
 
 // ---------------------------------------------------------------------------------- descriptors
@@ -283,7 +331,7 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
                float alpha, float beta, int32_t num_wg_x, int32_t num_wg_y,
                float *ws, uint32_t *status, uint32_t split_k,
-               uint32_t *wave_sync, uint32_t wave_sync_base,
+               uint32_t *wave_sync, uint32_t wave_sync_base, uint32_t acc_chunk,
                const __grid_constant__ TcTensorMap map_a_hi, const __grid_constant__ TcTensorMap map_a_lo,
                const __grid_constant__ TcTensorMap map_b_hi, const __grid_constant__ TcTensorMap map_b_lo) {
     (void)a; (void)b; (void)lda; (void)ldb;
@@ -315,6 +363,9 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
     const uint32_t num_tiles = tiles_mn * split_k;
     const uint32_t kb_total = (k + TC_BK - 1) / TC_BK;
     const uint32_t kb_per = (kb_total + split_k - 1) / split_k;
+    // k-blocks per tensor-core accumulation chain (0: the whole K range in one chain); kernels generated without the
+    // register path (TC_ACC_CHUNK == 0) ignore the argument
+    const uint32_t chunk_blocks = TC_ACC_CHUNK ? acc_chunk : 0u;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
@@ -358,6 +409,20 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
     sgemm_launch_dependents();
     sgemm_grid_dependency_wait();
 
+    // Register hand-over between warp groups (each scheduler partition holds one warp of every group): the groups
+    // without a running sum shrink to TC_REGS_SMALL registers per thread, the epilogue groups grow to TC_REGS_EPI.
+    // The counts add up to no more than a partition owns (checked above), so a growing group never waits for more
+    // registers than the shrinking ones release.  Each group executes its instruction at the top of its own branch.
+#if TC_REG_HANDOVER
+#define TC_SHRINK_REGS() asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(TC_REGS_SMALL))
+#define TC_GROW_REGS() asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(TC_REGS_EPI))
+#else
+#define TC_SHRINK_REGS()
+#define TC_GROW_REGS()
+#endif
+
+    if (warp < TC_FIRST_EPI_WARP) {
+    TC_SHRINK_REGS();
     if (warp == 0) {
         // ------------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -455,68 +520,80 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
     } else if (warp == 1) {
         // -------------------------------------------------------------------------- MMA issuer
         if (lane == 0 && cta_rank == 0) {
-            uint32_t stage = 0, phase = 0, local = 0;
+            uint32_t stage = 0, phase = 0, handover = 0;   // handover: accumulator buffers given to the epilogue so far
             bool alive = true;
-            for (uint32_t tile = unit0; alive && tile < num_tiles; tile += unit_stride, ++local) {
+            for (uint32_t tile = unit0; alive && tile < num_tiles; tile += unit_stride) {
                 const uint32_t z = tile / tiles_mn;
                 const uint32_t kb_begin = min(kb_total, z * kb_per), kb_end = min(kb_total, kb_begin + kb_per);
-                const uint32_t buf = local & 1u, acc_phase = (local >> 1) & 1u;
-                if (!tc_wait(waiter, bar_tempty + 8 * buf, acc_phase ^ 1u, 0x200u + buf, tile, 0)) { alive = false; break; }
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * TC_BN;
-                if (kb_begin == kb_end) {  // empty K range: nothing to wait for, hand the buffer over
+                if (kb_begin == kb_end) {  // empty K range: nothing to wait for, hand a buffer over
+                    const uint32_t buf = handover & 1u, acc_phase = (handover >> 1) & 1u;
+                    if (!tc_wait(waiter, bar_tempty + 8 * buf, acc_phase ^ 1u, 0x200u + buf, tile, 0)) { alive = false; break; }
                     tc_mbar_arrive(bar_tfull + 8 * buf);
                     if (TC_CTA_GROUP == 2) tc_mbar_arrive_cluster(tc_map_to_cta(bar_tfull + 8 * buf, 1u));
+                    ++handover;
                     continue;
                 }
-                for (uint32_t kb = kb_begin; kb < kb_end; ++kb) {
-                    // operands of this stage are complete: TMA bytes landed (and, with the in-kernel split, lo tiles written)
-                    if (!tc_wait(waiter, (TC_SPLIT_INKERNEL ? bar_ready : bar_full) + 8 * stage, phase, 0x300u + stage, tile, kb)) { alive = false; break; }
+                // With chunk_blocks != 0 the K range is accumulated in chunks: each chunk starts a fresh accumulator in the
+                // other TMEM buffer and is handed to the epilogue warps, which add the chunks up in FP32 registers.
+                for (uint32_t kb = kb_begin; alive && kb < kb_end;) {
+                    const uint32_t buf = handover & 1u, acc_phase = (handover >> 1) & 1u;
+                    if (!tc_wait(waiter, bar_tempty + 8 * buf, acc_phase ^ 1u, 0x200u + buf, tile, kb)) { alive = false; break; }
                     tc_fence_after();
-                    const uint32_t sa_hi = smem_base + stage * TC_STAGE_BYTES;
-                    const uint32_t sa_lo = sa_hi + TC_A_BYTES;
-                    const uint32_t sb_hi = sa_lo + TC_A_BYTES;
-                    const uint32_t sb_lo = sb_hi + TC_B_BYTES;
+                    const uint32_t d_tmem = tmem_base + buf * TC_BN;
+                    const uint32_t chunk_begin = kb;
+                    const uint32_t chunk_end = chunk_blocks ? min(kb_end, kb + tc_chunk_span(kb - kb_begin, chunk_blocks)) : kb_end;
+                    for (; kb < chunk_end; ++kb) {
+                        // operands of this stage are complete: TMA bytes landed (and, with the in-kernel split, lo tiles written)
+                        if (!tc_wait(waiter, (TC_SPLIT_INKERNEL ? bar_ready : bar_full) + 8 * stage, phase, 0x300u + stage, tile, kb)) { alive = false; break; }
+                        tc_fence_after();
+                        const uint32_t sa_hi = smem_base + stage * TC_STAGE_BYTES;
+                        const uint32_t sa_lo = sa_hi + TC_A_BYTES;
+                        const uint32_t sb_hi = sa_lo + TC_A_BYTES;
+                        const uint32_t sb_lo = sb_hi + TC_B_BYTES;
 #pragma unroll
-                    for (int kk = 0; kk < TC_BK / 8; ++kk) {
+                        for (int kk = 0; kk < TC_BK / 8; ++kk) {
 #if TC_A_KMAJOR
-                        const uint32_t a_off = TC_KMAJOR_OFF(kk, TC_A_SUB_BYTES);
-                        const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);
-                        const uint64_t da_lo = tc_smem_desc(sa_lo + a_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);
+                            const uint32_t a_off = TC_KMAJOR_OFF(kk, TC_A_SUB_BYTES);
+                            const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);
+                            const uint64_t da_lo = tc_smem_desc(sa_lo + a_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);
 #else
-                        const uint32_t a_off = kk * 1024;
-                        const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
-                        const uint64_t da_lo = tc_smem_desc(sa_lo + a_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
+                            const uint32_t a_off = kk * 1024;
+                            const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
+                            const uint64_t da_lo = tc_smem_desc(sa_lo + a_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
 #endif
 #if TC_B_MNMAJOR
-                        const uint32_t b_off = kk * 1024;
-                        const uint64_t db_hi = tc_smem_desc(sb_hi + b_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
-                        const uint64_t db_lo = tc_smem_desc(sb_lo + b_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
+                            const uint32_t b_off = kk * 1024;
+                            const uint64_t db_hi = tc_smem_desc(sb_hi + b_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
+                            const uint64_t db_lo = tc_smem_desc(sb_lo + b_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
 #else
-                        const uint32_t b_off = TC_KMAJOR_OFF(kk, TC_B_SUB_BYTES);
-                        const uint64_t db_hi = tc_smem_desc(sb_hi + b_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);
-                        const uint64_t db_lo = tc_smem_desc(sb_lo + b_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);
+                            const uint32_t b_off = TC_KMAJOR_OFF(kk, TC_B_SUB_BYTES);
+                            const uint64_t db_hi = tc_smem_desc(sb_hi + b_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);
+                            const uint64_t db_lo = tc_smem_desc(sb_lo + b_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);
 #endif
-                        const uint32_t first = (kb == kb_begin && kk == 0) ? 0u : 1u;
+                            const uint32_t first = (kb == chunk_begin && kk == 0) ? 0u : 1u;
 #if TC_TERMS == 3
-                        tc_mma_tf32(d_tmem, da_lo, db_hi, TC_IDESC, first);
-                        tc_mma_tf32(d_tmem, da_hi, db_lo, TC_IDESC, 1u);
-                        tc_mma_tf32(d_tmem, da_hi, db_hi, TC_IDESC, 1u);
+                            tc_mma_tf32(d_tmem, da_lo, db_hi, TC_IDESC, first);
+                            tc_mma_tf32(d_tmem, da_hi, db_lo, TC_IDESC, 1u);
+                            tc_mma_tf32(d_tmem, da_hi, db_hi, TC_IDESC, 1u);
 #else
-                        (void)da_lo; (void)db_lo;
-                        tc_mma_tf32(d_tmem, da_hi, db_hi, TC_IDESC, first);
+                            (void)da_lo; (void)db_lo;
+                            tc_mma_tf32(d_tmem, da_hi, db_hi, TC_IDESC, first);
 #endif
+                        }
+                        tc_commit(bar_empty + 8 * stage);
+                        if (++stage == TC_STAGES) { stage = 0; phase ^= 1u; }
                     }
-                    tc_commit(bar_empty + 8 * stage);
-                    if (++stage == TC_STAGES) { stage = 0; phase ^= 1u; }
+                    if (alive) tc_commit(bar_tfull + 8 * buf);
+                    ++handover;
                 }
-                if (alive) tc_commit(bar_tfull + 8 * buf);
             }
         }
-    } else if (warp >= 2 + TC_EPI_WARPS) {
+    }
+    } else if (warp >= TC_FIRST_EPI_WARP + TC_EPI_WARPS) {
         // ------------------------------------------------------------------- transform (in-kernel split)
+        TC_SHRINK_REGS();
 #if TC_SPLIT_INKERNEL
-        const uint32_t t = threadIdx.x - 32 * (2 + TC_EPI_WARPS);   // 0 .. 32*TC_XFORM_WARPS-1
+        const uint32_t t = threadIdx.x - 32 * (TC_FIRST_EPI_WARP + TC_EPI_WARPS);   // 0 .. 32*TC_XFORM_WARPS-1
         const uint32_t ready_base = TC_CTA_GROUP == 2 ? tc_map_to_cta(bar_ready, 0u) : bar_ready;
         uint32_t stage = 0, phase = 0;
         bool alive = true;
@@ -556,25 +633,116 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
 #endif
     } else {
         // ---------------------------------------------------------------------------- epilogue
+        TC_GROW_REGS();
         const uint32_t quarter = warp & 3u;  // TMEM lane quarter this warp may read
-        const uint32_t cbase = ((warp - 2u) >> 2) * TC_EPI_COLS;  // first accumulator column of this warp's share
-        uint32_t local = 0;
+        const uint32_t cbase = ((warp - TC_FIRST_EPI_WARP) >> 2) * TC_EPI_COLS;  // first accumulator column of this warp's share
+        uint32_t handover = 0;               // accumulator buffers taken from the MMA issuer so far
         bool alive = true;
         // the accumulator buffer is handed back to the leader's MMA thread
         const uint32_t tempty_base = TC_CTA_GROUP == 2 ? tc_map_to_cta(bar_tempty, 0u) : bar_tempty;
-        for (uint32_t tile = unit0; alive && tile < num_tiles; tile += unit_stride, ++local) {
+        for (uint32_t tile = unit0; alive && tile < num_tiles; tile += unit_stride) {
             const uint32_t z = tile / tiles_mn;
             uint32_t tx, ty;
             sgemm_tile_raster(tile - z * tiles_mn, (uint32_t)num_wg_x, (uint32_t)num_wg_y, OPT_WGM, tx, ty);
             const uint32_t kb_begin = min(kb_total, z * kb_per), kb_end = min(kb_total, kb_begin + kb_per);
             const bool empty_k = kb_begin == kb_end;
-            const uint32_t buf = local & 1u, acc_phase = (local >> 1) & 1u;
             const uint32_t row = tx * TC_UMMA_M + cta_rank * TC_BM + quarter * 32 + lane;
             const uint32_t col0 = ty * TC_BN;
             const bool partial = split_k > 1;
             float *out = partial ? ws + (uint64_t)z * m * n : d;
             const uint32_t ldo = partial ? m : ldd;
             const bool use_c = !partial && beta != 0.0f;
+#if TC_ACC_CHUNK
+            const uint32_t chunks = (empty_k || !chunk_blocks) ? 1u : tc_chunk_count(kb_end - kb_begin, chunk_blocks);
+            {
+                // ---- the tile's accumulation chunks are added up in a running sum held in registers, then the sum
+                // is scaled, combined with C and stored.  (Why chunks: the tensor core adds into its accumulator with
+                // truncation — toward zero, two guard bits — so a long chain of MMAs drifts toward zero in proportion
+                // to its length.  The chain is cut every acc_chunk k-blocks; the partial sums are added here in FP32
+                // with round-to-nearest, in chunk order, so results do not depend on timing.)  Every TMEM buffer goes
+                // back to the issuer as soon as it is added, so the issuer runs two chunks ahead while this tile is
+                // written out.
+                if (use_c) {
+                    // ask L2 for this warp's part of the C tile now: lane L covers columns L, L + 32, ... of the warp's
+                    // share (first and last row: a warp's 128 bytes of a column may straddle two lines)
+                    const uint32_t row_first = row - lane;
+                    if (row_first < m) {
+                        const uint32_t row_last = min(row_first + 31u, m - 1u);
+#pragma unroll
+                        for (int j = 0; j < TC_EPI_COLS / 32; ++j) {
+                            const uint32_t col = col0 + cbase + j * 32 + lane;
+                            if (col < n) {
+                                asm volatile("prefetch.global.L2 [%0];" ::"l"(c + row_first + (uint64_t)col * ldc));
+                                asm volatile("prefetch.global.L2 [%0];" ::"l"(c + row_last + (uint64_t)col * ldc));
+                            }
+                        }
+                    }
+                }
+                // C is fetched TC_CW columns at a time, two pieces ahead of its use (three register buffers); the
+                // first two pieces are requested before the main loop of the tile has even finished.  (C may be the
+                // same buffer as D: every element is read before this same thread overwrites it.)
+                float cv[3][TC_CW];
+                auto fetch_cw = [&](int piece, float (&dst)[TC_CW]) {
+                    if (use_c && row < m) {
+#pragma unroll
+                        for (int j = 0; j < TC_CW; ++j) {
+                            const uint32_t col = col0 + cbase + piece * TC_CW + j;
+                            dst[j] = col < n ? c[row + (uint64_t)col * ldc] : 0.0f;
+                        }
+                    }
+                };
+                fetch_cw(0, cv[0]);
+                if (TC_EPI_COLS / TC_CW > 1) fetch_cw(1, cv[1]);
+                float sum[TC_EPI_COLS];
+                for (uint32_t ch = 0; ch < chunks; ++ch, ++handover) {
+                    const uint32_t buf = handover & 1u, acc_phase = (handover >> 1) & 1u;
+                    alive = __all_sync(0xffffffffu, tc_wait(waiter, bar_tfull + 8 * buf, acc_phase, 0x400u + buf, tile, ch));
+                    if (!alive) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int cc = 0; cc < TC_EPI_COLS / 16; ++cc) {
+                        uint32_t r[16];
+                        tc_tmem_ld16(tmem_base + ((quarter * 32u) << 16) + buf * TC_BN + cbase + cc * 16, r);
+                        tc_tmem_ld_wait();
+                        if (ch == 0) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) sum[cc * 16 + j] = empty_k ? 0.0f : __uint_as_float(r[j]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) sum[cc * 16 + j] += __uint_as_float(r[j]);
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (TC_CTA_GROUP == 2) tc_mbar_arrive_cluster(tempty_base + 8 * buf);
+                        else tc_mbar_arrive(bar_tempty + 8 * buf);
+                    }
+                }
+                if (!alive) break;
+#pragma unroll
+                for (int piece = 0; piece < TC_EPI_COLS / TC_CW; ++piece) {
+                    if (piece + 2 < TC_EPI_COLS / TC_CW) fetch_cw(piece + 2, cv[(piece + 2) % 3]);
+                    if (row < m) {
+#pragma unroll
+                        for (int j = 0; j < TC_CW; ++j) {
+                            const uint32_t col = col0 + cbase + piece * TC_CW + j;
+                            if (col < n) {
+                                float v = sum[piece * TC_CW + j];
+                                if (!partial) {
+                                    v *= alpha;
+                                    if (use_c) v = fmaf(beta, cv[piece % 3][j], v);
+                                }
+                                out[row + (uint64_t)col * ldo] = v;
+                            }
+                        }
+                    }
+                }
+            }
+#else
+            // one accumulator per tile: drained straight from TMEM
+            const uint32_t buf = handover & 1u, acc_phase = (handover >> 1) & 1u;
+            ++handover;
             // C is fetched one 32-column chunk ahead of its use, all 32 loads of a chunk in flight together; the
             // first chunk is requested before the accumulator is even complete, so its latency hides behind the
             // tile's main loop.  (C may be the same buffer as D: every element is read before this same thread
@@ -620,6 +788,7 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                 if (TC_CTA_GROUP == 2) tc_mbar_arrive_cluster(tempty_base + 8 * buf);
                 else tc_mbar_arrive(bar_tempty + 8 * buf);
             }
+#endif  // TC_ACC_CHUNK
         }
     }
 

@@ -55,6 +55,7 @@ VARIANT_TENSOR = "tcgen05_3xtf32"
 VARIANT_SIMT = "simt_ffma"
 KERNEL_ENTRY = "generated_gemm"     # the entry name the runner and the tuner hard-code
 SIMT_FALLBACK_ENTRY = "generated_gemm_simt"
+WHOLEK_ENTRY = "generated_gemm_wholek"   # twin of the main tcgen05 kernel that accumulates all of K in one chain
 SKINNY_ENTRY = "generated_gemm_skinny"   # companion tcgen05 kernel for low-intensity shapes (tensor cubins)
 
 # The 15 arguments of the kernel ABI in order: (typename, name, bytes).
@@ -157,7 +158,7 @@ class GemmSolutionConfig:
                  mfma: Tuple[int, int, int, int], wave_group: Tuple[int, int], wave_tiling: Tuple[int, int],
                  depth_k: int, trans_a: bool, trans_b: bool, vmem_stage: int = 1, *,
                  a_major: str = "mn", terms: int = 3, split: str = "prepass",
-                 epilogue_warps: Optional[int] = None, companion: bool = True):
+                 epilogue_warps: Optional[int] = None, companion: bool = True, acc_chain: Optional[int] = None):
         self.a_type = a_type
         self.b_type = b_type
         self.cd_type = cd_type
@@ -180,6 +181,12 @@ class GemmSolutionConfig:
         # that the runner uses for problems of low arithmetic intensity, where a pre-pass over the operands would
         # cost as much as the GEMM itself
         self.companion = companion
+        # tensor variant: how many k a product is accumulated inside the tensor core before the partial sum is added,
+        # in FP32 with round-to-nearest, to a running sum in the epilogue warps' registers.  The tensor core adds with
+        # truncation, so an unbroken chain drifts toward zero in proportion to its length (for same-signed data the
+        # error of a K = 8192 chain is 16 times the parity bound; a chain of 128 stays at a quarter of it for any K).
+        # None: 128 when the running sum fits the register file, else 0; 0: all of K in one chain
+        self.acc_chain = acc_chain
         self.split = split          # tensor variant: where lo = x - trunc_tf32(x) is made: "prepass" (a kernel writes
                                     # A_lo, B_lo to global memory once per call) or "inkernel" (transform warps make the
                                     # lo tiles in shared memory from the TMA-landed raw tiles)
@@ -244,6 +251,23 @@ class GemmSolutionConfig:
             raise RuntimeError("a transposed B is staged in 32-column chunks: tile N per CTA must be a multiple of 32")
         if self.split == "inkernel" and self.a_major == "k":
             raise RuntimeError("the K-major packed copy of A is made by a pre-pass; it excludes split='inkernel'")
+        # the running sum of chunked accumulation: tile N / (epilogue warps per lane quarter) registers per epilogue
+        # thread, next to about 72 others, for every thread of the block (one register allocation per kernel)
+        threads = 128 + 32 * self.epilogue_warps + (128 if self.split == "inkernel" else 0)
+        sum_regs = bn // (self.epilogue_warps // 4)
+        # registers an epilogue thread can have: an even share of its scheduler partition's 512 per lane, or, with
+        # 8 epilogue warps, what is left when the other warp groups shrink to 56 (the kernel's register hand-over)
+        per_partition = threads // 128
+        epi_regs = (512 - (per_partition - 2) * 56) // 2 if self.epilogue_warps == 8 else min(255, 512 // per_partition)
+        fits = sum_regs + 72 <= min(epi_regs // 8 * 8, 232)
+        self._acc_chain_requested = self.acc_chain
+        if self.acc_chain is None:
+            self.acc_chain = max(128, self.depth_k) if fits else 0
+        if self.acc_chain < 0 or self.acc_chain % self.depth_k:
+            raise RuntimeError(f"acc_chain = {self.acc_chain} must be 0 or a multiple of depth_k = {self.depth_k}")
+        if self.acc_chain and not fits:
+            raise RuntimeError(f"acc_chain: a running sum of {sum_regs} registers per thread does not "
+                               f"fit a block of {threads} threads")
         if self.stages * 24 + 40 > 256:
             raise RuntimeError(f"{self.stages} stages exceed the barrier block of the kernel")
         if self.stages < 2:
@@ -286,8 +310,8 @@ class GemmSolutionConfig:
     @property
     def num_workitems(self) -> int:
         if self.variant == VARIANT_TENSOR:
-            # TMA warp + MMA warp + epilogue warps (+ four transform warps for the in-kernel split)
-            return 64 + 32 * self.epilogue_warps + (128 if self.split == "inkernel" else 0)
+            # first group of four warps (TMA, MMA, two spare) + epilogue warps (+ four transform warps for the in-kernel split)
+            return 128 + 32 * self.epilogue_warps + (128 if self.split == "inkernel" else 0)
         bm, bn = self.tile_size
         tm, tn = self.simt_thread_tile
         return (bm // tm) * (bn // tn)
@@ -309,13 +333,16 @@ class GemmSolutionConfig:
             cols *= 2
         return cols
 
+    def _ring_bytes(self) -> int:
+        bn_cta = self.tile_size[1] // self.wave_group[0]                         # a CTA pair splits B's columns
+        stage = 2 * (128 * self.depth_k * 4) + 2 * (bn_cta * self.depth_k * 4)   # A_hi, A_lo, B_hi, B_lo
+        return self.stages * stage + 1024 + 256                                  # + alignment slack + barriers
+
     @property
     def lds_usage_bytes(self) -> int:
         bm, bn = self.tile_size
         if self.variant == VARIANT_TENSOR:
-            bn_cta = bn // self.wave_group[0]                                    # a CTA pair splits B's columns
-            stage = 2 * (128 * self.depth_k * 4) + 2 * (bn_cta * self.depth_k * 4)  # A_hi, A_lo, B_hi, B_lo
-            return self.stages * stage + 1024 + 256                              # + alignment slack + barriers
+            return self._ring_bytes()
         return 2 * self.depth_k * (bm + 4 + bn + 4) * 4                          # double-buffered, padded A and B
 
     @property
@@ -328,7 +355,7 @@ class GemmSolutionConfig:
             return None
         return GemmSolutionConfig(self.a_type, self.b_type, self.cd_type, self.scalar_type, (128, 128, 1, 8), (1, 1), (1, 1),
                                   32, self.trans_a, self.trans_b, vmem_stage=2, split="inkernel", terms=self.terms,
-                                  companion=False)
+                                  companion=False, acc_chain=0 if self._acc_chain_requested == 0 else None)
 
     def to_dict(self) -> Dict:
         d = {
@@ -364,6 +391,8 @@ class GemmSolutionConfig:
                 "terms": self.terms,
                 "split": self.split,
                 "epilogue_warps": self.epilogue_warps,
+                "acc_chain": self.acc_chain,
+                "wholek_entry": WHOLEK_ENTRY if self.acc_chain else "",
                 "fallback_entry": SIMT_FALLBACK_ENTRY,
                 "fallback_tile": [fb.tile_size[0], fb.tile_size[1], fb.depth_k],
                 "fallback_threads": fb.num_workitems,
@@ -375,6 +404,7 @@ class GemmSolutionConfig:
                     "skinny_tile": [sk.tile_size[0], sk.tile_size[1], sk.depth_k],
                     "skinny_threads": sk.num_workitems,
                     "skinny_smem_bytes": sk.lds_usage_bytes,
+                    "skinny_acc_chain": sk.acc_chain,
                 })
         return d
 
@@ -421,7 +451,8 @@ def _tensor_defines(config: GemmSolutionConfig):
             ("TC_CTA_GROUP", config.wave_group[0]), ("TC_SPLIT_INKERNEL", 1 if config.split == "inkernel" else 0),
             ("TC_EPI_WARPS", config.epilogue_warps),
             ("TC_A_KMAJOR", 1 if (config.a_major == "k" or config.trans_a) else 0),
-            ("TC_B_MNMAJOR", 1 if config.trans_b else 0), ("TC_TERMS", config.terms)]
+            ("TC_B_MNMAJOR", 1 if config.trans_b else 0), ("TC_TERMS", config.terms),
+            ("TC_ACC_CHUNK", config.acc_chain // config.depth_k)]
 
 
 def _trans_defines(cfg: GemmSolutionConfig):
@@ -461,6 +492,18 @@ def gemm(context: GpuContext, name: str, arch: str, config: GemmSolutionConfig, 
         template = _read("sgemm_tcgen05.cuh")
         out.write(_defines(_tensor_defines(config)))
         out.write(template)
+        if config.acc_chain:
+            # twin of the main kernel without the running sum (all of K in one tensor-core chain, accumulator written
+            # out straight from TMEM): what the runner launches when a tile has a single accumulation chunk anyway
+            # (K up to two chains) or the caller turns chunking off
+            body = template.split("// ==== end of the per-kernel section")[0]
+            body = re.sub(r"\bTC_", "TCW_", body)
+            body = re.sub(r"\btc_", "tcw_", body)
+            body = re.sub(r"\bTc(?=[A-Z])", "Tcw", body)
+            body = re.sub(r"\b%s\b" % KERNEL_ENTRY, WHOLEK_ENTRY, body)
+            out.write("\n// ---- twin of the main kernel: whole-K accumulation, epilogue straight from TMEM ----\n")
+            out.write(_defines([(k.replace("TC_", "TCW_", 1), 0 if k == "TC_ACC_CHUNK" else v) for k, v in _tensor_defines(config)]))
+            out.write(body)
         companion = config.companion_config()
         if companion is not None:
             # second instance of the per-kernel part of the template under its own names: macros TC_* -> TCS_*,

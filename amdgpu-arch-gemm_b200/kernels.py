@@ -5,8 +5,8 @@ from __future__ import annotations
 from pathlib import Path
 from typing import Dict, Tuple
 
-from generator.generator import (GemmOptimizations, GemmSolutionConfig, DataType, build_kernel, simt_config,
-                                 tensor_config)
+from generator.generator import (KERNEL_ENTRY, GemmOptimizations, GemmSolutionConfig, DataType, build_kernel,
+                                 default_arguments, gemm, simt_config, tensor_config)
 
 GENERATED_DIR = Path(__file__).resolve().parent / "_generated"
 F = DataType.FP32
@@ -38,7 +38,9 @@ REGISTRY = {
     # the same tile reading A from K-major packed copies, and a plain-TF32 build (bring-up aids)
     "tc_128x128x32_s3_ak": (lambda: tensor_config(128, 32, 3, a_major="k"), dict(wgm=8)),
     "tc_128x128x16_s6_ak": (lambda: tensor_config(128, 16, 6, a_major="k"), dict(wgm=8)),
-    "tc_128x128x32_s3_1x": (lambda: tensor_config(128, 32, 3, terms=1), dict(wgm=8)),
+    # whole-K accumulation inside the tensor core (no chunking): the kernels the recorded device arithmetic is pinned with
+    "tc_128x128x32_s3_1x": (lambda: tensor_config(128, 32, 3, terms=1, acc_chain=0), dict(wgm=8)),
+    "tc2_256x256x32_s3_c0": (lambda: tensor_config(256, 32, 3, cluster=2, acc_chain=0), dict(wgm=8)),
     # transposed operands (TN: A stored K x M, NT: B stored N x K, TT: both)
     "tc2_256x256x32_s3_tn": (lambda: tensor_config(256, 32, 3, cluster=2, trans_a=True), dict(wgm=8)),
     "tc2_256x256x32_s3_nt": (lambda: tensor_config(256, 32, 3, cluster=2, trans_b=True), dict(wgm=8)),
@@ -66,12 +68,24 @@ def paths(name: str) -> Tuple[str, str]:
     return str(d / "generated_gemm.cubin"), str(d / "generated_gemm.toml")
 
 
+_fresh = set()   # kernels whose in-tree files were checked (or built) by this process
+
+
 def ensure(name: str, force: bool = False) -> Tuple[str, str]:
-    """Return (cubin, toml) of a registered kernel, generating and compiling it if it is not there."""
+    """Return (cubin, toml) of a registered kernel, generating and compiling it if it is not there or if the source
+    the generator emits today differs from the one the cubin was compiled from (a changed knob or kernel template)."""
     cubin, toml = paths(name)
-    if force or not (Path(cubin).exists() and Path(toml).exists()):
-        factory, opt_kwargs = REGISTRY[name]
-        build_kernel(str(GENERATED_DIR / name), factory(), GemmOptimizations(1, **opt_kwargs))
+    if name in _fresh and not force:
+        return cubin, toml
+    factory, opt_kwargs = REGISTRY[name]
+    config, opt = factory(), GemmOptimizations(1, **opt_kwargs)
+    stale = force or not (Path(cubin).exists() and Path(toml).exists())
+    if not stale:
+        source = Path(cubin).with_suffix(".cu")
+        stale = not source.exists() or source.read_text() != gemm(None, KERNEL_ENTRY, "sm_100a", config, opt, default_arguments())
+    if stale:
+        build_kernel(str(GENERATED_DIR / name), config, opt)
+    _fresh.add(name)
     return cubin, toml
 
 

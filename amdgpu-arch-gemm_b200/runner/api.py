@@ -37,7 +37,8 @@ class SgemmConfig(ctypes.Structure):
         ("fallback_tile", ctypes.c_int32 * 3),
         ("fallback_threads", ctypes.c_int32), ("entry", ctypes.c_char * 64), ("fallback_entry", ctypes.c_char * 64),
         ("skinny_tile", ctypes.c_int32 * 3), ("skinny_threads", ctypes.c_int32), ("skinny_smem_bytes", ctypes.c_int32),
-        ("skinny_entry", ctypes.c_char * 64),
+        ("skinny_entry", ctypes.c_char * 64), ("acc_chain", ctypes.c_int32), ("skinny_acc_chain", ctypes.c_int32),
+        ("wholek_entry", ctypes.c_char * 64),
     ]
 
 

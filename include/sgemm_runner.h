@@ -70,6 +70,13 @@ typedef struct sgemm_config {
     int32_t skinny_threads;
     int32_t skinny_smem_bytes;
     char skinny_entry[64];
+    /* tensor variant: k accumulated inside the tensor core before the partial sum moves to FP32 registers, as the
+     * kernels were generated (0: the kernel has no such path and accumulates all of K in one chain) */
+    int32_t acc_chain;
+    int32_t skinny_acc_chain;
+    /* twin of the main tensor kernel that accumulates all of K in one chain (empty: none); same tile, threads and
+     * shared memory as the main kernel */
+    char wholek_entry[64];
 } sgemm_config;
 
 /* Replaces getAsmKernelConfig (runner/generator_runner.cpp:100-124).  Host only, needs no GPU. */
@@ -149,10 +156,17 @@ int sgemm_wait_selftest(sgemm_handle *h, uint32_t timeout_ms, uint32_t tag);
  * "wave_sync" 1 (default) lets the persistent CTAs of the tensor kernel wait briefly for each other at tile
  * boundaries so that they keep sharing operand panels in L2 (a bounded, soft wait: performance only);
  * "pipeline_host" 1 (default) lets sgemm_run_host overlap transfers and compute over column chunks;
- * "profile" 1 brackets every main-GEMM-kernel launch with an event pair (read with "profile_main_ns"). */
+ * "profile" 1 brackets every main-GEMM-kernel launch with an event pair (read with "profile_main_ns");
+ * "acc_chain": k per tensor-core accumulation chain, -1 (default) = as the kernel was generated (128 unless its
+ * TOML says otherwise), 0 = all of K in one chain (fastest; the tensor core's truncating adds then drift toward zero
+ * in proportion to K), otherwise a multiple of the kernel's k-block; a kernel generated without the register path
+ * (acc_chain = 0 in its TOML) accepts only -1 and 0.  Problems whose K is at most two chains long are accumulated
+ * in one chain in any case, and, like acc_chain 0, run on the cubin's whole-K twin of the main kernel. */
 int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value);
 
 /* Facts: "variant" (of the cubin), "last_variant" (1 tensor main / 2 simt / 3 tensor companion), "last_split_k", "last_grid",
+ * "last_acc_chain" (k per accumulation chain of the last tensor launch, 0 = whole K), "acc_chain" and
+ * "skinny_acc_chain" (the chains the main and the companion tensor kernel were generated with),
  * "launches" (kernel launches issued so far), "tile_m", "tile_n", "sm_count", "workspace_bytes",
  * "profile_count" (bracketed launches since the last read), "profile_main_ns" (their summed device time in
  * nanoseconds; synchronises on them and resets the tally). */

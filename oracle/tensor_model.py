@@ -122,12 +122,39 @@ def _epilogue(partials, c, alpha, beta) -> np.ndarray:
     return v
 
 
-def gemm(a, b, c=None, alpha: float = 1.0, beta: float = 0.0, terms: int = 3, split_k: int = 1, bk: int = 32) -> np.ndarray:
-    """D (m x n array) as a tensor kernel with k-block bk writes it: per split the accumulator above, then
-    v = alpha * (sum of the partials); fma(beta, c, v) when beta != 0."""
+def chain_ranges(k: int, chain: int):
+    """The k ranges of the accumulation chunks of one launch unit: chunks of `chain`, the first two twice as long
+    (tc_chunk_span in csrc/sgemm_tcgen05.cuh); one range when chain is 0."""
+    if chain <= 0:
+        return [(0, k)]
+    out, k0 = [], 0
+    while k0 < k:
+        span = 2 * chain if k0 < 4 * chain else chain
+        out.append((k0, min(k, k0 + span)))
+        k0 += span
+    return out
+
+
+def chained(a: np.ndarray, b: np.ndarray, terms: int = 3, chain: int = 0) -> np.ndarray:
+    """One launch unit's result for its k range.  chain = 0: one accumulator for the whole range.  chain > 0 (the
+    kernels' acc_chain): the tensor core accumulates the chunks of chain_ranges, and the chunks are added in order,
+    in FP32 with round-to-nearest, to a running sum that starts at zero; a single chunk is not re-added."""
+    ranges = chain_ranges(a.shape[1], chain)
+    if len(ranges) == 1:
+        return accumulate(a, b, terms)
+    total = np.zeros((a.shape[0], b.shape[1]), dtype=np.float32)
+    for k0, k1 in ranges:
+        total = (total + accumulate(a[:, k0:k1], b[k0:k1, :], terms)).astype(np.float32)
+    return total
+
+
+def gemm(a, b, c=None, alpha: float = 1.0, beta: float = 0.0, terms: int = 3, split_k: int = 1, bk: int = 32,
+         chain: int = 0) -> np.ndarray:
+    """D (m x n array) as a tensor kernel with k-block bk and accumulation chain `chain` writes it: per split the
+    result above, then v = alpha * (sum of the partials); fma(beta, c, v) when beta != 0."""
     a = np.ascontiguousarray(a, dtype=np.float32)
     b = np.ascontiguousarray(b, dtype=np.float32)
-    parts = [accumulate(a[:, k0:k1], b[k0:k1, :], terms) for k0, k1 in split_ranges(a.shape[1], bk, split_k)]
+    parts = [chained(a[:, k0:k1], b[k0:k1, :], terms, chain) for k0, k1 in split_ranges(a.shape[1], bk, split_k)]
     return _epilogue(parts, c, alpha, beta)
 
 

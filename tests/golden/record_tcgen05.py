@@ -20,7 +20,7 @@ import kernels  # noqa: E402
 import tensor_cases  # noqa: E402
 from runner import api  # noqa: E402
 
-KERNEL_OF_TERMS = {1: "tc_128x128x32_s3_1x", 3: "tc2_256x256x32_s3"}
+KERNEL_OF_TERMS = {1: "tc_128x128x32_s3_1x", 3: "tc2_256x256x32_s3_c0"}   # both accumulate all of K in TMEM
 
 
 def device_gemm(r, a_mat, b_mat):

@@ -10,8 +10,10 @@ kernel's roles as coroutines over a small mbarrier simulator and lets a seeded r
 * transform      (in-kernel split only) waits ``full[s]``, writes the lo tile, arrives on ``ready[s]``;
 * MMA issuer     (leader CTA only) waits ``tmem_empty[b]``, then per k-block ``full[s]``/``ready[s]``; its MMAs
                  complete asynchronously and in order, commits fire after them (``empty[s]``, ``tmem_full[b]``, in a
-                 pair to both CTAs);
-* epilogue       waits ``tmem_full[b]``, reads the accumulator, arrives on the leader's ``tmem_empty[b]``.
+                 pair to both CTAs).  With ``chunk`` > 0 a tile's k-blocks are accumulated in chunks: every chunk
+                 starts a fresh accumulator in the next buffer and is handed over on its own;
+* epilogue       waits ``tmem_full[b]``, reads the accumulator (adding the chunks of a tile up in chunk order),
+                 arrives on the leader's ``tmem_empty[b]``; buffers alternate per hand-over, not per tile.
 
 Shared-memory stages and TMEM buffers carry tags (tile, k-block); every read checks the tag it expects, every
 overwrite checks that the previous contents were consumed.  A run fails on a wrong tag, an overwrite of live data, a
@@ -66,14 +68,15 @@ class Cta:
     hi: List[Optional[Tuple[int, int]]] = field(default_factory=list)    # tag of the raw tiles in each stage
     lo: List[Optional[Tuple[int, int]]] = field(default_factory=list)    # tag of the lo tiles
     reads_left: List[int] = field(default_factory=list)                  # MMAs that still have to read the stage
-    tmem: List[Optional[Tuple[int, int]]] = field(default_factory=list)  # (tile, k-blocks accumulated)
+    tmem: List[Optional[Tuple[int, int, int]]] = field(default_factory=list)  # (tile, first k-block, k-blocks accumulated)
     tmem_readers: List[int] = field(default_factory=list)
 
 
 class Model:
     def __init__(self, tiles: int, kblocks: int, stages: int, cta_group: int = 1, epi_warps: int = 4,
-                 inkernel: bool = False, units: int = 2, seed: int = 0, bug: str = ""):
+                 inkernel: bool = False, units: int = 2, seed: int = 0, bug: str = "", chunk: int = 0):
         self.tiles, self.kblocks, self.stages = tiles, kblocks, stages
+        self.chunk = chunk if chunk > 0 else kblocks      # k-blocks per accumulator hand-over
         self.G, self.E, self.inkernel, self.units, self.bug = cta_group, epi_warps, inkernel, units, bug
         self.rng = random.Random(seed)
         self.pending_async: List = []      # (callable) asynchronous completions (TMA landings, MMA completions)
@@ -145,54 +148,78 @@ class Model:
                     stage, phase = 0, phase ^ 1
                 yield
 
+    def chunks_of_tile(self):
+        """Chunks of `chunk` k-blocks, the first two twice as long (tc_chunk_span in the kernel)."""
+        out, first = [], 0
+        while first < self.kblocks:
+            span = 2 * self.chunk if first < 4 * self.chunk else self.chunk
+            out.append((first, min(self.kblocks, first + span)))
+            first += span
+        return out
+
     def mma(self, unit):
         ctas = self.clusters[unit]
         leader = ctas[0]
         stage = phase = 0
-        for local, tile in enumerate(self.my_tiles(unit)):
-            buf, acc_phase = local & 1, (local >> 1) & 1
-            while not leader.tempty[buf].try_wait(acc_phase ^ 1):
-                yield
-            for c in ctas:
-                if c.tmem_readers[buf]:
-                    raise ProtocolError(f"MMA overwrites accumulator {buf} while the epilogue reads it")
-            for kb in range(self.kblocks):
-                bar = leader.ready[stage] if self.inkernel else leader.full[stage]
-                while not bar.try_wait(phase):
+        handover = 0
+        for tile in self.my_tiles(unit):
+            for first, end in self.chunks_of_tile():
+                buf, acc_phase = handover & 1, (handover >> 1) & 1
+                if self.bug == "buffer_per_tile":
+                    local = (tile - unit) // self.units
+                    buf, acc_phase = local & 1, (local >> 1) & 1
+                while not leader.tempty[buf].try_wait(acc_phase ^ 1):
                     yield
                 for c in ctas:
-                    if c.hi[stage] != (tile, kb) or c.lo[stage] != (tile, kb):
-                        raise ProtocolError(f"MMA of {(tile, kb)} finds {c.hi[stage]}/{c.lo[stage]} in stage {stage} of CTA {c.rank}")
-                    c.reads_left[stage] += 1
+                    if c.tmem_readers[buf]:
+                        raise ProtocolError(f"MMA overwrites accumulator {buf} while the epilogue reads it")
+                for kb in range(first, end):
+                    bar = leader.ready[stage] if self.inkernel else leader.full[stage]
+                    while not bar.try_wait(phase):
+                        yield
+                    for c in ctas:
+                        if c.hi[stage] != (tile, kb) or c.lo[stage] != (tile, kb):
+                            raise ProtocolError(f"MMA of {(tile, kb)} finds {c.hi[stage]}/{c.lo[stage]} in stage {stage} of CTA {c.rank}")
+                        c.reads_left[stage] += 1
 
-                def done(s=stage, t=tile, k=kb, b=buf, last=(kb == self.kblocks - 1)):
-                    for c in ctas:      # in-order completion: accumulate, then the commits fire
-                        c.reads_left[s] -= 1
-                        c.tmem[b] = (t, k + 1) if (k == 0 or c.tmem[b] == (t, k)) else ("corrupt", c.tmem[b], t, k)
-                        if self.bug != "no_empty_commit_to_peer" or c.rank == 0:
-                            c.empty[s].arrive()
-                        if last:
-                            c.tfull[b].arrive()
-                self.pending_async.append(("ordered", unit, done))
-                stage += 1
-                if stage == self.stages:
-                    stage, phase = 0, phase ^ 1
-                yield
+                    def done(s=stage, t=tile, k=kb, b=buf, f=first, last=(kb == end - 1)):
+                        for c in ctas:      # in-order completion: accumulate, then the commits fire
+                            c.reads_left[s] -= 1
+                            fresh = k == f   # the first MMA of a chunk overwrites the buffer
+                            c.tmem[b] = (t, f, k - f + 1) if (fresh or c.tmem[b] == (t, f, k - f)) else ("corrupt", c.tmem[b], t, k)
+                            if self.bug != "no_empty_commit_to_peer" or c.rank == 0:
+                                c.empty[s].arrive()
+                            if last:
+                                c.tfull[b].arrive()
+                    self.pending_async.append(("ordered", unit, done))
+                    stage += 1
+                    if stage == self.stages:
+                        stage, phase = 0, phase ^ 1
+                    yield
+                handover += 1
 
     def epilogue(self, unit, cta, warp):
         leader = self.clusters[unit][0]
-        for local, tile in enumerate(self.my_tiles(unit)):
-            buf, acc_phase = local & 1, (local >> 1) & 1
-            while not cta.tfull[buf].try_wait(acc_phase):
+        handover = 0
+        for tile in self.my_tiles(unit):
+            blocks_summed = 0
+            for first, end in self.chunks_of_tile():
+                buf, acc_phase = handover & 1, (handover >> 1) & 1
+                while not cta.tfull[buf].try_wait(acc_phase):
+                    yield
+                if cta.tmem[buf] != (tile, first, end - first):
+                    raise ProtocolError(f"epilogue of tile {tile} chunk {first} finds {cta.tmem[buf]} in accumulator {buf}")
+                cta.tmem_readers[buf] += 1
                 yield
-            if cta.tmem[buf] != (tile, self.kblocks):
-                raise ProtocolError(f"epilogue of tile {tile} finds {cta.tmem[buf]} in accumulator {buf}")
-            cta.tmem_readers[buf] += 1
-            yield
+                blocks_summed += end - first          # the running sum in registers
+                cta.tmem_readers[buf] -= 1
+                leader.tempty[buf].arrive()
+                handover += 1
+                yield
+            if blocks_summed != self.kblocks:
+                raise ProtocolError(f"tile {tile}: {blocks_summed} of {self.kblocks} k-blocks reached the output")
             key = (tile, cta.rank, warp)
             self.output[key] = self.output.get(key, 0) + 1
-            cta.tmem_readers[buf] -= 1
-            leader.tempty[buf].arrive()
             yield
 
     # -------------------------------------------------------------------------------------------- scheduler

@@ -32,9 +32,17 @@ def test_basic_sgemm_gen_reference_style():
 
 def test_tile_product_rule_and_properties():
     cfg = g.tensor_config(256, 32, 2)
-    assert cfg.tile_size == (128, 256) and cfg.num_workitems == 64 + 32 * 8 and cfg.stages == 2
-    assert g.tensor_config(256, 32, 2, epilogue_warps=4).num_workitems == 192
-    assert cfg.lds_usage_bytes == 2 * (2 * 128 * 32 * 4 + 2 * 256 * 32 * 4) + 1024 + 256
+    assert cfg.tile_size == (128, 256) and cfg.num_workitems == 128 + 32 * 8 and cfg.stages == 2
+    assert g.tensor_config(256, 32, 2, epilogue_warps=4).num_workitems == 256   # warp groups of four: 4 + 4 warps
+    ring = 2 * (2 * 128 * 32 * 4 + 2 * 256 * 32 * 4) + 1024 + 256
+    assert cfg.acc_chain == 128 and cfg.lds_usage_bytes == ring      # chunked accumulation by default (chains of 128 k)
+    whole_k = g.tensor_config(256, 32, 2, acc_chain=0)
+    assert whole_k.lds_usage_bytes == ring and whole_k.to_dict()["acc_chain"] == 0
+    with pytest.raises(RuntimeError):
+        g.tensor_config(256, 32, 2, acc_chain=100)                   # not a multiple of depth_k
+    with pytest.raises(RuntimeError):
+        g.tensor_config(256, 32, 2, epilogue_warps=4, acc_chain=128)   # 256 running-sum registers per thread
+    assert g.tensor_config(256, 32, 2, epilogue_warps=4).acc_chain == 0   # ... so the default there is one chain
     assert cfg.tmem_columns == 512
     s = g.simt_config(128, 128, 16, 8, 8)
     assert s.tile_size == (128, 128) and s.num_workitems == 256

@@ -21,7 +21,7 @@ def as_matrix(flat, rows, cols):
 
 def test_recorded_cases_model_and_device_agree(runner_of, golden_dir):
     recorded = np.load(golden_dir / "tcgen05_recorded.npz")
-    runners = {1: runner_of("tc_128x128x32_s3_1x"), 3: runner_of("tc2_256x256x32_s3")}
+    runners = {1: runner_of("tc_128x128x32_s3_1x"), 3: runner_of("tc2_256x256x32_s3_c0")}   # whole K in one chain
     for name, (a_mat, b_mat, terms) in tensor_cases.cases().items():
         m, k = a_mat.shape
         n = b_mat.shape[1]
@@ -41,15 +41,16 @@ def test_hand_examples_on_the_device(runner_of):
         assert float(d[0, 0]) == expected, rule
 
 
-TENSOR_CASES = [("tc2_256x256x32_s3", TENSOR), ("tc_128x256x32_s2", TENSOR), ("tc_128x128x16_s7", TENSOR),
+TENSOR_CASES = [("tc2_256x256x32_s3", TENSOR), ("tc2_256x256x32_s3_c0", TENSOR), ("tc_128x256x32_s2", TENSOR), ("tc_128x128x16_s7", TENSOR),
                 ("tc2i_256x256x32_s3", TENSOR), ("tc_128x128x32_s3_ak", TENSOR), ("tc2_256x256x32_s3_e4", TENSOR),
                 ("tc2_256x256x32_s3", SKINNY), ("tc2_256x256x32_s3_tt", TENSOR), ("tc2_256x256x32_s3_tn", TENSOR)]
 
 
 @pytest.mark.parametrize("kernel,force", TENSOR_CASES)
 @pytest.mark.parametrize("mnk", [(96, 80, 72), (130, 4, 300), (257, 129, 65), (200, 136, 520)])
-@pytest.mark.parametrize("alpha,beta,split_k", [(1.0, 0.0, 1), (0.75, -1.25, 1), (-2.5, 0.3, 3)])
-def test_tensor_kernels_equal_the_model_bit_for_bit(runner_of, kernel, force, mnk, alpha, beta, split_k):
+@pytest.mark.parametrize("alpha,beta,split_k,chain", [(1.0, 0.0, 1, -1), (0.75, -1.25, 1, -1), (-2.5, 0.3, 3, -1),
+                                                       (0.75, -1.25, 1, 64), (1.0, 0.5, 2, 0)])
+def test_tensor_kernels_equal_the_model_bit_for_bit(runner_of, kernel, force, mnk, alpha, beta, split_k, chain):
     m, n, k = mnk
     ta = kernel.endswith("_tt") or kernel.endswith("_tn")
     tb = kernel.endswith("_tt") or kernel.endswith("_nt")
@@ -60,11 +61,27 @@ def test_tensor_kernels_equal_the_model_bit_for_bit(runner_of, kernel, force, mn
     a, lda = stored(colmajor(a_mat), m, k, ta, ld=((k if ta else m) + 3) // 4 * 4)
     b, ldb = stored(colmajor(b_mat), k, n, tb, ld=((n if tb else k) + 3) // 4 * 4)
     r = runner_of(kernel)
-    d = run(r, a, b, colmajor(c_mat), m, n, k, alpha, beta, force=force, split_k=split_k, lda=lda, ldb=ldb)
+    if chain > 0 and r.info("skinny_acc_chain" if force == SKINNY else "acc_chain") == 0:
+        with pytest.raises(Exception, match="without chunked accumulation"):
+            r.set_option("acc_chain", chain)
+            try:
+                run(r, a, b, colmajor(c_mat), m, n, k, alpha, beta, force=force, split_k=split_k, lda=lda, ldb=ldb)
+            finally:
+                r.set_option("acc_chain", -1)
+        return
+    r.set_option("acc_chain", chain)    # -1: as generated, 0: one chain, else k per chain
+    try:
+        d = run(r, a, b, colmajor(c_mat), m, n, k, alpha, beta, force=force, split_k=split_k, lda=lda, ldb=ldb)
+    finally:
+        r.set_option("acc_chain", -1)
     assert r.info("last_variant") == force
+    # the runner reports the chain it launched with: the requested one, or 0 when the whole-K twin of the main kernel
+    # served a problem of at most two chains
+    assert chain < 0 or r.info("last_acc_chain") == (0 if force == TENSOR and k <= 2 * chain else chain)
     used_split = r.info("last_split_k")
     bk = 32 if force == SKINNY else int(kernel.split("_")[1].split("x")[2])
-    want = tensor_model.gemm(a_mat, b_mat, c_mat, alpha, beta, terms=3, split_k=used_split, bk=bk)
+    want = tensor_model.gemm(a_mat, b_mat, c_mat, alpha, beta, terms=3, split_k=used_split, bk=bk,
+                             chain=r.info("last_acc_chain"))
     assert np.array_equal(as_matrix(d, m, n), want)
 
 
@@ -87,3 +104,24 @@ def test_simt_kernels_equal_the_fma_chain_bit_for_bit(runner_of, built, kernel, 
     d = run(r, a, b, colmajor(c_mat), m, n, k, alpha, beta, force=SIMT, split_k=split_k, lda=lda, ldb=ldb)
     want = tensor_model.simt_gemm(a_mat, b_mat, c_mat, alpha, beta, split_k=r.info("last_split_k"), bk=bk)
     assert np.array_equal(as_matrix(d, m, n), want)
+
+
+def test_same_signed_inputs_need_the_chunked_accumulation(runner_of):
+    """With inputs of one sign nothing cancels, and the truncating adds of one long tensor-core chain all err the same
+    way: at K = 8192 the whole-K kernel misses the parity bound by an order of magnitude, the chunked kernel (chains
+    of 128, added in FP32 with round-to-nearest) stays well inside it."""
+    from oracle import oracle
+    m, n, k = 256, 256, 8192
+    a, b, _ = oracle.make_inputs(m, n, k, seed=3)
+    a, b = np.abs(a), np.abs(b)
+    ref = oracle.gemm(a, b, None, 1.0, 0.0, m, n, k)
+    bound = oracle.abs_bound(a, b, m, n, k)
+    whole = oracle.worst_ratio(run(runner_of("tc2_256x256x32_s3_c0"), a, b, None, m, n, k, force=TENSOR, split_k=1), ref, bound)
+    chunked = oracle.worst_ratio(run(runner_of("tc2_256x256x32_s3"), a, b, None, m, n, k, force=TENSOR, split_k=1), ref, bound)
+    assert chunked <= 1.0, chunked
+    assert whole > 5.0, whole
+    # against the exact product (FP64) the chunked kernel is closer than the FP32 oracle's own sequential sum
+    exact = a.reshape(k, m).T.astype(np.float64) @ b.reshape(n, k).T.astype(np.float64)
+    got = run(runner_of("tc2_256x256x32_s3"), a, b, None, m, n, k, force=TENSOR, split_k=1).reshape(n, m).T
+    assert float((np.abs(got - exact) / (1e-5 * exact)).max()) <= 0.4
+    print(f"same-signed inputs, K = {k}: worst ratio {whole:.2f} (one chain) -> {chunked:.3f} (chains of 128)")

@@ -35,3 +35,19 @@ def test_accumulator_barrier_must_count_both_ctas():
         except ProtocolError:
             caught += 1
     assert caught >= 30
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("inkernel", [False, True])
+@pytest.mark.parametrize("stages,kblocks,tiles,chunk", [(3, 8, 5, 4), (2, 7, 4, 3), (3, 9, 3, 1), (4, 5, 6, 2), (3, 4, 5, 8)])
+def test_chunked_accumulation_hands_buffers_over_per_chunk(cta_group, inkernel, stages, kblocks, tiles, chunk):
+    """Accumulator buffers alternate per hand-over (a tile may take an odd number of them), every chunk reaches the
+    running sum exactly once and a buffer is never overwritten while it is read."""
+    for seed in range(4):
+        assert Model(tiles, kblocks, stages, cta_group, 8, inkernel, units=2, seed=seed, chunk=chunk).run()
+
+
+def test_buffer_choice_per_tile_is_caught_with_chunks():
+    with pytest.raises(ProtocolError):
+        for seed in range(8):   # the issuer picks the buffer by tile, the epilogue by hand-over: they disagree
+            Model(tiles=5, kblocks=6, stages=3, cta_group=1, units=1, seed=seed, chunk=2, bug="buffer_per_tile").run()

@@ -82,3 +82,22 @@ def test_split_ranges_tile_k_without_gaps(k, bk, split):
     for part in parts:
         want = (want + part).astype(np.float32)
     assert np.array_equal(tm.gemm(a_mat, b_mat, split_k=split, bk=bk), want)
+
+
+@pytest.mark.parametrize("k,chain,want", [(100, 128, [(0, 100)]), (256, 128, [(0, 256)]), (300, 128, [(0, 256), (256, 300)]),
+                                          (1024, 128, [(0, 256), (256, 512), (512, 640), (640, 768), (768, 896), (896, 1024)]),
+                                          (520, 64, [(0, 128), (128, 256), (256, 320), (320, 384), (384, 448), (448, 512), (512, 520)]),
+                                          (77, 0, [(0, 77)])])
+def test_accumulation_chunks_follow_the_kernel_rule(k, chain, want):
+    assert tm.chain_ranges(k, chain) == want
+
+
+def test_chunked_accumulation_is_what_keeps_same_signed_sums_accurate():
+    """Same-signed data, K = 2048: one tensor-core chain drifts toward zero by several times the parity bound, chains
+    of 128 (added up in FP32, round to nearest) stay within a third of it."""
+    a_mat, b_mat = np.abs(tensor_cases.uniform((24, 2048), 41)), np.abs(tensor_cases.uniform((2048, 24), 42))
+    exact = a_mat.astype(np.float64) @ b_mat.astype(np.float64)
+    ratio = lambda d: float((np.abs(d - exact) / (1e-5 * exact)).max())  # noqa: E731  (all terms positive: bound = sum)
+    assert ratio(tm.gemm(a_mat, b_mat, chain=0)) > 3.0
+    assert ratio(tm.gemm(a_mat, b_mat, chain=128)) < 0.35
+    assert ((tm.gemm(a_mat, b_mat, chain=0) - exact) < 0).all()     # the drift is toward zero, for every element
