@@ -693,7 +693,9 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                 };
                 fetch_cw(0, cv[0]);
                 if (TC_EPI_COLS / TC_CW > 1) fetch_cw(1, cv[1]);
-                float sum[TC_EPI_COLS];
+                // the running sum: two columns per 64-bit register pair, added with the packed FP32 add (one
+                // instruction per two columns; each half is an ordinary round-to-nearest FP32 add)
+                uint64_t sum2[TC_EPI_COLS / 2];
                 for (uint32_t ch = 0; ch < chunks; ++ch, ++handover) {
                     const uint32_t buf = handover & 1u, acc_phase = (handover >> 1) & 1u;
                     alive = __all_sync(0xffffffffu, tc_wait(waiter, bar_tfull + 8 * buf, acc_phase, 0x400u + buf, tile, ch));
@@ -706,10 +708,14 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                         tc_tmem_ld_wait();
                         if (ch == 0) {
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) sum[cc * 16 + j] = empty_k ? 0.0f : __uint_as_float(r[j]);
+                            for (int j = 0; j < 8; ++j)
+                                asm("mov.b64 %0, {%1, %2};" : "=l"(sum2[cc * 8 + j])
+                                    : "r"(empty_k ? 0u : r[2 * j]), "r"(empty_k ? 0u : r[2 * j + 1]));
                         } else {
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) sum[cc * 16 + j] += __uint_as_float(r[j]);
+                            for (int j = 0; j < 8; ++j)
+                                asm("{\n\t.reg .b64 t;\n\tmov.b64 t, {%1, %2};\n\tadd.rn.f32x2 %0, %0, t;\n\t}"
+                                    : "+l"(sum2[cc * 8 + j]) : "r"(r[2 * j]), "r"(r[2 * j + 1]));
                         }
                     }
                     tc_fence_before();
@@ -728,7 +734,9 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                         for (int j = 0; j < TC_CW; ++j) {
                             const uint32_t col = col0 + cbase + piece * TC_CW + j;
                             if (col < n) {
-                                float v = sum[piece * TC_CW + j];
+                                float lo, hi;
+                                asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(sum2[(piece * TC_CW + j) / 2]));
+                                float v = (j & 1) ? hi : lo;
                                 if (!partial) {
                                     v *= alpha;
                                     if (use_c) v = fmaf(beta, cv[piece % 3][j], v);
