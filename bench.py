@@ -159,6 +159,9 @@ def main():
                          "c5: the fixed M = N = 32768, K = 8192 problem column-sharded over the GPUs (strong scaling)")
     ap.add_argument("--allgather", action="store_true",
                     help="also time the optional NCCL all-gather of D's column shards (reported apart from the GEMM)")
+    ap.add_argument("--acc-chain", type=int, default=-1,
+                    help="k per tensor-core accumulation chain: -1 = as the kernel was generated (128), 0 = all of K in "
+                         "one chain (faster, drifts toward zero for same-signed inputs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -193,6 +196,7 @@ def main():
     kernel = args.kernel or kernels.DEFAULT_TENSOR
     cubin, toml = kernels.ensure(kernel)
     r = api.SgemmRunner(cubin, toml, local_rank)
+    r.set_option("acc_chain", args.acc_chain)
     tile_n = r.info("tile_n")
 
     # c3, weak scaling: N_total = N_PER_GPU * world columns; c5, strong scaling: one fixed problem.
@@ -304,6 +308,7 @@ def main():
             "data": "synthetic",
             "config": {"workload": f"column-major NN SGEMM M={M} N={n_total} K={K} (N={n_local} on rank 0), alpha=1, beta=0, "
                                    "seeded uniform[-1,1); 3xTF32 tcgen05 path", "kernel": kernel,
+                       "acc_chain": r.info("last_acc_chain"),
                        "parallelism": f"column-block shards x{world}, A replicated, no collective",
                        "l2": f"inputs (A + B = {(M * K + K * n_local) * 4 >> 20} MiB per GPU) exceed the 126 MB L2, no flush needed"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
