@@ -268,9 +268,15 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
         if (chain && (!tk->acc_chain || chain % tk->bk))
             return fail(h, SGEMM_ERR_UNSUPPORTED, "acc_chain %u: %s", chain,
                         tk->acc_chain ? "not a multiple of the kernel's k-block" : "this kernel was generated without chunked accumulation");
-        // a tile with one accumulation chunk (no chunking, or K up to two chains: the first chunks are double length)
-        // does not need the running sum: the main kernel's whole-K twin writes it out straight from TMEM
-        if (tk == &h->tk_main && h->tk_wholek.fn && (chain == 0 || k <= 2 * chain)) {
+        p->tiles_m = (m + tk->tile_m - 1) / tk->tile_m;
+        p->tiles_n = (n + tk->tile_n - 1) / tk->tile_n;
+        p->split_k = pick_split_k(h, p->tiles_m * p->tiles_n, k, tk->bk);
+        // a launch unit whose k range is one accumulation chunk (no chunking, or up to two chains: the first chunks
+        // are double length) does not need the running sum: the main kernel's whole-K twin (same tiles, same split)
+        // writes the accumulator out straight from TMEM
+        const uint32_t kb_total = (k + tk->bk - 1) / tk->bk;
+        const uint32_t k_per_unit = (kb_total + p->split_k - 1) / p->split_k * tk->bk;
+        if (tk == &h->tk_main && h->tk_wholek.fn && (chain == 0 || k_per_unit <= 2 * chain)) {
             tk = &h->tk_wholek;
             chain = 0;
         }
@@ -279,9 +285,6 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
     p->tk = variant == kVariantTensor ? tk : nullptr;
     size_t off = 0;
     if (variant == kVariantTensor) {
-        p->tiles_m = (m + tk->tile_m - 1) / tk->tile_m;
-        p->tiles_n = (n + tk->tile_n - 1) / tk->tile_n;
-        p->split_k = pick_split_k(h, p->tiles_m * p->tiles_n, k, tk->bk);
         // persistent grid: one CTA (or CTA pair) per SM (pair of SMs), never more launch units than tiles
         const uint64_t units = (uint64_t)p->tiles_m * p->tiles_n * p->split_k;
         const uint32_t group = tk->group;

@@ -75,11 +75,12 @@ def test_tensor_kernels_equal_the_model_bit_for_bit(runner_of, kernel, force, mn
     finally:
         r.set_option("acc_chain", -1)
     assert r.info("last_variant") == force
-    # the runner reports the chain it launched with: the requested one, or 0 when the whole-K twin of the main kernel
-    # served a problem of at most two chains
-    assert chain < 0 or r.info("last_acc_chain") == (0 if force == TENSOR and k <= 2 * chain else chain)
     used_split = r.info("last_split_k")
     bk = 32 if force == SKINNY else int(kernel.split("_")[1].split("x")[2])
+    # the runner reports the chain it launched with: the requested one, or 0 when the whole-K twin of the main kernel
+    # served a problem of at most two chains
+    per_unit = tensor_model.split_ranges(k, bk, used_split)[0][1]      # k range of one launch unit
+    assert chain < 0 or r.info("last_acc_chain") == (0 if force == TENSOR and per_unit <= 2 * chain else chain)
     want = tensor_model.gemm(a_mat, b_mat, c_mat, alpha, beta, terms=3, split_k=used_split, bk=bk,
                              chain=r.info("last_acc_chain"))
     assert np.array_equal(as_matrix(d, m, n), want)
