@@ -5,7 +5,8 @@
 //
 // hi is the raw FP32 operand (the tensor core reads only its top 19 bits), lo = x - trunc_tf32(x)
 // is written once per call by sgemm_split_lo.  All three products accumulate into one FP32 TMEM
-// accumulator, k ascending, so results do not depend on scheduling (bit-reproducible).
+// accumulator, k ascending, in chains of a fixed length that are added up in a fixed order (see
+// "chunked accumulation"), so results do not depend on scheduling (bit-reproducible).
 //
 // Roles of the warps of a CTA (persistent over output tiles, tile = blockIdx + i*gridDim).  Roles are laid out in
 // groups of four warps, the unit in which registers can be handed from one role to another (setmaxnreg):
@@ -25,12 +26,15 @@
 //                      is small or C is read).
 //   4 more warps     : (TC_SPLIT_INKERNEL) transform warps that write the lo tiles in shared memory.
 //
-// Chunked accumulation (kernels generated with TC_ACC_CHUNK > 0, launched with acc_chunk > 0).  The tensor core adds products into its accumulator with truncation
-// (toward zero, two guard bits), so an unbroken chain of MMAs drifts toward zero in proportion to its length.  The
-// issuer therefore starts a fresh accumulator, in the other TMEM buffer, every acc_chunk k-blocks, and the
-// epilogue warps add the finished chunks, in chunk order and with round-to-nearest FP32 adds, to a running sum in
-// registers; the epilogue proper then runs from registers.  The running sum needs TC_EPI_COLS registers per
-// epilogue thread; with 8 epilogue warps the first warp group gives registers up and the epilogue groups take them.
+// Chunked accumulation (kernels generated with TC_ACC_CHUNK > 0, launched with acc_chunk > 0).  The tensor core
+// adds products into its accumulator with truncation (toward zero, two guard bits), so an unbroken chain of MMAs
+// drifts toward zero in proportion to its length.  The issuer therefore starts a fresh accumulator, in the other
+// TMEM buffer, every acc_chunk k-blocks (the first two chunks of a tile are twice as long), and the epilogue warps
+// add the finished chunks, in chunk order and with round-to-nearest FP32 adds, to a running sum in registers; the
+// epilogue proper then runs from registers.  The running sum needs TC_EPI_COLS registers per epilogue thread; with
+// 8 epilogue warps the other warp groups give registers up and the epilogue groups take them.  The generator emits
+// this template a second time with TC_ACC_CHUNK = 0 (entry generated_gemm_wholek: one chain per launch unit, the
+// accumulator written out straight from TMEM) for problems whose k range per unit is a single chunk anyway.
 //
 // Operand tiles in shared memory (128-byte swizzle, written by TMA, read by the tensor core):
 //   A (column-major, M contiguous => "MN-major" operand): per 32 rows of M one chunk of TC_BK rows
@@ -53,10 +57,10 @@
 // CTAs' shared memory and write both CTAs' TMEM (each CTA holds its 128 rows x TC_BN columns).  Barriers:
 //   full[s]      lives in the leader; both CTAs' TMA loads report their bytes to it
 //   empty[s]     one per CTA; the leader commits to its own and to the peer's copy (two plain commits)
-//   tmem_full[b] one per CTA, committed the same way;  tmem_empty[b] in the leader, 4 warps x 2 CTAs arrive
+//   tmem_full[b] one per CTA, committed the same way;  tmem_empty[b] in the leader, the epilogue warps of both CTAs arrive
 //
 // TC_SPLIT_INKERNEL = 1 drops the pre-pass: TMA brings only the raw (hi) tiles, four extra "transform" warps
-// (warps 6..9) compute lo = x - trunc_tf32(x) from the landed tile into the stage's lo tile (element-wise,
+// (the last warp group) compute lo = x - trunc_tf32(x) from the landed tile into the stage's lo tile (element-wise,
 // so the swizzle does not matter), publish the writes to the tensor core's proxy with fence.proxy.async and
 // arrive on the stage's "ready" barrier, which the MMA issuer then waits on instead of "full".  In a CTA pair
 // "full" is then local to each CTA (each transforms what it loaded) and "ready" lives in the leader
@@ -70,7 +74,9 @@
 // return; the host reads the status after synchronising.
 //
 // Generator-supplied macros: TC_BN (tile columns), TC_BK (k per stage: 16 or a multiple of 32), TC_STAGES,
-// TC_CTA_GROUP (1/2), TC_EPI_WARPS (4/8), TC_SPLIT_INKERNEL (0/1), TC_A_KMAJOR (0/1), TC_TERMS (3 = 3xTF32, 1 = plain TF32 for bring-up), OPT_WGM.
+// TC_CTA_GROUP (1/2), TC_EPI_WARPS (4/8), TC_SPLIT_INKERNEL (0/1), TC_A_KMAJOR (0/1), TC_B_MNMAJOR (0/1),
+// TC_TERMS (3 = 3xTF32, 1 = plain TF32 for bring-up), TC_ACC_CHUNK (default accumulation chain in k-blocks, 0 = the
+// kernel has no running sum), OPT_WGM.
 // ---------------------------------------------------------------------------------------------
 #ifndef TC_TERMS
 #define TC_TERMS 3
