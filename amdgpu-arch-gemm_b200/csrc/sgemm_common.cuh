@@ -151,6 +151,25 @@ extern "C" __global__ void sgemm_pack_a_kmajor(const float *__restrict__ a, uint
     }
 }
 
+// The same packing for 16-bit operands (FP16 / BF16 words are copied as they are, there is no lo term):
+//   out[l + i*ldt] = a[i + l*lda]
+extern "C" __global__ void sgemm_pack16_kmajor(const uint16_t *__restrict__ a, uint32_t lda, uint32_t m, uint32_t k,
+                                               uint16_t *__restrict__ out, uint32_t ldt) {
+    __shared__ uint16_t tile[32][34];
+    sgemm_launch_dependents();
+    sgemm_grid_dependency_wait();
+    const uint32_t i0 = blockIdx.x * 32, l0 = blockIdx.y * 32;
+    for (uint32_t r = threadIdx.y; r < 32; r += blockDim.y) {
+        const uint32_t i = i0 + threadIdx.x, l = l0 + r;
+        tile[r][threadIdx.x] = (i < m && l < k) ? a[i + (uint64_t)l * lda] : (uint16_t)0;
+    }
+    __syncthreads();
+    for (uint32_t r = threadIdx.y; r < 32; r += blockDim.y) {
+        const uint32_t i = i0 + r, l = l0 + threadIdx.x;
+        if (i < m && l < k) out[l + (uint64_t)i * ldt] = tile[threadIdx.x][r];
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Deterministic split-K second pass: D = alpha * (ws[0] + ws[1] + ... in fixed order) + beta * C.
 // ws holds nsplit dense M x N partial products (leading dimension M).  nsplit = 0 gives

@@ -113,6 +113,8 @@ struct sgemm_handle {
     CUdevice cu_device = 0;
     CUcontext ctx = nullptr;
     CUmodule module = nullptr;
+    uint32_t elem_bytes = 4;    // size of an element of A and B: 4 (FP32) or 2 (FP16 / BF16, tensor variant only)
+    CUfunction fn_pack16 = nullptr;
     CUfunction fn_main = nullptr, fn_simt = nullptr, fn_split_lo = nullptr, fn_pack_a = nullptr,
                fn_reduce = nullptr, fn_fill = nullptr, fn_tile_map = nullptr, fn_wait_selftest = nullptr;
     int sm_count = 0;
@@ -210,9 +212,10 @@ struct Plan {
 bool tensor_eligible(const sgemm_handle *h, const void *a, const void *b, uint32_t lda, uint32_t ldb) {
     if (h->cfg.variant != kVariantTensor) return false;
     // TMA: 16-byte aligned bases and row pitches that are multiples of 16 bytes
+    const uint32_t per16 = 16 / h->elem_bytes;   // elements per 16 bytes
     if (((uintptr_t)a & 15) || ((uintptr_t)b & 15)) return false;
-    if ((ldb % 4) != 0) return false;
-    if ((!h->cfg.a_kmajor || h->cfg.trans_a) && (lda % 4) != 0) return false;   // a packed copy gets its own pitch
+    if ((ldb % per16) != 0) return false;
+    if ((!h->cfg.a_kmajor || h->cfg.trans_a) && (lda % per16) != 0) return false;   // a packed copy gets its own pitch
     return true;
 }
 
@@ -237,6 +240,10 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
     const bool eligible = tensor_eligible(h, a, b, lda, ldb);
     int variant;
     const TensorKernel *tk = &h->tk_main;
+    if (h->elem_bytes != 4 && (!eligible || h->force_variant == 2 || h->force_variant == 3))
+        return fail(h, SGEMM_ERR_UNSUPPORTED, "16-bit operands run on the tensor-core kernel only: %s",
+                    eligible ? "no FFMA or companion kernel exists for them"
+                             : "A and B must be 16-byte aligned with leading dimensions that are multiples of 8");
     if (h->force_variant == 3) {
         if (!eligible || !h->tk_skinny.fn)
             return fail(h, SGEMM_ERR_UNSUPPORTED, "companion tensor kernel forced but %s",
@@ -254,7 +261,7 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
         variant = kVariantSimt;
     } else {
         const double flops = 2.0 * m * n * k;
-        variant = (eligible && flops >= (double)h->simt_below_flops) ? kVariantTensor : kVariantSimt;
+        variant = (eligible && (flops >= (double)h->simt_below_flops || h->elem_bytes != 4)) ? kVariantTensor : kVariantSimt;
         // few flops per byte of A and B (a skinny M or N with a long K): the pre-pass, which reads both operands and
         // writes and re-reads their lo copies, would cost as much as the GEMM; the companion kernel (small tiles,
         // lo terms made in the kernel) has neither pre-pass nor copies
@@ -292,7 +299,14 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
         // floats between the first and the last element of an operand as stored (op(B) is K x N: stored K x N with
         // pitch ldb, or, transposed, N x K with pitch ldb)
         p->span_b = h->cfg.trans_b ? (uint64_t)ldb * (k - 1) + n : (uint64_t)ldb * (n - 1) + k;
-        if (tk->a_packed) {
+        if (h->elem_bytes != 4) {
+            // 16-bit operands: no lo copies; an untransposed A is read from a K-major packed copy
+            p->span_a = p->span_b = 0;
+            if (!h->cfg.trans_a) {
+                p->ldt = (uint32_t)round_up(k, 8);
+                p->hi_a_off = off; off += round_up((size_t)p->ldt * m * 2, 256);
+            }
+        } else if (tk->a_packed) {
             p->ldt = (uint32_t)round_up(k, 4);
             p->hi_a_off = off; off += round_up((size_t)p->ldt * m * 4, 256);
             p->lo_a_off = off; off += round_up((size_t)p->ldt * m * 4, 256);
@@ -301,7 +315,7 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
             p->span_a = h->cfg.trans_a ? (uint64_t)lda * (m - 1) + k : (uint64_t)lda * (k - 1) + m;
             p->lo_a_off = off; off += round_up(p->span_a * 4, 256);
         }
-        if (!tk->split_inkernel) { p->lo_b_off = off; off += round_up(p->span_b * 4, 256); }
+        if (!tk->split_inkernel && h->elem_bytes == 4) { p->lo_b_off = off; off += round_up(p->span_b * 4, 256); }
     } else {
         const bool own = h->cfg.variant == kVariantSimt;
         const uint32_t tm = own ? h->tile_m : (uint32_t)h->cfg.fallback_tile[0];
@@ -352,15 +366,16 @@ int ensure_workspace(sgemm_handle *h, size_t bytes, CUdeviceptr *ws) {
 // for K-major operand tiles, of 32-byte units for the MN-major A tile (the only shared-memory layout the
 // tensor core accepts for 32-bit MN-major operands).
 int encode_map(sgemm_handle *h, int slot, const void *base, uint64_t d0, uint64_t d1, uint64_t stride_bytes,
-               uint32_t b0, uint32_t b1, CUtensorMapSwizzle swizzle, const CUtensorMap **out) {
+               uint32_t b0, uint32_t b1, CUtensorMapSwizzle swizzle, const CUtensorMap **out,
+               CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_FLOAT32) {
     CachedMap &c = h->maps[slot];
-    TensorMapKey key{base, d0, d1, stride_bytes, b0, b1, (int)swizzle};
+    TensorMapKey key{base, d0, d1, stride_bytes, b0, b1, (int)swizzle * 16 + (int)dtype};
     if (!(c.valid && c.key == key)) {
         const cuuint64_t dims[2] = {d0, d1};
         const cuuint64_t strides[1] = {stride_bytes};
         const cuuint32_t box[2] = {b0, b1};
         const cuuint32_t estr[2] = {1, 1};
-        CUresult r = driver().cuTensorMapEncodeTiled_(&c.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+        CUresult r = driver().cuTensorMapEncodeTiled_(&c.map, dtype, 2,
                                                       const_cast<void *>(base), dims, strides, box, estr,
                                                       CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -474,7 +489,29 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
         const CUtensorMapSwizzle ksw = kspan == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
         const CUtensorMap *ma_hi, *ma_lo, *mb_hi, *mb_lo;
         const uint32_t blocks = (uint32_t)h->sm_count * 4;
-        if (tk.a_packed) {
+        if (h->elem_bytes != 4) {
+            // FP16 / BF16: both operands as K-major tiles of 64 k per 128-byte row (32 k and the 64-byte swizzle for
+            // depth_k = 32); A where it lies when it is stored K-contiguous, else from a packed copy made here
+            const CUtensorMapDataType dt = h->cfg.a_type == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+            const uint32_t span16 = std::min<uint32_t>(bk, 64);
+            const CUtensorMapSwizzle sw16 = span16 == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+            const void *a_src = dA;
+            uint64_t a_pitch = (uint64_t)lda * 2;
+            if (!h->cfg.trans_a) {
+                void *packed = reinterpret_cast<void *>(ws + p.hi_a_off);
+                void *pp[] = {&dA, &lda, &m, &k, &packed, &p.ldt};
+                if (!h->reuse_a_lo) {
+                    rc = launch(h, h->fn_pack16, (m + 31) / 32, (k + 31) / 32, 1, 32, 8, 0, stream, pp);
+                    if (rc) return rc;
+                }
+                a_src = packed;
+                a_pitch = (uint64_t)p.ldt * 2;
+            }
+            if ((rc = encode_map(h, 0, a_src, k, m, a_pitch, span16, 128, sw16, &ma_hi, dt))) return rc;
+            if ((rc = encode_map(h, 2, dB, k, n, (uint64_t)ldb * 2, span16, bn, sw16, &mb_hi, dt))) return rc;
+            ma_lo = ma_hi;
+            mb_lo = mb_hi;
+        } else if (tk.a_packed) {
             float *hi_t = reinterpret_cast<float *>(ws + p.hi_a_off);
             void *pp[] = {&dA, &lda, &m, &k, &hi_t, &lo_a, &p.ldt};
             if (!h->reuse_a_lo) {
@@ -510,7 +547,9 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
             if ((rc = encode_map(h, 0, dA, m, k, (uint64_t)lda * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &ma_hi))) return rc;
             if ((rc = encode_map(h, 1, lo_a, m, k, (uint64_t)lda * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &ma_lo))) return rc;
         }
-        if (h->cfg.trans_b) {
+        if (h->elem_bytes != 4) {
+            // (both maps were made above)
+        } else if (h->cfg.trans_b) {
             // B is stored N-contiguous: an MN-major operand, staged in 32-column chunks like the untransposed A
             if ((rc = encode_map(h, 2, dB, n, k, (uint64_t)ldb * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &mb_hi))) return rc;
             if (tk.split_inkernel) mb_lo = mb_hi;
@@ -687,6 +726,14 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
     sgemm_handle *h = new sgemm_handle();
     h->cfg = cfg;
     h->device = device;
+    // element types as the generator numbers them: 0 = FP32, 1 = FP16, 2 = BF16
+    if (cfg.a_type != cfg.b_type || cfg.a_type < 0 || cfg.a_type > 2 || cfg.cd_type != 0 || cfg.scalar_type != 0 ||
+        (cfg.a_type != 0 && (cfg.variant != kVariantTensor || cfg.trans_b))) {
+        delete h;
+        return fail(nullptr, SGEMM_ERR_UNSUPPORTED, "element types a %d b %d cd %d scalar %d are not served (FP32 everywhere, or "
+                    "FP16/BF16 A and B with the tensor variant and an untransposed B)", cfg.a_type, cfg.b_type, cfg.cd_type, cfg.scalar_type);
+    }
+    h->elem_bytes = cfg.a_type == 0 ? 4u : 2u;
     sgemm_config_tile(&cfg, &h->tile_m, &h->tile_n);
     auto bail = [&](int code) {
         g_open_error = h->error;
@@ -716,6 +763,7 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
         {&h->fn_simt, cfg.fallback_entry, cfg.variant == kVariantTensor},
         {&h->fn_split_lo, "sgemm_split_lo", true},
         {&h->fn_pack_a, "sgemm_pack_a_kmajor", true},
+        {&h->fn_pack16, "sgemm_pack16_kmajor", true},
         {&h->fn_reduce, "sgemm_splitk_reduce", true},
         {&h->fn_fill, "sgemm_fill_uniform", true},
         {&h->fn_tile_map, "sgemm_tile_map", true},
@@ -818,7 +866,8 @@ SGEMM_API int sgemm_run_host(sgemm_handle *h, const float *hA, const float *hB, 
     const bool use_c = beta != 0.0f;
     const size_t a_floats = h->cfg.trans_a ? (size_t)lda * (m - 1) + k : (size_t)lda * (k - 1) + m;
     const size_t b_floats = h->cfg.trans_b ? (size_t)ldb * (k - 1) + n : (size_t)ldb * (n - 1) + k;
-    const size_t bytes[4] = {k ? a_floats * 4 : 0, k ? b_floats * 4 : 0,
+    const size_t eb = h->elem_bytes;   // A and B elements; C and D are FP32
+    const size_t bytes[4] = {k ? a_floats * eb : 0, k ? b_floats * eb : 0,
                              use_c ? ((size_t)ldc * (n - 1) + m) * 4 : 0, ((size_t)ldd * (n - 1) + m) * 4};
     for (int i = 0; i < 4; ++i) {
         if (bytes[i] > h->stage_bytes[i]) {
@@ -868,8 +917,8 @@ SGEMM_API int sgemm_run_host(sgemm_handle *h, const float *hA, const float *hB, 
         for (uint32_t j = 0; j < chunks && rc == SGEMM_OK; ++j) {
             const uint32_t n0 = j * nc, nw = std::min(nc, n - n0);
             CUevent ev_in = h->pipe_events[1 + 2 * j], ev_done = h->pipe_events[2 + 2 * j];
-            const size_t off_b = (size_t)n0 * ldb * 4, off_c = (size_t)n0 * ldc * 4, off_d = (size_t)n0 * ldd * 4;
-            const size_t by_b = ((size_t)ldb * (nw - 1) + k) * 4, by_c = ((size_t)ldc * (nw - 1) + m) * 4,
+            const size_t off_b = (size_t)n0 * ldb * eb, off_c = (size_t)n0 * ldc * 4, off_d = (size_t)n0 * ldd * 4;
+            const size_t by_b = ((size_t)ldb * (nw - 1) + k) * eb, by_c = ((size_t)ldc * (nw - 1) + m) * 4,
                          by_d = ((size_t)ldd * (nw - 1) + m) * 4;
             CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[1] + off_b, reinterpret_cast<const char *>(hB) + off_b, by_b, s_in));
             if (use_c)

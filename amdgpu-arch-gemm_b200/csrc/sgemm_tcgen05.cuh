@@ -75,12 +75,21 @@
 //
 // Generator-supplied macros: TC_BN (tile columns), TC_BK (k per stage: 16 or a multiple of 32), TC_STAGES,
 // TC_CTA_GROUP (1/2), TC_EPI_WARPS (4/8), TC_SPLIT_INKERNEL (0/1), TC_A_KMAJOR (0/1), TC_B_MNMAJOR (0/1),
-// TC_TERMS (3 = 3xTF32, 1 = plain TF32 for bring-up), TC_ACC_CHUNK (default accumulation chain in k-blocks, 0 = the
+// TC_TERMS (3 = 3xTF32, 1 = one MMA per k-slice: plain TF32 for bring-up, or 16-bit operands), TC_ELEM_BYTES (4 / 2),
+// TC_AB_FORMAT (operand type code of the instruction descriptor), TC_ACC_CHUNK (default accumulation chain in k-blocks, 0 = the
 // kernel has no running sum), OPT_WGM.
 // ---------------------------------------------------------------------------------------------
 #ifndef TC_TERMS
 #define TC_TERMS 3
 #endif
+#ifndef TC_ELEM_BYTES
+#define TC_ELEM_BYTES 4   // operand element size: 4 = FP32 (kind::tf32, split precision), 2 = FP16 / BF16 (kind::f16)
+#endif
+#ifndef TC_AB_FORMAT
+#define TC_AB_FORMAT 2u   // operand type code of the instruction descriptor: 2 = TF32; with kind::f16: 0 = F16, 1 = BF16
+#endif
+#define TC_MMA_K (32 / TC_ELEM_BYTES)              // k extent of one MMA instruction: 32 bytes of K per operand row
+#define TC_OPERAND_TILES (TC_TERMS == 3 ? 2 : 1)   // tiles per operand and stage: hi and lo, or the operand alone
 #ifndef TC_TIMEOUT_NS
 #define TC_TIMEOUT_NS 2000000000ull
 #endif
@@ -127,11 +136,11 @@ static_assert(!TC_REG_HANDOVER || (2 * TC_REGS_EPI + (TC_WARPS_PER_PARTITION - 2
                                    TC_REGS_EPI <= 232 && TC_REGS_EPI > TC_REGS_LAUNCH && TC_REGS_SMALL < TC_REGS_LAUNCH),
               "the register hand-over must not ask for more than the launch allocated");
 static_assert(TC_EPI_COLS % 32 == 0, "an epilogue warp drains whole 32-column chunks");
-#define TC_A_BYTES (TC_BM * TC_BK * 4)
-#define TC_B_BYTES (TC_BN_CTA * TC_BK * 4)
-#define TC_STAGE_BYTES (2 * TC_A_BYTES + 2 * TC_B_BYTES)
-#define TC_KSPAN (TC_BK >= 32 ? 32 : TC_BK)    // k per swizzled row of a K-major tile (128-byte or 64-byte rows)
-#define TC_KROW_BYTES (TC_KSPAN * 4)
+#define TC_A_BYTES (TC_BM * TC_BK * TC_ELEM_BYTES)
+#define TC_B_BYTES (TC_BN_CTA * TC_BK * TC_ELEM_BYTES)
+#define TC_STAGE_BYTES (TC_OPERAND_TILES * (TC_A_BYTES + TC_B_BYTES))   // [A | A_lo] [B | B_lo]
+#define TC_KSPAN (TC_BK * TC_ELEM_BYTES >= 128 ? 128 / TC_ELEM_BYTES : TC_BK)   // k per swizzled row of a K-major tile (128- or 64-byte rows)
+#define TC_KROW_BYTES (TC_KSPAN * TC_ELEM_BYTES)
 #define TC_KSUBS (TC_BK / TC_KSPAN)            // K-major sub-tiles per stage
 #define TC_A_CHUNK_BYTES (TC_BK * 128)         // MN-major: 32 rows of M x TC_BK
 #define TC_A_SUB_BYTES (TC_BM * TC_KROW_BYTES) // K-major : TC_BM rows x TC_KSPAN k
@@ -141,7 +150,11 @@ static_assert(TC_EPI_COLS % 32 == 0, "an epilogue warp drains whole 32-column ch
                       TC_TMEM_COLS_NEEDED <= 128 ? 128 : TC_TMEM_COLS_NEEDED <= 256 ? 256 : 512)
 #define TC_SMEM_BYTES (TC_STAGES * TC_STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/)
 
-static_assert(TC_BK == 16 || TC_BK % 32 == 0, "k per stage: one 64-byte span or whole 128-byte swizzle spans");
+static_assert(TC_ELEM_BYTES == 4 || TC_ELEM_BYTES == 2, "FP32 or 16-bit operands");
+static_assert(TC_BK * TC_ELEM_BYTES == 64 || (TC_BK * TC_ELEM_BYTES) % 128 == 0, "k per stage: one 64-byte span or whole 128-byte swizzle spans");
+static_assert(TC_ELEM_BYTES == 4 || (TC_A_KMAJOR && !TC_B_MNMAJOR && TC_TERMS == 1 && !TC_SPLIT_INKERNEL),
+              "16-bit operands: K-major tiles only (A transposed or packed), one MMA per k-slice");
+static_assert(!TC_SPLIT_INKERNEL || TC_TERMS == 3, "the in-kernel split makes the lo tiles of the 3xTF32 scheme");
 static_assert(TC_CTA_GROUP == 1 || TC_CTA_GROUP == 2, "one CTA or a CTA pair per tile");
 static_assert(!TC_B_MNMAJOR || (TC_BN / TC_CTA_GROUP) % 32 == 0, "MN-major B is staged in 32-column chunks");
 static_assert(TC_BN % (16 * TC_CTA_GROUP) == 0 && TC_BN >= 16 * TC_CTA_GROUP && TC_BN <= 256, "UMMA N");
@@ -215,15 +228,20 @@ __device__ __forceinline__ void tc_prefetch_map(const TcTensorMap *map) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+#if TC_ELEM_BYTES == 4
+#define TC_MMA_KIND "kind::tf32"
+#else
+#define TC_MMA_KIND "kind::f16"
+#endif
 __device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                             uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
 #if TC_CTA_GROUP == 2
-        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        "tcgen05.mma.cta_group::2." TC_MMA_KIND " [%0], %1, %2, %3, p;\n\t}"
 #else
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        "tcgen05.mma.cta_group::1." TC_MMA_KIND " [%0], %1, %2, %3, p;\n\t}"
 #endif
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
@@ -313,9 +331,9 @@ __device__ __forceinline__ uint32_t tc_chunk_count(uint32_t blocks, uint32_t chu
 #define TC_LAYOUT_SW128 2ull
 #define TC_LAYOUT_SW64 4ull
 #define TC_LAYOUT_SW128_32B 1ull
-#define TC_LAYOUT_KMAJOR (TC_KSPAN == 32 ? TC_LAYOUT_SW128 : TC_LAYOUT_SW64)
+#define TC_LAYOUT_KMAJOR (TC_KROW_BYTES == 128 ? TC_LAYOUT_SW128 : TC_LAYOUT_SW64)
 #define TC_KMAJOR_SBO (8 * TC_KROW_BYTES)      // 8 rows of a K-major tile
-#define TC_KMAJOR_OFF(kk, sub_bytes) (((kk) / (TC_KSPAN / 8)) * (sub_bytes) + ((kk) % (TC_KSPAN / 8)) * 32)
+#define TC_KMAJOR_OFF(kk, sub_bytes) (((kk) / (TC_KSPAN / TC_MMA_K)) * (sub_bytes) + ((kk) % (TC_KSPAN / TC_MMA_K)) * 32)
 __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
                                                  uint64_t layout) {
     return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) |
@@ -323,7 +341,7 @@ __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr, uint32_t lbo_byt
 }
 // 32-bit instruction descriptor of kind::tf32: FP32 accumulate [4,6)=1, A/B format TF32 [7,10) and
 // [10,13) = 2, A/B major [15]/[16] (1 = MN-major), N>>3 at [17,23), M>>4 at [24,29).
-#define TC_IDESC ((1u << 4) | (2u << 7) | (2u << 10) | ((TC_A_KMAJOR ? 0u : 1u) << 15) | ((TC_B_MNMAJOR ? 1u : 0u) << 16) | \
+#define TC_IDESC ((1u << 4) | (TC_AB_FORMAT << 7) | (TC_AB_FORMAT << 10) | ((TC_A_KMAJOR ? 0u : 1u) << 15) | ((TC_B_MNMAJOR ? 1u : 0u) << 16) | \
                   ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_UMMA_M >> 4) << 24))
 
 // --------------------------------------------------------------------------------------- kernel
@@ -463,9 +481,9 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                     if (!tc_wait(waiter, bar_empty + 8 * stage, phase ^ 1u, 0x100u + stage, tile, kb)) { alive = false; break; }
                     const uint32_t full = full_base + 8 * stage;
                     const uint32_t sa_hi = smem_base + stage * TC_STAGE_BYTES;
-                    const uint32_t sa_lo = sa_hi + TC_A_BYTES;
-                    const uint32_t sb_hi = sa_lo + TC_A_BYTES;
-                    const uint32_t sb_lo = sb_hi + TC_B_BYTES;
+                    const uint32_t sa_lo = sa_hi + TC_A_BYTES;                       // (3xTF32 only)
+                    const uint32_t sb_hi = sa_hi + TC_OPERAND_TILES * TC_A_BYTES;
+                    const uint32_t sb_lo = sb_hi + TC_B_BYTES;                       // (3xTF32 only)
                     const int32_t k0 = (int32_t)(kb * TC_BK);
 #if TC_SPLIT_INKERNEL
                     // raw tiles only, reported to this CTA's own "full" barrier; the transform warps make the lo tiles
@@ -496,26 +514,26 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
 #pragma unroll
                     for (int sub = 0; sub < TC_KSUBS; ++sub) {
                         tc_tma_load_2d(sa_hi + sub * TC_A_SUB_BYTES, &map_a_hi, full, k0 + TC_KSPAN * sub, m0);
-                        tc_tma_load_2d(sa_lo + sub * TC_A_SUB_BYTES, &map_a_lo, full, k0 + TC_KSPAN * sub, m0);
+                        if (TC_TERMS == 3) tc_tma_load_2d(sa_lo + sub * TC_A_SUB_BYTES, &map_a_lo, full, k0 + TC_KSPAN * sub, m0);
                     }
 #else
 #pragma unroll
                     for (int ch = 0; ch < TC_BM / 32; ++ch) {
                         tc_tma_load_2d(sa_hi + ch * TC_A_CHUNK_BYTES, &map_a_hi, full, m0 + 32 * ch, k0);
-                        tc_tma_load_2d(sa_lo + ch * TC_A_CHUNK_BYTES, &map_a_lo, full, m0 + 32 * ch, k0);
+                        if (TC_TERMS == 3) tc_tma_load_2d(sa_lo + ch * TC_A_CHUNK_BYTES, &map_a_lo, full, m0 + 32 * ch, k0);
                     }
 #endif
 #if TC_B_MNMAJOR
 #pragma unroll
                     for (int ch = 0; ch < TC_BN_CTA / 32; ++ch) {
                         tc_tma_load_2d(sb_hi + ch * TC_A_CHUNK_BYTES, &map_b_hi, full, n0 + 32 * ch, k0);
-                        tc_tma_load_2d(sb_lo + ch * TC_A_CHUNK_BYTES, &map_b_lo, full, n0 + 32 * ch, k0);
+                        if (TC_TERMS == 3) tc_tma_load_2d(sb_lo + ch * TC_A_CHUNK_BYTES, &map_b_lo, full, n0 + 32 * ch, k0);
                     }
 #else
 #pragma unroll
                     for (int sub = 0; sub < TC_KSUBS; ++sub) {
                         tc_tma_load_2d(sb_hi + sub * TC_B_SUB_BYTES, &map_b_hi, full, k0 + TC_KSPAN * sub, n0);
-                        tc_tma_load_2d(sb_lo + sub * TC_B_SUB_BYTES, &map_b_lo, full, k0 + TC_KSPAN * sub, n0);
+                        if (TC_TERMS == 3) tc_tma_load_2d(sb_lo + sub * TC_B_SUB_BYTES, &map_b_lo, full, k0 + TC_KSPAN * sub, n0);
                     }
 #endif
 #endif  // TC_SPLIT_INKERNEL
@@ -553,11 +571,11 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                         if (!tc_wait(waiter, (TC_SPLIT_INKERNEL ? bar_ready : bar_full) + 8 * stage, phase, 0x300u + stage, tile, kb)) { alive = false; break; }
                         tc_fence_after();
                         const uint32_t sa_hi = smem_base + stage * TC_STAGE_BYTES;
-                        const uint32_t sa_lo = sa_hi + TC_A_BYTES;
-                        const uint32_t sb_hi = sa_lo + TC_A_BYTES;
-                        const uint32_t sb_lo = sb_hi + TC_B_BYTES;
+                        const uint32_t sa_lo = sa_hi + TC_A_BYTES;                       // (3xTF32 only)
+                        const uint32_t sb_hi = sa_hi + TC_OPERAND_TILES * TC_A_BYTES;
+                        const uint32_t sb_lo = sb_hi + TC_B_BYTES;                       // (3xTF32 only)
 #pragma unroll
-                        for (int kk = 0; kk < TC_BK / 8; ++kk) {
+                        for (int kk = 0; kk < TC_BK / TC_MMA_K; ++kk) {
 #if TC_A_KMAJOR
                             const uint32_t a_off = TC_KMAJOR_OFF(kk, TC_A_SUB_BYTES);
                             const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);

@@ -106,12 +106,19 @@ def gpu_function(func):
 
 
 class DataType(IntEnum):
+    """Element types.  The reference has FP32 only (generator/generator.py:816-824) and plumbs ``a_type`` ...
+    ``scalar_type`` to its TOML as these integers; FP16 and BF16 are additions for the A and B operands of the
+    tensor variant (C, D and the scalars stay FP32)."""
     FP32 = 0
+    FP16 = 1
+    BF16 = 2
 
 
 def datatype_size(dtype: DataType) -> int:
     if dtype == DataType.FP32:
         return 4
+    if dtype in (DataType.FP16, DataType.BF16):
+        return 2
     raise RuntimeError(f"unrecognized type {dtype}")
 
 
@@ -193,6 +200,11 @@ class GemmSolutionConfig:
 
         for t in (a_type, b_type, cd_type, scalar_type):
             datatype_size(t)
+        if cd_type != DataType.FP32 or scalar_type != DataType.FP32:
+            raise RuntimeError("C, D, alpha and beta are FP32")
+        if a_type != b_type:
+            raise RuntimeError("A and B have the same element type")
+        self.elem_bytes = datatype_size(a_type)
         self.trans_a, self.trans_b = bool(trans_a), bool(trans_b)
         if not all(_is_pow2(g) for g in self.wave_group):
             raise RuntimeError(f"Invalid wave group: {wave_group}")
@@ -202,14 +214,15 @@ class GemmSolutionConfig:
             raise RuntimeError("tiling parameters must be positive")
 
         m0 = self.mfma[0]
-        if m0 == 128 and self.mfma[3] == 8:
+        if m0 == 128 and self.mfma[3] == (8 if self.elem_bytes == 4 else 16):
             self.variant = VARIANT_TENSOR
             self._check_tensor()
         elif self.mfma == (1, 1, 1, 1) or self.mfma in ((16, 16, 1, 4), (32, 32, 1, 2)):
             self.variant = VARIANT_SIMT
             self._check_simt()
         else:
-            raise RuntimeError(f"unsupported MMA atom {self.mfma}: use (128, N, 1, 8) for tcgen05 tf32, "
+            raise RuntimeError(f"unsupported MMA atom {self.mfma}: use (128, N, 1, 8) for tcgen05 tf32 (FP32 operands), "
+                               f"(128, N, 1, 16) for tcgen05 f16/bf16, "
                                f"(1, 1, 1, 1) for FFMA, or a legacy (16,16,1,4)/(32,32,1,2) shape")
 
         limit = MAX_LDS_NUM_BYTES if self.variant == VARIANT_TENSOR else MAX_STATIC_LDS_NUM_BYTES
@@ -218,6 +231,20 @@ class GemmSolutionConfig:
 
     # ------------------------------------------------------------------ variant-specific checks
     def _check_tensor(self):
+        if self.elem_bytes == 2:
+            # FP16 / BF16 operands: one kind::f16 MMA per 16 k (no split), K-major tiles only — a transposed A is
+            # read where it lies, an untransposed A through a packed K-major copy made by a pre-pass
+            if self.trans_b:
+                raise RuntimeError("16-bit operands: a transposed B (an MN-major operand) is not implemented")
+            if self.split != "prepass":
+                raise RuntimeError("16-bit operands have no lo terms: split='inkernel' does not apply")
+            if self.depth_k != 32 and self.depth_k % 64:
+                raise RuntimeError(f"depth_k = {self.depth_k} must be 32 (one 64-byte span of 16-bit elements) or a "
+                                   f"multiple of 64 (whole 128-byte spans)")
+            self.terms = 1
+            self.companion = False
+            if not self.trans_a:
+                self.a_major = "k"
         if self.wave_group not in ((1, 1), (2, 1)):
             raise RuntimeError(f"cluster shape {self.wave_group} is not implemented for the tensor variant "
                                f"(1x1: one CTA per tile, 2x1: a CTA pair on a 256-row tile)")
@@ -230,7 +257,7 @@ class GemmSolutionConfig:
             raise RuntimeError(f"tile N = {bn} must be a multiple of 32 (epilogue reads 32 TMEM columns at a time)")
         if self.wave_group[0] == 2 and bn % 64:
             raise RuntimeError(f"tile N = {bn} must be a multiple of 64 for a CTA pair (each CTA stages N/2 columns)")
-        if self.depth_k != 16 and self.depth_k % 32:
+        if self.elem_bytes == 4 and self.depth_k != 16 and self.depth_k % 32:
             raise RuntimeError(f"depth_k = {self.depth_k} must be 16 (one 64-byte swizzle span of FP32) or a "
                                f"multiple of 32 (whole 128-byte spans)")
         if 2 * bn > MAX_TMEM_COLUMNS:
@@ -262,7 +289,9 @@ class GemmSolutionConfig:
         fits = sum_regs + 72 <= min(epi_regs // 8 * 8, 232)
         self._acc_chain_requested = self.acc_chain
         if self.acc_chain is None:
-            self.acc_chain = max(128, self.depth_k) if fits else 0
+            # 3xTF32 adds to the accumulator three times per 8 k, 16-bit operands once per 16 k: a sixth of the
+            # truncating adds per k, so their chain can be that much longer for the same drift
+            self.acc_chain = (max(128, self.depth_k) if self.elem_bytes == 4 else 1024) if fits else 0
         if self.acc_chain < 0 or self.acc_chain % self.depth_k:
             raise RuntimeError(f"acc_chain = {self.acc_chain} must be 0 or a multiple of depth_k = {self.depth_k}")
         if self.acc_chain and not fits:
@@ -274,6 +303,8 @@ class GemmSolutionConfig:
             raise RuntimeError("the TMA ring needs at least 2 stages")
 
     def _check_simt(self):
+        if self.elem_bytes != 4:
+            raise RuntimeError("the FFMA variant computes on FP32 operands only")
         bm, bn = self.tile_size
         tm, tn = self.simt_thread_tile
         if bm % tm or bn % tn:
@@ -335,7 +366,8 @@ class GemmSolutionConfig:
 
     def _ring_bytes(self) -> int:
         bn_cta = self.tile_size[1] // self.wave_group[0]                         # a CTA pair splits B's columns
-        stage = 2 * (128 * self.depth_k * 4) + 2 * (bn_cta * self.depth_k * 4)   # A_hi, A_lo, B_hi, B_lo
+        tiles = 2 if self.terms == 3 else 1                                      # A_hi, A_lo, B_hi, B_lo or A, B
+        stage = tiles * (128 + bn_cta) * self.depth_k * self.elem_bytes
         return self.stages * stage + 1024 + 256                                  # + alignment slack + barriers
 
     @property
@@ -351,8 +383,8 @@ class GemmSolutionConfig:
 
     def companion_config(self) -> Optional["GemmSolutionConfig"]:
         """Configuration of the companion kernel emitted next to a tensor-variant kernel (None: no companion)."""
-        if self.variant != VARIANT_TENSOR or not self.companion:
-            return None
+        if self.variant != VARIANT_TENSOR or not self.companion or self.terms != 3:
+            return None   # (the companion makes lo tiles in the kernel: it belongs to the 3xTF32 scheme)
         return GemmSolutionConfig(self.a_type, self.b_type, self.cd_type, self.scalar_type, (128, 128, 1, 8), (1, 1), (1, 1),
                                   32, self.trans_a, self.trans_b, vmem_stage=2, split="inkernel", terms=self.terms,
                                   companion=False, acc_chain=0 if self._acc_chain_requested == 0 else None)
@@ -452,6 +484,8 @@ def _tensor_defines(config: GemmSolutionConfig):
             ("TC_EPI_WARPS", config.epilogue_warps),
             ("TC_A_KMAJOR", 1 if (config.a_major == "k" or config.trans_a) else 0),
             ("TC_B_MNMAJOR", 1 if config.trans_b else 0), ("TC_TERMS", config.terms),
+            ("TC_ELEM_BYTES", config.elem_bytes),
+            ("TC_AB_FORMAT", {DataType.FP32: "2u", DataType.FP16: "0u", DataType.BF16: "1u"}[config.a_type]),
             ("TC_ACC_CHUNK", config.acc_chain // config.depth_k)]
 
 
@@ -544,10 +578,12 @@ def compile(kern_name: str, kern_str: str, arch: str, output_folder: str, gemm_c
 
 
 def tensor_config(bn: int = 256, bk: int = 32, stages: int = 2, cluster: int = 1, trans_a: bool = False,
-                  trans_b: bool = False, **kw) -> GemmSolutionConfig:
-    """Shorthand for a tensor-variant configuration with tile (128 * cluster) x bn x bk."""
-    return GemmSolutionConfig(DataType.FP32, DataType.FP32, DataType.FP32, DataType.FP32,
-                              (128, bn, 1, 8), (cluster, 1), (1, 1), bk, trans_a, trans_b, vmem_stage=stages - 1, **kw)
+                  trans_b: bool = False, ab_type: DataType = DataType.FP32, **kw) -> GemmSolutionConfig:
+    """Shorthand for a tensor-variant configuration with tile (128 * cluster) x bn x bk; ``ab_type`` is the element
+    type of A and B (FP32: 3xTF32 with atom K = 8; FP16 / BF16: one MMA per 16 k)."""
+    atom_k = 8 if ab_type == DataType.FP32 else 16
+    return GemmSolutionConfig(ab_type, ab_type, DataType.FP32, DataType.FP32,
+                              (128, bn, 1, atom_k), (cluster, 1), (1, 1), bk, trans_a, trans_b, vmem_stage=stages - 1, **kw)
 
 
 def simt_config(bm: int = 128, bn: int = 128, bk: int = 16, tm: int = 8, tn: int = 8, trans_a: bool = False,

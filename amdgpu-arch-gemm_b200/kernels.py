@@ -51,6 +51,11 @@ REGISTRY = {
     "simt_128x128x16_nt": (lambda: simt_config(128, 128, 16, 8, 8, trans_b=True), dict(wgm=8)),
     "simt_64x64x16_tt": (lambda: simt_config(64, 64, 16, 4, 4, trans_a=True, trans_b=True), dict(wgm=4)),
     # FFMA SIMT kernels
+    # FP16 / BF16 operands (FP32 accumulate, C and D FP32): untransposed A through a packed K-major copy, or A^T as it lies
+    "bf16_tc2_256x256x64_s4": (lambda: tensor_config(256, 64, 4, cluster=2, ab_type=DataType.BF16), dict(wgm=8)),
+    "fp16_tc_128x128x64_s4": (lambda: tensor_config(128, 64, 4, ab_type=DataType.FP16), dict(wgm=8)),
+    "bf16_tc_128x256x32_s4_tn": (lambda: tensor_config(256, 32, 4, trans_a=True, ab_type=DataType.BF16), dict(wgm=8)),
+    "fp16_tc2_256x128x64_s4_tn": (lambda: tensor_config(128, 64, 4, cluster=2, trans_a=True, ab_type=DataType.FP16), dict(wgm=8)),
     "simt_128x128x16": (lambda: simt_config(128, 128, 16, 8, 8), dict(wgm=8)),
     "simt_64x64x16": (lambda: simt_config(64, 64, 16, 4, 4), dict(wgm=4)),
     "simt_128x64x8_plr0": (lambda: simt_config(128, 64, 8, 8, 4), dict(wgm=1, plr=0)),
@@ -81,8 +86,11 @@ def ensure(name: str, force: bool = False) -> Tuple[str, str]:
     config, opt = factory(), GemmOptimizations(1, **opt_kwargs)
     stale = force or not (Path(cubin).exists() and Path(toml).exists())
     if not stale:
+        import tomllib
         source = Path(cubin).with_suffix(".cu")
         stale = not source.exists() or source.read_text() != gemm(None, KERNEL_ENTRY, "sm_100a", config, opt, default_arguments())
+        with open(toml, "rb") as f:
+            stale = stale or tomllib.load(f) != config.to_dict()
     if stale:
         build_kernel(str(GENERATED_DIR / name), config, opt)
     _fresh.add(name)

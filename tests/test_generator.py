@@ -142,3 +142,30 @@ def test_tile_raster_model(nx, ny, wgm):
     if nx % wgm == 0 and wgm > 1:  # the reference's formula, test/test_vm.py:735-740
         for z, (x, y) in enumerate(seen):
             assert (x, y) == ((z % wgm) + (z // wgm // ny) * wgm, (z // wgm) % ny)
+
+
+def test_sixteen_bit_operand_types():
+    """FP16 / BF16 A and B on the tensor variant (the reference has the type plumbing, FP32 only:
+    generator/generator.py:816-824): K-major tiles, one MMA per 16 k, no lo tiles, no companion kernel."""
+    cfg = g.tensor_config(256, 64, 4, cluster=2, ab_type=g.DataType.BF16)
+    assert cfg.variant == g.VARIANT_TENSOR and cfg.terms == 1 and cfg.a_major == "k" and cfg.companion_config() is None
+    assert cfg.lds_usage_bytes == 4 * (128 + 128) * 64 * 2 + 1024 + 256          # A and B tiles only, 2 bytes per element
+    d = cfg.to_dict()
+    assert (d["a_type"], d["b_type"], d["cd_type"], d["scalar_type"]) == (2, 2, 0, 0) and d["mfma"] == [128, 256, 1, 16]
+    src = g.gemm(None, "gemm", "sm_100a", cfg, g.GemmOptimizations(1), ARGS())
+    assert "#define TC_ELEM_BYTES 2" in src and "#define TC_AB_FORMAT 1u" in src and "#define TC_TERMS 1" in src
+    assert "generated_gemm_wholek" in src and "generated_gemm_skinny" not in src
+    tn = g.tensor_config(128, 32, 4, trans_a=True, ab_type=g.DataType.FP16)
+    assert tn.a_major == "mn" and tn.to_dict()["a_type"] == 1     # a transposed A is K-major as it lies: no packed copy
+    for bad in (dict(trans_b=True), dict(split="inkernel"), dict(bk=16), dict(bk=48)):
+        kw = dict(bn=128, bk=64, stages=3, ab_type=g.DataType.FP16)
+        kw.update(bad)
+        with pytest.raises(RuntimeError):
+            g.tensor_config(**kw)
+    F, H = g.DataType.FP32, g.DataType.FP16
+    with pytest.raises(RuntimeError):
+        g.GemmSolutionConfig(H, H, F, F, (1, 1, 1, 1), (16, 16), (8, 8), 16, False, False)    # no 16-bit FFMA kernel
+    with pytest.raises(RuntimeError):
+        g.GemmSolutionConfig(H, F, F, F, (128, 128, 1, 16), (1, 1), (1, 1), 64, False, False)  # mixed operand types
+    with pytest.raises(RuntimeError):
+        g.GemmSolutionConfig(H, H, H, F, (128, 128, 1, 16), (1, 1), (1, 1), 64, False, False)  # C and D stay FP32
