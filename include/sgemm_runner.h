@@ -94,7 +94,9 @@ int sgemm_open(const char *cubin_path, const char *toml_path, int device, sgemm_
 int sgemm_close(sgemm_handle *h);
 
 /* Replaces makeKernelArguments + launchASMKernel (runner/generator_runner.cpp:126-190) with device
- * pointers.  Chooses the kernel variant and split-K factor (see sgemm_set_option), runs the 3xTF32
+ * pointers.  (A and B are declared `const float *` as in the reference's FP32-only runner; with a cubin generated
+ * for FP16 or BF16 operands — `a_type` 1 or 2 in its TOML — they point to 16-bit elements, and lda, ldb count
+ * those elements.  C, D, alpha and beta are always FP32.)  Chooses the kernel variant and split-K factor (see sgemm_set_option), runs the 3xTF32
  * split pre-pass and the split-K reduction when they apply.  May allocate or grow the handle-owned
  * workspace (a synchronising cuMemAlloc) unless a workspace was lent with sgemm_set_workspace. */
 int sgemm_launch(sgemm_handle *h, const float *dA, const float *dB, const float *dC, float *dD,
