@@ -74,17 +74,18 @@ def mma_tf32(acc: np.ndarray, a8: np.ndarray, b8: np.ndarray) -> np.ndarray:
     return _round_toward_zero_f32(units * grid)
 
 
-def accumulate(a: np.ndarray, b: np.ndarray, terms: int = 3) -> np.ndarray:
+def accumulate(a: np.ndarray, b: np.ndarray, terms: int = 3, mma_k: int = MMA_K) -> np.ndarray:
     """The TMEM accumulator after the main loop.  a: m x k array (a[i, l]), b: k x n array, both FP32.
-    terms = 3 is the 3xTF32 kernel, terms = 1 the plain TF32 bring-up kernel."""
+    terms = 3 is the 3xTF32 kernel, terms = 1 one MMA per k-slice: the plain TF32 bring-up kernel, or, with
+    mma_k = 16 and operand values that are FP16 / BF16 numbers, the kind::f16 kernels."""
     a = np.ascontiguousarray(a, dtype=np.float32)
     b = np.ascontiguousarray(b, dtype=np.float32)
     m, k = a.shape
     n = b.shape[1]
     acc = np.zeros((m, n), dtype=np.float32)
     a_lo, b_lo = split_lo(a), split_lo(b)
-    for k0 in range(0, k, MMA_K):
-        sl = slice(k0, min(k, k0 + MMA_K))
+    for k0 in range(0, k, mma_k):
+        sl = slice(k0, min(k, k0 + mma_k))
         if terms == 3:
             acc = mma_tf32(acc, a_lo[:, sl], b[sl, :])
             acc = mma_tf32(acc, a[:, sl], b_lo[sl, :])
@@ -135,26 +136,26 @@ def chain_ranges(k: int, chain: int):
     return out
 
 
-def chained(a: np.ndarray, b: np.ndarray, terms: int = 3, chain: int = 0) -> np.ndarray:
+def chained(a: np.ndarray, b: np.ndarray, terms: int = 3, chain: int = 0, mma_k: int = MMA_K) -> np.ndarray:
     """One launch unit's result for its k range.  chain = 0: one accumulator for the whole range.  chain > 0 (the
     kernels' acc_chain): the tensor core accumulates the chunks of chain_ranges, and the chunks are added in order,
     in FP32 with round-to-nearest, to a running sum that starts at zero; a single chunk is not re-added."""
     ranges = chain_ranges(a.shape[1], chain)
     if len(ranges) == 1:
-        return accumulate(a, b, terms)
+        return accumulate(a, b, terms, mma_k)
     total = np.zeros((a.shape[0], b.shape[1]), dtype=np.float32)
     for k0, k1 in ranges:
-        total = (total + accumulate(a[:, k0:k1], b[k0:k1, :], terms)).astype(np.float32)
+        total = (total + accumulate(a[:, k0:k1], b[k0:k1, :], terms, mma_k)).astype(np.float32)
     return total
 
 
 def gemm(a, b, c=None, alpha: float = 1.0, beta: float = 0.0, terms: int = 3, split_k: int = 1, bk: int = 32,
-         chain: int = 0) -> np.ndarray:
+         chain: int = 0, mma_k: int = MMA_K) -> np.ndarray:
     """D (m x n array) as a tensor kernel with k-block bk and accumulation chain `chain` writes it: per split the
     result above, then v = alpha * (sum of the partials); fma(beta, c, v) when beta != 0."""
     a = np.ascontiguousarray(a, dtype=np.float32)
     b = np.ascontiguousarray(b, dtype=np.float32)
-    parts = [chained(a[:, k0:k1], b[k0:k1, :], terms, chain) for k0, k1 in split_ranges(a.shape[1], bk, split_k)]
+    parts = [chained(a[:, k0:k1], b[k0:k1, :], terms, chain, mma_k) for k0, k1 in split_ranges(a.shape[1], bk, split_k)]
     return _epilogue(parts, c, alpha, beta)
 
 
