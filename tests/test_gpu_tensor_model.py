@@ -128,7 +128,7 @@ def test_same_signed_inputs_need_the_chunked_accumulation(runner_of):
     print(f"same-signed inputs, K = {k}: worst ratio {whole:.2f} (one chain) -> {chunked:.3f} (chains of 128)")
 
 
-@pytest.mark.parametrize("kernel", ["bf16_tc2_256x256x64_s4", "fp16_tc_128x128x64_s4", "bf16_tc_128x256x32_s4_tn",
+@pytest.mark.parametrize("kernel", ["bf16_tc2_256x256x64_s6", "fp16_tc_128x128x64_s4", "bf16_tc_128x256x32_s4_tn",
                                     "fp16_tc2_256x128x64_s4_tn"])
 @pytest.mark.parametrize("mnk", [(96, 80, 72), (257, 129, 520), (64, 40, 2300)])
 @pytest.mark.parametrize("alpha,beta,split_k,chain", [(1.0, 0.0, 1, -1), (0.75, -1.25, 1, 128), (-2.5, 0.3, 3, -1)])
