@@ -78,6 +78,14 @@ int main(int argc, char **argv) {
     env = std::getenv("SGEMM_DEVICE");
     const int device = env ? std::atoi(env) : 0;
 
+    // this program fills and validates FP32 buffers, as the reference's runner does; cubins generated for FP16 or
+    // BF16 operands are driven through the C ABI directly
+    sgemm_config parsed;
+    if (sgemm_config_parse(argv[2], &parsed) == 0 && (parsed.a_type != 0 || parsed.b_type != 0)) {
+        std::fprintf(stderr, "GeneratorRunner: %s describes a kernel for 16-bit operands (a_type %d); this runner drives FP32 kernels\n",
+                     argv[2], parsed.a_type);
+        return 2;
+    }
     sgemm_handle *h = nullptr;
     int rc = sgemm_open(argv[1], argv[2], device, &h);
     if (rc) return die(nullptr, "sgemm_open", rc);

@@ -48,3 +48,11 @@ def test_cli_argument_and_file_errors(built):
     bad = subprocess.run([str(api.RUNNER_PATH), cubin + ".missing", toml, "64", "64", "64", "1", "1", "0"],
                          capture_output=True, text=True)
     assert bad.returncode not in (0, 255) and "sgemm_open" in bad.stderr
+
+
+def test_cli_refuses_cubins_for_sixteen_bit_operands(built):
+    from runner import api
+    api.build_library()
+    cubin, toml = built.ensure("fp16_tc_128x128x64_s4")
+    ret = subprocess.run([str(api.RUNNER_PATH), cubin, toml, "64", "64", "64", "1", "1", "0"], capture_output=True, text=True)
+    assert ret.returncode == 2 and "16-bit operands" in ret.stderr
