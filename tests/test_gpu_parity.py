@@ -493,3 +493,30 @@ def test_tile_rasterisation_on_device_matches_the_model(runner_of, built, kernel
     r = runner_of(kernel)
     for nx, ny in [(8, 8), (7, 5), (64, 32), (1, 9)]:
         assert r.tile_map(nx, ny) == [g.tile_raster(z, nx, ny, wgm) for z in range(nx * ny)]
+
+
+# ------------------------------------------------------------------------------------------ C and D aliased
+@pytest.mark.parametrize("kernel,force", [("tc2_256x256x32_s3", TENSOR), ("tc2_256x256x32_s3_c0", TENSOR),
+                                          ("tc2_256x256x32_s3", SKINNY), ("simt_128x128x16", SIMT)])
+@pytest.mark.parametrize("mnk,split_k", [((300, 520, 1100), 1), ((300, 520, 200), 1), ((260, 132, 1100), 3)])
+def test_in_place_update_c_is_d(runner_of, kernel, force, mnk, split_k):
+    """D = alpha*A*B + beta*D with C and D the same device buffer (BLAS semantics; the reference's runner keeps them
+    apart): every element of C is read by the thread that later overwrites it, before it does so."""
+    m, n, k = mnk
+    lda, ldb = (m + 3) // 4 * 4, (k + 3) // 4 * 4
+    a, b, c = oracle.make_inputs(m, n, k, seed=11, lda=lda, ldb=ldb)
+    r = runner_of(kernel)
+    r.set_option("force_variant", force)
+    r.set_option("split_k", split_k)
+    da, db, dd = r.dev_alloc(a.nbytes), r.dev_alloc(b.nbytes), r.dev_alloc(c.nbytes)
+    try:
+        r.upload(da, a); r.upload(db, b); r.upload(dd, c)
+        r.launch(da, db, dd, dd, m, n, k, alpha=0.75, beta=-1.25, lda=lda, ldb=ldb)
+        r.sync()
+        d = np.empty_like(c)
+        r.download(d, dd)
+    finally:
+        for p in (da, db, dd):
+            r.dev_free(p)
+    assert r.last_status()[0] == 0
+    check(d, a, b, c, m, n, k, 0.75, -1.25, lda=lda, ldb=ldb)
