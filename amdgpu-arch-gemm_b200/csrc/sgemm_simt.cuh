@@ -167,6 +167,26 @@ __device__ __forceinline__ void simt_read_frag(const SimtSmem &s, int buf, int k
     }
 }
 
+#ifndef SIMT_FMA2
+#define SIMT_FMA2 1   // accumulate with the packed FP32 FMA of sm_100 (fma.rn.f32x2): same results, half the FMA instructions
+#endif
+#if SIMT_FMA2
+// acc2[j][i] (+)= {fa[2i], fa[2i+1]} * {fb[j], fb[j]}: one packed FMA per two rows of the thread tile
+__device__ __forceinline__ void simt_outer_product2(uint64_t (&acc2)[SIMT_TN][SIMT_TM / 2], const float (&fa)[SIMT_TM],
+                                                    const float (&fb)[SIMT_TN]) {
+    uint64_t a2[SIMT_TM / 2];
+#pragma unroll
+    for (int i = 0; i < SIMT_TM / 2; ++i) asm("mov.b64 %0, {%1, %2};" : "=l"(a2[i]) : "f"(fa[2 * i]), "f"(fa[2 * i + 1]));
+#pragma unroll
+    for (int j = 0; j < SIMT_TN; ++j) {
+        uint64_t b2;
+        asm("mov.b64 %0, {%1, %1};" : "=l"(b2) : "f"(fb[j]));
+#pragma unroll
+        for (int i = 0; i < SIMT_TM / 2; ++i) asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc2[j][i]) : "l"(a2[i]), "l"(b2));
+    }
+}
+#endif
+
 extern "C" __global__ void __launch_bounds__(SIMT_THREADS)
 SIMT_ENTRY(const float *__restrict__ a, const float *__restrict__ b, const float *c, float *d,
            uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
@@ -194,11 +214,21 @@ SIMT_ENTRY(const float *__restrict__ a, const float *__restrict__ b, const float
     const bool a_vec = ((reinterpret_cast<uintptr_t>(a) & 15) == 0) && (lda % 4 == 0);
     const bool b_vec = ((reinterpret_cast<uintptr_t>(b) & 15) == 0) && (ldb % 4 == 0);
 
+#if SIMT_FMA2
+    // accumulators as pairs of rows in 64-bit registers, updated with the packed FP32 FMA (two IEEE fused
+    // multiply-adds per instruction: the same arithmetic, half the issue slots)
+    uint64_t acc2[SIMT_TN][SIMT_TM / 2];
+#pragma unroll
+    for (int j = 0; j < SIMT_TN; ++j)
+#pragma unroll
+        for (int i = 0; i < SIMT_TM / 2; ++i) acc2[j][i] = 0ull;
+#else
     float acc[SIMT_TN][SIMT_TM];
 #pragma unroll
     for (int j = 0; j < SIMT_TN; ++j)
 #pragma unroll
         for (int i = 0; i < SIMT_TM; ++i) acc[j][i] = 0.0f;
+#endif
 
     float4 ra[SIMT_A_VEC], rb[SIMT_B_VEC];
     if (steps > 0) {
@@ -221,27 +251,43 @@ SIMT_ENTRY(const float *__restrict__ a, const float *__restrict__ b, const float
 #pragma unroll
         for (int kk = 0; kk < SIMT_BK; ++kk) {
             if (kk + 1 < SIMT_BK) simt_read_frag(s, buf, kk + 1, tx, ty, fa[(kk + 1) & 1], fb[(kk + 1) & 1]);
+#if SIMT_FMA2
+            simt_outer_product2(acc2, fa[kk & 1], fb[kk & 1]);
+#else
 #pragma unroll
             for (int j = 0; j < SIMT_TN; ++j)
 #pragma unroll
                 for (int i = 0; i < SIMT_TM; ++i)
                     acc[j][i] = fmaf(fa[kk & 1][i], fb[kk & 1][j], acc[j][i]);
+#endif
         }
 #else
 #pragma unroll
         for (int kk = 0; kk < SIMT_BK; ++kk) {
             float fa[SIMT_TM], fb[SIMT_TN];
             simt_read_frag(s, buf, kk, tx, ty, fa, fb);
+#if SIMT_FMA2
+            simt_outer_product2(acc2, fa, fb);
+#else
 #pragma unroll
             for (int j = 0; j < SIMT_TN; ++j)
 #pragma unroll
                 for (int i = 0; i < SIMT_TM; ++i) acc[j][i] = fmaf(fa[i], fb[j], acc[j][i]);
+#endif
         }
 #endif
         if (more) simt_store_tiles(s, buf ^ 1, ra, rb);
         __syncthreads();
     }
 
+#if SIMT_FMA2
+    float acc[SIMT_TN][SIMT_TM];
+#pragma unroll
+    for (int j = 0; j < SIMT_TN; ++j)
+#pragma unroll
+        for (int i = 0; i < SIMT_TM / 2; ++i)
+            asm("mov.b64 {%0, %1}, %2;" : "=f"(acc[j][2 * i]), "=f"(acc[j][2 * i + 1]) : "l"(acc2[j][i]));
+#endif
     // epilogue: d = alpha*acc + beta*c (C is not read when beta == 0), or the raw partial to ws
     const bool partial = split_k > 1;
     float *out = partial ? ws + (uint64_t)blockIdx.z * m * n : d;
