@@ -42,7 +42,8 @@ SUPPORTED_SPLIT = ["prepass", "inkernel"]   # where the 3xTF32 lo terms are made
 # FFMA variant: (thread grid, per-thread tile, k per stage)
 SUPPORTED_SIMT = [((16, 16), (8, 8), 16), ((16, 16), (8, 8), 8), ((16, 8), (8, 8), 16), ((8, 16), (8, 8), 16),
                   ((16, 16), (8, 4), 16), ((16, 16), (4, 8), 16), ((32, 8), (4, 8), 16), ((16, 16), (4, 4), 16),
-                  ((16, 8), (8, 8), 8), ((32, 16), (4, 8), 16)]
+                  ((16, 8), (8, 8), 8), ((32, 16), (4, 8), 16), ((16, 16), (8, 16), 16), ((16, 16), (16, 8), 16),
+                  ((8, 16), (16, 8), 16), ((16, 16), (8, 8), 32)]
 SUPPORTED_WGM = [1, 4, 8, 16]
 SUPPORTED_PLR = [0, 1]
 VERBOSE = False

@@ -14,7 +14,7 @@ TENSOR_KERNELS = ["tc_128x256x32_s2", "tc_128x128x32_s3", "tc_128x64x32_s4", "tc
                   "tc2i_256x256x32_s3", "tc2i_256x256x16_s6", "tci_128x256x32_s2", "tci_128x128x32_s3",
                   "tc2_256x256x32_s3_e4"]
 # (kernels built for transposed operands have their own tests below)
-SIMT_KERNELS = ["simt_128x128x16", "simt_64x64x16", "simt_128x64x8_plr0", "legacy_32x32x2_1wave", "legacy_16x16x4_2x2x2x2"]
+SIMT_KERNELS = ["simt_128x128x16", "simt_128x128x16_t16x8", "simt_64x64x16", "simt_128x64x8_plr0", "legacy_32x32x2_1wave", "legacy_16x16x4_2x2x2x2"]
 AUTO, TENSOR, SIMT, SKINNY = 0, 1, 2, 3
 _runners = {}
 
