@@ -19,7 +19,8 @@ Reference interface mirrored here (paths relative to the reference project):
 How the reference's knobs are read on sm_100a
 ---------------------------------------------
 ``mfma = (M, N, B, K)`` is the MMA atom.  ``(128, N, 1, 8)`` selects the tensor-core variant
-(tcgen05 ``kind::tf32``, one CTA issues 128 x N x 8); ``(1, 1, 1, 1)`` selects the FFMA SIMT variant.
+(tcgen05 ``kind::tf32``, one CTA issues 128 x N x 8; with FP16 / BF16 operands the atom is
+``(128, N, 1, 16)``, tcgen05 ``kind::f16``); ``(1, 1, 1, 1)`` selects the FFMA SIMT variant.
 The GCN shapes ``(16,16,1,4)`` / ``(32,32,1,2)`` of the reference's tuner are still accepted: they have
 no tensor-core counterpart for FP32 operands, so they map to the SIMT variant with the same block tile.
 ``wave_group`` is the cluster shape for the tensor variant and the thread grid of a block for SIMT;
@@ -28,6 +29,12 @@ reference's product rule, so a runner that only knows the legacy keys still deri
 ``depth_k`` is K per shared-memory stage, ``vmem_stage + 1`` the number of stages (the reference
 allocates ``vmem_stage + 1`` LDS buffers the same way).  ``lds_usage_bytes`` is the shared memory one
 CTA needs (dynamic for the tensor variant, static for SIMT) and is checked against the sm_100a limit.
+
+Keyword-only additions of the tensor variant: ``a_major`` ("mn" / "k": read A where it lies or from a packed
+K-major copy), ``terms`` (3 = 3xTF32, 1 = one MMA per k-slice), ``split`` ("prepass" / "inkernel": where the lo terms
+are made), ``epilogue_warps`` (4 / 8), ``companion`` (emit the 128 x 128 companion kernel for low-intensity shapes)
+and ``acc_chain`` (k accumulated inside the tensor core before the partial sum is added, in FP32, to a running sum in
+registers; 0 = all of K in one chain).
 """
 from __future__ import annotations
 
