@@ -201,7 +201,7 @@ struct Plan {
     uint32_t split_k = 1;
     uint32_t tiles_m = 0, tiles_n = 0;
     uint32_t grid_x = 0;
-    size_t lo_a_off = 0, lo_b_off = 0, hi_a_off = 0, partial_off = 0;  // byte offsets into the workspace
+    size_t lo_a_off = 0, lo_b_off = 0, hi_a_off = 0, hi_b_off = 0, partial_off = 0;  // byte offsets into the workspace
     uint64_t span_a = 0, span_b = 0;                                    // floats walked by the split pre-pass
     uint32_t ldt = 0;                                                   // K-major packed A: leading dimension
     size_t ws_bytes = 0;
@@ -213,6 +213,13 @@ bool tensor_eligible(const sgemm_handle *h, const void *a, const void *b, uint32
     if (h->cfg.variant != kVariantTensor) return false;
     // TMA: 16-byte aligned bases and row pitches that are multiples of 16 bytes
     const uint32_t per16 = 16 / h->elem_bytes;   // elements per 16 bytes
+    if (h->elem_bytes != 4) {
+        // 16-bit operands: what is stored K-contiguous is read by TMA where it lies, the rest through packed copies
+        // (which have their own pitch and alignment)
+        if (h->cfg.trans_a && (((uintptr_t)a & 15) || (lda % per16) != 0)) return false;
+        if (!h->cfg.trans_b && (((uintptr_t)b & 15) || (ldb % per16) != 0)) return false;
+        return true;
+    }
     if (((uintptr_t)a & 15) || ((uintptr_t)b & 15)) return false;
     if ((ldb % per16) != 0) return false;
     if ((!h->cfg.a_kmajor || h->cfg.trans_a) && (lda % per16) != 0) return false;   // a packed copy gets its own pitch
@@ -243,7 +250,7 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
     if (h->elem_bytes != 4 && (!eligible || h->force_variant == 2 || h->force_variant == 3))
         return fail(h, SGEMM_ERR_UNSUPPORTED, "16-bit operands run on the tensor-core kernel only: %s",
                     eligible ? "no FFMA or companion kernel exists for them"
-                             : "A and B must be 16-byte aligned with leading dimensions that are multiples of 8");
+                             : "an operand stored K-contiguous must be 16-byte aligned with a leading dimension that is a multiple of 8");
     if (h->force_variant == 3) {
         if (!eligible || !h->tk_skinny.fn)
             return fail(h, SGEMM_ERR_UNSUPPORTED, "companion tensor kernel forced but %s",
@@ -302,10 +309,9 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
         if (h->elem_bytes != 4) {
             // 16-bit operands: no lo copies; an untransposed A is read from a K-major packed copy
             p->span_a = p->span_b = 0;
-            if (!h->cfg.trans_a) {
-                p->ldt = (uint32_t)round_up(k, 8);
-                p->hi_a_off = off; off += round_up((size_t)p->ldt * m * 2, 256);
-            }
+            p->ldt = (uint32_t)round_up(k, 8);
+            if (!h->cfg.trans_a) { p->hi_a_off = off; off += round_up((size_t)p->ldt * m * 2, 256); }
+            if (h->cfg.trans_b) { p->hi_b_off = off; off += round_up((size_t)p->ldt * n * 2, 256); }
         } else if (tk->a_packed) {
             p->ldt = (uint32_t)round_up(k, 4);
             p->hi_a_off = off; off += round_up((size_t)p->ldt * m * 4, 256);
@@ -507,8 +513,18 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
                 a_src = packed;
                 a_pitch = (uint64_t)p.ldt * 2;
             }
+            const void *b_src = dB;
+            uint64_t b_pitch = (uint64_t)ldb * 2;
+            if (h->cfg.trans_b) {   // B is stored N-contiguous: the same transposing copy, with N in the place of M
+                void *packed = reinterpret_cast<void *>(ws + p.hi_b_off);
+                void *pp[] = {&dB, &ldb, &n, &k, &packed, &p.ldt};
+                rc = launch(h, h->fn_pack16, (n + 31) / 32, (k + 31) / 32, 1, 32, 8, 0, stream, pp);
+                if (rc) return rc;
+                b_src = packed;
+                b_pitch = (uint64_t)p.ldt * 2;
+            }
             if ((rc = encode_map(h, 0, a_src, k, m, a_pitch, span16, 128, sw16, &ma_hi, dt))) return rc;
-            if ((rc = encode_map(h, 2, dB, k, n, (uint64_t)ldb * 2, span16, bn, sw16, &mb_hi, dt))) return rc;
+            if ((rc = encode_map(h, 2, b_src, k, n, b_pitch, span16, bn, sw16, &mb_hi, dt))) return rc;
             ma_lo = ma_hi;
             mb_lo = mb_hi;
         } else if (tk.a_packed) {
@@ -728,10 +744,10 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
     h->device = device;
     // element types as the generator numbers them: 0 = FP32, 1 = FP16, 2 = BF16
     if (cfg.a_type != cfg.b_type || cfg.a_type < 0 || cfg.a_type > 2 || cfg.cd_type != 0 || cfg.scalar_type != 0 ||
-        (cfg.a_type != 0 && (cfg.variant != kVariantTensor || cfg.trans_b))) {
+        (cfg.a_type != 0 && cfg.variant != kVariantTensor)) {
         delete h;
         return fail(nullptr, SGEMM_ERR_UNSUPPORTED, "element types a %d b %d cd %d scalar %d are not served (FP32 everywhere, or "
-                    "FP16/BF16 A and B with the tensor variant and an untransposed B)", cfg.a_type, cfg.b_type, cfg.cd_type, cfg.scalar_type);
+                    "FP16/BF16 A and B with the tensor variant)", cfg.a_type, cfg.b_type, cfg.cd_type, cfg.scalar_type);
     }
     h->elem_bytes = cfg.a_type == 0 ? 4u : 2u;
     sgemm_config_tile(&cfg, &h->tile_m, &h->tile_n);

@@ -239,10 +239,9 @@ class GemmSolutionConfig:
     # ------------------------------------------------------------------ variant-specific checks
     def _check_tensor(self):
         if self.elem_bytes == 2:
-            # FP16 / BF16 operands: one kind::f16 MMA per 16 k (no split), K-major tiles only — a transposed A is
-            # read where it lies, an untransposed A through a packed K-major copy made by a pre-pass
-            if self.trans_b:
-                raise RuntimeError("16-bit operands: a transposed B (an MN-major operand) is not implemented")
+            # FP16 / BF16 operands: one kind::f16 MMA per 16 k (no split), K-major tiles only — an operand stored
+            # K-contiguous (A transposed, B untransposed) is read where it lies, the other way round through a packed
+            # K-major copy made by a pre-pass
             if self.split != "prepass":
                 raise RuntimeError("16-bit operands have no lo terms: split='inkernel' does not apply")
             if self.depth_k != 32 and self.depth_k % 64:
@@ -281,7 +280,7 @@ class GemmSolutionConfig:
             raise RuntimeError("split is 'prepass' or 'inkernel'")
         if self.trans_a and self.a_major == "k":
             raise RuntimeError("a transposed A is K-major already: a_major='k' (packed copy) does not apply")
-        if self.trans_b and (bn // self.wave_group[0]) % 32:
+        if self.trans_b and self.elem_bytes == 4 and (bn // self.wave_group[0]) % 32:
             raise RuntimeError("a transposed B is staged in 32-column chunks: tile N per CTA must be a multiple of 32")
         if self.split == "inkernel" and self.a_major == "k":
             raise RuntimeError("the K-major packed copy of A is made by a pre-pass; it excludes split='inkernel'")
@@ -490,7 +489,7 @@ def _tensor_defines(config: GemmSolutionConfig):
             ("TC_CTA_GROUP", config.wave_group[0]), ("TC_SPLIT_INKERNEL", 1 if config.split == "inkernel" else 0),
             ("TC_EPI_WARPS", config.epilogue_warps),
             ("TC_A_KMAJOR", 1 if (config.a_major == "k" or config.trans_a) else 0),
-            ("TC_B_MNMAJOR", 1 if config.trans_b else 0), ("TC_TERMS", config.terms),
+            ("TC_B_MNMAJOR", 1 if (config.trans_b and config.elem_bytes == 4) else 0), ("TC_TERMS", config.terms),
             ("TC_ELEM_BYTES", config.elem_bytes),
             ("TC_AB_FORMAT", {DataType.FP32: "2u", DataType.FP16: "0u", DataType.BF16: "1u"}[config.a_type]),
             ("TC_ACC_CHUNK", config.acc_chain // config.depth_k)]

@@ -56,6 +56,8 @@ REGISTRY = {
     "fp16_tc_128x128x64_s4": (lambda: tensor_config(128, 64, 4, ab_type=DataType.FP16), dict(wgm=8)),
     "bf16_tc_128x256x32_s4_tn": (lambda: tensor_config(256, 32, 4, trans_a=True, ab_type=DataType.BF16), dict(wgm=8)),
     "fp16_tc2_256x128x64_s4_tn": (lambda: tensor_config(128, 64, 4, cluster=2, trans_a=True, ab_type=DataType.FP16), dict(wgm=8)),
+    "bf16_tc2_256x256x64_s6_tt": (lambda: tensor_config(256, 64, 6, cluster=2, trans_a=True, trans_b=True, ab_type=DataType.BF16), dict(wgm=8)),
+    "fp16_tc_128x128x64_s4_nt": (lambda: tensor_config(128, 64, 4, trans_b=True, ab_type=DataType.FP16), dict(wgm=8)),
     "simt_128x128x16": (lambda: simt_config(128, 128, 16, 8, 8), dict(wgm=8)),
     "simt_128x128x16_t16x8": (lambda: simt_config(128, 128, 16, 16, 8), dict(wgm=8)),   # best of the FFMA sweep at 4096^3
     "simt_64x64x16": (lambda: simt_config(64, 64, 16, 4, 4), dict(wgm=4)),

@@ -157,7 +157,9 @@ def test_sixteen_bit_operand_types():
     assert "generated_gemm_wholek" in src and "generated_gemm_skinny" not in src
     tn = g.tensor_config(128, 32, 4, trans_a=True, ab_type=g.DataType.FP16)
     assert tn.a_major == "mn" and tn.to_dict()["a_type"] == 1     # a transposed A is K-major as it lies: no packed copy
-    for bad in (dict(trans_b=True), dict(split="inkernel"), dict(bk=16), dict(bk=48)):
+    tt = g.tensor_config(128, 64, 3, trans_a=True, trans_b=True, ab_type=g.DataType.BF16)   # B^T goes through a packed copy
+    assert "#define TC_B_MNMAJOR 0" in g.gemm(None, "gemm", "sm_100a", tt, g.GemmOptimizations(1), ARGS())
+    for bad in (dict(split="inkernel"), dict(bk=16), dict(bk=48)):
         kw = dict(bn=128, bk=64, stages=3, ab_type=g.DataType.FP16)
         kw.update(bad)
         with pytest.raises(RuntimeError):

@@ -40,7 +40,8 @@ def stored16(flat_bits, rows, cols, transposed, ld):
     return out
 
 
-KERNELS = ["bf16_tc2_256x256x64_s6", "fp16_tc_128x128x64_s4", "bf16_tc_128x256x32_s4_tn", "fp16_tc2_256x128x64_s4_tn"]
+KERNELS = ["bf16_tc2_256x256x64_s6", "fp16_tc_128x128x64_s4", "bf16_tc_128x256x32_s4_tn", "fp16_tc2_256x128x64_s4_tn",
+           "bf16_tc2_256x256x64_s6_tt", "fp16_tc_128x128x64_s4_nt"]
 
 
 @pytest.mark.parametrize("kernel", KERNELS)
@@ -50,17 +51,17 @@ KERNELS = ["bf16_tc2_256x256x64_s6", "fp16_tc_128x128x64_s4", "bf16_tc_128x256x3
 def test_half_operands_match_oracle(runner_of, kernel, mnk, alpha, beta, split_k):
     m, n, k = mnk
     kind = kernel.split("_")[0]
-    trans_a = kernel.endswith("_tn")
+    trans_a, trans_b = kernel.endswith(("_tn", "_tt")), kernel.endswith(("_nt", "_tt"))
     a32, b32, c = oracle.make_inputs(m, n, k, seed=5)
     a_bits, a_val = narrow(a32, kind)
     b_bits, b_val = narrow(b32, kind)
-    lda = ((k if trans_a else m) + 7) // 8 * 8          # 16-byte pitches for the tensor maps
-    ldb = (k + 7) // 8 * 8
+    lda = ((k if trans_a else m) + 7) // 8 * 8          # 16-byte pitches for the tensor maps (packed copies need none)
+    ldb = ((n if trans_b else k) + 7) // 8 * 8
     r = runner_of(kernel)
     r.set_option("force_variant", AUTO)
     r.set_option("split_k", split_k)
     d = np.zeros(m * n, dtype=np.float32)
-    r.run_host(stored16(a_bits, m, k, trans_a, lda), stored16(b_bits, k, n, False, ldb), c if beta != 0.0 else None, d,
+    r.run_host(stored16(a_bits, m, k, trans_a, lda), stored16(b_bits, k, n, trans_b, ldb), c if beta != 0.0 else None, d,
                m, n, k, alpha=alpha, beta=beta, lda=lda, ldb=ldb)
     assert r.info("last_variant") == TENSOR and r.last_status()[0] == 0
     ref = oracle.gemm(a_val, b_val, c, alpha, beta, m, n, k)
@@ -70,7 +71,7 @@ def test_half_operands_match_oracle(runner_of, kernel, mnk, alpha, beta, split_k
     assert oracle.worst_ratio(d, ref, bound) <= 1.0
     # run to run the result is the same, bit for bit
     d2 = np.zeros(m * n, dtype=np.float32)
-    r.run_host(stored16(a_bits, m, k, trans_a, lda), stored16(b_bits, k, n, False, ldb), c if beta != 0.0 else None, d2,
+    r.run_host(stored16(a_bits, m, k, trans_a, lda), stored16(b_bits, k, n, trans_b, ldb), c if beta != 0.0 else None, d2,
                m, n, k, alpha=alpha, beta=beta, lda=lda, ldb=ldb)
     assert np.array_equal(d, d2)
 
@@ -103,5 +104,5 @@ def test_half_kernels_refuse_what_they_cannot_serve(runner_of):
     with pytest.raises(Exception, match="tensor-core kernel only"):
         r.run_host(a, a, None, d, 64, 64, 64)
     r.set_option("force_variant", AUTO)
-    with pytest.raises(Exception, match="multiples of 8"):
+    with pytest.raises(Exception, match="multiple of 8"):
         r.run_host(np.zeros(68 * 64, dtype=np.uint16), np.zeros(68 * 64, dtype=np.uint16), None, d, 64, 64, 64, lda=64, ldb=68)
