@@ -138,6 +138,7 @@ struct sgemm_handle {
     // options and facts
     int64_t force_variant = 0, split_k_opt = 0, simt_below_flops = (int64_t)1 << 27;
     int64_t skinny_below_intensity = 200;   // flop per byte of A and B below which the companion kernel is used
+    int64_t skinny_below_flops = (int64_t)1 << 33;   // ... and problems smaller than this many flops (no pre-pass launch)
     bool wave_sync = true;      // tensor kernel: soft alignment of the persistent CTAs at tile boundaries
     uint32_t wave_sync_base = 0;   // value of the alignment counter before the next launch (it only ever counts up)
     bool pipeline_host = true;  // sgemm_run_host overlaps uploads, GEMM and downloads over column chunks
@@ -226,15 +227,17 @@ bool tensor_eligible(const sgemm_handle *h, const void *a, const void *b, uint32
     return true;
 }
 
-uint32_t pick_split_k(const sgemm_handle *h, uint32_t tiles, uint32_t k, uint32_t bk) {
+uint32_t pick_split_k(const sgemm_handle *h, uint32_t tiles, uint32_t k, uint32_t bk, uint32_t group) {
     const uint32_t kb_total = (k + bk - 1) / bk;
+    const uint32_t slots = std::max<uint32_t>(1, (uint32_t)h->sm_count / std::max<uint32_t>(group, 1));   // launch units in flight
     uint32_t split = 1;
     if (h->split_k_opt > 0) {
         split = (uint32_t)h->split_k_opt;
-    } else if (tiles * 2 <= (uint32_t)h->sm_count && kb_total >= 16) {
-        // too few tiles to fill the device: cut K so that about one launch unit per SM exists, keeping at
-        // least 8 k-blocks per split so the partial-sum traffic stays small next to the operand traffic
-        split = std::min<uint32_t>({(uint32_t)h->sm_count / tiles, kb_total / 8, 32u});
+    } else if (tiles * 2 <= slots && kb_total >= 16) {
+        // too few tiles to fill the device: cut K so that the launch units still fit one wave (a CTA pair takes two
+        // SMs), keeping at least 8 k-blocks per split so the partial-sum traffic stays small next to the operand
+        // traffic
+        split = std::min<uint32_t>({slots / tiles, kb_total / 8, 32u});
     }
     split = std::max<uint32_t>(1, std::min(split, std::max<uint32_t>(kb_total, 1)));
     // no empty splits: recompute from the per-split block count
@@ -273,7 +276,10 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
         // writes and re-reads their lo copies, would cost as much as the GEMM; the companion kernel (small tiles,
         // lo terms made in the kernel) has neither pre-pass nor copies
         const double intensity = flops / (4.0 * ((double)m * k + (double)k * n));
-        if (variant == kVariantTensor && h->tk_skinny.fn && intensity < (double)h->skinny_below_intensity) tk = &h->tk_skinny;
+        // small problems too: the pre-pass is one more dependent launch in a call that lasts a few of them
+        if (variant == kVariantTensor && h->tk_skinny.fn &&
+            (intensity < (double)h->skinny_below_intensity || flops < (double)h->skinny_below_flops))
+            tk = &h->tk_skinny;
     }
     p->variant = variant;
     if (variant == kVariantTensor) {
@@ -284,7 +290,7 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
                         tk->acc_chain ? "not a multiple of the kernel's k-block" : "this kernel was generated without chunked accumulation");
         p->tiles_m = (m + tk->tile_m - 1) / tk->tile_m;
         p->tiles_n = (n + tk->tile_n - 1) / tk->tile_n;
-        p->split_k = pick_split_k(h, p->tiles_m * p->tiles_n, k, tk->bk);
+        p->split_k = pick_split_k(h, p->tiles_m * p->tiles_n, k, tk->bk, tk->group);
         // a launch unit whose k range is one accumulation chunk (no chunking, or up to two chains: the first chunks
         // are double length) does not need the running sum: the main kernel's whole-K twin (same tiles, same split)
         // writes the accumulator out straight from TMEM
@@ -329,7 +335,7 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
         const uint32_t bk = own ? (uint32_t)h->cfg.depth_k : (uint32_t)h->cfg.fallback_tile[2];
         p->tiles_m = (m + tm - 1) / tm;
         p->tiles_n = (n + tn - 1) / tn;
-        p->split_k = pick_split_k(h, p->tiles_m * p->tiles_n, k, bk);
+        p->split_k = pick_split_k(h, p->tiles_m * p->tiles_n, k, bk, 1);
         p->grid_x = p->tiles_m * p->tiles_n;
     }
     if (p->split_k > 1) {
@@ -1038,6 +1044,7 @@ SGEMM_API int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value) 
     const std::string k(key);
     if (k == "force_variant" && value >= 0 && value <= 3) h->force_variant = value;
     else if (k == "skinny_below_intensity" && value >= 0) h->skinny_below_intensity = value;
+    else if (k == "skinny_below_flops" && value >= 0) h->skinny_below_flops = value;
     else if (k == "split_k" && value >= 0 && value <= 1024) h->split_k_opt = value;
     else if (k == "simt_below_flops" && value >= 0) h->simt_below_flops = value;
     else if (k == "pdl" && (value == 0 || value == 1)) h->pdl = value != 0;

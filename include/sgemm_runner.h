@@ -151,7 +151,9 @@ int sgemm_wait_selftest(sgemm_handle *h, uint32_t timeout_ms, uint32_t tag);
 
 /* Options: "force_variant" 0 auto, 1 tensor (main kernel), 2 simt, 3 tensor (companion kernel for skinny shapes);
  * "skinny_below_intensity": in auto mode problems with fewer flop per byte of A and B than this (default 200: a
- * skinny M or N with a long K) run on the companion kernel (128 x 128 tiles, lo terms made in the kernel, no pre-pass);  "split_k" 0 auto, n >= 1 fixed;
+ * skinny M or N with a long K) run on the companion kernel (128 x 128 tiles, lo terms made in the kernel, no pre-pass);
+ * "skinny_below_flops": so do problems with 2*M*N*K below this (default 2^33: the pre-pass would be one more dependent
+ * launch in a call that only lasts a few); "split_k" 0 auto, n >= 1 fixed;
  * "simt_below_flops" problems with 2*M*N*K below this use the SIMT kernel (auto mode);
  * "pdl" 1 (default) launches every kernel with programmatic stream serialisation so that launch latency and per-CTA
  * set-up overlap with the tail of the previous kernel (all kernels wait on the grid dependency before touching memory);

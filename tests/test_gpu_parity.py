@@ -31,6 +31,7 @@ def runner_of(built):
         r.set_option("force_variant", AUTO)
         r.set_option("split_k", 0)
         r.set_option("skinny_below_intensity", 0)   # parity tests pick kernels explicitly
+        r.set_option("skinny_below_flops", 0)
         r.set_workspace(None, 0)
         return r
 
@@ -148,9 +149,10 @@ def test_companion_kernel_matches_oracle(runner_of, kernel, ta, tb, mnk):
 
 def test_low_intensity_shapes_take_the_companion_kernel(runner_of):
     r = runner_of("tc2_256x256x32_s3")
-    r.set_option("skinny_below_intensity", 200)          # the library's default: flop per byte of A and B
+    r.set_option("skinny_below_intensity", 200)          # the library's defaults: flop per byte of A and B,
+    r.set_option("skinny_below_flops", 1 << 33)          # and problems this small
     for (m, n, k), want in [((4096, 128, 4096), SKINNY), ((64, 4096, 8192), SKINNY), ((2048, 2048, 2048), TENSOR),
-                            ((4096, 4096, 256), TENSOR)]:
+                            ((4096, 4096, 256), TENSOR), ((1024, 1024, 1024), SKINNY), ((1536, 1536, 1536), SKINNY)]:
         a, b, c = oracle.make_inputs(m, n, k, seed=2)
         d = run(r, a, b, c, m, n, k, 1.0, 0.0)
         assert r.info("last_variant") == want, (m, n, k)
