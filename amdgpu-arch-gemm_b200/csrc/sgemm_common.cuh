@@ -151,6 +151,20 @@ extern "C" __global__ void sgemm_pack_a_kmajor(const float *__restrict__ a, uint
     }
 }
 
+// Copy of an operand to an aligned pitch, for operands TMA cannot describe (a base that is not 16-byte aligned, a
+// leading dimension that is not a multiple of 4): dst[i + j*ld_dst] = src[i + j*ld_src], i < inner, j < outer.
+extern "C" __global__ void sgemm_repitch(const float *__restrict__ src, uint32_t ld_src, uint32_t inner, uint32_t outer,
+                                         float *__restrict__ dst, uint32_t ld_dst) {
+    sgemm_launch_dependents();
+    sgemm_grid_dependency_wait();
+    const uint64_t total = (uint64_t)inner * outer;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t e = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+        const uint32_t i = (uint32_t)(e % inner), j = (uint32_t)(e / inner);
+        dst[i + (uint64_t)j * ld_dst] = __ldg(src + i + (uint64_t)j * ld_src);
+    }
+}
+
 // The same packing for 16-bit operands (FP16 / BF16 words are copied as they are, there is no lo term):
 //   out[l + i*ldt] = a[i + l*lda]
 extern "C" __global__ void sgemm_pack16_kmajor(const uint16_t *__restrict__ a, uint32_t lda, uint32_t m, uint32_t k,

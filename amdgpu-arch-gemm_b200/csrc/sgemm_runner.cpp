@@ -114,7 +114,7 @@ struct sgemm_handle {
     CUcontext ctx = nullptr;
     CUmodule module = nullptr;
     uint32_t elem_bytes = 4;    // size of an element of A and B: 4 (FP32) or 2 (FP16 / BF16, tensor variant only)
-    CUfunction fn_pack16 = nullptr;
+    CUfunction fn_pack16 = nullptr, fn_repitch = nullptr;
     CUfunction fn_main = nullptr, fn_simt = nullptr, fn_split_lo = nullptr, fn_pack_a = nullptr,
                fn_reduce = nullptr, fn_fill = nullptr, fn_tile_map = nullptr, fn_wait_selftest = nullptr;
     int sm_count = 0;
@@ -138,6 +138,8 @@ struct sgemm_handle {
     // options and facts
     int64_t force_variant = 0, split_k_opt = 0, simt_below_flops = (int64_t)1 << 27;
     int64_t skinny_below_intensity = 200;   // flop per byte of A and B below which the companion kernel is used
+    bool repitch = true;        // FP32 tensor path: operands TMA cannot describe are copied to an aligned pitch first
+    int64_t repitch_above_flops = (int64_t)1 << 31;   // ... in auto mode for problems of at least this many flops
     int64_t skinny_below_flops = (int64_t)1 << 33;   // ... and problems smaller than this many flops (no pre-pass launch)
     bool wave_sync = true;      // tensor kernel: soft alignment of the persistent CTAs at tile boundaries
     uint32_t wave_sync_base = 0;   // value of the alignment counter before the next launch (it only ever counts up)
@@ -207,8 +209,15 @@ struct Plan {
     uint32_t ldt = 0;                                                   // K-major packed A: leading dimension
     size_t ws_bytes = 0;
     const TensorKernel *tk = nullptr;   // the tcgen05 kernel chosen (tensor variant only)
+    // FP32 operands TMA cannot describe where they lie: aligned copies in the workspace, and the pitch they get
+    bool repitch_a = false, repitch_b = false;
+    size_t rp_a_off = 0, rp_b_off = 0;
+    uint32_t lda_eff = 0, ldb_eff = 0;  // leading dimensions the tensor kernel and its pre-pass see
     uint32_t acc_chain = 0;             // k per tensor-core accumulation chain (0: all of K in one chain)
 };
+
+// FP32: can TMA read this operand where it lies?  (a packed K-major copy of A gets its own pitch and alignment)
+bool operand_tma_ok(const void *base, uint32_t ld) { return (((uintptr_t)base & 15) == 0) && (ld % 4) == 0; }
 
 bool tensor_eligible(const sgemm_handle *h, const void *a, const void *b, uint32_t lda, uint32_t ldb) {
     if (h->cfg.variant != kVariantTensor) return false;
@@ -247,7 +256,21 @@ uint32_t pick_split_k(const sgemm_handle *h, uint32_t tiles, uint32_t k, uint32_
 
 int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_t n, uint32_t k, uint32_t lda,
               uint32_t ldb, Plan *p) {
-    const bool eligible = tensor_eligible(h, a, b, lda, ldb);
+    bool eligible = tensor_eligible(h, a, b, lda, ldb);
+    p->lda_eff = lda;
+    p->ldb_eff = ldb;
+    if (!eligible && h->repitch && h->cfg.variant == kVariantTensor && h->elem_bytes == 4 && h->force_variant != 2 &&
+        (h->force_variant != 0 || 2.0 * m * n * k >= (double)h->repitch_above_flops)) {
+        // the tensor path through aligned copies: one more pass over the offending operand, then everything as usual
+        const bool a_needs = !(h->cfg.a_kmajor && !h->cfg.trans_a) && !operand_tma_ok(a, lda);
+        p->repitch_a = a_needs;
+        p->repitch_b = !operand_tma_ok(b, ldb);
+        if (p->repitch_a) p->lda_eff = (uint32_t)round_up(h->cfg.trans_a ? k : m, 4);
+        if (p->repitch_b) p->ldb_eff = (uint32_t)round_up(h->cfg.trans_b ? n : k, 4);
+        eligible = true;
+    }
+    lda = p->lda_eff;   // from here on the plan is made for the operands the kernels will see
+    ldb = p->ldb_eff;
     int variant;
     const TensorKernel *tk = &h->tk_main;
     if (h->elem_bytes != 4 && (!eligible || h->force_variant == 2 || h->force_variant == 3))
@@ -304,6 +327,9 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
     }
     p->tk = variant == kVariantTensor ? tk : nullptr;
     size_t off = 0;
+    if (variant != kVariantTensor) p->repitch_a = p->repitch_b = false;
+    if (p->repitch_a) { p->rp_a_off = off; off += round_up((size_t)lda * (h->cfg.trans_a ? m : k) * 4, 256); }
+    if (p->repitch_b) { p->rp_b_off = off; off += round_up((size_t)ldb * (h->cfg.trans_b ? k : n) * 4, 256); }
     if (variant == kVariantTensor) {
         // persistent grid: one CTA (or CTA pair) per SM (pair of SMs), never more launch units than tiles
         const uint64_t units = (uint64_t)p->tiles_m * p->tiles_n * p->split_k;
@@ -492,6 +518,25 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
 
     if (p.variant == kVariantTensor) {
         const TensorKernel &tk = *p.tk;
+        if (p.repitch_a || p.repitch_b) {
+            const uint32_t copy_blocks = (uint32_t)h->sm_count * 8;
+            if (p.repitch_a && !h->reuse_a_lo) {
+                float *dst = reinterpret_cast<float *>(ws + p.rp_a_off);
+                uint32_t inner = h->cfg.trans_a ? k : m, outer = h->cfg.trans_a ? m : k;
+                void *pr[] = {&dA, &lda, &inner, &outer, &dst, &p.lda_eff};
+                if ((rc = launch(h, h->fn_repitch, copy_blocks, 1, 1, 256, 1, 0, stream, pr))) return rc;
+            }
+            if (p.repitch_b) {
+                float *dst = reinterpret_cast<float *>(ws + p.rp_b_off);
+                uint32_t inner = h->cfg.trans_b ? n : k, outer = h->cfg.trans_b ? k : n;
+                void *pr[] = {&dB, &ldb, &inner, &outer, &dst, &p.ldb_eff};
+                if ((rc = launch(h, h->fn_repitch, copy_blocks, 1, 1, 256, 1, 0, stream, pr))) return rc;
+            }
+            if (p.repitch_a) dA = reinterpret_cast<const float *>(ws + p.rp_a_off);
+            if (p.repitch_b) dB = reinterpret_cast<const float *>(ws + p.rp_b_off);
+            lda = p.lda_eff;
+            ldb = p.ldb_eff;
+        }
         float *lo_a = reinterpret_cast<float *>(ws + p.lo_a_off);
         float *lo_b = reinterpret_cast<float *>(ws + p.lo_b_off);
         // a CTA pair stages half of the tile's columns of B per CTA
@@ -786,6 +831,7 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
         {&h->fn_split_lo, "sgemm_split_lo", true},
         {&h->fn_pack_a, "sgemm_pack_a_kmajor", true},
         {&h->fn_pack16, "sgemm_pack16_kmajor", true},
+        {&h->fn_repitch, "sgemm_repitch", true},
         {&h->fn_reduce, "sgemm_splitk_reduce", true},
         {&h->fn_fill, "sgemm_fill_uniform", true},
         {&h->fn_tile_map, "sgemm_tile_map", true},
@@ -1045,6 +1091,8 @@ SGEMM_API int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value) 
     if (k == "force_variant" && value >= 0 && value <= 3) h->force_variant = value;
     else if (k == "skinny_below_intensity" && value >= 0) h->skinny_below_intensity = value;
     else if (k == "skinny_below_flops" && value >= 0) h->skinny_below_flops = value;
+    else if (k == "repitch" && (value == 0 || value == 1)) h->repitch = value != 0;
+    else if (k == "repitch_above_flops" && value >= 0) h->repitch_above_flops = value;
     else if (k == "split_k" && value >= 0 && value <= 1024) h->split_k_opt = value;
     else if (k == "simt_below_flops" && value >= 0) h->simt_below_flops = value;
     else if (k == "pdl" && (value == 0 || value == 1)) h->pdl = value != 0;

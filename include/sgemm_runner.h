@@ -155,6 +155,10 @@ int sgemm_wait_selftest(sgemm_handle *h, uint32_t timeout_ms, uint32_t tag);
  * "skinny_below_flops": so do problems with 2*M*N*K below this (default 2^33: the pre-pass would be one more dependent
  * launch in a call that only lasts a few); "split_k" 0 auto, n >= 1 fixed;
  * "simt_below_flops" problems with 2*M*N*K below this use the SIMT kernel (auto mode);
+ * "repitch" 1 (default): FP32 operands TMA cannot read where they lie (base not 16-byte aligned, leading dimension
+ * not a multiple of 4) are copied to an aligned pitch in the workspace so that the tensor kernel serves them — in auto
+ * mode for problems of at least "repitch_above_flops" (default 2^31), always when the tensor variant is forced; 0: such
+ * problems run on the FFMA kernel, and forcing the tensor variant on them is SGEMM_ERR_UNSUPPORTED;
  * "pdl" 1 (default) launches every kernel with programmatic stream serialisation so that launch latency and per-CTA
  * set-up overlap with the tail of the previous kernel (all kernels wait on the grid dependency before touching memory);
  * "wave_sync" 1 (default) lets the persistent CTAs of the tensor kernel wait briefly for each other at tile

@@ -32,6 +32,7 @@ def runner_of(built):
         r.set_option("split_k", 0)
         r.set_option("skinny_below_intensity", 0)   # parity tests pick kernels explicitly
         r.set_option("skinny_below_flops", 0)
+        r.set_option("repitch", 1)
         r.set_workspace(None, 0)
         return r
 
@@ -171,12 +172,18 @@ def test_variant_selection(runner_of):
         d = run(r, a, b, c, m, n, k, 1.0, 0.0)
         assert r.info("last_variant") == want, (m, n, k)
         check(d, a, b, c, m, n, k, 1.0, 0.0)
-    # a forced tensor path on a shape TMA cannot describe is an error, not a silent fallback
+    # a forced tensor path on a shape TMA cannot describe goes through aligned copies of the operands; with that
+    # switched off it is an error, not a silent fallback
     from runner import api
     a, b, c = oracle.make_inputs(127, 257, 513, seed=1)
+    d = run(r, a, b, c, 127, 257, 513, 0.5, 2.0, force=TENSOR)
+    assert r.info("last_variant") == TENSOR
+    check(d, a, b, c, 127, 257, 513, 0.5, 2.0)
+    r.set_option("repitch", 0)
     with pytest.raises(api.SgemmError) as e:
         run(r, a, b, c, 127, 257, 513, force=TENSOR)
     assert e.value.code == -6
+    r.set_option("repitch", 1)
     with pytest.raises(api.SgemmError) as e:  # lda smaller than M
         r.run_host(a, b, None, np.zeros(127 * 257, np.float32), 127, 257, 513, lda=100)
     assert e.value.code == -1
@@ -199,10 +206,17 @@ def test_unaligned_base_pointers_take_the_simt_kernel(runner_of):
         r.sync()
         r.download(got, pd)
         check(got, a, b, None, m, n, k, 1.0, 0.0)
-        r.set_option("force_variant", TENSOR)
+        r.set_option("force_variant", TENSOR)        # forced: the tensor kernel on an aligned copy of A
+        r.launch(pa + 4, pb, None, pd, m, n, k)
+        assert r.info("last_variant") == TENSOR
+        r.sync()
+        r.download(got, pd)
+        check(got, a, b, None, m, n, k, 1.0, 0.0)
+        r.set_option("repitch", 0)                   # ... unless copies are switched off: then it is refused
         with pytest.raises(api.SgemmError) as e:
             r.launch(pa + 4, pb, None, pd, m, n, k)
         assert e.value.code == -6
+        r.set_option("repitch", 1)
         r.set_option("force_variant", AUTO)
         r.launch(pa, pb, None, pd, m, n, k)          # aligned: tensor path (A's content is shifted, only the variant matters)
         assert r.info("last_variant") == TENSOR
@@ -522,3 +536,23 @@ def test_in_place_update_c_is_d(runner_of, kernel, force, mnk, split_k):
             r.dev_free(p)
     assert r.last_status()[0] == 0
     check(d, a, b, c, m, n, k, 0.75, -1.25, lda=lda, ldb=ldb)
+
+
+# --------------------------------------------------------------- operands TMA cannot describe, at tensor speed
+@pytest.mark.parametrize("kernel", ["tc2_256x256x32_s3", "tc2i_256x256x32_s3", "tc_128x128x32_s3_ak", "tc2_256x256x32_s3_tt",
+                                    "tc2_256x256x32_s3_tn"])
+@pytest.mark.parametrize("mnk", [(1031, 1027, 1029), (515, 2050, 1023)])
+def test_ragged_leading_dimensions_run_on_the_tensor_path(runner_of, kernel, mnk):
+    """Natural (odd) leading dimensions: in auto mode a problem of this size is served by the tensor kernel through
+    aligned copies of the operands (one more pass over them), not by the four times slower FFMA kernel."""
+    m, n, k = mnk
+    ta, tb = kernel.endswith(("_tt", "_tn")), kernel.endswith(("_tt", "_nt"))
+    a, b, c = oracle.make_inputs(m, n, k, seed=13)
+    sa, lda = stored(a, m, k, ta)
+    sb, ldb = stored(b, k, n, tb)
+    r = runner_of(kernel)
+    d = run(r, sa, sb, c, m, n, k, 0.75, -1.25, force=AUTO, lda=lda, ldb=ldb)
+    assert r.info("last_variant") == TENSOR and r.last_status()[0] == 0
+    check(d, a, b, c, m, n, k, 0.75, -1.25)
+    d2 = run(r, sa, sb, c, m, n, k, 0.75, -1.25, force=AUTO, lda=lda, ldb=ldb)
+    assert np.array_equal(d, d2)
