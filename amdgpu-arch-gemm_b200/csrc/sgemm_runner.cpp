@@ -121,6 +121,7 @@ struct sgemm_handle {
     uint32_t tile_m = 0, tile_n = 0;
     TensorKernel tk_main, tk_skinny;   // tk_skinny.fn == NULL: the cubin has no companion kernel
     TensorKernel tk_wholek;            // twin of tk_main with whole-K accumulation (fn == NULL: none)
+    TensorKernel tk_thin;              // the companion with 32-column tiles, for N of a few columns (fn == NULL: none)
     CUdeviceptr status = 0;
     CUdeviceptr counters = 0;   // device words shared by all launches of the handle: [0] = wave-alignment counter
     // workspace: owned (grow on demand) or lent
@@ -146,7 +147,7 @@ struct sgemm_handle {
     bool pipeline_host = true;  // sgemm_run_host overlaps uploads, GEMM and downloads over column chunks
     bool pdl = true;            // launch with programmatic stream serialisation (see launch())
     int64_t acc_chain_opt = -1;   // -1: as generated, 0: whole K in one chain, else k per chain
-    int64_t last_variant = 0, last_split_k = 1, last_grid = 0, launches = 0, last_acc_chain = 0;
+    int64_t last_variant = 0, last_split_k = 1, last_grid = 0, launches = 0, last_acc_chain = 0, last_tile_n = 0;
     CachedMap maps[4];
     // optional timing of the main GEMM kernel alone (events around it on the caller's stream)
     bool profile = false;
@@ -282,7 +283,7 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
             return fail(h, SGEMM_ERR_UNSUPPORTED, "companion tensor kernel forced but %s",
                         h->tk_skinny.fn ? "the operands are not TMA-eligible" : "the cubin has none");
         variant = kVariantTensor;
-        tk = &h->tk_skinny;
+        tk = (h->tk_thin.fn && n <= h->tk_thin.tile_n) ? &h->tk_thin : &h->tk_skinny;
     } else if (h->force_variant == 1) {
         if (!eligible)
             return fail(h, SGEMM_ERR_UNSUPPORTED,
@@ -302,7 +303,7 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
         // small problems too: the pre-pass is one more dependent launch in a call that lasts a few of them
         if (variant == kVariantTensor && h->tk_skinny.fn &&
             (intensity < (double)h->skinny_below_intensity || flops < (double)h->skinny_below_flops))
-            tk = &h->tk_skinny;
+            tk = (h->tk_thin.fn && n <= h->tk_thin.tile_n) ? &h->tk_thin : &h->tk_skinny;   // a few columns: 32-column tiles
     }
     p->variant = variant;
     if (variant == kVariantTensor) {
@@ -658,8 +659,9 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
         rc = launch(h, h->fn_reduce, blocks, 1, 1, 256, 1, 0, stream, params);
         if (rc) return rc;
     }
-    h->last_variant = p.variant != kVariantTensor ? 2 : (p.tk == &h->tk_skinny ? 3 : 1);
+    h->last_variant = p.variant != kVariantTensor ? 2 : ((p.tk == &h->tk_skinny || p.tk == &h->tk_thin) ? 3 : 1);
     if (p.variant != kVariantTensor) h->last_acc_chain = 0;
+    h->last_tile_n = p.variant == kVariantTensor ? p.tk->tile_n : 0;
     h->last_split_k = p.split_k;
     h->last_grid = p.grid_x;
     return SGEMM_OK;
@@ -719,6 +721,12 @@ int config_from_toml(const char *path, sgemm_config *c, std::string *err) {
     c->acc_chain = t.get_int("acc_chain", &v) ? (int32_t)v : 0;
     std::snprintf(c->wholek_entry, sizeof c->wholek_entry, "%s", t.get_string("wholek_entry", &s) ? s.c_str() : "");
     c->skinny_acc_chain = t.get_int("skinny_acc_chain", &v) ? (int32_t)v : 0;
+    if (t.get_int_array("thin_tile", &sk) && sk.size() == 3)
+        for (int i = 0; i < 3; ++i) c->thin_tile[i] = (int32_t)sk[i];
+    c->thin_threads = t.get_int("thin_threads", &v) ? (int32_t)v : 0;
+    c->thin_smem_bytes = t.get_int("thin_smem_bytes", &v) ? (int32_t)v : 0;
+    c->thin_acc_chain = t.get_int("thin_acc_chain", &v) ? (int32_t)v : 0;
+    std::snprintf(c->thin_entry, sizeof c->thin_entry, "%s", t.get_string("thin_entry", &s) ? s.c_str() : "");
     std::snprintf(c->entry, sizeof c->entry, "%s", t.get_string("entry", &s) ? s.c_str() : "generated_gemm");
     std::snprintf(c->fallback_entry, sizeof c->fallback_entry, "%s", t.get_string("fallback_entry", &s) ? s.c_str() : "");
     if (c->variant == kVariantTensor && (c->fallback_threads <= 0 || c->fallback_tile[0] <= 0 || !c->fallback_entry[0])) {
@@ -872,6 +880,18 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
         h->tk_skinny.split_inkernel = true; h->tk_skinny.a_packed = false;
         h->tk_skinny.acc_chain = (uint32_t)std::max(cfg.skinny_acc_chain, 0);
     }
+    if (cfg.variant == kVariantTensor && cfg.thin_entry[0] && cfg.thin_threads > 0 && cfg.thin_tile[0] > 0) {
+        if ((r = d.cuModuleGetFunction_(&h->tk_thin.fn, h->module, cfg.thin_entry)) != CUDA_SUCCESS ||
+            (r = d.cuFuncSetAttribute_(h->tk_thin.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, cfg.thin_smem_bytes)) != CUDA_SUCCESS) {
+            fail(h, SGEMM_ERR_MODULE, "entry point '%s' unusable in '%s': %s", cfg.thin_entry, cubin_path, cu_text(r).c_str());
+            return bail(SGEMM_ERR_MODULE);
+        }
+        h->tk_thin.tile_m = (uint32_t)cfg.thin_tile[0]; h->tk_thin.tile_n = (uint32_t)cfg.thin_tile[1];
+        h->tk_thin.bk = (uint32_t)cfg.thin_tile[2];
+        h->tk_thin.group = 1; h->tk_thin.threads = (uint32_t)cfg.thin_threads; h->tk_thin.smem = (uint32_t)cfg.thin_smem_bytes;
+        h->tk_thin.split_inkernel = true; h->tk_thin.a_packed = false;
+        h->tk_thin.acc_chain = (uint32_t)std::max(cfg.thin_acc_chain, 0);
+    }
     if (cfg.dynamic_smem_bytes > 0 &&
         (r = d.cuFuncSetAttribute_(h->fn_main, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, cfg.dynamic_smem_bytes)) != CUDA_SUCCESS) {
         fail(h, SGEMM_ERR_CUDA, "cannot opt in to %d bytes of dynamic shared memory: %s", cfg.dynamic_smem_bytes, cu_text(r).c_str());
@@ -976,7 +996,7 @@ SGEMM_API int sgemm_run_host(sgemm_handle *h, const float *hA, const float *hB, 
                             lda, ldb, &whole)))
             return rc;
         const int64_t saved_variant = h->force_variant, saved_split = h->split_k_opt;
-        h->force_variant = whole.variant != kVariantTensor ? 2 : (whole.tk == &h->tk_skinny ? 3 : 1);
+        h->force_variant = whole.variant != kVariantTensor ? 2 : ((whole.tk == &h->tk_skinny || whole.tk == &h->tk_thin) ? 3 : 1);
         h->split_k_opt = whole.split_k;
         CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[0], hA, bytes[0], s_in));
         CU_CHECK(h, d.cuEventRecord_(ev_a, s_in));
@@ -1111,6 +1131,7 @@ SGEMM_API int sgemm_get_info(sgemm_handle *h, const char *key, int64_t *value) {
     else if (k == "last_variant") *value = h->last_variant;
     else if (k == "last_split_k") *value = h->last_split_k;
     else if (k == "last_acc_chain") *value = h->last_acc_chain;
+    else if (k == "last_tile_n") *value = h->last_tile_n;
     else if (k == "acc_chain") *value = h->tk_main.acc_chain;
     else if (k == "skinny_acc_chain") *value = h->tk_skinny.acc_chain;
     else if (k == "last_grid") *value = h->last_grid;

@@ -64,6 +64,7 @@ KERNEL_ENTRY = "generated_gemm"     # the entry name the runner and the tuner ha
 SIMT_FALLBACK_ENTRY = "generated_gemm_simt"
 WHOLEK_ENTRY = "generated_gemm_wholek"   # twin of the main tcgen05 kernel that accumulates all of K in one chain
 SKINNY_ENTRY = "generated_gemm_skinny"   # companion tcgen05 kernel for low-intensity shapes (tensor cubins)
+THIN_ENTRY = "generated_gemm_thin"       # the companion with 32-column tiles, for N of a few columns
 
 # The 15 arguments of the kernel ABI in order: (typename, name, bytes).
 KERNEL_ABI = (
@@ -395,6 +396,15 @@ class GemmSolutionConfig:
                                   32, self.trans_a, self.trans_b, vmem_stage=2, split="inkernel", terms=self.terms,
                                   companion=False, acc_chain=0 if self._acc_chain_requested == 0 else None)
 
+    def thin_config(self) -> Optional["GemmSolutionConfig"]:
+        """The companion kernel's narrow sibling (128 x 32 x 32, 5 stages, lo terms made in the kernel): with N of a
+        few columns the 128-column companion would spend its tensor-pipe time on padding."""
+        if self.companion_config() is None:
+            return None
+        return GemmSolutionConfig(self.a_type, self.b_type, self.cd_type, self.scalar_type, (128, 32, 1, 8), (1, 1), (1, 1),
+                                  32, self.trans_a, self.trans_b, vmem_stage=4, split="inkernel", terms=self.terms,
+                                  companion=False, acc_chain=0 if self._acc_chain_requested == 0 else None)
+
     def to_dict(self) -> Dict:
         d = {
             # ---- the reference's 14 keys (generator/generator.py:1001-1017), same order and types ----
@@ -443,6 +453,15 @@ class GemmSolutionConfig:
                     "skinny_threads": sk.num_workitems,
                     "skinny_smem_bytes": sk.lds_usage_bytes,
                     "skinny_acc_chain": sk.acc_chain,
+                })
+            th = self.thin_config()
+            if th is not None:
+                d.update({
+                    "thin_entry": THIN_ENTRY,
+                    "thin_tile": [th.tile_size[0], th.tile_size[1], th.depth_k],
+                    "thin_threads": th.num_workitems,
+                    "thin_smem_bytes": th.lds_usage_bytes,
+                    "thin_acc_chain": th.acc_chain,
                 })
         return d
 
@@ -555,6 +574,15 @@ def gemm(context: GpuContext, name: str, arch: str, config: GemmSolutionConfig, 
             body = re.sub(r"\b%s\b" % KERNEL_ENTRY, SKINNY_ENTRY, body)
             out.write("\n// ---- companion kernel for low-intensity shapes: 128 x 128 x 32, one CTA per tile, in-kernel split ----\n")
             out.write(_defines([(k.replace("TC_", "TCS_", 1), v) for k, v in _tensor_defines(companion)]))
+            out.write(body)
+            thin = config.thin_config()
+            body = template.split("// ==== end of the per-kernel section")[0]
+            body = re.sub(r"\bTC_", "TCT_", body)
+            body = re.sub(r"\btc_", "tct_", body)
+            body = re.sub(r"\bTc(?=[A-Z])", "Tct", body)
+            body = re.sub(r"\b%s\b" % KERNEL_ENTRY, THIN_ENTRY, body)
+            out.write("\n// ---- the companion's narrow sibling: 128 x 32 x 32, 5 stages, in-kernel split, for N of a few columns ----\n")
+            out.write(_defines([(k.replace("TC_", "TCT_", 1), v) for k, v in _tensor_defines(thin)]))
             out.write(body)
     src = out.getvalue()
     context.content.write(src)

@@ -39,6 +39,8 @@ class SgemmConfig(ctypes.Structure):
         ("skinny_tile", ctypes.c_int32 * 3), ("skinny_threads", ctypes.c_int32), ("skinny_smem_bytes", ctypes.c_int32),
         ("skinny_entry", ctypes.c_char * 64), ("acc_chain", ctypes.c_int32), ("skinny_acc_chain", ctypes.c_int32),
         ("wholek_entry", ctypes.c_char * 64),
+        ("thin_tile", ctypes.c_int32 * 3), ("thin_threads", ctypes.c_int32), ("thin_smem_bytes", ctypes.c_int32),
+        ("thin_acc_chain", ctypes.c_int32), ("thin_entry", ctypes.c_char * 64),
     ]
 
 

@@ -77,6 +77,12 @@ typedef struct sgemm_config {
     /* twin of the main tensor kernel that accumulates all of K in one chain (empty: none); same tile, threads and
      * shared memory as the main kernel */
     char wholek_entry[64];
+    /* the companion's narrow sibling (128 x 32 tiles) for N of a few columns (empty entry: none) */
+    int32_t thin_tile[3];
+    int32_t thin_threads;
+    int32_t thin_smem_bytes;
+    int32_t thin_acc_chain;
+    char thin_entry[64];
 } sgemm_config;
 
 /* Replaces getAsmKernelConfig (runner/generator_runner.cpp:100-124).  Host only, needs no GPU. */
@@ -151,7 +157,8 @@ int sgemm_wait_selftest(sgemm_handle *h, uint32_t timeout_ms, uint32_t tag);
 
 /* Options: "force_variant" 0 auto, 1 tensor (main kernel), 2 simt, 3 tensor (companion kernel for skinny shapes);
  * "skinny_below_intensity": in auto mode problems with fewer flop per byte of A and B than this (default 200: a
- * skinny M or N with a long K) run on the companion kernel (128 x 128 tiles, lo terms made in the kernel, no pre-pass);
+ * skinny M or N with a long K) run on the companion kernel (128 x 128 tiles, lo terms made in the kernel, no pre-pass;
+ * with N <= 32 on its sibling with 128 x 32 tiles);
  * "skinny_below_flops": so do problems with 2*M*N*K below this (default 2^33: the pre-pass would be one more dependent
  * launch in a call that only lasts a few); "split_k" 0 auto, n >= 1 fixed;
  * "simt_below_flops" problems with 2*M*N*K below this use the SIMT kernel (auto mode);
@@ -173,6 +180,7 @@ int sgemm_wait_selftest(sgemm_handle *h, uint32_t timeout_ms, uint32_t tag);
 int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value);
 
 /* Facts: "variant" (of the cubin), "last_variant" (1 tensor main / 2 simt / 3 tensor companion), "last_split_k", "last_grid",
+ * "last_tile_n" (columns of the tile of the last launch: tells the companion, 128, from its narrow sibling, 32),
  * "last_acc_chain" (k per accumulation chain of the last tensor launch, 0 = whole K), "acc_chain" and
  * "skinny_acc_chain" (the chains the main and the companion tensor kernel were generated with),
  * "launches" (kernel launches issued so far), "tile_m", "tile_n", "sm_count", "workspace_bytes",

@@ -556,3 +556,21 @@ def test_ragged_leading_dimensions_run_on_the_tensor_path(runner_of, kernel, mnk
     check(d, a, b, c, m, n, k, 0.75, -1.25)
     d2 = run(r, sa, sb, c, m, n, k, 0.75, -1.25, force=AUTO, lda=lda, ldb=ldb)
     assert np.array_equal(d, d2)
+
+
+# ------------------------------------------------------------------ a few columns: the companion's 32-column tiles
+@pytest.mark.parametrize("kernel", ["tc2_256x256x32_s3", "tc2_256x256x32_s3_tt"])
+@pytest.mark.parametrize("mnk,tile_n", [((8192, 8, 1024), 32), ((3000, 32, 4096), 32), ((16384, 1, 8192), 32), ((2048, 33, 2048), 128),
+                                        ((4096, 128, 1024), 128)])
+def test_thin_problems_take_the_narrow_companion(runner_of, kernel, mnk, tile_n):
+    m, n, k = mnk
+    ta = tb = kernel.endswith("_tt")
+    r = runner_of(kernel)
+    r.set_option("skinny_below_intensity", 200)      # the library's default rule
+    lda, ldb = ((k if ta else m) + 3) // 4 * 4, ((n if tb else k) + 3) // 4 * 4
+    a, b, c = oracle.make_inputs(m, n, k, seed=17)
+    sa, lda = stored(a, m, k, ta, ld=lda)
+    sb, ldb = stored(b, k, n, tb, ld=ldb)
+    d = run(r, sa, sb, c, m, n, k, 0.5, -1.5, force=AUTO, lda=lda, ldb=ldb)
+    assert r.info("last_variant") == SKINNY and r.info("last_tile_n") == tile_n
+    check(d, a, b, c, m, n, k, 0.5, -1.5)
