@@ -329,8 +329,9 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
     p->tk = variant == kVariantTensor ? tk : nullptr;
     size_t off = 0;
     if (variant != kVariantTensor) p->repitch_a = p->repitch_b = false;
+    // (everything that belongs to A comes first: the pipelined host path reuses A's copies across column chunks of
+    // different widths, so their offsets must not depend on N)
     if (p->repitch_a) { p->rp_a_off = off; off += round_up((size_t)lda * (h->cfg.trans_a ? m : k) * 4, 256); }
-    if (p->repitch_b) { p->rp_b_off = off; off += round_up((size_t)ldb * (h->cfg.trans_b ? k : n) * 4, 256); }
     if (variant == kVariantTensor) {
         // persistent grid: one CTA (or CTA pair) per SM (pair of SMs), never more launch units than tiles
         const uint64_t units = (uint64_t)p->tiles_m * p->tiles_n * p->split_k;
@@ -354,6 +355,7 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
             p->span_a = h->cfg.trans_a ? (uint64_t)lda * (m - 1) + k : (uint64_t)lda * (k - 1) + m;
             p->lo_a_off = off; off += round_up(p->span_a * 4, 256);
         }
+        if (p->repitch_b) { p->rp_b_off = off; off += round_up((size_t)ldb * (h->cfg.trans_b ? k : n) * 4, 256); }
         if (!tk->split_inkernel && h->elem_bytes == 4) { p->lo_b_off = off; off += round_up(p->span_b * 4, 256); }
     } else {
         const bool own = h->cfg.variant == kVariantSimt;

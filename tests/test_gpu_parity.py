@@ -574,3 +574,18 @@ def test_thin_problems_take_the_narrow_companion(runner_of, kernel, mnk, tile_n)
     d = run(r, sa, sb, c, m, n, k, 0.5, -1.5, force=AUTO, lda=lda, ldb=ldb)
     assert r.info("last_variant") == SKINNY and r.info("last_tile_n") == tile_n
     check(d, a, b, c, m, n, k, 0.5, -1.5)
+
+
+def test_pipelined_host_call_with_ragged_leading_dimensions(runner_of):
+    """Large host call with natural odd leading dimensions: column chunks on three streams, every chunk through aligned
+    copies of its operands, the copy of A made once and reused by the later (and narrower, last) chunks."""
+    m, n, k = 2049, 4100, 2049
+    a, b, c = oracle.make_inputs(m, n, k, seed=19)
+    r = runner_of("tc2_256x256x32_s3")
+    d = run(r, a, b, c, m, n, k, 1.0, 0.5, force=AUTO)
+    assert r.info("last_variant") == TENSOR and r.last_status()[0] == 0
+    check(d, a, b, c, m, n, k, 1.0, 0.5)
+    r.set_option("pipeline_host", 0)
+    d1 = run(r, a, b, c, m, n, k, 1.0, 0.5, force=AUTO)
+    r.set_option("pipeline_host", 1)
+    assert np.array_equal(d, d1)          # the chunked call computes what the single launch computes
