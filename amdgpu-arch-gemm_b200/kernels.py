@@ -120,7 +120,9 @@ def recommend(m: int, n: int, k: int) -> str:
       * tiny problems: the FFMA kernel (launch-latency bound either way, and no pre-pass);
       * few flops per byte of A and B (a skinny M or N with a long K): small tiles with the in-kernel split — the
         default cubin switches to its companion kernel of this kind by itself, so it is returned here as well;
-      * fewer than one wave of 256 x 256 tiles: 128 x 128 tiles so that more SMs get work;
+      * small problems (below 2^33 flop): the default cubin again, whose companion kernel (128 x 128 tiles, no
+        pre-pass launch) the runner picks for them by itself;
+      * larger problems with fewer than half a wave of 256 x 256 tiles: 128 x 128 tiles so that more SMs get work;
       * everything else: CTA pairs on 256 x 256 tiles with the split pre-pass.
     """
     flops = 2.0 * m * n * k
@@ -128,6 +130,8 @@ def recommend(m: int, n: int, k: int) -> str:
         return DEFAULT_SIMT
     if flops / (4.0 * (m * k + k * n)) < 200.0:
         return DEFAULT_TENSOR if min(m, n) < 256 else "tc2i_256x256x32_s3"
+    if flops < 2 ** 33:
+        return DEFAULT_TENSOR
     if -(-m // 256) * -(-n // 256) < 37:
         return "tc_128x128x32_s3"
     return DEFAULT_TENSOR
