@@ -102,7 +102,8 @@ def test_shard_columns_cover_n_in_whole_tiles():
 
 def test_kernel_recommendation_names_registered_kernels(built):
     cases = {(8192, 8192, 8192): "tc2_256x256x32_s3", (32, 32, 32): "simt_128x128x16", (4096, 128, 16384): "tc2_256x256x32_s3",
-             (256, 8192, 16384): "tc2i_256x256x32_s3", (1024, 1024, 1024): "tc_128x128x32_s3", (32768, 4096, 8192): "tc2_256x256x32_s3"}
+             (256, 8192, 16384): "tc2i_256x256x32_s3", (1024, 1024, 1024): "tc2_256x256x32_s3", (1024, 1024, 16384): "tc_128x128x32_s3",
+             (32768, 4096, 8192): "tc2_256x256x32_s3"}
     for shape, want in cases.items():
         got = built.recommend(*shape)
         assert got in built.REGISTRY and got == want, (shape, got)
