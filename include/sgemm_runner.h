@@ -170,7 +170,8 @@ int sgemm_wait_selftest(sgemm_handle *h, uint32_t timeout_ms, uint32_t tag);
  * set-up overlap with the tail of the previous kernel (all kernels wait on the grid dependency before touching memory);
  * "wave_sync" 1 (default) lets the persistent CTAs of the tensor kernel wait briefly for each other at tile
  * boundaries so that they keep sharing operand panels in L2 (a bounded, soft wait: performance only);
- * "pipeline_host" 1 (default) lets sgemm_run_host overlap transfers and compute over column chunks;
+ * "pipeline_host" 1 (default) lets sgemm_run_host overlap transfers and compute over column chunks,
+ * "pipeline_chunks" (2..64, default 16) says how many;
  * "profile" 1 brackets every main-GEMM-kernel launch with an event pair (read with "profile_main_ns");
  * "acc_chain": k per tensor-core accumulation chain, -1 (default) = as the kernel was generated (128 unless its
  * TOML says otherwise), 0 = all of K in one chain (fastest; the tensor core's truncating adds then drift toward zero
