@@ -238,9 +238,11 @@ bool tensor_eligible(const sgemm_handle *h, const void *a, const void *b, uint32
     return true;
 }
 
-uint32_t pick_split_k(const sgemm_handle *h, uint32_t tiles, uint32_t k, uint32_t bk, uint32_t group) {
+// slots: launch units the device runs at a time (SMs / CTAs per unit for the persistent tensor kernels, two blocks
+// per SM for the FFMA kernel)
+uint32_t pick_split_k(const sgemm_handle *h, uint32_t tiles, uint32_t k, uint32_t bk, uint32_t slots) {
     const uint32_t kb_total = (k + bk - 1) / bk;
-    const uint32_t slots = std::max<uint32_t>(1, (uint32_t)h->sm_count / std::max<uint32_t>(group, 1));   // launch units in flight
+    slots = std::max<uint32_t>(1, slots);
     uint32_t split = 1;
     if (h->split_k_opt > 0) {
         split = (uint32_t)h->split_k_opt;
@@ -315,7 +317,7 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
                         tk->acc_chain ? "not a multiple of the kernel's k-block" : "this kernel was generated without chunked accumulation");
         p->tiles_m = (m + tk->tile_m - 1) / tk->tile_m;
         p->tiles_n = (n + tk->tile_n - 1) / tk->tile_n;
-        p->split_k = pick_split_k(h, p->tiles_m * p->tiles_n, k, tk->bk, tk->group);
+        p->split_k = pick_split_k(h, p->tiles_m * p->tiles_n, k, tk->bk, (uint32_t)h->sm_count / std::max<uint32_t>(tk->group, 1));
         // a launch unit whose k range is one accumulation chunk (no chunking, or up to two chains: the first chunks
         // are double length) does not need the running sum: the main kernel's whole-K twin (same tiles, same split)
         // writes the accumulator out straight from TMEM
@@ -365,7 +367,7 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
         const uint32_t bk = own ? (uint32_t)h->cfg.depth_k : (uint32_t)h->cfg.fallback_tile[2];
         p->tiles_m = (m + tm - 1) / tm;
         p->tiles_n = (n + tn - 1) / tn;
-        p->split_k = pick_split_k(h, p->tiles_m * p->tiles_n, k, bk, 1);
+        p->split_k = pick_split_k(h, p->tiles_m * p->tiles_n, k, bk, 2u * (uint32_t)h->sm_count);
         p->grid_x = p->tiles_m * p->tiles_n;
     }
     if (p->split_k > 1) {
