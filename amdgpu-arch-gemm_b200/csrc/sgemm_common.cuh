@@ -165,6 +165,22 @@ extern "C" __global__ void sgemm_repitch(const float *__restrict__ src, uint32_t
     }
 }
 
+// FP32 -> FP16 (kind 1) or BF16 (kind 2) words, round to nearest even: how callers that hold FP32 data (the runner
+// program, the tuner) make operands for the kernels with 16-bit A and B.
+extern "C" __global__ void sgemm_narrow16(const float *__restrict__ src, uint16_t *__restrict__ dst, uint64_t count,
+                                          uint32_t kind) {
+    sgemm_launch_dependents();
+    sgemm_grid_dependency_wait();
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        const float x = __ldg(src + i);
+        uint16_t w;
+        if (kind == 1) asm("cvt.rn.f16.f32 %0, %1;" : "=h"(w) : "f"(x));
+        else asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(w) : "f"(x));
+        dst[i] = w;
+    }
+}
+
 // The same packing for 16-bit operands (FP16 / BF16 words are copied as they are, there is no lo term):
 //   out[l + i*ldt] = a[i + l*lda]
 extern "C" __global__ void sgemm_pack16_kmajor(const uint16_t *__restrict__ a, uint32_t lda, uint32_t m, uint32_t k,

@@ -114,7 +114,7 @@ struct sgemm_handle {
     CUcontext ctx = nullptr;
     CUmodule module = nullptr;
     uint32_t elem_bytes = 4;    // size of an element of A and B: 4 (FP32) or 2 (FP16 / BF16, tensor variant only)
-    CUfunction fn_pack16 = nullptr, fn_repitch = nullptr;
+    CUfunction fn_pack16 = nullptr, fn_repitch = nullptr, fn_narrow16 = nullptr;
     CUfunction fn_main = nullptr, fn_simt = nullptr, fn_split_lo = nullptr, fn_pack_a = nullptr,
                fn_reduce = nullptr, fn_fill = nullptr, fn_tile_map = nullptr, fn_wait_selftest = nullptr;
     int sm_count = 0;
@@ -845,6 +845,7 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
         {&h->fn_pack_a, "sgemm_pack_a_kmajor", true},
         {&h->fn_pack16, "sgemm_pack16_kmajor", true},
         {&h->fn_repitch, "sgemm_repitch", true},
+        {&h->fn_narrow16, "sgemm_narrow16", true},
         {&h->fn_reduce, "sgemm_splitk_reduce", true},
         {&h->fn_fill, "sgemm_fill_uniform", true},
         {&h->fn_tile_map, "sgemm_tile_map", true},
@@ -1195,6 +1196,18 @@ SGEMM_API int sgemm_fill_uniform(sgemm_handle *h, float *dptr, uint64_t count, u
     void *params[] = {&dptr, &count, &first_index, &stream_id};
     const uint32_t blocks = (uint32_t)std::min<uint64_t>((count + 255) / 256, (uint64_t)h->sm_count * 16);
     return launch(h, h->fn_fill, blocks, 1, 1, 256, 1, 0, (CUstream)stream, params);
+}
+
+SGEMM_API int sgemm_narrow16(sgemm_handle *h, const float *dsrc, void *ddst, uint64_t count, void *stream) {
+    if (!h || ((!dsrc || !ddst) && count)) return SGEMM_ERR_INVALID_ARGUMENT;
+    if (h->elem_bytes != 2)
+        return fail(h, SGEMM_ERR_UNSUPPORTED, "sgemm_narrow16 converts to the operand type of a cubin for FP16 or BF16 operands; this one takes FP32");
+    if (count == 0) return SGEMM_OK;
+    CtxGuard guard(h);
+    uint32_t kind = (uint32_t)h->cfg.a_type;   // 1 = FP16, 2 = BF16
+    void *params[] = {&dsrc, &ddst, &count, &kind};
+    const uint32_t blocks = (uint32_t)std::min<uint64_t>((count + 255) / 256, (uint64_t)h->sm_count * 16);
+    return launch(h, h->fn_narrow16, blocks, 1, 1, 256, 1, 0, (CUstream)stream, params);
 }
 
 SGEMM_API int sgemm_tile_map(sgemm_handle *h, int32_t *host_xy, uint32_t nx, uint32_t ny) {

@@ -69,6 +69,7 @@ ABI = {
     "sgemm_workspace_bytes": (ctypes.c_int, [_vp, _u32, _u32, _u32, _u32, _u32, ctypes.POINTER(ctypes.c_size_t)]),
     "sgemm_set_workspace": (ctypes.c_int, [_vp, _vp, ctypes.c_size_t]),
     "sgemm_fill_uniform": (ctypes.c_int, [_vp, _vp, _u64, _u64, _u64, _vp]),
+    "sgemm_narrow16": (ctypes.c_int, [_vp, _vp, _vp, _u64, _vp]),
     "sgemm_tile_map": (ctypes.c_int, [_vp, ctypes.POINTER(ctypes.c_int32), _u32, _u32]),
     "sgemm_dev_alloc": (ctypes.c_int, [_vp, ctypes.c_size_t, ctypes.POINTER(_vp)]),
     "sgemm_dev_free": (ctypes.c_int, [_vp, _vp]),
@@ -235,6 +236,10 @@ class SgemmRunner:
     def fill_uniform(self, dptr, count: int, stream_id: int, first_index: int = 0, stream=0):
         self._check(self._L.sgemm_fill_uniform(self._h, _ptr(dptr), count, first_index, stream_id, stream),
                     "sgemm_fill_uniform")
+
+    def narrow16(self, dsrc, ddst, count: int, stream=0):
+        """FP32 -> the cubin's 16-bit operand type (FP16 / BF16), on the device."""
+        self._check(self._L.sgemm_narrow16(self._h, _ptr(dsrc), _ptr(ddst), count, stream), "sgemm_narrow16")
 
     def tile_map(self, nx: int, ny: int):
         buf = (ctypes.c_int32 * (2 * nx * ny))()

@@ -202,6 +202,10 @@ int sgemm_set_workspace(sgemm_handle *h, void *dptr, size_t bytes);
 int sgemm_fill_uniform(sgemm_handle *h, float *dptr, uint64_t count, uint64_t first_index,
                        uint64_t stream_id, void *stream);
 
+/* No counterpart in the reference (FP32 only).  Device conversion of `count` FP32 values to the 16-bit operand type of
+ * the loaded cubin (FP16 or BF16, round to nearest even); SGEMM_ERR_UNSUPPORTED on an FP32 cubin. */
+int sgemm_narrow16(sgemm_handle *h, const float *dsrc, void *ddst, uint64_t count, void *stream);
+
 /* Tile rasterisation of the loaded kernel: xy[2*z], xy[2*z+1] = (tile x, tile y) of launch unit z for an
  * nx x ny tile grid, computed on the device by the kernel's own mapping function (the workgroup remap of
  * generator/generator.py:1437-1464). */

@@ -50,9 +50,18 @@ def test_cli_argument_and_file_errors(built):
     assert bad.returncode not in (0, 255) and "sgemm_open" in bad.stderr
 
 
-def test_cli_refuses_cubins_for_sixteen_bit_operands(built):
+@pytest.mark.parametrize("kernel", ["fp16_tc_128x128x64_s4", "bf16_tc2_256x256x64_s6"])
+def test_cli_drives_cubins_for_sixteen_bit_operands(built, kernel):
+    """FP32 draws converted on the device, CPU check on the converted values, an empty SIMT block (there is no FFMA
+    kernel for 16-bit operands) so that the tuner's parse of the third line from the end still works."""
+    ret = run_cli(built, kernel, 512, 768, 640, 1)
+    assert ret.returncode == 0, ret.stdout + ret.stderr
+    lines = ret.stdout.split("\n")
+    assert lines[1] == "SIMT gemm: 0 ms" and lines[4].startswith("ASM gemm: ")
+    assert lines[7] == f"# of mismatches: 0/{512 * 768}"
+    assert float(lines[-3].split(":")[-1]) > 0            # tuner/sgemm_tuner.py:115
+    assert ("BF16" if kernel.startswith("bf16") else "FP16") in ret.stderr
+    cubin, toml = built.ensure("bf16_tc2_256x256x64_s6_tt")   # transposed layouts are not what this program drives
     from runner import api
-    api.build_library()
-    cubin, toml = built.ensure("fp16_tc_128x128x64_s4")
-    ret = subprocess.run([str(api.RUNNER_PATH), cubin, toml, "64", "64", "64", "1", "1", "0"], capture_output=True, text=True)
-    assert ret.returncode == 2 and "16-bit operands" in ret.stderr
+    bad = subprocess.run([str(api.RUNNER_PATH), cubin, toml, "64", "64", "64", "1", "1", "0"], capture_output=True, text=True)
+    assert bad.returncode == 2 and "NN layout" in bad.stderr
