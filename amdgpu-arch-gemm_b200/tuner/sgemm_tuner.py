@@ -37,6 +37,7 @@ from generator.generator import (  # noqa: E402
 SUPPORTED_CLUSTERS = [(1, 1), (2, 1)]
 SUPPORTED_TILE_N = [128, 256]
 SUPPORTED_DEPTH_K = [16, 32, 64]
+SUPPORTED_DEPTH_K_16BIT = [32, 64, 128]   # 16-bit operands: 64-byte rows, or whole 128-byte rows of 64 k
 SUPPORTED_STAGES = [2, 3, 4, 5, 6, 7]
 SUPPORTED_SPLIT = ["prepass", "inkernel"]   # where the 3xTF32 lo terms are made
 # FFMA variant: (thread grid, per-thread tile, k per stage)
@@ -58,18 +59,23 @@ def kernel_arguments():
     return [FunctionArgument(t, n, None, s) for t, n, s in names]
 
 
-def candidates(include_simt: bool = True, include_tensor: bool = True):
-    """Yield (key, config factory, optimisation factory) for every point of the search space."""
+def candidates(include_simt: bool = True, include_tensor: bool = True, ab_type: DataType = DataType.FP32):
+    """Yield (key, config factory, optimisation factory) for every point of the search space.  ``ab_type`` FP16 or
+    BF16 searches the tensor variant for 16-bit operands (atom K = 16, no split placement, no FFMA variant)."""
     F = DataType.FP32
-    tensor_space = product(SUPPORTED_CLUSTERS, SUPPORTED_TILE_N, SUPPORTED_DEPTH_K, SUPPORTED_STAGES, SUPPORTED_SPLIT,
+    half = ab_type != DataType.FP32
+    depth_ks = SUPPORTED_DEPTH_K_16BIT if half else SUPPORTED_DEPTH_K
+    splits = ["prepass"] if half else SUPPORTED_SPLIT
+    tensor_space = product(SUPPORTED_CLUSTERS, SUPPORTED_TILE_N, depth_ks, SUPPORTED_STAGES, splits,
                            SUPPORTED_WGM) if include_tensor else ()
     for cluster, bn, dk, stages, split, wgm in tensor_space:
-        key = f"tensor c{cluster[0]}x{cluster[1]} n{bn} k{dk} s{stages} {split} wgm{wgm}"
+        key = f"tensor{'' if not half else ' ' + ab_type.name.lower()} c{cluster[0]}x{cluster[1]} n{bn} k{dk} s{stages} {split} wgm{wgm}"
         yield (key,
                lambda cluster=cluster, bn=bn, dk=dk, stages=stages, split=split: GemmSolutionConfig(
-                   F, F, F, F, (128, bn, 1, 8), cluster, (1, 1), dk, False, False, vmem_stage=stages - 1, split=split),
+                   ab_type, ab_type, F, F, (128, bn, 1, 16 if half else 8), cluster, (1, 1), dk, False, False,
+                   vmem_stage=stages - 1, split=split),
                lambda wgm=wgm: GemmOptimizations(1, wgm=wgm))
-    if include_simt:
+    if include_simt and not half:
         for (wg, wt, dk), wgm, plr in product(SUPPORTED_SIMT, SUPPORTED_WGM, SUPPORTED_PLR):
             key = f"simt g{wg[0]}x{wg[1]} t{wt[0]}x{wt[1]} k{dk} wgm{wgm} plr{plr}"
             yield (key,
@@ -95,13 +101,13 @@ def load_done(path: Path):
 
 
 def tune(m: int, n: int, k: int, bench: str, output_folder: str, include_simt: bool = True, allow_ragged: bool = False,
-         limit: int | None = None, include_tensor: bool = True):
+         limit: int | None = None, include_tensor: bool = True, ab_type: DataType = DataType.FP32):
     os.makedirs(output_folder, exist_ok=True)
     log_path = Path(output_folder) / "tuner_results.jsonl"
     done = load_done(log_path)
     best = None
     measured = 0
-    for key, make_config, make_opt in candidates(include_simt, include_tensor):
+    for key, make_config, make_opt in candidates(include_simt, include_tensor, ab_type):
         problem_key = f"{m}x{n}x{k} {key}"
         if problem_key in done:
             rec = done[problem_key]
@@ -165,6 +171,9 @@ if __name__ == "__main__":
     ap.add_argument("--no-tensor", action="store_true", help="search the FFMA variant only")
     ap.add_argument("--allow-ragged", action="store_true", help="keep tilings that do not divide M, N, K")
     ap.add_argument("--limit", type=int, default=None, help="stop after this many new measurements")
+    ap.add_argument("--ab-type", choices=["fp32", "fp16", "bf16"], default="fp32",
+                    help="element type of A and B (fp16 / bf16: tensor variant only; the reference has fp32 only)")
     args = ap.parse_args()
     tune(args.m, args.n, args.k, args.bench, args.output_folder, include_simt=not args.no_simt,
-         allow_ragged=args.allow_ragged, limit=args.limit, include_tensor=not args.no_tensor)
+         allow_ragged=args.allow_ragged, limit=args.limit, include_tensor=not args.no_tensor,
+         ab_type=DataType[args.ab_type.upper()])

@@ -72,3 +72,17 @@ def test_runner_failure_is_recorded_not_fatal(tmp_path, monkeypatch, capsys):
     # ragged problems are filtered like the reference does (tuner/sgemm_tuner.py:97) unless asked otherwise
     assert t.tune(250, 256, 256, "/bin/false", str(tmp_path / "o2"), include_simt=False) is None
     assert not (tmp_path / "o2" / "tuner_results.jsonl").exists()
+
+
+def test_sixteen_bit_search_space():
+    from generator.generator import DataType
+    keys, built = [], 0
+    for key, make_config, _ in t.candidates(ab_type=DataType.BF16):
+        keys.append(key)
+        try:
+            cfg = make_config()
+        except RuntimeError:
+            continue                     # infeasible points are the tuner's skips
+        built += 1
+        assert cfg.a_type == DataType.BF16 and cfg.mfma[3] == 16 and cfg.terms == 1
+    assert built > 20 and all(k.startswith("tensor bf16 ") for k in keys) and len(set(keys)) == len(keys)
