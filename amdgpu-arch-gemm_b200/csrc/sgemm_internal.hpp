@@ -13,11 +13,23 @@ int handle_device(const sgemm_handle *h);
 // Record a failure message on the handle (what sgemm_last_error returns) and hand `code` back.
 int set_error(sgemm_handle *h, int code, const char *message);
 
-// Scratch bytes sgemm_launch would need for this problem under the handle's current options.
-int scratch_bytes(sgemm_handle *h, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb, size_t *bytes);
+// Scratch bytes sgemm_launch would need for this problem under the handle's current options, planned for the
+// operands the call will really get (a base TMA cannot read where it lies adds an aligned copy to the need).
+int scratch_bytes(sgemm_handle *h, const void *dA, const void *dB, uint32_t m, uint32_t n, uint32_t k, uint32_t lda,
+                  uint32_t ldb, size_t *bytes);
+
+// Run `fn(arg)` with the handle's CUDA context current on this thread (pushed before, popped after), so that
+// CUDA runtime calls made inside bind to the device the handle was opened on without cudaSetDevice.  Returns
+// what `fn` returns, or SGEMM_ERR_CUDA when the context cannot be made current.
+int with_context(sgemm_handle *h, int (*fn)(void *), void *arg);
+
+// One pointer-sized slot per handle for sgemm_noalloc.cu: the device address of the library's static scratch
+// array as resolved in the handle's context (NULL until the first allocation-free call on the handle).
+void **noalloc_scratch_slot(sgemm_handle *h);
 
 // sgemm_launch with the scratch taken from [scratch, scratch + scratch_bytes) for this one call only; the
-// handle's own workspace settings are put back before returning.  Never allocates device memory.
+// handle's own workspace settings are put back before returning.  Never allocates device memory; a need beyond
+// `scratch_bytes` comes back as SGEMM_ERR_SCRATCH_LIMIT.
 int launch_with_scratch(sgemm_handle *h, void *scratch, size_t scratch_bytes, const float *dA, const float *dB,
                         const float *dC, float *dD, float alpha, float beta, uint32_t m, uint32_t n, uint32_t k,
                         uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, void *stream);

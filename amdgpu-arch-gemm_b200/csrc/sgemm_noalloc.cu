@@ -12,10 +12,11 @@
 // process exits.  Problems whose scratch does not fit are refused with SGEMM_ERR_SCRATCH_LIMIT.
 //
 // What to know before using it:
-//   * The first call on a device looks up the array's device address (cudaGetSymbolAddress, which also
-//     makes the CUDA runtime load this library's device image on that GPU).  That one-time set-up is not a
-//     cudaMalloc, but it is work the driver does outside any stream: make the first call on each device
-//     before starting a stream capture.
+//   * The first call on a handle looks up the array's device address (cudaGetSymbolAddress, made with the
+//     handle's own context current; on the first handle of a device it also makes the CUDA runtime load
+//     this library's device image on that GPU).  That one-time set-up is not a cudaMalloc, but it is work
+//     the driver does outside any stream: make the first call on each handle before starting a stream
+//     capture.  The thread's current device and context are left as they were.
 //   * All calls on a device share the one array, and it keeps whatever the previous call left in it.
 //     Nothing in it has to start from zero — every call first overwrites each byte it later reads — but
 //     two calls whose kernels overlap in time on the same GPU (different streams, different handles,
@@ -34,36 +35,46 @@
 namespace {
 
 constexpr size_t kScratchBytes = SGEMM_NOALLOC_SCRATCH_BYTES;
-constexpr int kMaxDevices = 64;
 
 // The scratch itself.  On the host this name is only a handle for the runtime's symbol table, never an
-// address a kernel could use; the device address is obtained below, once per device.
+// address a kernel could use; the device address is obtained below, once per handle, in the handle's context.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kScratchBytes];
 
-std::mutex g_lock;
-void *g_scratch_address[kMaxDevices] = {};
+struct Lookup {
+    void *address = nullptr;
+    cudaError_t error = cudaSuccess;
+};
 
-// Device address of g_noalloc_scratch on `device`, looked up on first use with that device current.
-int scratch_address(sgemm_handle *h, int device, void **out) {
+// Runs with the handle's context current (sgemm_internal::with_context): the runtime binds to whatever context
+// is current on the thread, so no cudaSetDevice is needed — and none is made, because a caller that only uses
+// this C ABI has no "current runtime device", and switching to one (and back to ordinal 0) would create a
+// primary context on GPU 0 in every process of a multi-GPU job.
+int lookup_scratch(void *arg) {
+    Lookup *out = static_cast<Lookup *>(arg);
+    out->error = cudaGetSymbolAddress(&out->address, g_noalloc_scratch);
+    return SGEMM_OK;
+}
+
+std::mutex g_lock;   // serialises first calls; the cached address itself lives in the handle
+
+// Device address of g_noalloc_scratch for the device (and context) of `h`, looked up on the handle's first
+// allocation-free call.  The handle keeps its context alive, so the address stays valid as long as the handle.
+int scratch_address(sgemm_handle *h, void **out) {
+    void **slot = sgemm_internal::noalloc_scratch_slot(h);
     std::lock_guard<std::mutex> guard(g_lock);
-    if (device < 0 || device >= kMaxDevices)
-        return sgemm_internal::set_error(h, SGEMM_ERR_INVALID_ARGUMENT, "device ordinal out of range for the static scratch table");
-    if (!g_scratch_address[device]) {
-        int previous = -1;
-        cudaError_t e = cudaGetDevice(&previous);
-        if (e == cudaSuccess) e = cudaSetDevice(device);
-        void *ptr = nullptr;
-        if (e == cudaSuccess) e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
-        if (previous >= 0 && previous != device) cudaSetDevice(previous);
-        if (e != cudaSuccess || !ptr) {
+    if (!*slot) {
+        Lookup found;
+        int rc = sgemm_internal::with_context(h, lookup_scratch, &found);
+        if (rc) return rc;
+        if (found.error != cudaSuccess || !found.address) {
             char msg[256];
-            std::snprintf(msg, sizeof msg, "cudaGetSymbolAddress for the static scratch on device %d failed: %s", device,
-                          cudaGetErrorString(e));
+            std::snprintf(msg, sizeof msg, "cudaGetSymbolAddress for the static scratch on device %d failed: %s",
+                          sgemm_internal::handle_device(h), cudaGetErrorString(found.error));
             return sgemm_internal::set_error(h, SGEMM_ERR_CUDA, msg);
         }
-        g_scratch_address[device] = ptr;
+        *slot = found.address;
     }
-    *out = g_scratch_address[device];
+    *out = *slot;
     return SGEMM_OK;
 }
 
@@ -77,7 +88,8 @@ SGEMM_API int sgemm_launch_noalloc(sgemm_handle *h, const float *dA, const float
     if (!h) return SGEMM_ERR_INVALID_ARGUMENT;
     // size check first: nothing is touched on the device when the problem does not fit
     size_t need = 0;
-    int rc = sgemm_internal::scratch_bytes(h, m, n, k, lda, ldb, &need);
+    // (planned for the real operands: an unaligned base or an odd leading dimension adds an aligned copy to the need)
+    int rc = sgemm_internal::scratch_bytes(h, dA, dB, m, n, k, lda, ldb, &need);
     if (rc) return rc;
     if (need > kScratchBytes) {
         char msg[256];
@@ -87,7 +99,7 @@ SGEMM_API int sgemm_launch_noalloc(sgemm_handle *h, const float *dA, const float
         return sgemm_internal::set_error(h, SGEMM_ERR_SCRATCH_LIMIT, msg);
     }
     void *scratch = nullptr;
-    rc = scratch_address(h, sgemm_internal::handle_device(h), &scratch);
+    rc = scratch_address(h, &scratch);
     if (rc) return rc;
     return sgemm_internal::launch_with_scratch(h, scratch, kScratchBytes, dA, dB, dC, dD, alpha, beta, m, n, k, lda, ldb,
                                                ldc, ldd, stream);

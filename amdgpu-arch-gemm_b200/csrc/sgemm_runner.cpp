@@ -154,6 +154,7 @@ struct sgemm_handle {
     bool profile = false;
     std::vector<std::pair<CUevent, CUevent>> prof_events;
     size_t prof_used = 0;
+    void *noalloc_scratch = nullptr;   // device address of the library's static scratch array in this handle's context
     std::string error;
 };
 
@@ -1002,14 +1003,34 @@ SGEMM_API int sgemm_run_host(sgemm_handle *h, const float *hA, const float *hB, 
         if ((rc = make_plan(h, reinterpret_cast<const void *>(h->stage[0]), reinterpret_cast<const void *>(h->stage[1]), m, n, k,
                             lda, ldb, &whole)))
             return rc;
-        const int64_t saved_variant = h->force_variant, saved_split = h->split_k_opt;
+        // Whatever happens inside the chunk loop — a failed copy, event or launch — the handle gets its options
+        // back and all three streams are drained before this function returns: nothing of the call may still be
+        // reading or writing the caller's host buffers afterwards.
+        struct Restore {
+            sgemm_handle *h;
+            int64_t variant, split;
+            CUstream streams[3];
+            CUresult drained = CUDA_SUCCESS;
+            bool done = false;
+            void run() {
+                if (done) return;
+                done = true;
+                for (CUstream st : streams) {
+                    CUresult r = driver().cuStreamSynchronize_(st);
+                    if (r != CUDA_SUCCESS && drained == CUDA_SUCCESS) drained = r;
+                }
+                h->force_variant = variant;
+                h->split_k_opt = split;
+                h->reuse_a_lo = false;
+            }
+            ~Restore() { run(); }
+        } restore{h, h->force_variant, h->split_k_opt, {s_in, s_cmp, s_out}};
         h->force_variant = whole.variant != kVariantTensor ? 2 : ((whole.tk == &h->tk_skinny || whole.tk == &h->tk_thin) ? 3 : 1);
         h->split_k_opt = whole.split_k;
         CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[0], hA, bytes[0], s_in));
         CU_CHECK(h, d.cuEventRecord_(ev_a, s_in));
         CU_CHECK(h, d.cuStreamWaitEvent_(s_cmp, ev_a, 0));
-        rc = SGEMM_OK;
-        for (uint32_t j = 0; j < chunks && rc == SGEMM_OK; ++j) {
+        for (uint32_t j = 0; j < chunks; ++j) {
             const uint32_t n0 = j * nc, nw = std::min(nc, n - n0);
             CUevent ev_in = h->pipe_events[1 + 2 * j], ev_done = h->pipe_events[2 + 2 * j];
             const size_t off_b = (size_t)n0 * ldb * eb, off_c = (size_t)n0 * ldc * 4, off_d = (size_t)n0 * ldd * 4;
@@ -1028,18 +1049,14 @@ SGEMM_API int sgemm_run_host(sgemm_handle *h, const float *hA, const float *hB, 
                                use_c ? reinterpret_cast<const float *>(h->stage[2] + off_c) : nullptr,
                                reinterpret_cast<float *>(h->stage[3] + off_d), alpha, beta, m, nw, k, lda, ldb, ldc, ldd, s_cmp);
             h->reuse_a_lo = false;
-            if (rc) break;
+            if (rc) return rc;
             CU_CHECK(h, d.cuEventRecord_(ev_done, s_cmp));
             CU_CHECK(h, d.cuStreamWaitEvent_(s_out, ev_done, 0));
             CU_CHECK(h, d.cuMemcpyDtoHAsync_(reinterpret_cast<char *>(hD) + off_d, h->stage[3] + off_d, by_d, s_out));
         }
-        // drain all three streams on every path: nothing of this call may still be in flight when it returns
-        CUresult r1 = d.cuStreamSynchronize_(s_in), r2 = d.cuStreamSynchronize_(s_cmp), r3 = d.cuStreamSynchronize_(s_out);
-        h->force_variant = saved_variant;
-        h->split_k_opt = saved_split;
-        if (rc) return rc;
-        if (r1 != CUDA_SUCCESS || r2 != CUDA_SUCCESS || r3 != CUDA_SUCCESS)
-            return fail(h, SGEMM_ERR_CUDA, "pipelined host call failed: %s", cu_text(r1 != CUDA_SUCCESS ? r1 : r2 != CUDA_SUCCESS ? r2 : r3).c_str());
+        restore.run();
+        if (restore.drained != CUDA_SUCCESS)
+            return fail(h, SGEMM_ERR_CUDA, "pipelined host call failed: %s", cu_text(restore.drained).c_str());
         return SGEMM_OK;
     }
     CUstream s = nullptr;
@@ -1166,17 +1183,22 @@ SGEMM_API int sgemm_get_info(sgemm_handle *h, const char *key, int64_t *value) {
     return SGEMM_OK;
 }
 
-SGEMM_API int sgemm_workspace_bytes(sgemm_handle *h, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb,
-                                    size_t *bytes) {
+SGEMM_API int sgemm_workspace_bytes_for(sgemm_handle *h, const void *dA, const void *dB, uint32_t m, uint32_t n,
+                                        uint32_t k, uint32_t lda, uint32_t ldb, size_t *bytes) {
     if (!h || !bytes) return SGEMM_ERR_INVALID_ARGUMENT;
     *bytes = 0;
     if (m == 0 || n == 0 || k == 0) return SGEMM_OK;
     Plan p;
-    // alignment of the real operands is unknown here; assume aligned bases (the common case)
-    int rc = make_plan(h, nullptr, nullptr, m, n, k, lda, ldb, &p);
+    int rc = make_plan(h, dA, dB, m, n, k, lda, ldb, &p);
     if (rc) return rc;
     *bytes = p.ws_bytes;
     return SGEMM_OK;
+}
+
+SGEMM_API int sgemm_workspace_bytes(sgemm_handle *h, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb,
+                                    size_t *bytes) {
+    // the operands' addresses are unknown here: NULL stands for bases that are 16-byte aligned (the common case)
+    return sgemm_workspace_bytes_for(h, nullptr, nullptr, m, n, k, lda, ldb, bytes);
 }
 
 SGEMM_API int sgemm_set_workspace(sgemm_handle *h, void *dptr, size_t bytes) {
@@ -1278,9 +1300,19 @@ int handle_device(const sgemm_handle *h) { return h ? h->device : -1; }
 
 int set_error(sgemm_handle *h, int code, const char *message) { return fail(h, code, "%s", message); }
 
-int scratch_bytes(sgemm_handle *h, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb, size_t *bytes) {
-    return sgemm_workspace_bytes(h, m, n, k, lda, ldb, bytes);
+int scratch_bytes(sgemm_handle *h, const void *dA, const void *dB, uint32_t m, uint32_t n, uint32_t k, uint32_t lda,
+                  uint32_t ldb, size_t *bytes) {
+    return sgemm_workspace_bytes_for(h, dA, dB, m, n, k, lda, ldb, bytes);
 }
+
+int with_context(sgemm_handle *h, int (*fn)(void *), void *arg) {
+    if (!h || !fn) return SGEMM_ERR_INVALID_ARGUMENT;
+    CtxGuard guard(h);
+    if (!guard.pushed) return fail(h, SGEMM_ERR_CUDA, "cannot make the handle's CUDA context current");
+    return fn(arg);
+}
+
+void **noalloc_scratch_slot(sgemm_handle *h) { return h ? &h->noalloc_scratch : nullptr; }
 
 int launch_with_scratch(sgemm_handle *h, void *scratch, size_t scratch_bytes, const float *dA, const float *dB,
                         const float *dC, float *dD, float alpha, float beta, uint32_t m, uint32_t n, uint32_t k,
@@ -1300,6 +1332,8 @@ int launch_with_scratch(sgemm_handle *h, void *scratch, size_t scratch_bytes, co
     }
     h->ws_lent = saved_ptr;
     h->ws_lent_bytes = saved_bytes;
+    // the only workspace failure possible here is "the borrowed block is too small": say so in this entry point's terms
+    if (rc == SGEMM_ERR_WORKSPACE) rc = SGEMM_ERR_SCRATCH_LIMIT;
     return rc;
 }
 

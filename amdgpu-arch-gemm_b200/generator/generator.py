@@ -596,19 +596,36 @@ def nvcc_command(src: str, out: str, extra: Optional[List[str]] = None) -> List[
 
 def compile(kern_name: str, kern_str: str, arch: str, output_folder: str, gemm_config: GemmSolutionConfig) -> int:
     """Write ``<kern_name>.cu``, compile it to ``<kern_name>.cubin`` and write ``<kern_name>.toml``.
-    Returns nvcc's return code (0 = success); the TOML is written only for a kernel that compiled."""
+    Returns nvcc's return code (0 = success).
+
+    The three files appear together or not at all: everything is built in a scratch directory inside
+    ``output_folder`` and moved into place (``os.replace``, atomic within a file system) only after nvcc has
+    succeeded — cubin and TOML first, the source last.  A failed or interrupted build therefore leaves the previous
+    kernel intact AND leaves its old source beside it, so that a freshness check that compares the emitted source with
+    the ``.cu`` on disk (``kernels.ensure``) keeps reporting the kernel as stale, and no reader ever opens a
+    half-written cubin.  (The reference writes ``.s`` first and ignores the assembler's return code,
+    generator/generator.py:2535-2555.)"""
+    import shutil
+    import tempfile
+
     os.makedirs(output_folder, exist_ok=True)
-    src = f"{output_folder}/{kern_name}.cu"
-    with open(src, "w") as f:
-        f.write(kern_str)
-    ret = subprocess.run(nvcc_command(src, f"{output_folder}/{kern_name}.cubin"),
-                         stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
-    if ret.returncode:
-        print(ret.stdout)
-        return ret.returncode
-    with open(f"{output_folder}/{kern_name}.toml", "wb") as f:
-        tomli_w.dump(gemm_config.to_dict(), f)
-    return ret.returncode
+    scratch = tempfile.mkdtemp(prefix=".build-", dir=output_folder)
+    try:
+        src = f"{scratch}/{kern_name}.cu"
+        with open(src, "w") as f:
+            f.write(kern_str)
+        ret = subprocess.run(nvcc_command(src, f"{scratch}/{kern_name}.cubin"),
+                             stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if ret.returncode:
+            print(ret.stdout)
+            return ret.returncode
+        with open(f"{scratch}/{kern_name}.toml", "wb") as f:
+            tomli_w.dump(gemm_config.to_dict(), f)
+        for suffix in ("cubin", "toml", "cu"):
+            os.replace(f"{scratch}/{kern_name}.{suffix}", f"{output_folder}/{kern_name}.{suffix}")
+        return 0
+    finally:
+        shutil.rmtree(scratch, ignore_errors=True)
 
 
 def tensor_config(bn: int = 256, bk: int = 32, stages: int = 2, cluster: int = 1, trans_a: bool = False,

@@ -81,21 +81,34 @@ _fresh = set()   # kernels whose in-tree files were checked (or built) by this p
 
 def ensure(name: str, force: bool = False) -> Tuple[str, str]:
     """Return (cubin, toml) of a registered kernel, generating and compiling it if it is not there or if the source
-    the generator emits today differs from the one the cubin was compiled from (a changed knob or kernel template)."""
+    the generator emits today differs from the one the cubin was compiled from (a changed knob or kernel template).
+
+    Check and build run under an exclusive file lock per kernel, so that several processes asking for the same
+    kernel at once (one rank per GPU under torchrun) build it once, one after the other finds it fresh, and none
+    loads files that another is still writing."""
     cubin, toml = paths(name)
     if name in _fresh and not force:
         return cubin, toml
+    import fcntl
+
     factory, opt_kwargs = REGISTRY[name]
     config, opt = factory(), GemmOptimizations(1, **opt_kwargs)
-    stale = force or not (Path(cubin).exists() and Path(toml).exists())
-    if not stale:
-        import tomllib
-        source = Path(cubin).with_suffix(".cu")
-        stale = not source.exists() or source.read_text() != gemm(None, KERNEL_ENTRY, "sm_100a", config, opt, default_arguments())
-        with open(toml, "rb") as f:
-            stale = stale or tomllib.load(f) != config.to_dict()
-    if stale:
-        build_kernel(str(GENERATED_DIR / name), config, opt)
+    folder = GENERATED_DIR / name
+    folder.mkdir(parents=True, exist_ok=True)
+    with open(folder / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            stale = force or not (Path(cubin).exists() and Path(toml).exists())
+            if not stale:
+                import tomllib
+                source = Path(cubin).with_suffix(".cu")
+                stale = not source.exists() or source.read_text() != gemm(None, KERNEL_ENTRY, "sm_100a", config, opt, default_arguments())
+                with open(toml, "rb") as f:
+                    stale = stale or tomllib.load(f) != config.to_dict()
+            if stale:
+                build_kernel(str(folder), config, opt)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     _fresh.add(name)
     return cubin, toml
 

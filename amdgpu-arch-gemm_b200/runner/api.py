@@ -67,6 +67,7 @@ ABI = {
     "sgemm_set_option": (ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.c_int64]),
     "sgemm_get_info": (ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.POINTER(ctypes.c_int64)]),
     "sgemm_workspace_bytes": (ctypes.c_int, [_vp, _u32, _u32, _u32, _u32, _u32, ctypes.POINTER(ctypes.c_size_t)]),
+    "sgemm_workspace_bytes_for": (ctypes.c_int, [_vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, ctypes.POINTER(ctypes.c_size_t)]),
     "sgemm_set_workspace": (ctypes.c_int, [_vp, _vp, ctypes.c_size_t]),
     "sgemm_fill_uniform": (ctypes.c_int, [_vp, _vp, _u64, _u64, _u64, _vp]),
     "sgemm_narrow16": (ctypes.c_int, [_vp, _vp, _vp, _u64, _vp]),
@@ -223,10 +224,17 @@ class SgemmRunner:
         self._check(self._L.sgemm_get_info(self._h, key.encode(), ctypes.byref(v)), "sgemm_get_info")
         return v.value
 
-    def workspace_bytes(self, m, n, k, lda=0, ldb=0) -> int:
+    def workspace_bytes(self, m, n, k, lda=0, ldb=0, a=None, b=None) -> int:
+        """Scratch bytes a launch of this problem needs; with `a` / `b` (device addresses) the need of these very
+        operands, aligned copies of unaligned ones included."""
         out = ctypes.c_size_t()
-        self._check(self._L.sgemm_workspace_bytes(self._h, m, n, k, lda or m, ldb or k, ctypes.byref(out)),
-                    "sgemm_workspace_bytes")
+        self._check(self._L.sgemm_workspace_bytes_for(self._h, _ptr(a), _ptr(b), m, n, k, lda or m, ldb or k,
+                                                      ctypes.byref(out)), "sgemm_workspace_bytes_for")
+        if a is None and b is None:
+            plain = ctypes.c_size_t()
+            self._check(self._L.sgemm_workspace_bytes(self._h, m, n, k, lda or m, ldb or k, ctypes.byref(plain)),
+                        "sgemm_workspace_bytes")
+            assert plain.value == out.value
         return out.value
 
     def set_workspace(self, dptr, nbytes: int):

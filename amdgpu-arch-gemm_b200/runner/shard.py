@@ -26,6 +26,16 @@ def all_shards(n: int, world: int, tile_n: int = 1) -> List[Tuple[int, int]]:
     return [shard_columns(n, world, r, tile_n) for r in range(world)]
 
 
+def fill_shard_inputs(runner, a, b, m: int, k: int, n0: int, n1: int, seed: int = 0, stream=0) -> None:
+    """Fill this rank's operands of the sharded workload on the device: the replicated A (M x K, generator stream
+    ``seed``) and the columns [n0, n1) of B (K x N, stream ``seed + 1``), both by GLOBAL element index — column j of
+    B starts at index j*K — so that 1, 2, 4 and 8 GPUs compute on the same matrices.  ``a`` and ``b`` are device
+    buffers (tensors or addresses) of M*K and K*(n1 - n0) floats."""
+    runner.fill_uniform(a, m * k, stream_id=seed, stream=stream)
+    if n1 > n0:
+        runner.fill_uniform(b, k * (n1 - n0), stream_id=seed + 1, first_index=n0 * k, stream=stream)
+
+
 def gather_columns(dist, local_d, m: int, n: int, world: int, tile_n: int = 1):
     """All-gather the column shards of D (flat column-major tensors) into the full M x N matrix on every rank.
     Shards may differ in width, so each is padded to the widest one for the collective."""

@@ -9,10 +9,22 @@ M = K = 8192, N_total = 8192 * N, column-block sharded: A replicated, B and D co
 on the compute path (weak scaling: fixed work per GPU).  Inputs are seeded uniform[-1, 1) FP32 filled on the
 device by global element index, so every N sees the same matrices.
 
-Timed region: K steps between CUDA events on the launching stream, bracketed by barrier + synchronise, max over
-ranks.  `value` counts algorithmic flops 2*M*N*K only (the 3x tensor work of the split is not counted) and
-includes the split pre-pass that is part of every call.  `e2e` repeats the measurement through
-sgemm_run_host with pinned HOST buffers (upload A and B, download D inside the timed region).
+What one JSON line carries:
+  value / ms_per_step   K steps between CUDA events on the launching stream, bracketed by barrier + synchronise, max
+                        over ranks; algorithmic flops 2*M*N*K only (the 3x tensor work of the split is not counted),
+                        the split pre-pass that is part of every call included.
+  roofline              the main kernel alone (event pairs around each of its launches inside the same timed region)
+                        against the tensor ceiling for FP32-accurate flops; the ceiling is the burst figure of the
+                        measured peaks for a timed region shorter than a second, the sustained one otherwise.
+  sustained             the same step repeated for at least three seconds with the SM clock sampled throughout.
+  parity                after the timed regions every rank checks sampled columns of its own shard of D against the CPU
+                        oracle (the checker; never inside a timed region).
+  c5                    the fixed M = N = 32768, K = 8192 problem column-sharded over the N ranks (strong scaling),
+                        at least two seconds of timed steps, with its own parity check.
+  e2e                   the measurement through the host-buffer entry points with pinned HOST buffers, uploads and
+                        downloads inside the timed region; with N ranks every rank uploads 1/N of the replicated A and
+                        the ranks complete it with an all-gather over NVLink (sgemm_run_host_sharded).
+  cpu_baseline          the reference's CPU GEMM (oracle restatement) on the box's host cores, N = 1 only.
 
 --impl reference times the reference's CPU GEMM (restated in oracle/, its native runner needs HIP and cannot be
 built here) on all host cores, on a column block of the same 8192^3 problem.
@@ -20,8 +32,10 @@ built here) on all host cores, on a column block of the same 8192^3 problem.
 from __future__ import annotations
 
 import argparse
+import hashlib
 import importlib
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -36,11 +50,11 @@ sys.path.insert(0, str(ROOT))
 M = N_PER_GPU = K = 8192
 METRIC = "sgemm_fp32_accurate_tflops_8192"
 UNIT = "TFLOP/s"
-
-# DRAM bytes one launch of the dominant kernel moved in an ncu capture (dram__bytes_read.sum +
-# dram__bytes_write.sum), keyed by kernel name, for the 8192^3 workload.
-# Source: profiles/bench_default_8192cubed_launches_and_dram.md (three launches, identical to three digits).
-NCU_TRAFFIC_BYTES = {"tc2_256x256x32_s3": 4.83e9}
+C5_M, C5_N, C5_K = 32768, 32768, 8192
+TRAFFIC_FILE = ROOT / "profiles" / "dram_traffic.json"
+# flops per clock and SM of the tensor pipe on TF32 operands (the ncu counter sm__ops_path_tensor_op_utchmma_src_tf32
+# saturates at this value); a third of it is the ceiling of the 3xTF32 scheme at a given clock
+TF32_FLOPS_PER_CLK_SM = 4096
 
 
 def measured_peaks():
@@ -51,51 +65,123 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
+def ncu_traffic(kernel: str, cubin: str, shape):
+    """DRAM bytes one launch of the dominant kernel moved in an ncu capture, from the tracked record beside the
+    profile summaries — valid only for the very source the capture ran: the record carries a hash of the emitted .cu,
+    and a kernel that has changed since gets null instead of a stale figure."""
+    try:
+        rec = json.loads(TRAFFIC_FILE.read_text()).get(kernel)
+        src = Path(cubin).with_suffix(".cu").read_bytes()
+    except (OSError, ValueError):
+        return None, "no record"
+    if not rec or list(rec.get("shape", [])) != list(shape):
+        return None, "no record for this kernel and shape"
+    if rec.get("source_sha256") != hashlib.sha256(src).hexdigest():
+        return None, "kernel source changed since the capture"
+    return rec.get("dram_bytes_per_launch"), rec.get("capture")
+
+
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 100 ms while the timed region runs."""
+    """SM clock, power and throttle reasons of one GPU, read (never set) every few milliseconds through NVML in a
+    thread of this process while a timed region runs; falls back to an `nvidia-smi -lms 100` child when the NVML
+    binding is not importable.  A region with fewer than five samples is reported as `valid: false`."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
-        self.gpu_index = gpu_index
-        self.proc = None
-        self.lines = []
-        self.t = None
+    def __init__(self, gpu_uuid: str | None, gpu_index: int, period_s: float = 0.004):
+        self.uuid, self.gpu_index, self.period_s = gpu_uuid, gpu_index, period_s
+        self.samples = []            # (sm_mhz, power_w, reasons bitmask)
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._proc = None
+        self._lines = []
+        self._nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._dev = (pynvml.nvmlDeviceGetHandleByUUID(gpu_uuid.encode() if isinstance(gpu_uuid, str) else gpu_uuid)
+                         if gpu_uuid else pynvml.nvmlDeviceGetHandleByIndex(gpu_index))
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._dev, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nvml = None
+
+    def _loop(self):
+        nv = self._nvml
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self._dev, nv.NVML_CLOCK_SM)
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._dev)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._dev)
+                try:
+                    power = nv.nvmlDeviceGetPowerUsage(self._dev) / 1000.0
+                except Exception:
+                    power = None
+                self.samples.append((float(mhz), power, int(mask)))
+            except Exception:
+                pass
+            self._stop.wait(self.period_s)
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu_index)],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+        self.samples, self._lines = [], []
+        self._stop.clear()
+        if self._nvml:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
             return
-        self.t = threading.Thread(target=lambda: [self.lines.append(l) for l in self.proc.stdout], daemon=True)
-        self.t.start()
+        try:
+            self._proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                           "-lms", "100", "-i", str(self.gpu_index)],
+                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self._thread = threading.Thread(target=lambda: [self._lines.append(l) for l in self._proc.stdout], daemon=True)
+            self._thread.start()
+        except OSError:
+            self._proc = None
 
     def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, smax, power, reasons = [], [], [], set()
-        for line in self.lines:
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
-                continue
+        self._stop.set()
+        if self._nvml:
+            if self._thread:
+                self._thread.join(timeout=2)
+            nv = self._nvml
+            names = (("hw_slowdown", nv.nvmlClocksThrottleReasonHwSlowdown),
+                     ("hw_thermal_slowdown", nv.nvmlClocksThrottleReasonHwThermalSlowdown),
+                     ("sw_thermal_slowdown", nv.nvmlClocksThrottleReasonSwThermalSlowdown),
+                     ("sw_power_cap", nv.nvmlClocksThrottleReasonSwPowerCap))
+            sm = [s[0] for s in self.samples]
+            power = [s[1] for s in self.samples if s[1] is not None]
+            reasons = sorted({name for name, bit in names for s in self.samples if s[2] & bit})
+            source = "nvml"
+        elif self._proc:
+            self._proc.terminate()
             try:
-                sm.append(float(f[1])); smax.append(float(f[2])); power.append(float(f[3]))
-            except ValueError:
-                continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+                self._proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self._proc.kill()
+            sm, smax, power, found = [], [], [], set()
+            for line in self._lines:
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); smax.append(float(f[2])); power.append(float(f[3]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        found.add(name)
+            self.max_mhz = max(smax) if smax else None
+            reasons = sorted(found)
+            source = "nvidia-smi"
+        else:
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "valid": False, "reasons": ["no clock source available"]}
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_mhz_min": min(sm) if sm else None,
+                "sm_max_mhz": self.max_mhz, "power_w_max": max(power) if power else None, "samples": len(sm),
+                "valid": len(sm) >= 5, "reasons": reasons, "source": source}
 
 
 def cpu_reference_tflops(oracle, budget_s: float = 12.0, cols: int | None = None):
@@ -115,6 +201,22 @@ def cpu_reference_tflops(oracle, budget_s: float = 12.0, cols: int | None = None
             break
         cols = min(N_PER_GPU, max(cols * 2, int(cols * (budget_s * 0.6) / max(dt, 1e-3)) // 64 * 64))
     return 2.0 * M * cols * K / dt * 1e-12, cols, dt, oracle.num_threads()
+
+
+def cpu_reference_order(oracle):
+    """The reference's loop nest as written (i, j, l; one thread; runner/generator_runner.cpp:21-32) timed at 32^3 and
+    1024^3 — the reference's own CPU path, next to the reordered all-core figure."""
+    out = {}
+    for size, repeats in ((32, 200), (1024, 1)):
+        a, b, c = oracle.make_inputs(size, size, size, seed=0)
+        oracle.gemm(a[: 32 * 32], b[: 32 * 32], None, 1.0, 0.0, 32, 32, 32, ref_order=True)   # page the code in
+        t0 = time.perf_counter()
+        for _ in range(repeats):
+            oracle.gemm(a, b, c, 1.0, 0.0, size, size, size, ref_order=True)
+        dt = (time.perf_counter() - t0) / repeats
+        out[f"{size}^3"] = {"seconds": dt, "gflops": 2.0 * size ** 3 / dt * 1e-9}
+    out["8192^3"] = {"seconds": out["1024^3"]["seconds"] * 512, "extrapolated": "1024^3 time x 512"}
+    return out
 
 
 def run_reference(args, rank):
@@ -146,6 +248,95 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+class Job:
+    """One rank's view of a column-sharded SGEMM workload on its GPU: buffers, workspace, step, timing, parity."""
+
+    def __init__(self, torch, dist, api_runner, dev, world, rank, m, n_total, k, stream):
+        from runner.shard import fill_shard_inputs, shard_columns
+        self.torch, self.dist, self.r, self.dev, self.world, self.rank = torch, dist, api_runner, dev, world, rank
+        self.m, self.n_total, self.k, self.stream = m, n_total, k, stream
+        self.tile_n = self.r.info("tile_n")
+        self.n0, self.n1 = shard_columns(n_total, world, rank, self.tile_n)
+        self.n_local = self.n1 - self.n0
+        self.a = torch.empty(m * k, dtype=torch.float32, device=dev)
+        self.b = torch.empty(max(k * self.n_local, 1), dtype=torch.float32, device=dev)
+        self.d = torch.zeros(max(m * self.n_local, 1), dtype=torch.float32, device=dev)
+        fill_shard_inputs(self.r, self.a, self.b, m, k, self.n0, self.n1, seed=0, stream=stream)
+        ws_bytes = self.r.workspace_bytes(m, max(self.n_local, 1), k)
+        self.ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+        self.r.set_workspace(self.ws, ws_bytes)
+        torch.cuda.synchronize()
+
+    def step(self):
+        if self.n_local:
+            self.r.launch(self.a, self.b, None, self.d, self.m, self.n_local, self.k, alpha=1.0, beta=0.0, stream=self.stream)
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, x: float) -> float:
+        from runner.shard import max_over_ranks
+        return max_over_ranks(self.dist, x, self.dev) if self.world > 1 else x
+
+    def timed(self, steps: int, sampler=None):
+        """`steps` steps between two events, barrier + synchronise on both sides; returns (ms per step as the max over
+        ranks, clock record or None, main-kernel ns per launch on this rank, launches counted by the library)."""
+        torch = self.torch
+        self.barrier()
+        self.r.set_option("profile", 1)
+        launches0 = self.r.info("launches")
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if sampler:
+            sampler.start()
+        self.barrier()
+        e0.record()
+        for _ in range(steps):
+            self.step()
+        e1.record()
+        self.barrier()
+        clocks = sampler.stop() if sampler else None
+        ms = e0.elapsed_time(e1)
+        launches = self.r.info("launches") - launches0
+        count = self.r.info("profile_count")
+        main_ns = self.r.info("profile_main_ns")
+        self.r.set_option("profile", 0)
+        return self.max_over_ranks(ms) / steps, clocks, (main_ns / count if count else None), launches
+
+    def parity(self, columns: int):
+        """Sampled columns of this rank's shard of D against the CPU oracle, max over ranks (outside any timed region)."""
+        from oracle import oracle, shard_check
+        oracle.use_all_cores()
+        ratio, count = 0.0, 0
+        if self.n_local:
+            cols = shard_check.sample_columns(self.n0, self.n1, self.tile_n, columns, seed=17)
+            import numpy as np
+            idx = self.torch.from_numpy((cols - self.n0).astype(np.int64)).to(self.dev)
+            sampled = self.d[: self.m * self.n_local].view(self.n_local, self.m).index_select(0, idx).cpu().numpy()
+            ratio = shard_check.worst_ratio_of_columns(sampled, cols, self.m, self.k)
+            count = len(cols)
+            if not math.isfinite(ratio):
+                ratio = float("inf")
+        worst = self.max_over_ranks(ratio if math.isfinite(ratio) else 1e30)
+        return {"worst_ratio": worst, "columns_per_rank": count, "ranks": self.world,
+                "rule": "max |D - D_oracle| / (1e-5 * sum|a||b|) <= 1 (oracle = the reference's cpuGemm arithmetic)",
+                "ok": bool(worst <= 1.0)}
+
+    def free(self):
+        self.r.set_workspace(None, 0)
+        del self.a, self.b, self.d, self.ws
+        self.torch.cuda.empty_cache()
+
+
+def gather_list(dist, world, value):
+    if world == 1:
+        return [value]
+    out = [None] * world
+    dist.all_gather_object(out, value)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -155,13 +346,16 @@ def main():
     ap.add_argument("--kernel", default=None, help="registered kernel name (default: the tensor-core default)")
     ap.add_argument("--size", type=int, default=8192, help="M = N_per_gpu = K (profiling runs use a smaller case)")
     ap.add_argument("--workload", choices=["c3", "c5"], default="c3",
-                    help="c3: M = K = N per GPU = --size, N grows with the GPU count (weak scaling, the default); "
-                         "c5: the fixed M = N = 32768, K = 8192 problem column-sharded over the GPUs (strong scaling)")
+                    help="c3: M = K = N per GPU = --size, N grows with the GPU count (weak scaling, the default headline); "
+                         "c5: make the fixed M = N = 32768, K = 8192 problem (strong scaling) the headline instead")
     ap.add_argument("--allgather", action="store_true",
                     help="also time the optional NCCL all-gather of D's column shards (reported apart from the GEMM)")
     ap.add_argument("--acc-chain", type=int, default=-1,
                     help="k per tensor-core accumulation chain: -1 = as the kernel was generated (128), 0 = all of K in "
                          "one chain (faster, drifts toward zero for same-signed inputs)")
+    ap.add_argument("--sustained-seconds", type=float, default=3.0, help="length of the clock-sampled sustained loop (0: skip)")
+    ap.add_argument("--c5-seconds", type=float, default=2.5, help="timed length of the 32768 x 32768 x 8192 record (0: skip)")
+    ap.add_argument("--parity-columns", type=int, default=16, help="columns of D every rank checks against the oracle (0: skip)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -182,7 +376,6 @@ def main():
 
     importlib.import_module("amdgpu-arch-gemm_b200")
     from runner import api
-    from runner.shard import max_over_ranks, shard_columns
     import kernels
 
     if not torch.cuda.is_available():
@@ -197,76 +390,65 @@ def main():
     cubin, toml = kernels.ensure(kernel)
     r = api.SgemmRunner(cubin, toml, local_rank)
     r.set_option("acc_chain", args.acc_chain)
-    tile_n = r.info("tile_n")
-
-    # c3, weak scaling: N_total = N_PER_GPU * world columns; c5, strong scaling: one fixed problem.
-    # Either way this rank owns the columns [n0, n1).
-    if args.workload == "c5":
-        M, K = 32768, 8192
-        n_total = 32768
-    else:
-        n_total = N_PER_GPU * world
-    n0, n1 = shard_columns(n_total, world, rank, tile_n)
-    n_local = n1 - n0
-    a = torch.empty(M * K, dtype=torch.float32, device=dev)
-    b = torch.empty(K * n_local, dtype=torch.float32, device=dev)
-    d = torch.zeros(M * n_local, dtype=torch.float32, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
-    r.fill_uniform(a, M * K, stream_id=0, stream=stream)                              # A replicated
-    r.fill_uniform(b, K * n_local, stream_id=1, first_index=n0 * K, stream=stream)    # B[:, n0:n1]
-    ws_bytes = r.workspace_bytes(M, n_local, K)
-    ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
-    r.set_workspace(ws, ws_bytes)
-    torch.cuda.synchronize()
+    try:
+        uuid = "GPU-" + str(torch.cuda.get_device_properties(local_rank).uuid)
+    except Exception:
+        uuid = None
+    sampler = ClockSampler(uuid, local_rank)
+    peaks, peak_src = measured_peaks()
+    sm_count = r.info("sm_count")
 
-    def step():
-        r.launch(a, b, None, d, M, n_local, K, alpha=1.0, beta=0.0, stream=stream)
-
-    def barrier():
+    def record_of(job, steps, with_clocks=True):
+        ms_step, clocks, main_ns, launches = job.timed(steps, sampler if with_clocks else None)
+        flops_all = 2.0 * job.m * job.n_total * job.k
+        rec = {"value": flops_all / (ms_step * 1e-3) * 1e-12, "ms_per_step": ms_step, "steps": steps,
+               "seconds": ms_step * steps * 1e-3, "launches": launches}
+        rec["per_gpu_tflops"] = rec["value"] / world
+        main_ms = gather_list(dist, world, main_ns * 1e-6 if main_ns else None)
+        rec["main_kernel_ms_per_rank"] = main_ms
+        all_clocks = gather_list(dist, world, clocks)
+        rec["clocks"] = all_clocks[0]
         if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+            rec["sm_mhz_median_per_rank"] = [c and c.get("sm_mhz") for c in all_clocks]
+        mhz = clocks and clocks.get("sm_mhz")
+        if main_ns and mhz and clocks.get("valid"):
+            rec["main_kernel_ms_x_sm_mhz"] = main_ns * 1e-6 * mhz
+            rec["value_per_ghz"] = rec["per_gpu_tflops"] / (mhz * 1e-3)
+        return rec, main_ns
 
+    # ------------------------------------------------------------------ the headline: 8192 columns per GPU (weak)
+    if args.workload == "c5":
+        job = Job(torch, dist, r, dev, world, rank, C5_M, C5_N, C5_K, stream)
+    else:
+        job = Job(torch, dist, r, dev, world, rank, M, N_PER_GPU * world, K, stream)
     for _ in range(args.warmup):
-        step()
-    barrier()
-    r.set_option("profile", 1)
-    launches0 = r.info("launches")
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    ms_total = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
-    launches = r.info("launches") - launches0
-    main_count = r.info("profile_count")
-    main_ns = r.info("profile_main_ns")
-    r.set_option("profile", 0)
+        job.step()
+    head, main_ns = record_of(job, args.steps)
     status = r.last_status()
-    ms_total = max_over_ranks(dist, ms_total, dev) if world > 1 else ms_total
-    ms_step = ms_total / args.steps
-    flops_step_all = 2.0 * M * n_total * K
-    value = flops_step_all / (ms_step * 1e-3) * 1e-12
+    n_local = job.n_local
+
+    # sustained: the same step for a few seconds, clock-sampled, so that the power-capped rate is on record
+    sustained = None
+    if args.sustained_seconds > 0:
+        steps = max(args.steps, int(math.ceil(args.sustained_seconds * 1e3 / head["ms_per_step"])))
+        sustained, sus_main_ns = record_of(job, steps)
+        sustained["main_kernel_tflops"] = (2.0 * job.m * n_local * job.k) / (sus_main_ns * 1e-9) * 1e-12 if sus_main_ns else None
+    parity = job.parity(args.parity_columns) if args.parity_columns > 0 else None
 
     # ---- optional: all-gather of the column shards of D over NVLink (NCCL); never part of `value`
     allgather = None
     if args.allgather and world > 1:
         from runner.shard import gather_columns
-        gather_columns(dist, d, M, n_total, world, tile_n)      # warm-up (NCCL channel set-up)
-        barrier()
+        gather_columns(dist, job.d, job.m, job.n_total, world, job.tile_n)      # warm-up (NCCL channel set-up)
+        job.barrier()
         g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         g0.record()
-        full_d = gather_columns(dist, d, M, n_total, world, tile_n)
+        full_d = gather_columns(dist, job.d, job.m, job.n_total, world, job.tile_n)
         g1.record()
-        barrier()
-        ag_ms = max_over_ranks(dist, g0.elapsed_time(g1), dev)
-        recv_bytes = (full_d.numel() - d.numel()) * 4
+        job.barrier()
+        ag_ms = job.max_over_ranks(g0.elapsed_time(g1))
+        recv_bytes = (full_d.numel() - job.d.numel()) * 4
         allgather = {"ms": ag_ms, "bytes_received_per_gpu": recv_bytes, "gb_per_s_per_gpu": recv_bytes / ag_ms * 1e-6,
                      "full_d_elements": full_d.numel()}
         del full_d
@@ -277,51 +459,93 @@ def main():
         ha = torch.empty(M * K, dtype=torch.float32).pin_memory()
         hb = torch.empty(K * n_local, dtype=torch.float32).pin_memory()
         hd = torch.empty(M * n_local, dtype=torch.float32).pin_memory()
-        ha.copy_(a)
-        hb.copy_(b)
+        ha.copy_(job.a)
+        hb.copy_(job.b)
+        r.set_workspace(None, 0)     # the host entry point sizes its own scratch (A's copies are shared by the chunks)
         e2e_steps = max(1, min(args.steps, 5))
         r.run_host(ha, hb, None, hd, M, n_local, K, alpha=1.0, beta=0.0)   # warm-up: allocates the staging buffers
-        barrier()
+        job.barrier()
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
             r.run_host(ha, hb, None, hd, M, n_local, K, alpha=1.0, beta=0.0)   # synchronises before returning
-        dt = time.perf_counter() - t0
-        dt = max_over_ranks(dist, dt, dev) if world > 1 else dt
+        dt = job.max_over_ranks(time.perf_counter() - t0)
         # the result the host now holds must be the one the device path computed
-        same = bool(torch.equal(hd, d.cpu()))
-        e2e = {"value": flops_step_all / (dt / e2e_steps) * 1e-12, "unit": UNIT,
+        same = bool(torch.equal(hd, job.d.cpu()))
+        same = bool(job.max_over_ranks(0.0 if same else 1.0) == 0.0)
+        e2e = {"value": 2.0 * job.m * job.n_total * job.k / (dt / e2e_steps) * 1e-12, "unit": UNIT,
                "h2d_bytes_per_step": (M * K + K * n_local) * 4, "d2h_bytes_per_step": M * n_local * 4,
-               "steps": e2e_steps, "host_result_equals_device_result": same}
+               "steps": e2e_steps, "host_result_equals_device_result": same,
+               "path": "sgemm_run_host (pinned host buffers, column chunks pipelined over three streams)"}
+        del ha, hb, hd
+    head_shape = (job.m, n_local, job.k)
+    head_total = job.n_total
+    job.free()
+
+    # ------------------------------------------------- strong scaling: 32768 x 32768 x 8192 sharded over the ranks
+    c5 = None
+    if args.c5_seconds > 0 and args.workload == "c3" and args.size == 8192:
+        big = Job(torch, dist, r, dev, world, rank, C5_M, C5_N, C5_K, stream)
+        for _ in range(3):
+            big.step()
+        est_ms, _, _, _ = big.timed(2)
+        steps = max(3, int(math.ceil(args.c5_seconds * 1e3 / est_ms)))
+        c5, _ = record_of(big, steps)
+        c5["scaling"] = "strong"
+        c5["workload"] = f"M={C5_M} N={C5_N} K={C5_K}, columns sharded over {world} GPU(s) ({big.n_local} on rank 0), A replicated"
+        if args.parity_columns > 0:
+            c5["parity"] = big.parity(args.parity_columns)
+        big.free()
+    status2 = r.last_status()
 
     if rank == 0:
-        peaks, peak_src = measured_peaks()
         # roofline of the dominant kernel (generated_gemm): algorithmic flops of one launch / its mean duration.
-        # Peak: the tensor pipe runs TF32 at half the BF16 rate and the split issues 3 MMAs per product, so the
-        # ceiling for FP32-accurate flops is BF16 / 6 (sustained figure: the kernel is timed inside a long step).
-        peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]) / 6.0
-        achieved = (2.0 * M * n_local * K) / (main_ns / max(main_count, 1) * 1e-9) * 1e-12 if main_ns else None
-        traffic = NCU_TRAFFIC_BYTES.get(kernel) if (M, n_local, K) == (8192, 8192, 8192) else None
+        # Ceiling: the tensor pipe runs TF32 at half the BF16 rate and the split issues 3 MMAs per product, so
+        # FP32-accurate flops top out at BF16 / 6.  A timed region shorter than a second never reaches the power cap:
+        # the burst figure applies; a longer one is held to the sustained figure.
+        timed_s = head["seconds"]
+        key = "bf16_tflops" if timed_s < 1.0 else "bf16_tflops_sustained"
+        peak = peaks.get(key, peaks["bf16_tflops"]) / 6.0
+        achieved = (2.0 * head_shape[0] * head_shape[1] * head_shape[2]) / (main_ns * 1e-9) * 1e-12 if main_ns else None
+        traffic, traffic_src = ncu_traffic(kernel, cubin, head_shape)
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                    "frac": (achieved / peak) if achieved else None, "traffic": traffic, "traffic_source": traffic_src,
+                    "kernel": "generated_gemm", "launches_timed": args.steps,
+                    "peak_source": f"{peak_src} {key} / 6 (TF32 = 1/2 BF16 rate, 3 MMAs per product); timed region "
+                                   f"{timed_s:.3f} s -> {'burst' if timed_s < 1.0 else 'sustained'} figure"}
+        clk = head["clocks"]
+        if achieved and clk and clk.get("valid") and clk.get("sm_mhz"):
+            pipe = TF32_FLOPS_PER_CLK_SM * sm_count * clk["sm_mhz"] * 1e6 / 3.0 * 1e-12
+            roofline["pipe_peak_at_sampled_clock"] = pipe
+            roofline["frac_of_pipe_at_sampled_clock"] = achieved / pipe
+        if sustained and sustained.get("main_kernel_tflops"):
+            sus_peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]) / 6.0
+            sustained["frac_of_sustained_peak"] = sustained["main_kernel_tflops"] / sus_peak
+            sustained["peak"] = sus_peak
+            sclk = sustained["clocks"]
+            if sclk and sclk.get("valid") and sclk.get("sm_mhz"):
+                pipe = TF32_FLOPS_PER_CLK_SM * sm_count * sclk["sm_mhz"] * 1e6 / 3.0 * 1e-12
+                sustained["frac_of_pipe_at_sampled_clock"] = sustained["main_kernel_tflops"] / pipe
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if args.workload == "c5" else "weak",
+            "metric": METRIC, "value": head["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong" if args.workload == "c5" else "weak",
             "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": f"column-major NN SGEMM M={M} N={n_total} K={K} (N={n_local} on rank 0), alpha=1, beta=0, "
+            "config": {"workload": f"column-major NN SGEMM M={head_shape[0]} N={head_total} K={head_shape[2]} (N={head_shape[1]} on rank 0), alpha=1, beta=0, "
                                    "seeded uniform[-1,1); 3xTF32 tcgen05 path", "kernel": kernel,
                        "acc_chain": r.info("last_acc_chain"),
                        "parallelism": f"column-block shards x{world}, A replicated, no collective",
-                       "l2": f"inputs (A + B = {(M * K + K * n_local) * 4 >> 20} MiB per GPU) exceed the 126 MB L2, no flush needed"},
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": (achieved / peak) if achieved else None, "traffic": traffic,
-                         "kernel": "generated_gemm", "launches_timed": main_count,
-                         "peak_source": f"{peak_src} bf16_tflops_sustained / 6 (TF32 = 1/2 BF16 rate, 3 MMAs per product)"},
-            "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "device_status": status[0], "allgather": allgather,
+                       "l2": f"inputs (A + B = {(head_shape[0] * head_shape[2] + head_shape[2] * head_shape[1]) * 4 >> 20} MiB per GPU) exceed the 126 MB L2, no flush needed"},
+            "roofline": roofline, "e2e": e2e, "gpu_launches": head["launches"], "clocks": head["clocks"],
+            "main_kernel_ms_per_rank": head["main_kernel_ms_per_rank"],
+            "sustained": sustained, "parity": parity, "c5": c5,
+            "device_status": max(status[0], status2[0]), "allgather": allgather,
         }
         if world == 1 and not args.no_cpu_baseline:
             from oracle import oracle
             tf, cols, dt, threads = cpu_reference_tflops(oracle)
             line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": threads, "kind": "port",
-                                    "sample": f"{cols} of 8192 columns of the same problem, {dt:.1f} s of CPU work"}
+                                    "sample": f"{cols} of 8192 columns of the same problem, {dt:.1f} s of CPU work",
+                                    "reference_loop_order_one_thread": cpu_reference_order(oracle)}
         print(json.dumps(line), flush=True)
     r.close()
     if world > 1:

@@ -115,9 +115,11 @@ int sgemm_launch(sgemm_handle *h, const float *dA, const float *dB, const float 
  * results as sgemm_launch, but the scratch (3xTF32 lo copies, split-K partials) comes from a fixed array of
  * SGEMM_NOALLOC_SCRATCH_BYTES that is part of the library image on every GPU that loads it; no cudaMalloc,
  * cuMemAlloc or other allocating call is made.  Problems needing more scratch fail with
- * SGEMM_ERR_SCRATCH_LIMIT before anything is launched (sgemm_workspace_bytes tells the need).  The first call
- * on a device resolves the array's device address (one-time set-up; make it before any stream capture).  All
- * calls on a device share the array: kernels of two such calls must not overlap in time on one GPU. */
+ * SGEMM_ERR_SCRATCH_LIMIT before anything is launched (sgemm_workspace_bytes_for tells the need, copies of
+ * operands that TMA cannot read where they lie included).  The first call on a handle resolves the array's device
+ * address in the handle's own context (one-time set-up; make it before any stream capture; the calling thread's
+ * current device and context are left untouched).  All calls on a device share the array: kernels of two such
+ * calls must not overlap in time on one GPU. */
 #define SGEMM_NOALLOC_SCRATCH_BYTES (32u << 20)
 int sgemm_launch_noalloc(sgemm_handle *h, const float *dA, const float *dB, const float *dC, float *dD,
                          float alpha, float beta, uint32_t m, uint32_t n, uint32_t k,
@@ -189,9 +191,15 @@ int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value);
  * nanoseconds; synchronises on them and resets the tally). */
 int sgemm_get_info(sgemm_handle *h, const char *key, int64_t *value);
 
-/* Scratch bytes sgemm_launch needs for this problem under the current options (0 = none). */
+/* Scratch bytes sgemm_launch needs for this problem under the current options (0 = none), for operands whose base
+ * addresses are 16-byte aligned.  (No counterpart in the reference, whose kernel needs no scratch.) */
 int sgemm_workspace_bytes(sgemm_handle *h, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb,
                           size_t *bytes);
+/* The same for the operands a call will really get: an FP32 operand TMA cannot read where it lies (base not 16-byte
+ * aligned, or leading dimension not a multiple of 4) is first copied to an aligned pitch inside the workspace, which
+ * adds to the need.  dA / dB are only inspected, never dereferenced; NULL means "aligned". */
+int sgemm_workspace_bytes_for(sgemm_handle *h, const void *dA, const void *dB, uint32_t m, uint32_t n, uint32_t k,
+                              uint32_t lda, uint32_t ldb, size_t *bytes);
 
 /* Lend device scratch (256-byte aligned) so that sgemm_launch never allocates; NULL returns to the
  * handle-owned, grow-on-demand workspace. */

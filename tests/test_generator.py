@@ -171,3 +171,58 @@ def test_sixteen_bit_operand_types():
         g.GemmSolutionConfig(H, F, F, F, (128, 128, 1, 16), (1, 1), (1, 1), 64, False, False)  # mixed operand types
     with pytest.raises(RuntimeError):
         g.GemmSolutionConfig(H, H, H, F, (128, 128, 1, 16), (1, 1), (1, 1), 64, False, False)  # C and D stay FP32
+
+
+def test_failed_compile_leaves_the_old_kernel_and_ensure_keeps_calling_it_stale(tmp_path, monkeypatch):
+    """compile() must not leave a new source beside an old cubin: after a compiler failure the three files of the
+    previous build are still there, unchanged, and kernels.ensure() still reports the kernel as stale (it raises again
+    instead of handing out the old cubin as fresh); once the compiler works again the kernel is rebuilt."""
+    import kernels
+
+    monkeypatch.setattr(kernels, "GENERATED_DIR", tmp_path)
+    monkeypatch.setattr(kernels, "_fresh", set())
+    name = "simt_64x64x16"
+    monkeypatch.setitem(kernels.REGISTRY, name, (kernels.REGISTRY[name][0], dict(wgm=4)))
+    cubin, toml = kernels.ensure(name)
+    files = {s: (tmp_path / name / f"generated_gemm.{s}") for s in ("cu", "cubin", "toml")}
+    before = {s: f.read_bytes() for s, f in files.items()}
+    assert not any(p.name.startswith(".build-") for p in (tmp_path / name).iterdir())   # the scratch directory is gone
+
+    # a changed knob makes the emitted source differ; the compiler is "broken"
+    monkeypatch.setitem(kernels.REGISTRY, name, (kernels.REGISTRY[name][0], dict(wgm=2)))
+    monkeypatch.setattr(kernels, "_fresh", set())
+    monkeypatch.setattr(g, "DEFAULT_NVCC_PATH", "/bin/false")
+    for _ in range(2):                                   # stale the first time, and still stale the second time
+        with pytest.raises(RuntimeError):
+            kernels.ensure(name)
+        assert {s: f.read_bytes() for s, f in files.items()} == before
+        assert not any(p.name.startswith(".build-") for p in (tmp_path / name).iterdir())
+    monkeypatch.undo()
+    monkeypatch.setattr(kernels, "GENERATED_DIR", tmp_path)
+    monkeypatch.setattr(kernels, "_fresh", set())
+    monkeypatch.setitem(kernels.REGISTRY, name, (kernels.REGISTRY[name][0], dict(wgm=2)))
+    kernels.ensure(name)
+    assert files["cu"].read_bytes() != before["cu"] and b"OPT_WGM 2" in files["cu"].read_bytes()
+
+
+def test_concurrent_ensure_builds_once(tmp_path):
+    """Several processes asking for the same missing kernel (ranks under torchrun) serialise on the kernel's lock:
+    all of them end up with the same complete files, and none fails on a half-written cubin."""
+    import subprocess, sys, textwrap
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    code = textwrap.dedent(f"""
+        import importlib, sys, hashlib
+        sys.path.insert(0, {str(root)!r})
+        importlib.import_module("amdgpu-arch-gemm_b200")
+        import kernels
+        from pathlib import Path
+        kernels.GENERATED_DIR = Path({str(tmp_path)!r})
+        cubin, toml = kernels.ensure("simt_64x64x16")
+        print(hashlib.sha256(Path(cubin).read_bytes()).hexdigest(), Path(cubin).stat().st_mtime_ns)
+    """)
+    procs = [subprocess.Popen([sys.executable, "-c", code], stdout=subprocess.PIPE, text=True) for _ in range(3)]
+    outs = [p.communicate()[0].split() for p in procs]
+    assert all(p.returncode == 0 for p in procs)
+    assert len({o[0] for o in outs}) == 1 and len({o[1] for o in outs}) == 1    # one build, seen by all

@@ -8,14 +8,25 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def run_cli(built, kernel, m, n, k, validate, env=None):
+def run_cli(built, kernel, m, n, k, validate, env=None, warmup=2, runs=5):
     from runner import api
     api.build_library()
     cubin, toml = built.ensure(kernel)
     e = dict(os.environ)
     e.update(env or {})
-    return subprocess.run([str(api.RUNNER_PATH), cubin, toml, str(m), str(n), str(k), "2", "5", str(validate)],
+    return subprocess.run([str(api.RUNNER_PATH), cubin, toml, str(m), str(n), str(k), str(warmup), str(runs), str(validate)],
                           stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=e, timeout=600)
+
+
+def test_cli_on_the_1024_cubed_configuration_as_worded(built):
+    """`GeneratorRunner <cubin> <toml> 1024 1024 1024 10 100 1` with beta = 0 on the default cubin: 10 warm-up and 100
+    timed runs, validated against the runner's CPU GEMM with the reference's own rule (|gpu - cpu| < 1e-3,
+    runner/generator_runner.cpp:289-304) — no mismatch among the 1024 * 1024 elements."""
+    ret = run_cli(built, built.DEFAULT_TENSOR, 1024, 1024, 1024, 1, env={"SGEMM_BETA": "0"}, warmup=10, runs=100)
+    assert ret.returncode == 0, ret.stdout + ret.stderr
+    lines = ret.stdout.strip().split("\n")
+    assert lines[-1] == "# of mismatches: 0/1048576"
+    assert float(lines[-3].split(":")[-1]) > 0 and "tcgen05 3xTF32" in ret.stderr
 
 
 @pytest.mark.parametrize("kernel", ["tc_128x256x32_s2", "simt_128x128x16"])

@@ -95,3 +95,22 @@ def test_worst_ratio_flags_errors():
     assert oracle.worst_ratio(bad, d, s) > 1.0
     bad[5] = np.nan
     assert oracle.worst_ratio(bad, d, s) == np.inf
+
+
+def test_shard_checks_accept_a_correct_shard_and_catch_an_offset_error():
+    """The checker of the multi-GPU workload (oracle/shard_check.py) on the CPU: a shard of D computed in FP64 from
+    the globally indexed inputs passes the sampled-column check and both checksums; the same shard computed from a B
+    that was filled with the wrong first index (one column off) fails all three."""
+    from oracle import shard_check
+    m, n, k, tile_n = 96, 320, 200, 64
+    a = shard_check.global_a(m, k)
+    for n0, n1 in ((0, 128), (128, 320)):
+        cols = shard_check.sample_columns(n0, n1, tile_n, 24, seed=1)
+        assert cols[0] == n0 and cols[-1] == n1 - 1 and len(set(cols)) == len(cols) <= 24
+        assert {n0 + tile_n - 1, n0 + tile_n}.issubset(set(cols) | {n1}) or n1 - n0 <= tile_n
+        for shift, ok in ((0, True), (1, False)):
+            b = oracle.fill_uniform(k * (n1 - n0), 1, first_index=(n0 + shift) * k)
+            d = (b.reshape(n1 - n0, k).astype(np.float64) @ a.reshape(k, m).astype(np.float64)).astype(np.float32)
+            ratio = shard_check.worst_ratio_of_columns(d[cols - n0], cols, m, k)
+            rows, columns = shard_check.checksum_ratios(d.reshape(-1), n0, n1, m, k, block=64)
+            assert (ratio <= 1.0) == ok and (rows <= 1.0) == ok and (columns <= 1.0) == ok, (n0, shift, ratio, rows, columns)

@@ -92,3 +92,43 @@ def test_refuses_problems_beyond_the_fixed_scratch(runner):
         assert r.info("launches") == launches
     finally:
         r.dev_free(dummy)
+
+
+def test_counts_the_aligned_copies_of_operands_tma_cannot_read(runner):
+    """An A that starts 4 bytes into an allocation cannot be read by TMA where it lies: the tensor path first copies it
+    to an aligned pitch inside the scratch.  The size check must count that copy — a problem that fits with an aligned A
+    and does not fit with this one is refused with the scratch-limit code before anything is launched, and a smaller one
+    of the same kind is computed correctly out of the fixed array."""
+    from runner import api
+    r = runner
+    r.set_option("force_variant", 1)
+    r.set_option("split_k", 1)
+    m, n, k = 2048, 128, 2048              # lo copies of A and B: 17 MiB, with the aligned copy of A: 33 MiB
+    base = r.dev_alloc(m * k * 4 + 256)
+    other = r.dev_alloc(max(k * n, m * n) * 4)
+    try:
+        assert r.workspace_bytes(m, n, k) <= api.noalloc_scratch_bytes() < r.workspace_bytes(m, n, k, a=base + 4, b=other)
+        launches = r.info("launches")
+        with pytest.raises(api.SgemmError) as e:
+            r.launch_noalloc(base + 4, other, None, other, m, n, k)
+        assert e.value.code == -9 and r.info("launches") == launches
+    finally:
+        r.dev_free(base)
+        r.dev_free(other)
+    m, n, k = 512, 128, 1024
+    a, b, c = oracle.make_inputs(m, n, k, seed=23)
+    pa, pb, pd = r.dev_alloc(a.nbytes + 16), r.dev_alloc(b.nbytes), r.dev_alloc(m * n * 4)
+    try:
+        r.upload(pa + 4, a)
+        r.upload(pb, b)
+        for _ in range(2):
+            r.memset(pd, 0, m * n * 4)
+            r.launch_noalloc(pa + 4, pb, None, pd, m, n, k)
+            got = fetch(r, pd, m * n)
+            assert r.info("last_variant") == 1
+            ref = oracle.gemm(a, b, None, 1.0, 0.0, m, n, k)
+            assert oracle.worst_ratio(got, ref, oracle.abs_bound(a, b, m, n, k)) <= 1.0
+    finally:
+        r.sync()
+        for p in (pa, pb, pd):
+            r.dev_free(p)
