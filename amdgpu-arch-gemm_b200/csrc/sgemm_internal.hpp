@@ -27,6 +27,23 @@ int with_context(sgemm_handle *h, int (*fn)(void *), void *arg);
 // array as resolved in the handle's context (NULL until the first allocation-free call on the handle).
 void **noalloc_scratch_slot(sgemm_handle *h);
 
+// The handle's communicator over the GPUs that share one sharded SGEMM (sgemm_multi.cpp owns the NCCL side):
+// `comm` is an ncclComm_t, NULL until sgemm_comm_init / sgemm_comm_init_all.
+struct CommState {
+    void *comm = nullptr;
+    int rank = 0;
+    int world = 1;
+};
+CommState *comm_state(sgemm_handle *h);
+
+// In-place exchange over the handle's communicator, ordered on `stream`: piece r — `bytes[r]` bytes at
+// `base + offsets[r]` on every rank, valid on rank r — is copied to the same place on all other ranks.  Equal,
+// back-to-back pieces go as one all-gather, ragged ones as grouped broadcasts.
+int comm_complete(sgemm_handle *h, void *base, const size_t *offsets, const size_t *bytes, void *stream);
+
+// Destroy an ncclComm_t stored in a CommState (no-op for NULL or without NCCL).
+void comm_release(void *comm);
+
 // sgemm_launch with the scratch taken from [scratch, scratch + scratch_bytes) for this one call only; the
 // handle's own workspace settings are put back before returning.  Never allocates device memory; a need beyond
 // `scratch_bytes` comes back as SGEMM_ERR_SCRATCH_LIMIT.

@@ -155,6 +155,7 @@ struct sgemm_handle {
     std::vector<std::pair<CUevent, CUevent>> prof_events;
     size_t prof_used = 0;
     void *noalloc_scratch = nullptr;   // device address of the library's static scratch array in this handle's context
+    sgemm_internal::CommState comm;    // communicator over the GPUs of a sharded SGEMM (see sgemm_multi.cpp)
     std::string error;
 };
 
@@ -760,6 +761,7 @@ SGEMM_API const char *sgemm_strerror(int code) {
         case SGEMM_ERR_WORKSPACE: return "workspace too small or allocation failed";
         case SGEMM_ERR_DEVICE_STATUS: return "a kernel gave up on a bounded wait";
         case SGEMM_ERR_SCRATCH_LIMIT: return "problem needs more scratch than the allocation-free entry point has";
+        case SGEMM_ERR_COMM: return "NCCL not available, communicator missing, or a collective failed";
         default: return "unknown error";
     }
 }
@@ -922,6 +924,8 @@ SGEMM_API int sgemm_close(sgemm_handle *h) {
         {
             CtxGuard guard(h);
             d.cuCtxSynchronize_();
+            if (h->comm.comm) sgemm_internal::comm_release(h->comm.comm);
+            h->comm = sgemm_internal::CommState{};
             for (auto &pr : h->prof_events) {
                 d.cuEventDestroy_(pr.first);
                 d.cuEventDestroy_(pr.second);
@@ -950,20 +954,74 @@ SGEMM_API int sgemm_launch(sgemm_handle *h, const float *dA, const float *dB, co
     return launch_device(h, dA, dB, dC, dD, alpha, beta, m, n, k, lda, ldb, ldc, ldd, (CUstream)stream);
 }
 
+namespace {
+
+// Upload A as stored (`outer` columns of pitch lda, `inner` elements each) into the staging buffer, ordered on `s`:
+// all of it, or — sharded — only this rank's slice of the columns, after which the ranks complete each other's
+// buffers over NVLink (an in-place all-gather of the slices; ragged slices as grouped broadcasts).  A replicated
+// operand then crosses the host link once per box instead of once per GPU.
+int upload_a(sgemm_handle *h, const float *hA, size_t bytes_a, uint32_t inner, uint32_t outer, uint32_t lda, CUstream s,
+             bool sharded) {
+    Driver &d = driver();
+    if (!bytes_a) return SGEMM_OK;
+    if (!sharded || h->comm.world <= 1) {
+        CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[0], hA, bytes_a, s));
+        return SGEMM_OK;
+    }
+    const int world = h->comm.world;
+    const size_t eb = h->elem_bytes;
+    std::vector<size_t> offsets((size_t)world), bytes((size_t)world);
+    for (int r = 0; r < world; ++r) {
+        const uint64_t o0 = (uint64_t)outer * r / world, o1 = (uint64_t)outer * (r + 1) / world;
+        offsets[r] = (size_t)o0 * lda * eb;
+        // whole columns of pitch lda, except that the buffer ends with the last element of the last column
+        bytes[r] = o1 > o0 ? ((size_t)(o1 - o0 - 1) * lda + (o1 == outer ? inner : lda)) * eb : 0;
+    }
+    const int me = h->comm.rank;
+    if (bytes[me])
+        CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[0] + offsets[me], reinterpret_cast<const char *>(hA) + offsets[me], bytes[me], s));
+    return sgemm_internal::comm_complete(h, reinterpret_cast<void *>(h->stage[0]), offsets.data(), bytes.data(), s);
+}
+
+int run_host_impl(sgemm_handle *h, const float *hA, const float *hB, const float *hC, float *hD,
+                  float alpha, float beta, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb,
+                  uint32_t ldc, uint32_t ldd, bool sharded);
+
+}  // namespace
+
 SGEMM_API int sgemm_run_host(sgemm_handle *h, const float *hA, const float *hB, const float *hC, float *hD,
                              float alpha, float beta, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb,
                              uint32_t ldc, uint32_t ldd) {
+    return run_host_impl(h, hA, hB, hC, hD, alpha, beta, m, n, k, lda, ldb, ldc, ldd, false);
+}
+
+SGEMM_API int sgemm_run_host_sharded(sgemm_handle *h, const float *hA, const float *hB, const float *hC, float *hD,
+                                     float alpha, float beta, uint32_t m, uint32_t n_local, uint32_t k, uint32_t lda,
+                                     uint32_t ldb, uint32_t ldc, uint32_t ldd) {
+    if (!h) return SGEMM_ERR_INVALID_ARGUMENT;
+    if (!h->comm.comm) return fail(h, SGEMM_ERR_COMM, "no communicator on this handle: call sgemm_comm_init first");
+    // every rank must take part in the exchange of A, also one whose shard is empty
+    return run_host_impl(h, hA, hB, hC, hD, alpha, beta, m, n_local, k, lda, ldb, ldc, ldd, true);
+}
+
+namespace {
+
+int run_host_impl(sgemm_handle *h, const float *hA, const float *hB, const float *hC, float *hD,
+                  float alpha, float beta, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb,
+                  uint32_t ldc, uint32_t ldd, bool sharded) {
     int rc = check_problem(h, hA, hB, hC, hD, beta, m, n, k, lda, ldb, ldc, ldd);
     if (rc) return rc;
-    if (m == 0 || n == 0) return SGEMM_OK;
+    if (sharded && m && k && !hA) return fail(h, SGEMM_ERR_INVALID_ARGUMENT, "A is NULL");
+    if (m == 0 || (n == 0 && !sharded)) return SGEMM_OK;
+    const uint32_t a_inner = h->cfg.trans_a ? k : m, a_outer = h->cfg.trans_a ? m : k;
     CtxGuard guard(h);
     Driver &d = driver();
     const bool use_c = beta != 0.0f;
     const size_t a_floats = h->cfg.trans_a ? (size_t)lda * (m - 1) + k : (size_t)lda * (k - 1) + m;
-    const size_t b_floats = h->cfg.trans_b ? (size_t)ldb * (k - 1) + n : (size_t)ldb * (n - 1) + k;
+    const size_t b_floats = !n ? 0 : h->cfg.trans_b ? (size_t)ldb * (k - 1) + n : (size_t)ldb * (n - 1) + k;
     const size_t eb = h->elem_bytes;   // A and B elements; C and D are FP32
     const size_t bytes[4] = {k ? a_floats * eb : 0, k ? b_floats * eb : 0,
-                             use_c ? ((size_t)ldc * (n - 1) + m) * 4 : 0, ((size_t)ldd * (n - 1) + m) * 4};
+                             use_c && n ? ((size_t)ldc * (n - 1) + m) * 4 : 0, n ? ((size_t)ldd * (n - 1) + m) * 4 : 0};
     for (int i = 0; i < 4; ++i) {
         if (bytes[i] > h->stage_bytes[i]) {
             if (h->stage[i]) {
@@ -1027,7 +1085,7 @@ SGEMM_API int sgemm_run_host(sgemm_handle *h, const float *hA, const float *hB, 
         } restore{h, h->force_variant, h->split_k_opt, {s_in, s_cmp, s_out}};
         h->force_variant = whole.variant != kVariantTensor ? 2 : ((whole.tk == &h->tk_skinny || whole.tk == &h->tk_thin) ? 3 : 1);
         h->split_k_opt = whole.split_k;
-        CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[0], hA, bytes[0], s_in));
+        if ((rc = upload_a(h, hA, bytes[0], a_inner, a_outer, lda, s_in, sharded))) return rc;
         CU_CHECK(h, d.cuEventRecord_(ev_a, s_in));
         CU_CHECK(h, d.cuStreamWaitEvent_(s_cmp, ev_a, 0));
         for (uint32_t j = 0; j < chunks; ++j) {
@@ -1060,7 +1118,11 @@ SGEMM_API int sgemm_run_host(sgemm_handle *h, const float *hA, const float *hB, 
         return SGEMM_OK;
     }
     CUstream s = nullptr;
-    if (bytes[0]) CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[0], hA, bytes[0], s));
+    if ((rc = upload_a(h, hA, bytes[0], a_inner, a_outer, lda, s, sharded))) return rc;
+    if (n == 0) {   // (sharded call of a rank without columns: it only takes part in the exchange of A)
+        CU_CHECK(h, d.cuStreamSynchronize_(s));
+        return SGEMM_OK;
+    }
     if (bytes[1]) CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[1], hB, bytes[1], s));
     if (bytes[2]) CU_CHECK(h, d.cuMemcpyHtoDAsync_(h->stage[2], hC, bytes[2], s));
     if (ldd != m)  // keep the caller's padding rows of D: the kernel writes only rows < M of each column
@@ -1073,6 +1135,8 @@ SGEMM_API int sgemm_run_host(sgemm_handle *h, const float *hA, const float *hB, 
     CU_CHECK(h, d.cuStreamSynchronize_(s));
     return SGEMM_OK;
 }
+
+}  // namespace
 
 SGEMM_API int sgemm_bench(sgemm_handle *h, const float *dA, const float *dB, const float *dC, float *dD, float alpha,
                           float beta, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldb, uint32_t ldc,
@@ -1164,6 +1228,8 @@ SGEMM_API int sgemm_get_info(sgemm_handle *h, const char *key, int64_t *value) {
     else if (k == "tile_m") *value = h->tile_m;
     else if (k == "tile_n") *value = h->tile_n;
     else if (k == "sm_count") *value = h->sm_count;
+    else if (k == "comm_rank") *value = h->comm.comm ? h->comm.rank : -1;
+    else if (k == "comm_world") *value = h->comm.comm ? h->comm.world : 0;
     else if (k == "workspace_bytes") *value = (int64_t)(h->ws_lent ? h->ws_lent_bytes : h->ws_owned_bytes);
     else if (k == "profile_count") *value = (int64_t)h->prof_used;
     else if (k == "profile_main_ns") {  // total device time of the bracketed main-kernel launches; resets the tally
@@ -1313,6 +1379,8 @@ int with_context(sgemm_handle *h, int (*fn)(void *), void *arg) {
 }
 
 void **noalloc_scratch_slot(sgemm_handle *h) { return h ? &h->noalloc_scratch : nullptr; }
+
+CommState *comm_state(sgemm_handle *h) { return h ? &h->comm : nullptr; }
 
 int launch_with_scratch(sgemm_handle *h, void *scratch, size_t scratch_bytes, const float *dA, const float *dB,
                         const float *dC, float *dD, float alpha, float beta, uint32_t m, uint32_t n, uint32_t k,

@@ -61,6 +61,13 @@ ABI = {
     "sgemm_launch_noalloc": (ctypes.c_int, _GEMM_ARGS + [_vp]),
     "sgemm_noalloc_scratch_bytes": (ctypes.c_size_t, []),
     "sgemm_run_host": (ctypes.c_int, _GEMM_ARGS),
+    "sgemm_run_host_sharded": (ctypes.c_int, _GEMM_ARGS),
+    "sgemm_shard_columns": (ctypes.c_int, [_u32, _u32, _u32, _u32, ctypes.POINTER(_u32), ctypes.POINTER(_u32)]),
+    "sgemm_comm_unique_id": (ctypes.c_int, [ctypes.c_char_p]),
+    "sgemm_comm_init": (ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.c_int, ctypes.c_int]),
+    "sgemm_comm_init_all": (ctypes.c_int, [ctypes.POINTER(_vp), ctypes.c_int]),
+    "sgemm_comm_destroy": (ctypes.c_int, [_vp]),
+    "sgemm_allgather_columns": (ctypes.c_int, [_vp, _vp, _u32, _u32, _u32, _u32, _vp]),
     "sgemm_bench": (ctypes.c_int, _GEMM_ARGS + [_u32, _u32, _vp, ctypes.POINTER(ctypes.c_float)]),
     "sgemm_last_status": (ctypes.c_int, [_vp, ctypes.POINTER(_u32 * 8)]),
     "sgemm_wait_selftest": (ctypes.c_int, [_vp, _u32, _u32]),
@@ -198,6 +205,27 @@ class SgemmRunner:
         self._check(self._L.sgemm_run_host(self._h, _ptr(a), _ptr(b), _ptr(c), _ptr(d), alpha, beta, m, n, k,
                                            lda, ldb, ldc, ldd), "sgemm_run_host")
 
+    def run_host_sharded(self, a, b, c, d, m, n_local, k, alpha=1.0, beta=0.0, lda=0, ldb=0, ldc=0, ldd=0):
+        """``run_host`` for one rank of a column-sharded call: ``a`` is the whole replicated A in host memory (only this
+        rank's slice is uploaded, the ranks complete each other's copies over NVLink), ``b``, ``c``, ``d`` are this
+        rank's column shards.  Collective over the handle's communicator (``comm_init``)."""
+        lda, ldb, ldc, ldd = self._lds(m, n_local, k, lda, ldb, ldc, ldd)
+        self._check(self._L.sgemm_run_host_sharded(self._h, _ptr(a), _ptr(b), _ptr(c), _ptr(d), alpha, beta, m, n_local, k,
+                                                   lda, ldb, ldc, ldd), "sgemm_run_host_sharded")
+
+    # ------------------------------------------------------------------------------- multi-GPU
+    def comm_init(self, comm_id: bytes, rank: int, world: int):
+        """Join the communicator ``comm_id`` (from ``comm_unique_id()`` on one rank) as ``rank`` of ``world``."""
+        self._check(self._L.sgemm_comm_init(self._h, comm_id, rank, world), "sgemm_comm_init")
+
+    def comm_destroy(self):
+        self._check(self._L.sgemm_comm_destroy(self._h), "sgemm_comm_destroy")
+
+    def allgather_columns(self, d_full, m, n, ldd=0, tile_n=0, stream=0):
+        """In-place all-gather of D's column shards (this rank's shard already lies at its place in ``d_full``)."""
+        self._check(self._L.sgemm_allgather_columns(self._h, _ptr(d_full), m, n, ldd or max(m, 1), tile_n or self.info("tile_n"),
+                                                    stream), "sgemm_allgather_columns")
+
     def bench(self, a, b, c, d, m, n, k, alpha=1.0, beta=0.0, warmup=5, runs=50, stream=0) -> float:
         """Mean milliseconds of ``runs`` back-to-back launches after ``warmup`` (CUDA events)."""
         ms = ctypes.c_float()
@@ -273,6 +301,32 @@ class SgemmRunner:
 
     def sync(self):
         self._check(self._L.sgemm_dev_sync(self._h), "sgemm_dev_sync")
+
+
+def shard_columns(n: int, world: int, rank: int, tile_n: int = 1) -> Tuple[int, int]:
+    """The library's column-shard rule (``sgemm_shard_columns``); ``runner.shard.shard_columns`` restates it in Python."""
+    n0, n1 = _u32(), _u32()
+    rc = lib().sgemm_shard_columns(n, world, rank, tile_n, ctypes.byref(n0), ctypes.byref(n1))
+    if rc:
+        raise SgemmError(rc, "sgemm_shard_columns", "bad shard request")
+    return n0.value, n1.value
+
+
+def comm_unique_id() -> bytes:
+    """Id of a new communicator (128 bytes): one rank makes it, the host program hands it to all ranks."""
+    buf = ctypes.create_string_buffer(128)
+    rc = lib().sgemm_comm_unique_id(buf)
+    if rc:
+        raise SgemmError(rc, "sgemm_comm_unique_id", lib().sgemm_last_error(None).decode())
+    return buf.raw
+
+
+def comm_init_all(runners) -> None:
+    """One process, several ``SgemmRunner`` on distinct GPUs: one communicator over them, runner i = rank i."""
+    arr = (_vp * len(runners))(*[r._h for r in runners])
+    rc = lib().sgemm_comm_init_all(arr, len(runners))
+    if rc:
+        raise SgemmError(rc, "sgemm_comm_init_all", lib().sgemm_last_error(runners[0]._h).decode())
 
 
 def noalloc_scratch_bytes() -> int:

@@ -37,17 +37,36 @@ def fill_shard_inputs(runner, a, b, m: int, k: int, n0: int, n1: int, seed: int 
 
 
 def gather_columns(dist, local_d, m: int, n: int, world: int, tile_n: int = 1):
-    """All-gather the column shards of D (flat column-major tensors) into the full M x N matrix on every rank.
-    Shards may differ in width, so each is padded to the widest one for the collective."""
+    """All-gather the column shards of D (flat column-major tensors) into the full M x N matrix on every rank through
+    ``torch.distributed`` (any backend; the native in-place form over NCCL is ``SgemmRunner.allgather_columns``).
+    Equal shards are gathered straight into the result; shards of different width are padded to the widest one for
+    the collective and cut back afterwards."""
     import torch
 
     shards = all_shards(n, world, tile_n)
-    widest = max(n1 - n0 for n0, n1 in shards)
+    widths = [n1 - n0 for n0, n1 in shards]
+    if len(set(widths)) == 1:
+        full = torch.empty(m * n, dtype=local_d.dtype, device=local_d.device)
+        dist.all_gather_into_tensor(full, local_d[: m * widths[0]].contiguous())
+        return full
+    widest = max(widths)
     padded = torch.zeros(m * widest, dtype=local_d.dtype, device=local_d.device)
     padded[: local_d.numel()] = local_d
     parts = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(parts, padded)
-    return torch.cat([parts[r][: m * (n1 - n0)] for r, (n0, n1) in enumerate(shards)])
+    return torch.cat([parts[r][: m * w] for r, w in enumerate(widths)])
+
+
+def make_communicator(dist, runner, rank: int, world: int) -> None:
+    """Give ``runner`` (one ``SgemmRunner`` per process, one process per GPU) the library's own communicator over all
+    ranks: rank 0 makes the id, ``torch.distributed`` (the host-side plumbing) hands it to the others, every rank
+    joins with its GPU."""
+    from runner import api
+
+    box = [api.comm_unique_id() if rank == 0 else None]
+    if world > 1:
+        dist.broadcast_object_list(box, src=0)
+    runner.comm_init(box[0], rank, world)
 
 
 def max_over_ranks(dist, value: float, device="cpu") -> float:

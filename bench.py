@@ -390,6 +390,9 @@ def main():
     cubin, toml = kernels.ensure(kernel)
     r = api.SgemmRunner(cubin, toml, local_rank)
     r.set_option("acc_chain", args.acc_chain)
+    if world > 1:
+        from runner.shard import make_communicator
+        make_communicator(dist, r, rank, world)     # the library's own NCCL communicator: sharded host call, all-gather of D
     stream = torch.cuda.current_stream().cuda_stream
     try:
         uuid = "GPU-" + str(torch.cuda.get_device_properties(local_rank).uuid)
@@ -436,22 +439,36 @@ def main():
         sustained["main_kernel_tflops"] = (2.0 * job.m * n_local * job.k) / (sus_main_ns * 1e-9) * 1e-12 if sus_main_ns else None
     parity = job.parity(args.parity_columns) if args.parity_columns > 0 else None
 
-    # ---- optional: all-gather of the column shards of D over NVLink (NCCL); never part of `value`
+    # ---- optional: all-gather of the column shards of D over NVLink (NCCL, in place in a full-size D on every GPU:
+    # sgemm_allgather_columns); never part of `value`
     allgather = None
     if args.allgather and world > 1:
-        from runner.shard import gather_columns
-        gather_columns(dist, job.d, job.m, job.n_total, world, job.tile_n)      # warm-up (NCCL channel set-up)
+        full_d = torch.empty(job.m * job.n_total, dtype=torch.float32, device=dev)
+        mine = full_d[job.m * job.n0: job.m * job.n1]
+        mine.copy_(job.d[: job.m * n_local])
+        r.allgather_columns(full_d, job.m, job.n_total, stream=stream)      # warm-up (NCCL channel set-up)
         job.barrier()
         g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         g0.record()
-        full_d = gather_columns(dist, job.d, job.m, job.n_total, world, job.tile_n)
+        r.allgather_columns(full_d, job.m, job.n_total, stream=stream)
         g1.record()
         job.barrier()
         ag_ms = job.max_over_ranks(g0.elapsed_time(g1))
-        recv_bytes = (full_d.numel() - job.d.numel()) * 4
+        recv_bytes = (full_d.numel() - job.m * n_local) * 4
+        # what arrived must be what the owners computed: this rank's neighbour's first column against the oracle
+        check = None
+        if args.parity_columns > 0:
+            from oracle import shard_check
+            other = (rank + 1) % world
+            from runner.shard import shard_columns
+            o0, o1 = shard_columns(job.n_total, world, other, job.tile_n)
+            if o1 > o0:
+                col = full_d[job.m * o0: job.m * (o0 + 1)].cpu().numpy()
+                check = job.max_over_ranks(shard_check.worst_ratio_of_columns(col, [o0], job.m, job.k))
         allgather = {"ms": ag_ms, "bytes_received_per_gpu": recv_bytes, "gb_per_s_per_gpu": recv_bytes / ag_ms * 1e-6,
-                     "full_d_elements": full_d.numel()}
-        del full_d
+                     "full_d_elements": full_d.numel(), "path": "sgemm_allgather_columns (in place, ncclAllGather)",
+                     "received_column_worst_ratio": check}
+        del full_d, mine
 
     # ---- end to end through the host-buffer entry point (pinned host memory, copies inside the timed region)
     e2e = None
@@ -463,19 +480,23 @@ def main():
         hb.copy_(job.b)
         r.set_workspace(None, 0)     # the host entry point sizes its own scratch (A's copies are shared by the chunks)
         e2e_steps = max(1, min(args.steps, 5))
-        r.run_host(ha, hb, None, hd, M, n_local, K, alpha=1.0, beta=0.0)   # warm-up: allocates the staging buffers
+        # one rank: the host-buffer call; several: its sharded form — every rank uploads 1/world of the replicated A
+        # and its own columns of B, the ranks complete A over NVLink, every rank downloads its columns of D
+        host_call = r.run_host_sharded if world > 1 else r.run_host
+        host_call(ha, hb, None, hd, M, n_local, K, alpha=1.0, beta=0.0)   # warm-up: allocates the staging buffers
         job.barrier()
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
-            r.run_host(ha, hb, None, hd, M, n_local, K, alpha=1.0, beta=0.0)   # synchronises before returning
+            host_call(ha, hb, None, hd, M, n_local, K, alpha=1.0, beta=0.0)   # synchronises before returning
         dt = job.max_over_ranks(time.perf_counter() - t0)
         # the result the host now holds must be the one the device path computed
         same = bool(torch.equal(hd, job.d.cpu()))
         same = bool(job.max_over_ranks(0.0 if same else 1.0) == 0.0)
         e2e = {"value": 2.0 * job.m * job.n_total * job.k / (dt / e2e_steps) * 1e-12, "unit": UNIT,
-               "h2d_bytes_per_step": (M * K + K * n_local) * 4, "d2h_bytes_per_step": M * n_local * 4,
-               "steps": e2e_steps, "host_result_equals_device_result": same,
-               "path": "sgemm_run_host (pinned host buffers, column chunks pipelined over three streams)"}
+               "h2d_bytes_per_step": (M * K // world + K * n_local) * 4, "d2h_bytes_per_step": M * n_local * 4,
+               "bytes_are": "per rank", "steps": e2e_steps, "host_result_equals_device_result": same,
+               "path": ("sgemm_run_host_sharded (A uploaded in 1/N slices and completed by an all-gather over NVLink; "
+                        if world > 1 else "sgemm_run_host (") + "pinned host buffers, column chunks pipelined over three streams)"}
         del ha, hb, hd
     head_shape = (job.m, n_local, job.k)
     head_total = job.n_total

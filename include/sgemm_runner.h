@@ -39,7 +39,8 @@ typedef enum sgemm_error {
     SGEMM_ERR_UNSUPPORTED = -6,      /* the loaded kernel cannot serve this request (e.g. forced variant) */
     SGEMM_ERR_WORKSPACE = -7,        /* lent workspace too small, or allocation failed */
     SGEMM_ERR_DEVICE_STATUS = -8,    /* a kernel reported a bounded wait that ran out (sgemm_last_status) */
-    SGEMM_ERR_SCRATCH_LIMIT = -9     /* problem needs more scratch than sgemm_launch_noalloc's fixed array holds */
+    SGEMM_ERR_SCRATCH_LIMIT = -9,    /* problem needs more scratch than sgemm_launch_noalloc's fixed array holds */
+    SGEMM_ERR_COMM = -10             /* NCCL not loadable, no communicator on the handle, or a collective failed */
 } sgemm_error;
 
 /* Kernel configuration as read from the generator's TOML (generator/generator.py:1001-1017 writes it,
@@ -137,6 +138,47 @@ int sgemm_run_host(sgemm_handle *h, const float *hA, const float *hB, const floa
                    float alpha, float beta, uint32_t m, uint32_t n, uint32_t k,
                    uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd);
 
+/* ---- one SGEMM over several GPUs of a box: column shards --------------------------------------------------------
+ * No counterpart in the reference, which is single-GPU (its runner never selects a device,
+ * runner/generator_runner.cpp:192-324).  D's columns are independent: GPU r of g computes D[:, n0:n1] from a
+ * replicated A and B[:, n0:n1]; in column-major storage these are contiguous ranges, so a shard is a pointer offset
+ * and each GPU runs the ordinary single-GPU call (sgemm_launch) on n1 - n0 columns.  No collective sits on the
+ * compute path.  One handle per GPU, in one process (sgemm_comm_init_all) or one process per GPU (sgemm_comm_init with
+ * an id made by one rank and handed to the others by the host program).  The communicator is NCCL's, bound at run
+ * time; it is used in exactly two places: to complete the replicated A on the host-buffer path, and for the optional
+ * all-gather of D.  Only NCCL touches peer memory. */
+
+/* Columns [*n0, *n1) of rank `rank` of `world`: whole tiles of tile_n columns, as even as possible, earlier ranks take
+ * the extra tile, the last non-empty shard absorbs a ragged tail.  Host only. */
+int sgemm_shard_columns(uint32_t n, uint32_t world, uint32_t rank, uint32_t tile_n, uint32_t *n0, uint32_t *n1);
+
+#define SGEMM_COMM_ID_BYTES 128
+/* Make the id of a new communicator (one rank calls this; the host program hands the bytes to all ranks). */
+int sgemm_comm_unique_id(uint8_t id[SGEMM_COMM_ID_BYTES]);
+/* Join the communicator as rank `rank` of `world` with this handle's GPU.  Collective: returns when all ranks joined. */
+int sgemm_comm_init(sgemm_handle *h, const uint8_t id[SGEMM_COMM_ID_BYTES], int rank, int world);
+/* One process, `count` handles on distinct GPUs: make one communicator over them, handle i = rank i. */
+int sgemm_comm_init_all(sgemm_handle *const *handles, int count);
+/* Leave it (sgemm_close does this too). */
+int sgemm_comm_destroy(sgemm_handle *h);
+
+/* sgemm_run_host for one rank of a sharded call: hB, hC, hD are this rank's column shards (n_local columns, may be 0),
+ * hA is the whole replicated A as every rank holds it in host memory — of which only this rank's 1/world slice of
+ * the columns is uploaded; the ranks then complete each other's device copies over NVLink (in-place all-gather of the
+ * slices into each GPU's own memory, before any kernel reads it), so A crosses the host link once per box, not once
+ * per GPU.  Collective: every rank of the communicator must make the call.  The result equals sgemm_run_host's bit
+ * for bit. */
+int sgemm_run_host_sharded(sgemm_handle *h, const float *hA, const float *hB, const float *hC, float *hD,
+                           float alpha, float beta, uint32_t m, uint32_t n_local, uint32_t k,
+                           uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd);
+
+/* Optional all-gather of D: dD_full is a full M x N matrix (pitch ldd) on every rank, in which this rank's shard —
+ * columns sgemm_shard_columns(n, world, rank, tile_n) — has been computed in place (pass dD_full + n0 * ldd to
+ * sgemm_launch).  Afterwards every rank holds all of D.  In place: equal shards go as one ncclAllGather, ragged ones
+ * as grouped broadcasts; no padding, no temporary.  Asynchronous on `stream`; collective. */
+int sgemm_allgather_columns(sgemm_handle *h, float *dD_full, uint32_t m, uint32_t n, uint32_t ldd, uint32_t tile_n,
+                            void *stream);
+
 /* Replaces the timed loop of main (runner/generator_runner.cpp:270-280): `warmup` untimed launches, then
  * `runs` back-to-back launches between two events on `stream`; *ms_mean = elapsed / runs. Synchronises. */
 int sgemm_bench(sgemm_handle *h, const float *dA, const float *dB, const float *dC, float *dD,
@@ -187,6 +229,7 @@ int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value);
  * "last_acc_chain" (k per accumulation chain of the last tensor launch, 0 = whole K), "acc_chain" and
  * "skinny_acc_chain" (the chains the main and the companion tensor kernel were generated with),
  * "launches" (kernel launches issued so far), "tile_m", "tile_n", "sm_count", "workspace_bytes",
+ * "comm_rank" / "comm_world" (-1 / 0 without a communicator),
  * "profile_count" (bracketed launches since the last read), "profile_main_ns" (their summed device time in
  * nanoseconds; synchronises on them and resets the tally). */
 int sgemm_get_info(sgemm_handle *h, const char *key, int64_t *value);

@@ -76,3 +76,27 @@ def test_cli_drives_cubins_for_sixteen_bit_operands(built, kernel):
     from runner import api
     bad = subprocess.run([str(api.RUNNER_PATH), cubin, toml, "64", "64", "64", "1", "1", "0"], capture_output=True, text=True)
     assert bad.returncode == 2 and "NN layout" in bad.stderr
+
+
+@pytest.mark.parametrize("ngpus", [1, 2, 8])
+def test_cli_shards_over_gpus_and_gathers(built, ngpus, tmp_path):
+    """SGEMM_NGPUS / SGEMM_ALLGATHER: the same positional CLI and stdout, the problem column-sharded over the GPUs of
+    the box in one process, D all-gathered in place over NVLink and validated on the last GPU's copy.  (One GPU: a
+    communicator of one rank — the code path is the same.)"""
+    import json
+    from runner import api
+    if api.device_count() < ngpus:
+        pytest.skip(f"needs {ngpus} GPUs")
+    out = tmp_path / "r.json"
+    env = {"SGEMM_NGPUS": str(ngpus), "SGEMM_ALLGATHER": "1", "SGEMM_BETA": "0", "SGEMM_JSON": str(out)}
+    ret = run_cli(built, built.DEFAULT_TENSOR, 1024, 2048 + 96, 1024, 1, env=env)
+    assert ret.returncode == 0, ret.stdout + ret.stderr
+    lines = ret.stdout.strip().split("\n")
+    assert lines[-1] == f"# of mismatches: 0/{1024 * (2048 + 96)}" and lines[-4].startswith("ASM gemm: ")
+    rec = json.load(open(out))
+    assert rec["ngpus"] == ngpus and len(rec["per_gpu"]) == ngpus and rec["mismatches"] == 0
+    assert rec["per_gpu"][0]["n0"] == 0 and rec["per_gpu"][-1]["n1"] == 2048 + 96
+    assert all(a["n1"] == b["n0"] for a, b in zip(rec["per_gpu"], rec["per_gpu"][1:]))
+    assert "all-gather of D" in ret.stderr and rec["allgather_ms"] > 0
+    if ngpus > 1:
+        assert f"{ngpus} GPUs, columns sharded" in ret.stderr

@@ -28,7 +28,7 @@ def test_strerror_is_total(built):
     from runner import api
     L = api.lib()
     assert L.sgemm_strerror(0) == b"ok"
-    for code in range(-9, 0):
+    for code in range(-10, 0):
         assert L.sgemm_strerror(code) not in (b"", b"unknown error")
     assert L.sgemm_strerror(-99) == b"unknown error"
 
@@ -109,3 +109,56 @@ def test_kernel_recommendation_names_registered_kernels(built):
         assert got in built.REGISTRY and got == want, (shape, got)
     for shape in [(1024, 1024, 1024), (300, 5000, 700), (1, 1, 1), (65536, 64, 64)]:
         assert built.recommend(*shape) in built.REGISTRY
+
+
+def test_shard_rule_of_the_library_equals_the_python_restatement(built):
+    """sgemm_shard_columns (C ABI, used by the runner program) and runner.shard.shard_columns (used by the benchmark)
+    must cut the same shards: whole tiles, as even as possible, ragged tail in the last non-empty shard."""
+    from runner import api
+    from runner.shard import shard_columns
+    for n in (0, 1, 255, 256, 4100, 8192, 32768, 70001):
+        for world in (1, 2, 3, 4, 8):
+            for tile_n in (1, 32, 128, 256):
+                spans = [api.shard_columns(n, world, r, tile_n) for r in range(world)]
+                assert spans == [shard_columns(n, world, r, tile_n) for r in range(world)]
+                assert spans[0][0] == 0 and spans[-1][1] == n
+                assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+    assert api.lib().sgemm_shard_columns(8, 2, 2, 1, None, None) == -1      # rank out of range, NULL outputs
+
+
+def test_missing_nccl_is_reported_not_fatal(built):
+    """The communicator entry points bind NCCL at run time.  With a library that cannot be loaded (simulated through
+    SGEMM_NCCL_LIBRARY) they return SGEMM_ERR_COMM with the loader's message; nothing aborts and the single-GPU entry
+    points are unaffected.  Runs in a child process because the binding is made once per process."""
+    import subprocess, sys, textwrap
+    code = textwrap.dedent(f"""
+        import importlib, sys
+        sys.path.insert(0, {str(ROOT)!r})
+        importlib.import_module("amdgpu-arch-gemm_b200")
+        from runner import api
+        try:
+            api.comm_unique_id()
+        except api.SgemmError as e:
+            print(e.code, "cannot load NCCL" in str(e))
+        print(api.lib().sgemm_strerror(-10).decode())
+        print(api.shard_columns(1000, 4, 3, 128))
+    """)
+    env = dict(__import__("os").environ, SGEMM_NCCL_LIBRARY="/nonexistent/libnccl.so.2")
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env)
+    assert out.returncode == 0, out.stderr
+    lines = out.stdout.strip().split("\n")
+    assert lines[0] == "-10 True" and "NCCL" in lines[1] and lines[2] == "(768, 1000)"
+
+
+def test_runner_program_refuses_more_gpus_than_visible(built, tmp_path):
+    """`SGEMM_NGPUS` beyond the visible devices is a request the program cannot serve: exit status 3 and a message,
+    before anything is opened (host-side failure path; needs no GPU)."""
+    import os, subprocess
+    from runner import api
+    cubin, toml = built.ensure("simt_64x64x16")
+    env = dict(os.environ, SGEMM_NGPUS="64")
+    ret = subprocess.run([str(api.RUNNER_PATH), cubin, toml, "64", "64", "64", "1", "1", "0"], capture_output=True, text=True, env=env)
+    assert ret.returncode == 3 and "more GPUs than" in ret.stderr and ret.stdout == ""
+    env = dict(os.environ, SGEMM_NGPUS="0")
+    ret = subprocess.run([str(api.RUNNER_PATH), cubin, toml, "64", "64", "64", "1", "1", "0"], capture_output=True, text=True, env=env)
+    assert ret.returncode == 3
