@@ -17,6 +17,8 @@
 // Device status words written by a kernel that gave up on a bounded wait.
 //   status[0] = code (0 ok, 1 a bounded wait ran out)   status[1] = role/barrier tag
 //   status[2] = tile index   status[3] = k-block   status[4] = block index   status[5] = parity waited for
+// Behind them, status[8..9] and status[10..11] are two 64-bit sums kept by the tensor-core GEMM kernels: SM cycles and
+// nanoseconds that block 0 of each launch ran for (their quotient is the SM clock the launches really had).
 #define SGEMM_STATUS_WORDS 8
 #define SGEMM_STATUS_OK 0u
 #define SGEMM_STATUS_TIMEOUT 1u

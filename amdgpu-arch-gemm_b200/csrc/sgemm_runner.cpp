@@ -74,7 +74,8 @@ Driver &driver() {
 
 thread_local std::string g_open_error;
 
-constexpr int kStatusWords = 8;
+constexpr int kStatusWords = 8;    // what a kernel that gave up reports
+constexpr int kStatusAlloc = 16;   // ... followed by the tensor kernels' stopwatch: 64-bit sums of SM cycles and nanoseconds
 constexpr uint32_t kCounterWords = 64;
 constexpr int kVariantSimt = 0, kVariantTensor = 1;
 
@@ -906,8 +907,8 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
         fail(h, SGEMM_ERR_CUDA, "cannot opt in to %d bytes of dynamic shared memory: %s", cfg.dynamic_smem_bytes, cu_text(r).c_str());
         return bail(SGEMM_ERR_CUDA);
     }
-    if ((r = d.cuMemAlloc_(&h->status, kStatusWords * 4)) != CUDA_SUCCESS ||
-        (r = d.cuMemsetD8_(h->status, 0, kStatusWords * 4)) != CUDA_SUCCESS ||
+    if ((r = d.cuMemAlloc_(&h->status, kStatusAlloc * 4)) != CUDA_SUCCESS ||
+        (r = d.cuMemsetD8_(h->status, 0, kStatusAlloc * 4)) != CUDA_SUCCESS ||
         (r = d.cuMemAlloc_(&h->counters, (size_t)kCounterWords * 4)) != CUDA_SUCCESS ||
         (r = d.cuMemsetD8_(h->counters, 0, (size_t)kCounterWords * 4)) != CUDA_SUCCESS) {
         fail(h, SGEMM_ERR_CUDA, "cannot allocate the status buffer: %s", cu_text(r).c_str());
@@ -1231,6 +1232,17 @@ SGEMM_API int sgemm_get_info(sgemm_handle *h, const char *key, int64_t *value) {
     else if (k == "comm_rank") *value = h->comm.comm ? h->comm.rank : -1;
     else if (k == "comm_world") *value = h->comm.comm ? h->comm.world : 0;
     else if (k == "workspace_bytes") *value = (int64_t)(h->ws_lent ? h->ws_lent_bytes : h->ws_owned_bytes);
+    else if (k == "sm_khz_effective") {
+        // SM clock the tensor-kernel launches since the last read really ran at: cycles / nanoseconds as counted by
+        // block 0 of each launch (0: no such launch).  Synchronises; clears the two sums.
+        CtxGuard guard(h);
+        Driver &d = driver();
+        uint64_t sums[2] = {0, 0};
+        CU_CHECK(h, d.cuCtxSynchronize_());
+        CU_CHECK(h, d.cuMemcpyDtoH_(sums, h->status + kStatusWords * 4, sizeof sums));
+        CU_CHECK(h, d.cuMemsetD8_(h->status + kStatusWords * 4, 0, sizeof sums));
+        *value = sums[1] ? (int64_t)((double)sums[0] / (double)sums[1] * 1e6) : 0;
+    }
     else if (k == "profile_count") *value = (int64_t)h->prof_used;
     else if (k == "profile_main_ns") {  // total device time of the bracketed main-kernel launches; resets the tally
         CtxGuard guard(h);

@@ -433,6 +433,17 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
     sgemm_launch_dependents();
     sgemm_grid_dependency_wait();
 
+    // Stopwatch: one thread of a warp that has no other work (warp 2 of block 0) reads the SM's cycle counter and the
+    // global nanosecond timer here and again at the end, and adds both differences to status[8..11] (two 64-bit sums
+    // the host reads and clears).  cycles / ns is the SM clock this launch really ran at — the number a clock sampled
+    // from outside only approximates for launches of a few milliseconds.
+    const bool stopwatch = blockIdx.x == 0 && threadIdx.x == 64;
+    uint64_t watch_clk = 0, watch_ns = 0;
+    if (stopwatch) {
+        watch_clk = (uint64_t)clock64();
+        watch_ns = tc_globaltimer();
+    }
+
     // Register hand-over between warp groups (each scheduler partition holds one warp of every group): the groups
     // without a running sum shrink to TC_REGS_SMALL registers per thread, the epilogue groups grow to TC_REGS_EPI.
     // The counts add up to no more than a partition owns (checked above), so a growing group never waits for more
@@ -825,6 +836,10 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
     }
 
     // teardown: every thread gets here on both the normal and the abort path
+    if (stopwatch) {
+        atomicAdd(reinterpret_cast<unsigned long long *>(status + SGEMM_STATUS_WORDS), (unsigned long long)((uint64_t)clock64() - watch_clk));
+        atomicAdd(reinterpret_cast<unsigned long long *>(status + SGEMM_STATUS_WORDS + 2), (unsigned long long)(tc_globaltimer() - watch_ns));
+    }
     tc_fence_before();
 #if TC_CTA_GROUP == 2
     tc_cluster_sync();   // neither CTA may release TMEM or exit while the other can still reach into it

@@ -124,27 +124,72 @@ def build_all(force: bool = True, jobs: int = 0) -> Dict[str, Tuple[str, str]]:
     return dict(zip(REGISTRY, results))
 
 
-def recommend(m: int, n: int, k: int) -> str:
-    """Registered kernel that measured best for a problem of this shape on a B200 (NN layout).
+TUNED_TABLE = Path(__file__).resolve().parent / "tuner" / "tuned.json"
+
+
+def _registered_like(entry) -> str | None:
+    """Registered NN kernel with the structure of a tuner-table entry (tile, k per stage, stages, cluster, split
+    placement, operand type); the rasterisation width may differ."""
+    want_type = {"fp32": DataType.FP32, "fp16": DataType.FP16, "bf16": DataType.BF16}[entry["operands"]]
+    for name, (factory, _) in REGISTRY.items():
+        try:
+            cfg = factory()
+        except RuntimeError:
+            continue
+        if cfg.trans_a or cfg.trans_b or cfg.a_type != want_type or cfg.variant != entry["variant"]:
+            continue
+        if (list(cfg.tile_size), cfg.depth_k, list(cfg.wave_group)) != (entry["tile"], entry["depth_k"], entry["cluster"]):
+            continue
+        if cfg.variant == "tcgen05_3xtf32" and (cfg.stages != entry["stages"] or getattr(cfg, "split", "prepass") != entry["split"]
+                                                or getattr(cfg, "a_major", "mn") == "k" or getattr(cfg, "terms", 3) != (3 if want_type == DataType.FP32 else 1)
+                                                or getattr(cfg, "epilogue_warps", 8) != 8):
+            continue
+        return name
+    return None
+
+
+def recommend(m: int, n: int, k: int, operands: str = "fp32") -> str:
+    """Registered kernel to use for a problem of this shape on a B200 (NN layout).
 
     A handle serves one cubin, so choosing between configurations is the caller's (or the tuner's) job, as in the
-    reference where the tuner picks one configuration per problem size.  The rules condense the sweeps recorded in
-    the design notes:
-      * tiny problems: the FFMA kernel (launch-latency bound either way, and no pre-pass);
-      * few flops per byte of A and B (a skinny M or N with a long K): small tiles with the in-kernel split — the
-        default cubin switches to its companion kernel of this kind by itself, so it is returned here as well;
-      * small problems (below 2^33 flop): the default cubin again, whose companion kernel (128 x 128 tiles, no
-        pre-pass launch) the runner picks for them by itself;
-      * larger problems with fewer than half a wave of 256 x 256 tiles: 128 x 128 tiles so that more SMs get work;
-      * everything else: CTA pairs on 256 x 256 tiles with the split pre-pass.
+    reference where the tuner picks one configuration per problem size.  Two sources, in this order:
+
+      * shapes the runner handles inside the default cubin get the default cubin — tiny problems (its FFMA kernel),
+        few flops per byte of A and B or fewer than 2^33 flop (its companion kernels: no pre-pass launch);
+      * otherwise the tuner's table (``tuner/tuned.json``, written by ``sgemm_tuner.py --summarise`` from measured
+        sweeps): the entry of the same operand type whose problem is nearest in log2 distance, within a factor of two
+        in every dimension, if a registered kernel has its structure;
+      * otherwise rules condensed from the sweeps: fewer than half a wave of 256 x 256 tiles -> 128 x 128 tiles so
+        that more SMs get work; everything else -> CTA pairs on 256 x 256 tiles with the split pre-pass.
     """
+    import json
+    import math
+
     flops = 2.0 * m * n * k
-    if flops < 2 ** 27:
-        return DEFAULT_SIMT
-    if flops / (4.0 * (m * k + k * n)) < 200.0:
-        return DEFAULT_TENSOR if min(m, n) < 256 else "tc2i_256x256x32_s3"
-    if flops < 2 ** 33:
-        return DEFAULT_TENSOR
+    if operands == "fp32":
+        if flops < 2 ** 27:
+            return DEFAULT_SIMT
+        if flops / (4.0 * (m * k + k * n)) < 200.0:
+            return DEFAULT_TENSOR if min(m, n) < 256 else "tc2i_256x256x32_s3"
+        if flops < 2 ** 33:
+            return DEFAULT_TENSOR
+    try:
+        entries = json.loads(TUNED_TABLE.read_text())["entries"]
+    except (OSError, ValueError, KeyError):
+        entries = []
+    nearest = None
+    for e in entries:
+        if e["operands"] != operands or e["variant"] != "tcgen05_3xtf32":
+            continue
+        steps = [abs(math.log2(x / y)) for x, y in ((m, e["m"]), (n, e["n"]), (k, e["k"]))]
+        if max(steps) <= 1.0 and (nearest is None or sum(steps) < nearest[0]):
+            nearest = (sum(steps), e)
+    if nearest is not None:
+        name = _registered_like(nearest[1])
+        if name is not None:
+            return name
+    if operands != "fp32":
+        return "bf16_tc2_256x256x64_s6" if operands == "bf16" else "fp16_tc_128x128x64_s4"
     if -(-m // 256) * -(-n // 256) < 37:
         return "tc_128x128x32_s3"
     return DEFAULT_TENSOR

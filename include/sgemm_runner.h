@@ -230,6 +230,8 @@ int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value);
  * "skinny_acc_chain" (the chains the main and the companion tensor kernel were generated with),
  * "launches" (kernel launches issued so far), "tile_m", "tile_n", "sm_count", "workspace_bytes",
  * "comm_rank" / "comm_world" (-1 / 0 without a communicator),
+ * "sm_khz_effective" (SM clock the tensor-kernel launches since the last read of this key really ran at, counted on
+ * the device as SM cycles per nanosecond of block 0; 0 without such a launch; synchronises and clears the tally),
  * "profile_count" (bracketed launches since the last read), "profile_main_ns" (their summed device time in
  * nanoseconds; synchronises on them and resets the tally). */
 int sgemm_get_info(sgemm_handle *h, const char *key, int64_t *value);

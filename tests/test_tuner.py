@@ -46,7 +46,7 @@ def test_tune_picks_best_and_resumes(tmp_path, monkeypatch, capsys):
     monkeypatch.setattr(t, "SUPPORTED_WGM", [4])
     monkeypatch.setattr(t, "SUPPORTED_SPLIT", ["prepass"])
     out = tmp_path / "out"
-    best = t.tune(512, 512, 512, runner, str(out), include_simt=False)
+    best = t.tune(512, 512, 512, runner, str(out), include_simt=False, exhaustive=True)
     assert best["gflops"] == 103 and best["stages"] == 3 and best["tile"] == [256, 256]
     log = [json.loads(l) for l in (out / "tuner_results.jsonl").read_text().splitlines()]
     assert [r["stages"] for r in log] == [2, 3]
@@ -54,9 +54,13 @@ def test_tune_picks_best_and_resumes(tmp_path, monkeypatch, capsys):
     assert "Best: 103.0 Gflops" in text and "MT: (256, 256)" in text
     # resume: nothing is measured again (a runner that fails would be noticed)
     failing = fake_runner(tmp_path, "exit 3\n")
-    again = t.tune(512, 512, 512, failing, str(out), include_simt=False)
+    again = t.tune(512, 512, 512, failing, str(out), include_simt=False, exhaustive=True)
     assert again["gflops"] == 103
     assert len((out / "tuner_results.jsonl").read_text().splitlines()) == 2
+    # the staged search (the default) reuses the log as well: every point it asks for was measured with 50 runs
+    staged = t.tune(512, 512, 512, failing, str(out), include_simt=False)
+    assert staged["gflops"] == 103 and len((out / "tuner_results.jsonl").read_text().splitlines()) == 2
+    assert "staged search" in capsys.readouterr().out
 
 
 def test_runner_failure_is_recorded_not_fatal(tmp_path, monkeypatch, capsys):
@@ -86,3 +90,79 @@ def test_sixteen_bit_search_space():
         built += 1
         assert cfg.a_type == DataType.BF16 and cfg.mfma[3] == 16 and cfg.terms == 1
     assert built > 20 and all(k.startswith("tensor bf16 ") for k in keys) and len(set(keys)) == len(keys)
+
+
+# ------------------------------------------------------------------ the staged search replayed on recorded sweeps
+def recorded_points(path):
+    """(records, points) of a result file of an exhaustive sweep on a B200: the points are rebuilt from the records
+    (structure -> configuration, recorded rasterisation widths / prefetch depths -> variations, default one first)."""
+    from generator.generator import DataType, GemmSolutionConfig, GemmOptimizations
+    F = DataType.FP32
+    recs = [json.loads(l) for l in open(path)]
+    recs = [r for r in recs if not r.get("returncode")]
+    def canonical(key):     # the tuner's key order: structure (prefetch depth included), then the rasterisation width
+        words = key.split(" ", 1)[1].split()
+        return " ".join([w for w in words if not w.startswith("wgm")] + [w for w in words if w.startswith("wgm")])
+    by_key = {canonical(r["key"]): r for r in recs}
+    groups = {}
+    for r in recs:
+        words = r["key"].split(" ", 1)[1].split()
+        knobs = [w for w in words if w.startswith("wgm")]
+        structure = " ".join(w for w in words if w not in knobs)
+        groups.setdefault(structure, []).append((" " + " ".join(knobs), r))
+    points = []
+    for structure, members in groups.items():
+        r = members[0][1]
+        if r["variant"] == "simt_ffma":
+            wg = tuple(r["cluster"])
+            wt = (r["tile"][0] // wg[0], r["tile"][1] // wg[1])
+            config = GemmSolutionConfig(F, F, F, F, (1, 1, 1, 1), wg, wt, r["depth_k"], False, False)
+        else:
+            config = GemmSolutionConfig(F, F, F, F, (128, r["tile"][1], 1, 8), tuple(r["cluster"]), (1, 1), r["depth_k"], False, False,
+                                        vmem_stage=r["stages"] - 1, split=r.get("split") or "prepass")
+        default = lambda item: 0 if item[1]["wgm"] == 8 else 1
+        variations = [(suffix, (lambda rec=rec: GemmOptimizations(1, wgm=rec["wgm"], plr=rec["plr"]))) for suffix, rec in sorted(members, key=default)]
+        points.append((structure, config, variations))
+    return recs, by_key, points
+
+
+@pytest.mark.parametrize("name,m,n,k,shortlist", [("tuner_sweep_8192cubed_tensor", 8192, 8192, 8192, 12),
+                                                 ("tuner_sweep_1024cubed_tensor", 1024, 1024, 1024, 14),
+                                                 ("tuner_sweep_4096cubed_simt", 4096, 4096, 4096, 10)])
+def test_staged_search_finds_the_recorded_best_with_a_quarter_of_the_measurements(golden_dir, name, m, n, k, shortlist, capsys):
+    """Replay on sweeps recorded on a B200 (every point of a sub-space measured): the staged search — analytic ranking,
+    successive halving, then the rasterisation width on the two best — must end within 1 % of the best
+    recorded throughput while asking for at most a quarter of the measurements the exhaustive product made."""
+    recs, by_key, points = recorded_points(golden_dir / f"{name}.jsonl")
+    asked = []
+
+    def measure(key, config, opt, runs):
+        asked.append(key)
+        return by_key[key]
+
+    best, calls = t.staged_search(points, measure, m, n, k, shortlist=shortlist)
+    top = max(r["gflops"] for r in recs)
+    assert calls == len(asked) and calls <= 0.25 * len(recs), (calls, len(recs))
+    assert best["gflops"] >= 0.99 * top, (best["key"], best["gflops"], top)
+
+
+def test_analytic_ranking_orders_the_known_cases():
+    """What the sweeps showed, as inequalities the ranking must respect at 8192^3: CTA pairs on 256-column tiles
+    before single CTAs, 128-column tiles last; more k in flight before less; and a last wave that is nearly empty
+    costs what it wastes."""
+    from generator.generator import tensor_config
+    e = lambda cfg, shape=(8192, 8192, 8192): t.predict_efficiency(cfg, *shape)
+    assert e(tensor_config(256, 32, 3, cluster=2)) > e(tensor_config(256, 32, 2)) > e(tensor_config(128, 32, 3))
+    assert e(tensor_config(256, 32, 3, cluster=2)) > e(tensor_config(256, 32, 3, cluster=2, split="inkernel"))
+    assert e(tensor_config(256, 16, 6, cluster=2)) > e(tensor_config(256, 16, 2, cluster=2))
+    full, ragged = (2048, 9472, 4096), (2048, 9728, 4096)       # 8 x 37 = 296 tiles = 4 waves of 74 pairs; 8 x 38 = 304: 5 waves
+    assert e(tensor_config(256, 32, 3, cluster=2), full) > 1.15 * e(tensor_config(256, 32, 3, cluster=2), ragged)
+
+
+def test_summarise_writes_the_table_recommend_reads(golden_dir, tmp_path):
+    table = t.summarise([golden_dir / "tuner_sweep_8192cubed_tensor.jsonl", golden_dir / "tuner_sweep_4096cubed_simt.jsonl"],
+                        str(tmp_path / "tuned.json"))
+    entries = {(e["m"], e["variant"]): e for e in table["entries"]}
+    assert entries[(8192, "tcgen05_3xtf32")]["tile"] == [256, 256] and entries[(8192, "tcgen05_3xtf32")]["cluster"] == [2, 1]
+    assert entries[(4096, "simt_ffma")]["tile"] == [128, 128]
+    assert json.loads((tmp_path / "tuned.json").read_text()) == table
