@@ -229,10 +229,10 @@ bool tensor_eligible(const sgemm_handle *h, const void *a, const void *b, uint32
     // TMA: 16-byte aligned bases and row pitches that are multiples of 16 bytes
     const uint32_t per16 = 16 / h->elem_bytes;   // elements per 16 bytes
     if (h->elem_bytes != 4) {
-        // 16-bit operands: what is stored K-contiguous is read by TMA where it lies, the rest through packed copies
-        // (which have their own pitch and alignment)
-        if (h->cfg.trans_a && (((uintptr_t)a & 15) || (lda % per16) != 0)) return false;
-        if (!h->cfg.trans_b && (((uintptr_t)b & 15) || (ldb % per16) != 0)) return false;
+        // 16-bit operands are read by TMA where they lie, in either orientation; only an A that goes through a packed
+        // K-major copy (a_major = "k") has a pitch and an alignment of its own
+        if (!(h->cfg.a_kmajor && !h->cfg.trans_a) && (((uintptr_t)a & 15) || (lda % per16) != 0)) return false;
+        if (((uintptr_t)b & 15) || (ldb % per16) != 0) return false;
         return true;
     }
     if (((uintptr_t)a & 15) || ((uintptr_t)b & 15)) return false;
@@ -283,7 +283,7 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
     if (h->elem_bytes != 4 && (!eligible || h->force_variant == 2 || h->force_variant == 3))
         return fail(h, SGEMM_ERR_UNSUPPORTED, "16-bit operands run on the tensor-core kernel only: %s",
                     eligible ? "no FFMA or companion kernel exists for them"
-                             : "an operand stored K-contiguous must be 16-byte aligned with a leading dimension that is a multiple of 8");
+                             : "operands must be 16-byte aligned with leading dimensions that are multiples of 8");
     if (h->force_variant == 3) {
         if (!eligible || !h->tk_skinny.fn)
             return fail(h, SGEMM_ERR_UNSUPPORTED, "companion tensor kernel forced but %s",
@@ -347,11 +347,10 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
         // pitch ldb, or, transposed, N x K with pitch ldb)
         p->span_b = h->cfg.trans_b ? (uint64_t)ldb * (k - 1) + n : (uint64_t)ldb * (n - 1) + k;
         if (h->elem_bytes != 4) {
-            // 16-bit operands: no lo copies; an untransposed A is read from a K-major packed copy
+            // 16-bit operands: no lo copies; with a_major = "k" an untransposed A is read from a K-major packed copy
             p->span_a = p->span_b = 0;
             p->ldt = (uint32_t)round_up(k, 8);
-            if (!h->cfg.trans_a) { p->hi_a_off = off; off += round_up((size_t)p->ldt * m * 2, 256); }
-            if (h->cfg.trans_b) { p->hi_b_off = off; off += round_up((size_t)p->ldt * n * 2, 256); }
+            if (tk->a_packed && !h->cfg.trans_a) { p->hi_a_off = off; off += round_up((size_t)p->ldt * m * 2, 256); }
         } else if (tk->a_packed) {
             p->ldt = (uint32_t)round_up(k, 4);
             p->hi_a_off = off; off += round_up((size_t)p->ldt * m * 4, 256);
@@ -556,35 +555,30 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
         const CUtensorMap *ma_hi, *ma_lo, *mb_hi, *mb_lo;
         const uint32_t blocks = (uint32_t)h->sm_count * 4;
         if (h->elem_bytes != 4) {
-            // FP16 / BF16: both operands as K-major tiles of 64 k per 128-byte row (32 k and the 64-byte swizzle for
-            // depth_k = 32); A where it lies when it is stored K-contiguous, else from a packed copy made here
+            // FP16 / BF16.  An operand stored K-contiguous (A transposed, B untransposed) is a K-major tile of 64 k per
+            // 128-byte row (32 k and the 64-byte swizzle for depth_k = 32); one stored M- or N-contiguous is an MN-major
+            // tile in chunks of 64 rows of M (columns of N), bk rows of 128 bytes each, 128-byte swizzle.  Either way TMA
+            // reads it where it lies; only a_major = "k" goes through a packed K-major copy of A made here.
             const CUtensorMapDataType dt = h->cfg.a_type == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
             const uint32_t span16 = std::min<uint32_t>(bk, 64);
             const CUtensorMapSwizzle sw16 = span16 == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-            const void *a_src = dA;
-            uint64_t a_pitch = (uint64_t)lda * 2;
-            if (!h->cfg.trans_a) {
+            if (h->cfg.trans_a) {
+                rc = encode_map(h, 0, dA, k, m, (uint64_t)lda * 2, span16, 128, sw16, &ma_hi, dt);
+            } else if (tk.a_packed) {
                 void *packed = reinterpret_cast<void *>(ws + p.hi_a_off);
                 void *pp[] = {&dA, &lda, &m, &k, &packed, &p.ldt};
                 if (!h->reuse_a_lo) {
                     rc = launch(h, h->fn_pack16, (m + 31) / 32, (k + 31) / 32, 1, 32, 8, 0, stream, pp);
                     if (rc) return rc;
                 }
-                a_src = packed;
-                a_pitch = (uint64_t)p.ldt * 2;
+                rc = encode_map(h, 0, packed, k, m, (uint64_t)p.ldt * 2, span16, 128, sw16, &ma_hi, dt);
+            } else {
+                rc = encode_map(h, 0, dA, m, k, (uint64_t)lda * 2, 64, bk, CU_TENSOR_MAP_SWIZZLE_128B, &ma_hi, dt);
             }
-            const void *b_src = dB;
-            uint64_t b_pitch = (uint64_t)ldb * 2;
-            if (h->cfg.trans_b) {   // B is stored N-contiguous: the same transposing copy, with N in the place of M
-                void *packed = reinterpret_cast<void *>(ws + p.hi_b_off);
-                void *pp[] = {&dB, &ldb, &n, &k, &packed, &p.ldt};
-                rc = launch(h, h->fn_pack16, (n + 31) / 32, (k + 31) / 32, 1, 32, 8, 0, stream, pp);
-                if (rc) return rc;
-                b_src = packed;
-                b_pitch = (uint64_t)p.ldt * 2;
-            }
-            if ((rc = encode_map(h, 0, a_src, k, m, a_pitch, span16, 128, sw16, &ma_hi, dt))) return rc;
-            if ((rc = encode_map(h, 2, b_src, k, n, b_pitch, span16, bn, sw16, &mb_hi, dt))) return rc;
+            if (rc) return rc;
+            if (h->cfg.trans_b) rc = encode_map(h, 2, dB, n, k, (uint64_t)ldb * 2, 64, bk, CU_TENSOR_MAP_SWIZZLE_128B, &mb_hi, dt);
+            else rc = encode_map(h, 2, dB, k, n, (uint64_t)ldb * 2, span16, bn, sw16, &mb_hi, dt);
+            if (rc) return rc;
             ma_lo = ma_hi;
             mb_lo = mb_hi;
         } else if (tk.a_packed) {

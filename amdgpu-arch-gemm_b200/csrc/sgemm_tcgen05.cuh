@@ -49,6 +49,9 @@
 //   With TC_A_KMAJOR the A operand is K-major — the caller's A is stored transposed (K contiguous), or
 //   packed copies made by sgemm_pack_a_kmajor are read — and uses B's layout.  With TC_B_MNMAJOR the
 //   caller's B is stored transposed (N contiguous) and uses A's MN-major layout (32-column chunks).
+//   16-bit operands (TC_ELEM_BYTES = 2) use the same two layouts with twice the elements per 128-byte row:
+//   K-major rows of 64 k, MN-major chunks of 64 rows of M (or columns of N) with the ordinary 128-byte swizzle
+//   of 16-byte units (repeating unit 8 rows: SBO = 1024 B; one K=16 MMA step spans two units, 2048 B).
 //
 // TC_CTA_GROUP = 2 pairs two CTAs (a 2x1 cluster, two neighbouring SMs) on one 256 x TC_BN tile with
 // tcgen05.mma.cta_group::2: CTA r of the pair loads rows 128r.. of the A tile and columns (TC_BN/2)r.. of
@@ -142,7 +145,10 @@ static_assert(TC_EPI_COLS % 32 == 0, "an epilogue warp drains whole 32-column ch
 #define TC_KSPAN (TC_BK * TC_ELEM_BYTES >= 128 ? 128 / TC_ELEM_BYTES : TC_BK)   // k per swizzled row of a K-major tile (128- or 64-byte rows)
 #define TC_KROW_BYTES (TC_KSPAN * TC_ELEM_BYTES)
 #define TC_KSUBS (TC_BK / TC_KSPAN)            // K-major sub-tiles per stage
-#define TC_A_CHUNK_BYTES (TC_BK * 128)         // MN-major: 32 rows of M x TC_BK
+#define TC_MN_CHUNK (128 / TC_ELEM_BYTES)      // MN-major: rows of M (columns of N) per chunk = elements per 128-byte row
+#define TC_A_CHUNK_BYTES (TC_BK * 128)         // MN-major: TC_MN_CHUNK rows of M x TC_BK
+#define TC_MN_SBO (TC_ELEM_BYTES == 4 ? 512 : 1024)      // MN-major: bytes between the swizzle's repeating units along K
+#define TC_MN_STEP (TC_MMA_K * 128)            // MN-major: bytes one MMA's k extent spans
 #define TC_A_SUB_BYTES (TC_BM * TC_KROW_BYTES) // K-major : TC_BM rows x TC_KSPAN k
 #define TC_B_SUB_BYTES (TC_BN_CTA * TC_KROW_BYTES) // K-major : TC_BN_CTA rows x TC_KSPAN k
 #define TC_TMEM_COLS_NEEDED (2 * TC_BN)
@@ -152,11 +158,10 @@ static_assert(TC_EPI_COLS % 32 == 0, "an epilogue warp drains whole 32-column ch
 
 static_assert(TC_ELEM_BYTES == 4 || TC_ELEM_BYTES == 2, "FP32 or 16-bit operands");
 static_assert(TC_BK * TC_ELEM_BYTES == 64 || (TC_BK * TC_ELEM_BYTES) % 128 == 0, "k per stage: one 64-byte span or whole 128-byte swizzle spans");
-static_assert(TC_ELEM_BYTES == 4 || (TC_A_KMAJOR && !TC_B_MNMAJOR && TC_TERMS == 1 && !TC_SPLIT_INKERNEL),
-              "16-bit operands: K-major tiles only (A transposed or packed), one MMA per k-slice");
+static_assert(TC_ELEM_BYTES == 4 || (TC_TERMS == 1 && !TC_SPLIT_INKERNEL), "16-bit operands: one MMA per k-slice, no lo tiles");
 static_assert(!TC_SPLIT_INKERNEL || TC_TERMS == 3, "the in-kernel split makes the lo tiles of the 3xTF32 scheme");
 static_assert(TC_CTA_GROUP == 1 || TC_CTA_GROUP == 2, "one CTA or a CTA pair per tile");
-static_assert(!TC_B_MNMAJOR || (TC_BN / TC_CTA_GROUP) % 32 == 0, "MN-major B is staged in 32-column chunks");
+static_assert(!TC_B_MNMAJOR || (TC_BN / TC_CTA_GROUP) % TC_MN_CHUNK == 0, "MN-major B is staged in chunks of 128 bytes of N");
 static_assert(TC_BN % (16 * TC_CTA_GROUP) == 0 && TC_BN >= 16 * TC_CTA_GROUP && TC_BN <= 256, "UMMA N");
 static_assert(TC_SMEM_BYTES <= 232448, "shared memory budget of one CTA");
 
@@ -332,6 +337,7 @@ __device__ __forceinline__ uint32_t tc_chunk_count(uint32_t blocks, uint32_t chu
 #define TC_LAYOUT_SW64 4ull
 #define TC_LAYOUT_SW128_32B 1ull
 #define TC_LAYOUT_KMAJOR (TC_KROW_BYTES == 128 ? TC_LAYOUT_SW128 : TC_LAYOUT_SW64)
+#define TC_LAYOUT_MNMAJOR (TC_ELEM_BYTES == 4 ? TC_LAYOUT_SW128_32B : TC_LAYOUT_SW128)   // 32-bit MN-major needs 32-byte swizzle units
 #define TC_KMAJOR_SBO (8 * TC_KROW_BYTES)      // 8 rows of a K-major tile
 #define TC_KMAJOR_OFF(kk, sub_bytes) (((kk) / (TC_KSPAN / TC_MMA_K)) * (sub_bytes) + ((kk) % (TC_KSPAN / TC_MMA_K)) * 32)
 __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
@@ -507,13 +513,13 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                         tc_tma_load_2d_local(sa_hi + sub * TC_A_SUB_BYTES, &map_a_hi, own_full, k0 + TC_KSPAN * sub, m0);
 #else
 #pragma unroll
-                    for (int ch = 0; ch < TC_BM / 32; ++ch)
-                        tc_tma_load_2d_local(sa_hi + ch * TC_A_CHUNK_BYTES, &map_a_hi, own_full, m0 + 32 * ch, k0);
+                    for (int ch = 0; ch < TC_BM / TC_MN_CHUNK; ++ch)
+                        tc_tma_load_2d_local(sa_hi + ch * TC_A_CHUNK_BYTES, &map_a_hi, own_full, m0 + TC_MN_CHUNK * ch, k0);
 #endif
 #if TC_B_MNMAJOR
 #pragma unroll
-                    for (int ch = 0; ch < TC_BN_CTA / 32; ++ch)
-                        tc_tma_load_2d_local(sb_hi + ch * TC_A_CHUNK_BYTES, &map_b_hi, own_full, n0 + 32 * ch, k0);
+                    for (int ch = 0; ch < TC_BN_CTA / TC_MN_CHUNK; ++ch)
+                        tc_tma_load_2d_local(sb_hi + ch * TC_A_CHUNK_BYTES, &map_b_hi, own_full, n0 + TC_MN_CHUNK * ch, k0);
 #else
 #pragma unroll
                     for (int sub = 0; sub < TC_KSUBS; ++sub)
@@ -529,16 +535,16 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                     }
 #else
 #pragma unroll
-                    for (int ch = 0; ch < TC_BM / 32; ++ch) {
-                        tc_tma_load_2d(sa_hi + ch * TC_A_CHUNK_BYTES, &map_a_hi, full, m0 + 32 * ch, k0);
-                        if (TC_TERMS == 3) tc_tma_load_2d(sa_lo + ch * TC_A_CHUNK_BYTES, &map_a_lo, full, m0 + 32 * ch, k0);
+                    for (int ch = 0; ch < TC_BM / TC_MN_CHUNK; ++ch) {
+                        tc_tma_load_2d(sa_hi + ch * TC_A_CHUNK_BYTES, &map_a_hi, full, m0 + TC_MN_CHUNK * ch, k0);
+                        if (TC_TERMS == 3) tc_tma_load_2d(sa_lo + ch * TC_A_CHUNK_BYTES, &map_a_lo, full, m0 + TC_MN_CHUNK * ch, k0);
                     }
 #endif
 #if TC_B_MNMAJOR
 #pragma unroll
-                    for (int ch = 0; ch < TC_BN_CTA / 32; ++ch) {
-                        tc_tma_load_2d(sb_hi + ch * TC_A_CHUNK_BYTES, &map_b_hi, full, n0 + 32 * ch, k0);
-                        if (TC_TERMS == 3) tc_tma_load_2d(sb_lo + ch * TC_A_CHUNK_BYTES, &map_b_lo, full, n0 + 32 * ch, k0);
+                    for (int ch = 0; ch < TC_BN_CTA / TC_MN_CHUNK; ++ch) {
+                        tc_tma_load_2d(sb_hi + ch * TC_A_CHUNK_BYTES, &map_b_hi, full, n0 + TC_MN_CHUNK * ch, k0);
+                        if (TC_TERMS == 3) tc_tma_load_2d(sb_lo + ch * TC_A_CHUNK_BYTES, &map_b_lo, full, n0 + TC_MN_CHUNK * ch, k0);
                     }
 #else
 #pragma unroll
@@ -592,14 +598,14 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                             const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);
                             const uint64_t da_lo = tc_smem_desc(sa_lo + a_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);
 #else
-                            const uint32_t a_off = kk * 1024;
-                            const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
-                            const uint64_t da_lo = tc_smem_desc(sa_lo + a_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
+                            const uint32_t a_off = kk * TC_MN_STEP;
+                            const uint64_t da_hi = tc_smem_desc(sa_hi + a_off, TC_A_CHUNK_BYTES, TC_MN_SBO, TC_LAYOUT_MNMAJOR);
+                            const uint64_t da_lo = tc_smem_desc(sa_lo + a_off, TC_A_CHUNK_BYTES, TC_MN_SBO, TC_LAYOUT_MNMAJOR);
 #endif
 #if TC_B_MNMAJOR
-                            const uint32_t b_off = kk * 1024;
-                            const uint64_t db_hi = tc_smem_desc(sb_hi + b_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
-                            const uint64_t db_lo = tc_smem_desc(sb_lo + b_off, TC_A_CHUNK_BYTES, 512, TC_LAYOUT_SW128_32B);
+                            const uint32_t b_off = kk * TC_MN_STEP;
+                            const uint64_t db_hi = tc_smem_desc(sb_hi + b_off, TC_A_CHUNK_BYTES, TC_MN_SBO, TC_LAYOUT_MNMAJOR);
+                            const uint64_t db_lo = tc_smem_desc(sb_lo + b_off, TC_A_CHUNK_BYTES, TC_MN_SBO, TC_LAYOUT_MNMAJOR);
 #else
                             const uint32_t b_off = TC_KMAJOR_OFF(kk, TC_B_SUB_BYTES);
                             const uint64_t db_hi = tc_smem_desc(sb_hi + b_off, 16, TC_KMAJOR_SBO, TC_LAYOUT_KMAJOR);

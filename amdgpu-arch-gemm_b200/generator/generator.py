@@ -240,9 +240,10 @@ class GemmSolutionConfig:
     # ------------------------------------------------------------------ variant-specific checks
     def _check_tensor(self):
         if self.elem_bytes == 2:
-            # FP16 / BF16 operands: one kind::f16 MMA per 16 k (no split), K-major tiles only — an operand stored
-            # K-contiguous (A transposed, B untransposed) is read where it lies, the other way round through a packed
-            # K-major copy made by a pre-pass
+            # FP16 / BF16 operands: one kind::f16 MMA per 16 k (no split).  Every operand is read where it lies: stored
+            # K-contiguous (A transposed, B untransposed) as a K-major tile, stored M- or N-contiguous as an MN-major
+            # tile in chunks of 64 rows (128 bytes); a_major="k" instead reads an untransposed A through a packed
+            # K-major copy made by a pre-pass (the first implementation, kept for comparison)
             if self.split != "prepass":
                 raise RuntimeError("16-bit operands have no lo terms: split='inkernel' does not apply")
             if self.depth_k != 32 and self.depth_k % 64:
@@ -250,8 +251,6 @@ class GemmSolutionConfig:
                                    f"multiple of 64 (whole 128-byte spans)")
             self.terms = 1
             self.companion = False
-            if not self.trans_a:
-                self.a_major = "k"
         if self.wave_group not in ((1, 1), (2, 1)):
             raise RuntimeError(f"cluster shape {self.wave_group} is not implemented for the tensor variant "
                                f"(1x1: one CTA per tile, 2x1: a CTA pair on a 256-row tile)")
@@ -281,8 +280,9 @@ class GemmSolutionConfig:
             raise RuntimeError("split is 'prepass' or 'inkernel'")
         if self.trans_a and self.a_major == "k":
             raise RuntimeError("a transposed A is K-major already: a_major='k' (packed copy) does not apply")
-        if self.trans_b and self.elem_bytes == 4 and (bn // self.wave_group[0]) % 32:
-            raise RuntimeError("a transposed B is staged in 32-column chunks: tile N per CTA must be a multiple of 32")
+        if self.trans_b and (bn // self.wave_group[0]) % (128 // self.elem_bytes):
+            raise RuntimeError(f"a transposed B is staged in chunks of {128 // self.elem_bytes} columns (128 bytes): tile N per "
+                               f"CTA must be a multiple of that")
         if self.split == "inkernel" and self.a_major == "k":
             raise RuntimeError("the K-major packed copy of A is made by a pre-pass; it excludes split='inkernel'")
         # the running sum of chunked accumulation: tile N / (epilogue warps per lane quarter) registers per epilogue
@@ -508,7 +508,7 @@ def _tensor_defines(config: GemmSolutionConfig):
             ("TC_CTA_GROUP", config.wave_group[0]), ("TC_SPLIT_INKERNEL", 1 if config.split == "inkernel" else 0),
             ("TC_EPI_WARPS", config.epilogue_warps),
             ("TC_A_KMAJOR", 1 if (config.a_major == "k" or config.trans_a) else 0),
-            ("TC_B_MNMAJOR", 1 if (config.trans_b and config.elem_bytes == 4) else 0), ("TC_TERMS", config.terms),
+            ("TC_B_MNMAJOR", 1 if config.trans_b else 0), ("TC_TERMS", config.terms),
             ("TC_ELEM_BYTES", config.elem_bytes),
             ("TC_AB_FORMAT", {DataType.FP32: "2u", DataType.FP16: "0u", DataType.BF16: "1u"}[config.a_type]),
             ("TC_ACC_CHUNK", config.acc_chain // config.depth_k)]

@@ -51,8 +51,10 @@ REGISTRY = {
     "simt_128x128x16_nt": (lambda: simt_config(128, 128, 16, 8, 8, trans_b=True), dict(wgm=8)),
     "simt_64x64x16_tt": (lambda: simt_config(64, 64, 16, 4, 4, trans_a=True, trans_b=True), dict(wgm=4)),
     # FFMA SIMT kernels
-    # FP16 / BF16 operands (FP32 accumulate, C and D FP32): untransposed A through a packed K-major copy, or A^T as it lies
+    # FP16 / BF16 operands (FP32 accumulate, C and D FP32), every operand read where it lies in all four layouts;
+    # "_ak": an untransposed A through a packed K-major copy instead (the first implementation, kept for comparison)
     "bf16_tc2_256x256x64_s6": (lambda: tensor_config(256, 64, 6, cluster=2, ab_type=DataType.BF16), dict(wgm=8)),
+    "bf16_tc2_256x256x64_s6_ak": (lambda: tensor_config(256, 64, 6, cluster=2, ab_type=DataType.BF16, a_major="k"), dict(wgm=8)),
     "fp16_tc_128x128x64_s4": (lambda: tensor_config(128, 64, 4, ab_type=DataType.FP16), dict(wgm=8)),
     "bf16_tc_128x256x32_s4_tn": (lambda: tensor_config(256, 32, 4, trans_a=True, ab_type=DataType.BF16), dict(wgm=8)),
     "fp16_tc2_256x128x64_s4_tn": (lambda: tensor_config(128, 64, 4, cluster=2, trans_a=True, ab_type=DataType.FP16), dict(wgm=8)),

@@ -146,9 +146,13 @@ def test_tile_raster_model(nx, ny, wgm):
 
 def test_sixteen_bit_operand_types():
     """FP16 / BF16 A and B on the tensor variant (the reference has the type plumbing, FP32 only:
-    generator/generator.py:816-824): K-major tiles, one MMA per 16 k, no lo tiles, no companion kernel."""
+    generator/generator.py:816-824): operands read where they lie (K-major or MN-major tiles), one MMA per 16 k, no lo
+    tiles, no companion kernel."""
     cfg = g.tensor_config(256, 64, 4, cluster=2, ab_type=g.DataType.BF16)
-    assert cfg.variant == g.VARIANT_TENSOR and cfg.terms == 1 and cfg.a_major == "k" and cfg.companion_config() is None
+    assert cfg.variant == g.VARIANT_TENSOR and cfg.terms == 1 and cfg.a_major == "mn" and cfg.companion_config() is None
+    assert "#define TC_A_KMAJOR 0" in g.gemm(None, "gemm", "sm_100a", cfg, g.GemmOptimizations(1), ARGS())   # MN-major A as it lies
+    packed = g.tensor_config(256, 64, 4, cluster=2, ab_type=g.DataType.BF16, a_major="k")                    # ... or a packed copy
+    assert "#define TC_A_KMAJOR 1" in g.gemm(None, "gemm", "sm_100a", packed, g.GemmOptimizations(1), ARGS())
     assert cfg.lds_usage_bytes == 4 * (128 + 128) * 64 * 2 + 1024 + 256          # A and B tiles only, 2 bytes per element
     d = cfg.to_dict()
     assert (d["a_type"], d["b_type"], d["cd_type"], d["scalar_type"]) == (2, 2, 0, 0) and d["mfma"] == [128, 256, 1, 16]
@@ -157,8 +161,10 @@ def test_sixteen_bit_operand_types():
     assert "generated_gemm_wholek" in src and "generated_gemm_skinny" not in src
     tn = g.tensor_config(128, 32, 4, trans_a=True, ab_type=g.DataType.FP16)
     assert tn.a_major == "mn" and tn.to_dict()["a_type"] == 1     # a transposed A is K-major as it lies: no packed copy
-    tt = g.tensor_config(128, 64, 3, trans_a=True, trans_b=True, ab_type=g.DataType.BF16)   # B^T goes through a packed copy
-    assert "#define TC_B_MNMAJOR 0" in g.gemm(None, "gemm", "sm_100a", tt, g.GemmOptimizations(1), ARGS())
+    tt = g.tensor_config(128, 64, 3, trans_a=True, trans_b=True, ab_type=g.DataType.BF16)   # B^T: an MN-major tile as it lies
+    assert "#define TC_B_MNMAJOR 1" in g.gemm(None, "gemm", "sm_100a", tt, g.GemmOptimizations(1), ARGS())
+    with pytest.raises(RuntimeError):
+        g.tensor_config(64, 64, 3, cluster=2, trans_b=True, ab_type=g.DataType.BF16)          # 32 columns per CTA: less than a 64-column chunk
     for bad in (dict(split="inkernel"), dict(bk=16), dict(bk=48)):
         kw = dict(bn=128, bk=64, stages=3, ab_type=g.DataType.FP16)
         kw.update(bad)
