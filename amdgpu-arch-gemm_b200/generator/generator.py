@@ -431,6 +431,10 @@ class GemmSolutionConfig:
             "dynamic_smem_bytes": self.lds_usage_bytes if self.variant == VARIANT_TENSOR else 0,
             "tmem_columns": self.tmem_columns,
             "entry": KERNEL_ENTRY,
+            # optimisation knobs of the reference that are accepted for compatibility and change nothing in these
+            # kernels (so that a tuner log does not suggest they were searched): the epilogue register strategy and the
+            # schedule level only set defaults, the K-start stagger is refused because it changes the summation order
+            "knobs_without_effect": "gw level map_k_idx",
         }
         if self.variant == VARIANT_TENSOR:
             fb = simt_fallback_config(self.trans_a, self.trans_b)
