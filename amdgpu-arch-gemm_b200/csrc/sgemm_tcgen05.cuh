@@ -842,16 +842,16 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
     }
 
     // teardown: every thread gets here on both the normal and the abort path
-    if (stopwatch) {
-        atomicAdd(reinterpret_cast<unsigned long long *>(status + SGEMM_STATUS_WORDS), (unsigned long long)((uint64_t)clock64() - watch_clk));
-        atomicAdd(reinterpret_cast<unsigned long long *>(status + SGEMM_STATUS_WORDS + 2), (unsigned long long)(tc_globaltimer() - watch_ns));
-    }
     tc_fence_before();
 #if TC_CTA_GROUP == 2
     tc_cluster_sync();   // neither CTA may release TMEM or exit while the other can still reach into it
 #else
     __syncthreads();
 #endif
+    if (stopwatch) {   // all roles of this (persistent) block are done: the interval is the block's working life
+        atomicAdd(reinterpret_cast<unsigned long long *>(status + SGEMM_STATUS_WORDS), (unsigned long long)((uint64_t)clock64() - watch_clk));
+        atomicAdd(reinterpret_cast<unsigned long long *>(status + SGEMM_STATUS_WORDS + 2), (unsigned long long)(tc_globaltimer() - watch_ns));
+    }
     if (warp == 1) {
         if (*abort_flag) {
             // give copies and MMAs that may still be in flight time to land before TMEM is released

@@ -502,7 +502,30 @@ def main():
         # the result the host now holds must be the one the device path computed
         same = bool(torch.equal(hd, job.d.cpu()))
         same = bool(job.max_over_ranks(0.0 if same else 1.0) == 0.0)
+        # what the host side of the box sustains: the bytes every rank moved over its link per second, their sum, and —
+        # measured on rank 0 alone with all host cores while the GPUs are idle — a plain copy in host memory (read +
+        # write bytes), the ceiling all ranks' transfers share when the GPUs hang off one NUMA node
+        step_s = dt / e2e_steps
+        link_rank = ((M * K // world + K * n_local) * 4 + M * n_local * 4) / step_s * 1e-9
+        host_copy = None
+        job.barrier()
+        if rank == 0:
+            cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+            before = torch.get_num_threads()
+            torch.set_num_threads(cores)
+            src = torch.ones(1 << 28, dtype=torch.float32)
+            dst = torch.empty_like(src)
+            dst.copy_(src)
+            t1 = time.perf_counter()
+            for _ in range(3):
+                dst.copy_(src)
+            host_copy = 3 * 2 * src.numel() * 4 / (time.perf_counter() - t1) * 1e-9
+            torch.set_num_threads(before)
+            del src, dst
+        job.barrier()
         e2e = {"value": 2.0 * job.m * job.n_total * job.k / (dt / e2e_steps) * 1e-12, "unit": UNIT,
+               "host_link_gb_per_s_per_rank": link_rank, "host_link_gb_per_s_all_ranks": link_rank * world,
+               "host_memory_copy_gb_per_s": host_copy,
                "h2d_bytes_per_step": (M * K // world + K * n_local) * 4, "d2h_bytes_per_step": M * n_local * 4,
                "bytes_are": "per rank", "steps": e2e_steps, "host_result_equals_device_result": same,
                "path": ("sgemm_run_host_sharded (A uploaded in 1/N slices and completed by an all-gather over NVLink; "
