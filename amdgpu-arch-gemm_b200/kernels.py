@@ -40,6 +40,9 @@ REGISTRY = {
     "tc_128x128x16_s6_ak": (lambda: tensor_config(128, 16, 6, a_major="k"), dict(wgm=8)),
     # whole-K accumulation inside the tensor core (no chunking): the kernels the recorded device arithmetic is pinned with
     "tc_128x128x32_s3_1x": (lambda: tensor_config(128, 32, 3, terms=1, acc_chain=0), dict(wgm=8)),
+    # one MMA per k-slice on the raw FP32 words (plain TF32, a third of the tensor work, NOT FP32-accurate): the bench
+    # uses it as a probe of the TF32 tensor rate this pipeline reaches on the box at hand
+    "tc2_256x256x32_s6_1x": (lambda: tensor_config(256, 32, 6, cluster=2, terms=1, acc_chain=0), dict(wgm=8)),
     "tc2_256x256x32_s3_c0": (lambda: tensor_config(256, 32, 3, cluster=2, acc_chain=0), dict(wgm=8)),
     # transposed operands (TN: A stored K x M, NT: B stored N x K, TT: both)
     "tc2_256x256x32_s3_tn": (lambda: tensor_config(256, 32, 3, cluster=2, trans_a=True), dict(wgm=8)),

@@ -104,5 +104,5 @@ def test_half_kernels_refuse_what_they_cannot_serve(runner_of):
     with pytest.raises(Exception, match="tensor-core kernel only"):
         r.run_host(a, a, None, d, 64, 64, 64)
     r.set_option("force_variant", AUTO)
-    with pytest.raises(Exception, match="multiple of 8"):
+    with pytest.raises(Exception, match="multiples of 8"):
         r.run_host(np.zeros(68 * 64, dtype=np.uint16), np.zeros(68 * 64, dtype=np.uint16), None, d, 64, 64, 64, lda=64, ldb=68)
