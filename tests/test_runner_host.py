@@ -162,3 +162,29 @@ def test_runner_program_refuses_more_gpus_than_visible(built, tmp_path):
     env = dict(os.environ, SGEMM_NGPUS="0")
     ret = subprocess.run([str(api.RUNNER_PATH), cubin, toml, "64", "64", "64", "1", "1", "0"], capture_output=True, text=True, env=env)
     assert ret.returncode == 3
+
+
+def test_bench_reports_ncu_traffic_only_for_the_source_it_was_captured_on(built, tmp_path, monkeypatch):
+    """bench.py's `roofline.traffic` comes from the tracked record beside the profile summaries, which carries a hash
+    of the emitted kernel source: the figure is reported for exactly that source and shape, and a kernel that changed
+    since (or another shape) gets null instead of a stale number."""
+    import hashlib, importlib, json, sys
+    sys.path.insert(0, str(ROOT))
+    bench = importlib.import_module("bench")
+    cubin = tmp_path / "generated_gemm.cubin"
+    cu = tmp_path / "generated_gemm.cu"
+    cu.write_text("// kernel source v1\n")
+    record = tmp_path / "dram_traffic.json"
+    record.write_text(json.dumps({"k": {"shape": [8, 8, 8], "dram_bytes_per_launch": 123.0, "capture": "cmd",
+                                        "source_sha256": hashlib.sha256(cu.read_bytes()).hexdigest()}}))
+    monkeypatch.setattr(bench, "TRAFFIC_FILE", record)
+    assert bench.ncu_traffic("k", str(cubin), (8, 8, 8)) == (123.0, "cmd")
+    assert bench.ncu_traffic("k", str(cubin), (8, 8, 16))[0] is None
+    assert bench.ncu_traffic("other", str(cubin), (8, 8, 8))[0] is None
+    cu.write_text("// kernel source v2\n")
+    assert bench.ncu_traffic("k", str(cubin), (8, 8, 8)) == (None, "kernel source changed since the capture")
+    # the tracked record: the figure for the default kernel as generated today, or null when the kernel has changed since
+    real = json.loads((ROOT / "profiles" / "dram_traffic.json").read_text())
+    cubin_path, _ = built.ensure(built.DEFAULT_TENSOR)
+    value, _ = importlib.reload(bench).ncu_traffic(built.DEFAULT_TENSOR, cubin_path, real[built.DEFAULT_TENSOR]["shape"])
+    assert value in (None, real[built.DEFAULT_TENSOR]["dram_bytes_per_launch"])
