@@ -442,10 +442,12 @@ def main():
     status = r.last_status()
     n_local = job.n_local
 
-    # TF32 probe (outside every reported figure; taken right after the headline region, in the same thermal state): the same pipeline issuing ONE plain-TF32 MMA per
-    # k-slice instead of the three of the split.  A third of its rate is what the 3xTF32 kernel could reach on this box,
-    # in this thermal state, if the two extra MMAs cost nothing but pipe time — a ceiling measured with the bench's own
-    # harness, next to the one derived from the measured BF16 rate.
+    # TF32 probe (outside every reported figure; taken right after the headline region, in the same thermal state): the
+    # same pipeline issuing ONE plain-TF32 MMA per k-slice instead of the three of the split — the TF32 tensor rate this
+    # code reaches on this box, measured with the bench's own harness next to the peak derived from the BF16 figure.
+    # It is a yardstick, not a ceiling: plain TF32 needs three times the operand bytes per pipe clock (the split reuses
+    # each staged tile in two MMAs), which puts its stage ring at the shared-memory bandwidth limit, so the 3xTF32
+    # kernel keeps the pipe busier than a third of the probe would suggest.
     probe = None
     if args.tf32_probe and args.workload == "c3":
         try:
@@ -465,7 +467,10 @@ def main():
             pr.close()
             rate = 2.0 * job.m * n_local * job.k / (ns / cnt * 1e-9) * 1e-12
             probe = {"kernel": "tc2_256x256x32_s6_1x (one kind::tf32 MMA per k-slice, same tile and CTA pairs)", "launches": cnt,
-                     "tf32_tflops": rate, "third": rate / 3.0, "sm_mhz_counted_on_device": mhz or None}
+                     "tf32_tflops": rate, "third": rate / 3.0, "sm_mhz_counted_on_device": mhz or None,
+                     "frac_of_pipe_at_kernel_clock": (rate / (TF32_FLOPS_PER_CLK_SM * sm_count * mhz * 1e6 * 1e-12)) if mhz else None,
+                     "note": "plain TF32 stages 3x the operand bytes per pipe clock and is shared-memory bound: a third of "
+                             "its rate is a yardstick for the 3xTF32 kernel, not a ceiling"}
             job.step()          # D holds the probe's plain-TF32 product: recompute it before anything reads it
             torch.cuda.synchronize()
         except Exception as exc:   # noqa: BLE001 - the probe is informational

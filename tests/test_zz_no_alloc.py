@@ -132,3 +132,54 @@ def test_counts_the_aligned_copies_of_operands_tma_cannot_read(runner):
         r.sync()
         for p in (pa, pb, pd):
             r.dev_free(p)
+
+
+def test_on_another_gpu_it_touches_no_other_gpu_and_no_thread_state(built):
+    """A rank that works on GPU 1 must not grow a context on GPU 0 behind its back, and a caller that only uses this C
+    ABI has no "current device" for the entry point to switch or restore: the array's address is looked up with the
+    handle's own context pushed.  Checked in a fresh process (no other test has touched a GPU there): after two
+    allocation-free calls on GPU 1 that equal the allocating entry point's results, GPU 0 has no active primary context
+    in this process, GPU 1 has one, and the calling thread still has no current context.  Needs two GPUs."""
+    import subprocess, sys, textwrap
+    from pathlib import Path
+    from runner import api
+    if api.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    root = Path(__file__).resolve().parent.parent
+    cubin, toml = built.ensure(built.DEFAULT_TENSOR)
+    code = textwrap.dedent(f"""
+        import ctypes, importlib, sys
+        import numpy as np
+        sys.path.insert(0, {str(root)!r})
+        importlib.import_module("amdgpu-arch-gemm_b200")
+        from runner import api
+        from oracle import oracle
+        m, n, k = 256, 320, 1024
+        a, b, c = oracle.make_inputs(m, n, k, seed=31)
+        r = api.SgemmRunner({cubin!r}, {toml!r}, 1)
+        r.set_option("force_variant", 1)
+        bufs = [r.dev_alloc(x.nbytes) for x in (a, b, c)] + [r.dev_alloc(m * n * 4)]
+        for p, x in zip(bufs, (a, b, c)):
+            r.upload(p, x)
+        outs = []
+        for call in (r.launch, r.launch_noalloc, r.launch_noalloc):
+            r.memset(bufs[3], 0, m * n * 4)
+            call(bufs[0], bufs[1], bufs[2], bufs[3], m, n, k, alpha=1.0, beta=0.5)
+            d = np.empty(m * n, np.float32)
+            r.sync()
+            r.download(d, bufs[3])
+            outs.append(d.tobytes())
+        cuda = ctypes.CDLL("libcuda.so.1")
+        flags, active = ctypes.c_uint(), ctypes.c_int()
+        state = []
+        for dev in (0, 1):
+            assert cuda.cuDevicePrimaryCtxGetState(dev, ctypes.byref(flags), ctypes.byref(active)) == 0
+            state.append(active.value)
+        current = ctypes.c_void_p()
+        assert cuda.cuCtxGetCurrent(ctypes.byref(current)) == 0
+        print(outs[0] == outs[1] == outs[2], state, current.value)
+        r.close()
+    """)
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert out.stdout.strip().splitlines()[-1] == "True [0, 1] None"
