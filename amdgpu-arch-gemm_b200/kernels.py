@@ -57,7 +57,7 @@ REGISTRY = {
     # FP16 / BF16 operands (FP32 accumulate, C and D FP32), every operand read where it lies in all four layouts;
     # "_ak": an untransposed A through a packed K-major copy instead (the first implementation, kept for comparison)
     "bf16_tc2_256x256x64_s6": (lambda: tensor_config(256, 64, 6, cluster=2, ab_type=DataType.BF16), dict(wgm=8)),
-    "bf16_tc2_256x256x128_s3": (lambda: tensor_config(256, 128, 3, cluster=2, ab_type=DataType.BF16), dict(wgm=8)),   # fastest measured at 8192^3
+    "bf16_tc2_256x256x128_s3": (lambda: tensor_config(256, 128, 3, cluster=2, ab_type=DataType.BF16), dict(wgm=16)),   # the tuner's best at 8192^3
     "bf16_tc2_256x256x64_s6_ak": (lambda: tensor_config(256, 64, 6, cluster=2, ab_type=DataType.BF16, a_major="k"), dict(wgm=8)),
     "fp16_tc_128x128x64_s4": (lambda: tensor_config(128, 64, 4, ab_type=DataType.FP16), dict(wgm=8)),
     "bf16_tc_128x256x32_s4_tn": (lambda: tensor_config(256, 32, 4, trans_a=True, ab_type=DataType.BF16), dict(wgm=8)),

@@ -369,6 +369,8 @@ def summarise(paths, table_path: str) -> dict:
         for rec in load_done(Path(path)).values():
             if rec.get("returncode") or "gflops" not in rec:
                 continue
+            if rec.get("runs", 50) < 20:
+                continue   # a first-round measurement of the staged search: a few launches at burst clocks, not comparable
             problem, _, rest = rec["key"].partition(" ")
             words = rest.split()
             operand = words[1] if len(words) > 1 and words[1] in ("bf16", "fp16") else "fp32"

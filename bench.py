@@ -585,6 +585,7 @@ def main():
             c5["parity"] = big.parity(args.parity_columns)
         big.free()
     status2 = r.last_status()
+    failed = False
 
     if rank == 0:
         # roofline of the dominant kernel (generated_gemm): algorithmic flops of one launch / its mean duration.
@@ -642,9 +643,19 @@ def main():
                                     "sample": f"{cols} of 8192 columns of the same problem, {dt:.1f} s of CPU work",
                                     "reference_loop_order_one_thread": cpu_reference_order(oracle)}
         print(json.dumps(line), flush=True)
+        # a number next to a wrong result is worth nothing: the line is printed for the record, the run fails
+        wrong = [name for name, bad in (("parity", parity is not None and not parity["ok"]),
+                                        ("c5 parity", bool(c5 and c5.get("parity")) and not c5["parity"]["ok"]),
+                                        ("e2e result differs from the device result", bool(e2e) and not e2e["host_result_equals_device_result"]),
+                                        ("device status", max(status[0], status2[0]) != 0)) if bad]
+        if wrong:
+            print("bench.py: FAILED checks: " + ", ".join(wrong), file=sys.stderr, flush=True)
+            failed = True
     r.close()
     if world > 1:
         dist.destroy_process_group()
+    if failed:
+        raise SystemExit(3)
 
 
 if __name__ == "__main__":
