@@ -58,6 +58,7 @@ REGISTRY = {
     # "_ak": an untransposed A through a packed K-major copy instead (the first implementation, kept for comparison)
     "bf16_tc2_256x256x64_s6": (lambda: tensor_config(256, 64, 6, cluster=2, ab_type=DataType.BF16), dict(wgm=8)),
     "bf16_tc2_256x256x128_s3": (lambda: tensor_config(256, 128, 3, cluster=2, ab_type=DataType.BF16), dict(wgm=16)),   # the tuner's best at 8192^3
+    "fp16_tc2_256x256x128_s3": (lambda: tensor_config(256, 128, 3, cluster=2, ab_type=DataType.FP16), dict(wgm=16)),
     "bf16_tc2_256x256x64_s6_ak": (lambda: tensor_config(256, 64, 6, cluster=2, ab_type=DataType.BF16, a_major="k"), dict(wgm=8)),
     "fp16_tc_128x128x64_s4": (lambda: tensor_config(128, 64, 4, ab_type=DataType.FP16), dict(wgm=8)),
     "bf16_tc_128x256x32_s4_tn": (lambda: tensor_config(256, 32, 4, trans_a=True, ab_type=DataType.BF16), dict(wgm=8)),
@@ -195,7 +196,7 @@ def recommend(m: int, n: int, k: int, operands: str = "fp32") -> str:
         if name is not None:
             return name
     if operands != "fp32":
-        return "bf16_tc2_256x256x128_s3" if operands == "bf16" else "fp16_tc_128x128x64_s4"
+        return "bf16_tc2_256x256x128_s3" if operands == "bf16" else "fp16_tc2_256x256x128_s3"
     if -(-m // 256) * -(-n // 256) < 37:
         return "tc_128x128x32_s3"
     return DEFAULT_TENSOR

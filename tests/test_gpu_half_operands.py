@@ -40,7 +40,7 @@ def stored16(flat_bits, rows, cols, transposed, ld):
     return out
 
 
-KERNELS = ["bf16_tc2_256x256x64_s6", "bf16_tc2_256x256x128_s3", "bf16_tc2_256x256x64_s6_ak", "fp16_tc_128x128x64_s4", "bf16_tc_128x256x32_s4_tn", "fp16_tc2_256x128x64_s4_tn",
+KERNELS = ["bf16_tc2_256x256x64_s6", "bf16_tc2_256x256x128_s3", "fp16_tc2_256x256x128_s3", "bf16_tc2_256x256x64_s6_ak", "fp16_tc_128x128x64_s4", "bf16_tc_128x256x32_s4_tn", "fp16_tc2_256x128x64_s4_tn",
            "bf16_tc2_256x256x64_s6_tt", "fp16_tc_128x128x64_s4_nt"]
 
 
