@@ -97,6 +97,7 @@ struct Rank {
     void *da = nullptr, *db = nullptr, *dc = nullptr, *dd = nullptr;   // dd: the shard, or the full D with SGEMM_ALLGATHER
     void *da16 = nullptr, *db16 = nullptr;
     float ms = 0.f;
+    double sm_mhz = 0.0;   // SM clock the measured tensor-kernel launches ran at, counted on the device (0: no such launch)
     int rc = 0;
     uint32_t width() const { return n1 - n0; }
 };
@@ -277,10 +278,13 @@ int main(int argc, char **argv) {
     for (Rank &r : g_ranks)
         if ((rc = sgemm_dev_memset(r.h, r.dd, 0, (allgather ? nc : std::max<size_t>((size_t)r.width() * m, 1)) * 4)))
             return die(r.h, "result reset", rc);
+    int64_t khz = 0;
+    for (Rank &r : g_ranks) sgemm_get_info(r.h, "sm_khz_effective", &khz);   // clears the device-side stopwatch
     if ((rc = bench_all(env ? std::atoi(env) : 0, &ms))) return die(h, "measured run", rc);
     for (Rank &r : g_ranks) {
         uint32_t status[8];
         if ((rc = sgemm_last_status(r.h, status))) return die(r.h, "device status check", rc);
+        if (sgemm_get_info(r.h, "sm_khz_effective", &khz) == 0) r.sm_mhz = (double)khz * 1e-3;
     }
     int64_t variant = 0, split = 0;
     sgemm_get_info(h, "last_variant", &variant);
@@ -291,8 +295,8 @@ int main(int argc, char **argv) {
                                : variant == 1 ? "tcgen05 3xTF32" : variant == 3 ? "tcgen05 3xTF32 (companion)" : "SIMT FFMA";
     const char *variant_key = half ? (parsed.a_type == 2 ? "tcgen05_bf16" : "tcgen05_fp16")
                               : variant == 1 ? "tcgen05_3xtf32" : variant == 3 ? "tcgen05_3xtf32_companion" : "simt_ffma";
-    std::fprintf(stderr, "measured kernel: %s, split_k %lld, %.3f TFLOPS, %lld launches in total\n",
-                 variant_text, (long long)split, gflops(m, n, k, ms) * 1e-3, (long long)info);
+    std::fprintf(stderr, "measured kernel: %s, split_k %lld, %.3f TFLOPS, %lld launches in total, SM clock counted on the device %.0f MHz\n",
+                 variant_text, (long long)split, gflops(m, n, k, ms) * 1e-3, (long long)info, g_ranks[0].sm_mhz);
     std::string per_gpu_json = "[";
     if (ngpus > 1)
         std::fprintf(stderr, "%d GPUs, columns sharded in whole tiles of %lld: aggregate %.3f TFLOPS (time of the slowest GPU)\n",
@@ -301,10 +305,11 @@ int main(int argc, char **argv) {
         const Rank &r = g_ranks[i];
         const double tf = r.ms > 0 ? gflops(m, r.width(), k, r.ms) * 1e-3 : 0.0;
         if (ngpus > 1)
-            std::fprintf(stderr, "  GPU %d: columns [%u, %u), %.4f ms, %.3f TFLOPS\n", device + i, r.n0, r.n1, r.ms, tf);
-        char item[160];
-        std::snprintf(item, sizeof item, "%s{\"device\": %d, \"n0\": %u, \"n1\": %u, \"ms\": %.6f, \"tflops\": %.4f}",
-                      i ? ", " : "", device + i, r.n0, r.n1, r.ms, tf);
+            std::fprintf(stderr, "  GPU %d: columns [%u, %u), %.4f ms, %.3f TFLOPS, SM clock counted on the device %.0f MHz\n",
+                         device + i, r.n0, r.n1, r.ms, tf, r.sm_mhz);
+        char item[200];
+        std::snprintf(item, sizeof item, "%s{\"device\": %d, \"n0\": %u, \"n1\": %u, \"ms\": %.6f, \"tflops\": %.4f, \"sm_mhz\": %.1f}",
+                      i ? ", " : "", device + i, r.n0, r.n1, r.ms, tf, r.sm_mhz);
         per_gpu_json += item;
     }
     per_gpu_json += "]";
