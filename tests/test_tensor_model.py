@@ -101,3 +101,25 @@ def test_chunked_accumulation_is_what_keeps_same_signed_sums_accurate():
     assert ratio(tm.gemm(a_mat, b_mat, chain=0)) > 3.0
     assert ratio(tm.gemm(a_mat, b_mat, chain=128)) < 0.35
     assert ((tm.gemm(a_mat, b_mat, chain=0) - exact) < 0).all()     # the drift is toward zero, for every element
+
+
+def test_model_shows_why_the_accumulation_chain_is_128_and_not_longer():
+    """Same-signed inputs (nothing cancels) at K = 8192 in the bit-level model of the device arithmetic: one chain over
+    all of K misses the parity bound by an order of magnitude, chains of 128 k (the kernels' default) stay well inside
+    it, chains of 256 — which would halve the cost of the chain drains — already sit at the bound, and 512 is outside.
+    The oracle is the reference's FP32 CPU GEMM, the bound 1e-5 * sum|a||b| per element."""
+    import numpy as np
+    from oracle import oracle, tensor_model as tm
+    m, n, k = 32, 32, 8192
+    rng = np.random.default_rng(3)
+    a = rng.uniform(0, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(0, 1, (k, n)).astype(np.float32)
+    af, bf = np.ascontiguousarray(a.T).reshape(-1), np.ascontiguousarray(b.T).reshape(-1)     # column-major, flat
+    ref = oracle.gemm(af, bf, None, 1.0, 0.0, m, n, k)
+    bound = oracle.abs_bound(af, bf, m, n, k)
+    ratio = {}
+    for chain in (0, 128, 256, 512):
+        d = np.asarray(tm.gemm(a, b, chain=chain), dtype=np.float32)
+        ratio[chain] = oracle.worst_ratio(np.ascontiguousarray(d.T).reshape(-1), ref, bound)
+    assert ratio[0] > 10.0 and ratio[128] < 0.8 and 0.8 < ratio[256] and ratio[512] > 1.0, ratio
+    assert ratio[128] < ratio[256] < ratio[512]
