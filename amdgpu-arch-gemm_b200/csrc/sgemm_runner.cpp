@@ -104,6 +104,7 @@ struct TensorKernel {
     uint32_t group = 1;                         // CTAs per launch unit (2 = CTA pair)
     uint32_t threads = 0, smem = 0;
     bool split_inkernel = false;                // lo tiles made in the kernel: no pre-pass, no lo copies
+    bool split_hybrid = false;                  // ... only B's: A's lo copy still comes from the pre-pass
     bool a_packed = false;                      // A is read from K-major packed copies made by a pre-pass
     uint32_t acc_chain = 0;                     // k per accumulation chain the kernel was generated for (0: no register path)
 };
@@ -356,7 +357,7 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
             p->hi_a_off = off; off += round_up((size_t)p->ldt * m * 4, 256);
             p->lo_a_off = off; off += round_up((size_t)p->ldt * m * 4, 256);
             p->span_a = 0;
-        } else if (!tk->split_inkernel) {
+        } else if (!tk->split_inkernel || tk->split_hybrid) {
             p->span_a = h->cfg.trans_a ? (uint64_t)lda * (m - 1) + k : (uint64_t)lda * (k - 1) + m;
             p->lo_a_off = off; off += round_up(p->span_a * 4, 256);
         }
@@ -601,6 +602,17 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
             else rc = encode_map(h, 0, dA, m, k, (uint64_t)lda * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &ma_hi);
             if (rc) return rc;
             ma_lo = ma_hi;
+            if (tk.split_hybrid) {
+                // ... except A's lo copy, which the pre-pass writes (B's span is empty for it) and TMA loads
+                uint64_t span_a = h->reuse_a_lo ? 0 : p.span_a, none = 0;
+                const float *nb = nullptr;
+                float *nlo = nullptr;
+                void *ps[] = {&dA, &lo_a, &span_a, &nb, &nlo, &none};
+                if (span_a && (rc = launch(h, h->fn_split_lo, blocks, 1, 1, 256, 1, 0, stream, ps))) return rc;
+                if (h->cfg.trans_a) rc = encode_map(h, 1, lo_a, k, m, (uint64_t)lda * 4, kspan, 128, ksw, &ma_lo);
+                else rc = encode_map(h, 1, lo_a, m, k, (uint64_t)lda * 4, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, &ma_lo);
+                if (rc) return rc;
+            }
         } else if (h->cfg.trans_a) {
             // A is stored K-contiguous: it is the K-major operand as it lies, and so is its lo copy
             uint64_t span_a = h->reuse_a_lo ? 0 : p.span_a;
@@ -709,7 +721,7 @@ int config_from_toml(const char *path, sgemm_config *c, std::string *err) {
     c->dynamic_smem_bytes = t.get_int("dynamic_smem_bytes", &v) ? (int32_t)v : 0;
     c->stages = t.get_int("stages", &v) ? (int32_t)v : c->vmem_stage + 1;
     c->a_kmajor = (t.get_string("a_major", &s) && s == "k") ? 1 : 0;
-    c->split_inkernel = (t.get_string("split", &s) && s == "inkernel") ? 1 : 0;
+    c->split_inkernel = !t.get_string("split", &s) ? 0 : s == "inkernel" ? 1 : s == "hybrid" ? 2 : 0;
     std::vector<int64_t> fb;
     if (t.get_int_array("fallback_tile", &fb) && fb.size() == 3)
         for (int i = 0; i < 3; ++i) c->fallback_tile[i] = (int32_t)fb[i];
@@ -861,6 +873,7 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
     h->tk_main.group = (uint32_t)std::max(1, cfg.wave_group[0]);
     h->tk_main.threads = (uint32_t)cfg.num_threads; h->tk_main.smem = (uint32_t)cfg.dynamic_smem_bytes;
     h->tk_main.split_inkernel = cfg.split_inkernel != 0; h->tk_main.a_packed = cfg.a_kmajor != 0;
+    h->tk_main.split_hybrid = cfg.split_inkernel == 2;
     h->tk_main.acc_chain = (uint32_t)std::max(cfg.acc_chain, 0);
     if (cfg.variant == kVariantTensor && cfg.wholek_entry[0]) {
         h->tk_wholek = h->tk_main;

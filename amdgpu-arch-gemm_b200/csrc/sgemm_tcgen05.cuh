@@ -68,6 +68,9 @@
 // arrive on the stage's "ready" barrier, which the MMA issuer then waits on instead of "full".  In a CTA pair
 // "full" is then local to each CTA (each transforms what it loaded) and "ready" lives in the leader
 // (4 warps x 2 CTAs arrive).  Operand traffic from L2/HBM halves and no lo copies exist in global memory.
+// TC_SPLIT_HYBRID = 1 (with TC_SPLIT_INKERNEL) is the middle way: A's lo tile still comes from the pre-pass by TMA,
+// only B's lo tile is made by the transform warps — three quarters of the TMA traffic of the pre-pass scheme, half of
+// the transform traffic of the in-kernel scheme.
 //
 // Split-K (split_k > 1): every launch unit covers one K range of one tile and stores its raw partial to the
 // workspace; the host runs sgemm_splitk_reduce afterwards (fixed summation order, no atomics).
@@ -116,6 +119,9 @@
 #ifndef TC_SPLIT_INKERNEL
 #define TC_SPLIT_INKERNEL 0
 #endif
+#ifndef TC_SPLIT_HYBRID
+#define TC_SPLIT_HYBRID 0
+#endif
 #ifndef TC_EPI_WARPS
 #define TC_EPI_WARPS 4
 #endif
@@ -160,6 +166,7 @@ static_assert(TC_ELEM_BYTES == 4 || TC_ELEM_BYTES == 2, "FP32 or 16-bit operands
 static_assert(TC_BK * TC_ELEM_BYTES == 64 || (TC_BK * TC_ELEM_BYTES) % 128 == 0, "k per stage: one 64-byte span or whole 128-byte swizzle spans");
 static_assert(TC_ELEM_BYTES == 4 || (TC_TERMS == 1 && !TC_SPLIT_INKERNEL), "16-bit operands: one MMA per k-slice, no lo tiles");
 static_assert(!TC_SPLIT_INKERNEL || TC_TERMS == 3, "the in-kernel split makes the lo tiles of the 3xTF32 scheme");
+static_assert(!TC_SPLIT_HYBRID || TC_SPLIT_INKERNEL, "the hybrid split is the in-kernel pipeline with A's lo tile loaded by TMA");
 static_assert(TC_CTA_GROUP == 1 || TC_CTA_GROUP == 2, "one CTA or a CTA pair per tile");
 static_assert(!TC_B_MNMAJOR || (TC_BN / TC_CTA_GROUP) % TC_MN_CHUNK == 0, "MN-major B is staged in chunks of 128 bytes of N");
 static_assert(TC_BN % (16 * TC_CTA_GROUP) == 0 && TC_BN >= 16 * TC_CTA_GROUP && TC_BN <= 256, "UMMA N");
@@ -503,18 +510,23 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                     const uint32_t sb_lo = sb_hi + TC_B_BYTES;                       // (3xTF32 only)
                     const int32_t k0 = (int32_t)(kb * TC_BK);
 #if TC_SPLIT_INKERNEL
-                    // raw tiles only, reported to this CTA's own "full" barrier; the transform warps make the lo tiles
+                    // raw tiles only (hybrid: and A's lo tile), reported to this CTA's own "full" barrier; the transform warps
+                    // make the lo tiles (hybrid: B's)
                     (void)sa_lo; (void)sb_lo; (void)full;
                     const uint32_t own_full = bar_full + 8 * stage;
-                    tc_mbar_expect_tx(own_full, TC_A_BYTES + TC_B_BYTES);
+                    tc_mbar_expect_tx(own_full, (TC_SPLIT_HYBRID ? 2 : 1) * TC_A_BYTES + TC_B_BYTES);
 #if TC_A_KMAJOR
 #pragma unroll
-                    for (int sub = 0; sub < TC_KSUBS; ++sub)
+                    for (int sub = 0; sub < TC_KSUBS; ++sub) {
                         tc_tma_load_2d_local(sa_hi + sub * TC_A_SUB_BYTES, &map_a_hi, own_full, k0 + TC_KSPAN * sub, m0);
+                        if (TC_SPLIT_HYBRID) tc_tma_load_2d_local(sa_lo + sub * TC_A_SUB_BYTES, &map_a_lo, own_full, k0 + TC_KSPAN * sub, m0);
+                    }
 #else
 #pragma unroll
-                    for (int ch = 0; ch < TC_BM / TC_MN_CHUNK; ++ch)
+                    for (int ch = 0; ch < TC_BM / TC_MN_CHUNK; ++ch) {
                         tc_tma_load_2d_local(sa_hi + ch * TC_A_CHUNK_BYTES, &map_a_hi, own_full, m0 + TC_MN_CHUNK * ch, k0);
+                        if (TC_SPLIT_HYBRID) tc_tma_load_2d_local(sa_lo + ch * TC_A_CHUNK_BYTES, &map_a_lo, own_full, m0 + TC_MN_CHUNK * ch, k0);
+                    }
 #endif
 #if TC_B_MNMAJOR
 #pragma unroll
@@ -649,12 +661,16 @@ generated_gemm(const float *a, const float *b, const float *c, float *d,
                 float4 *a_dst = reinterpret_cast<float4 *>(generic_base + stage * TC_STAGE_BYTES + TC_A_BYTES);
                 const float4 *b_src = reinterpret_cast<const float4 *>(generic_base + stage * TC_STAGE_BYTES + 2 * TC_A_BYTES);
                 float4 *b_dst = reinterpret_cast<float4 *>(generic_base + stage * TC_STAGE_BYTES + 2 * TC_A_BYTES + TC_B_BYTES);
+#if !TC_SPLIT_HYBRID
 #pragma unroll 4
                 for (uint32_t i = t; i < TC_A_BYTES / 16; i += 32 * TC_XFORM_WARPS) {
                     float4 v = a_src[i];
                     v.x = sgemm_tf32_lo(v.x); v.y = sgemm_tf32_lo(v.y); v.z = sgemm_tf32_lo(v.z); v.w = sgemm_tf32_lo(v.w);
                     a_dst[i] = v;
                 }
+#else
+                (void)a_src; (void)a_dst;   // A's lo tile came from the pre-pass by TMA
+#endif
 #pragma unroll 4
                 for (uint32_t i = t; i < TC_B_BYTES / 16; i += 32 * TC_XFORM_WARPS) {
                     float4 v = b_src[i];

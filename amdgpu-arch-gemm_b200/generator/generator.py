@@ -203,8 +203,9 @@ class GemmSolutionConfig:
         # None: 128 when the running sum fits the register file, else 0; 0: all of K in one chain
         self.acc_chain = acc_chain
         self.split = split          # tensor variant: where lo = x - trunc_tf32(x) is made: "prepass" (a kernel writes
-                                    # A_lo, B_lo to global memory once per call) or "inkernel" (transform warps make the
-                                    # lo tiles in shared memory from the TMA-landed raw tiles)
+                                    # A_lo, B_lo to global memory once per call), "inkernel" (transform warps make the
+                                    # lo tiles in shared memory from the TMA-landed raw tiles) or "hybrid" (A_lo by the
+                                    # pre-pass, B's lo tile by the transform warps)
 
         for t in (a_type, b_type, cd_type, scalar_type):
             datatype_size(t)
@@ -276,18 +277,19 @@ class GemmSolutionConfig:
             self.epilogue_warps = 8 if bn % 64 == 0 else 4
         if self.epilogue_warps not in (4, 8) or (self.epilogue_warps == 8 and bn % 64):
             raise RuntimeError("epilogue_warps is 4, or 8 when tile N is a multiple of 64")
-        if self.split not in ("prepass", "inkernel"):
-            raise RuntimeError("split is 'prepass' or 'inkernel'")
+        if self.split not in ("prepass", "inkernel", "hybrid"):
+            raise RuntimeError("split is 'prepass', 'inkernel' or 'hybrid'")
         if self.trans_a and self.a_major == "k":
             raise RuntimeError("a transposed A is K-major already: a_major='k' (packed copy) does not apply")
         if self.trans_b and (bn // self.wave_group[0]) % (128 // self.elem_bytes):
             raise RuntimeError(f"a transposed B is staged in chunks of {128 // self.elem_bytes} columns (128 bytes): tile N per "
                                f"CTA must be a multiple of that")
-        if self.split == "inkernel" and self.a_major == "k":
-            raise RuntimeError("the K-major packed copy of A is made by a pre-pass; it excludes split='inkernel'")
+        if self.split != "prepass" and self.a_major == "k":
+            raise RuntimeError("the K-major packed copy of A is made by a pre-pass that also writes both lo copies; it "
+                               "excludes split='inkernel' and 'hybrid'")
         # the running sum of chunked accumulation: tile N / (epilogue warps per lane quarter) registers per epilogue
         # thread, next to about 72 others, for every thread of the block (one register allocation per kernel)
-        threads = 128 + 32 * self.epilogue_warps + (128 if self.split == "inkernel" else 0)
+        threads = 128 + 32 * self.epilogue_warps + (128 if self.split != "prepass" else 0)
         sum_regs = bn // (self.epilogue_warps // 4)
         # registers an epilogue thread can have: an even share of its scheduler partition's 512 per lane, or, with
         # 8 epilogue warps, what is left when the other warp groups shrink to 56 (the kernel's register hand-over)
@@ -349,7 +351,7 @@ class GemmSolutionConfig:
     def num_workitems(self) -> int:
         if self.variant == VARIANT_TENSOR:
             # first group of four warps (TMA, MMA, two spare) + epilogue warps (+ four transform warps for the in-kernel split)
-            return 128 + 32 * self.epilogue_warps + (128 if self.split == "inkernel" else 0)
+            return 128 + 32 * self.epilogue_warps + (128 if self.split != "prepass" else 0)
         bm, bn = self.tile_size
         tm, tn = self.simt_thread_tile
         return (bm // tm) * (bn // tn)
@@ -509,7 +511,8 @@ def _simt_defines(cfg: GemmSolutionConfig, opt: GemmOptimizations, entry: str):
 
 def _tensor_defines(config: GemmSolutionConfig):
     return [("TC_BN", config.tile_size[1]), ("TC_BK", config.depth_k), ("TC_STAGES", config.stages),
-            ("TC_CTA_GROUP", config.wave_group[0]), ("TC_SPLIT_INKERNEL", 1 if config.split == "inkernel" else 0),
+            ("TC_CTA_GROUP", config.wave_group[0]), ("TC_SPLIT_INKERNEL", 1 if config.split != "prepass" else 0),
+            ("TC_SPLIT_HYBRID", 1 if config.split == "hybrid" else 0),
             ("TC_EPI_WARPS", config.epilogue_warps),
             ("TC_A_KMAJOR", 1 if (config.a_major == "k" or config.trans_a) else 0),
             ("TC_B_MNMAJOR", 1 if config.trans_b else 0), ("TC_TERMS", config.terms),

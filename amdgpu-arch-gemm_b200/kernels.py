@@ -32,6 +32,7 @@ REGISTRY = {
     "tc2_256x128x32_s4": (lambda: tensor_config(128, 32, 4, cluster=2), dict(wgm=4)),
     # lo tiles made inside the kernel by transform warps (no pre-pass, no lo copies in global memory)
     "tc2i_256x256x32_s3": (lambda: tensor_config(256, 32, 3, cluster=2, split="inkernel"), dict(wgm=8)),
+    "tc2h_256x256x32_s3": (lambda: tensor_config(256, 32, 3, cluster=2, split="hybrid"), dict(wgm=8)),   # A_lo by the pre-pass, B's lo tile in the kernel
     "tc2i_256x256x16_s6": (lambda: tensor_config(256, 16, 6, cluster=2, split="inkernel"), dict(wgm=8)),
     "tci_128x256x32_s2": (lambda: tensor_config(256, 32, 2, split="inkernel"), dict(wgm=8)),
     "tci_128x128x32_s3": (lambda: tensor_config(128, 32, 3, split="inkernel"), dict(wgm=8)),

@@ -51,7 +51,7 @@ SUPPORTED_TILE_N = [128, 256]
 SUPPORTED_DEPTH_K = [16, 32, 64]
 SUPPORTED_DEPTH_K_16BIT = [32, 64, 128]   # 16-bit operands: 64-byte rows, or whole 128-byte rows of 64 k
 SUPPORTED_STAGES = [2, 3, 4, 5, 6, 7]
-SUPPORTED_SPLIT = ["prepass", "inkernel"]   # where the 3xTF32 lo terms are made
+SUPPORTED_SPLIT = ["prepass", "inkernel", "hybrid"]   # where the 3xTF32 lo terms are made (hybrid: A's by the pre-pass, B's in the kernel)
 # FFMA variant: (thread grid, per-thread tile, k per stage)
 SUPPORTED_SIMT = [((16, 16), (8, 8), 16), ((16, 16), (8, 8), 8), ((16, 8), (8, 8), 16), ((8, 16), (8, 8), 16),
                   ((16, 16), (8, 4), 16), ((16, 16), (4, 8), 16), ((32, 8), (4, 8), 16), ((16, 16), (4, 4), 16),
@@ -146,8 +146,10 @@ def predict_time_us(config: GemmSolutionConfig, m: int, n: int, k: int, sm_count
     k_unit = -(-kb_total // split) * config.depth_k
     clks_per_slice = terms * 2.0 * 128 * tn * mma_k / rate
     reads = terms * (128 + tn / cluster) * mma_k * elem / clks_per_slice          # bytes per clock the tensor core reads
-    inkernel = getattr(config, "split", "prepass") == "inkernel"
-    writes = reads * (1.0 if inkernel else (2.0 / 3.0 if terms == 3 else 1.0))    # TMA (+ transform warps) into the ring
+    placement = getattr(config, "split", "prepass")
+    inkernel = placement != "prepass"
+    # TMA (+ transform warps) into the ring: four tiles by TMA; two by TMA and two read + written by the warps; three + one
+    writes = reads * ({"prepass": 2.0 / 3.0, "inkernel": 1.0, "hybrid": 5.0 / 6.0}[placement] if terms == 3 else 1.0)
     smem_eff = min(1.0, SMEM_BYTES_PER_CLK / (reads + writes))
     k_in_flight = (config.stages - 1) * config.depth_k * elem / 4.0
     depth_eff = min(1.0, 0.55 + 0.45 * k_in_flight / 96.0)
@@ -159,8 +161,9 @@ def predict_time_us(config: GemmSolutionConfig, m: int, n: int, k: int, sm_count
     t = (waves * main_clks + fill_clks + store_clks) / (ghz * 1e3) + launch_us
     if cluster > 1:
         t += 4.0   # a cluster launch is scheduled pair by pair and synchronises cluster-wide at set-up and teardown
-    if terms == 3 and not inkernel:
-        t += launch_us + 2.0 * (m * k + k * n) * 4 / hbm_bytes_per_us              # the split pre-pass reads and writes A and B
+    if terms == 3 and placement != "inkernel":
+        prepass_elems = (m * k + k * n) if placement == "prepass" else m * k        # the split pre-pass reads and writes A and B (hybrid: A)
+        t += launch_us + 2.0 * prepass_elems * 4 / hbm_bytes_per_us
     if split > 1:
         t += launch_us + (split + 1) * m * n * 4 / hbm_bytes_per_us               # partial sums out and in again
     return t

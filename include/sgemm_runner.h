@@ -61,7 +61,7 @@ typedef struct sgemm_config {
     int32_t dynamic_smem_bytes;
     int32_t stages;
     int32_t a_kmajor;           /* tensor variant reads A from a K-major packed copy */
-    int32_t split_inkernel;     /* tensor variant makes the 3xTF32 lo tiles inside the kernel (no pre-pass) */
+    int32_t split_inkernel;     /* tensor variant: 1 = the kernel makes the 3xTF32 lo tiles itself (no pre-pass), 2 = only B's (A's lo copy by the pre-pass) */
     int32_t fallback_tile[3];
     int32_t fallback_threads;
     char entry[64];

@@ -12,7 +12,7 @@ TENSOR_KERNELS = ["tc_128x256x32_s2", "tc_128x128x32_s3", "tc_128x64x32_s4", "tc
                   "tc_128x256x16_s4", "tc_128x128x16_s7", "tc_128x128x16_s6_ak",
                   "tc2_256x256x32_s3", "tc2_256x256x16_s6", "tc2_256x128x32_s4",
                   "tc2i_256x256x32_s3", "tc2i_256x256x16_s6", "tci_128x256x32_s2", "tci_128x128x32_s3",
-                  "tc2_256x256x32_s3_e4"]
+                  "tc2_256x256x32_s3_e4", "tc2h_256x256x32_s3"]
 # (kernels built for transposed operands have their own tests below)
 SIMT_KERNELS = ["simt_128x128x16", "simt_128x128x16_t16x8", "simt_64x64x16", "simt_128x64x8_plr0", "legacy_32x32x2_1wave", "legacy_16x16x4_2x2x2x2"]
 AUTO, TENSOR, SIMT, SKINNY = 0, 1, 2, 3
@@ -104,7 +104,7 @@ SHAPES = [(1, 1, 1), (8, 8, 8), (32, 32, 32), (33, 65, 129), (127, 257, 513), (1
 
 @pytest.mark.parametrize("kernel", ["tc_128x256x32_s2", "tc_128x128x32_s3", "tc_128x64x64_s2", "tc_128x128x32_s3_ak",
                                     "tc_128x256x16_s4", "tc_128x128x16_s6_ak", "tc2_256x256x32_s3", "tc2_256x128x32_s4",
-                                    "tc2i_256x256x32_s3", "tc2i_256x256x16_s6", "tci_128x256x32_s2"])
+                                    "tc2i_256x256x32_s3", "tc2i_256x256x16_s6", "tci_128x256x32_s2", "tc2h_256x256x32_s3"])
 @pytest.mark.parametrize("mnk", SHAPES)
 @pytest.mark.parametrize("alpha,beta", [(1.0, 0.0), (0.5, -1.5)])
 def test_tensor_kernels_match_oracle(runner_of, kernel, mnk, alpha, beta):
@@ -349,7 +349,7 @@ def test_random_shapes_layouts_and_options(runner_of):
     # 80 seeded cases: random sizes (ragged on purpose), leading-dimension padding, alpha/beta, kernel and variant;
     # every one against the oracle, a few also for run-to-run bit equality
     rng = np.random.default_rng(20240607)
-    pool = ["tc2_256x256x32_s3", "tc_128x256x32_s2", "tc_128x128x16_s7", "tc2i_256x256x32_s3", "tc2_256x256x32_s3_tt",
+    pool = ["tc2_256x256x32_s3", "tc_128x256x32_s2", "tc_128x128x16_s7", "tc2i_256x256x32_s3", "tc2h_256x256x32_s3", "tc2_256x256x32_s3_tt",
             "tc2_256x256x32_s3_tn", "simt_128x128x16", "simt_64x64x16_tt", "legacy_32x32x2_1wave"]
     for case in range(80):
         kernel = pool[int(rng.integers(len(pool)))]
@@ -414,7 +414,8 @@ def test_transposed_leading_dimension_checks(runner_of):
 
 
 # ------------------------------------------------------------------------------------ pipelined host path
-@pytest.mark.parametrize("kernel,force", [("tc2_256x256x32_s3", AUTO), ("tc_128x128x32_s3_ak", TENSOR), ("simt_128x128x16", SIMT)])
+@pytest.mark.parametrize("kernel,force", [("tc2_256x256x32_s3", AUTO), ("tc_128x128x32_s3_ak", TENSOR), ("tc2h_256x256x32_s3", TENSOR),
+                                          ("simt_128x128x16", SIMT)])
 @pytest.mark.parametrize("beta,ldd", [(0.0, 0), (0.75, 2052)])
 def test_pipelined_host_call_equals_the_single_launch(runner_of, kernel, force, beta, ldd):
     # sgemm_run_host overlaps uploads, GEMM and downloads over column chunks for large problems; chunking must not

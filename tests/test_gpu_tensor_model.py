@@ -42,7 +42,7 @@ def test_hand_examples_on_the_device(runner_of):
 
 
 TENSOR_CASES = [("tc2_256x256x32_s3", TENSOR), ("tc2_256x256x32_s3_c0", TENSOR), ("tc_128x256x32_s2", TENSOR), ("tc_128x128x16_s7", TENSOR),
-                ("tc2i_256x256x32_s3", TENSOR), ("tc_128x128x32_s3_ak", TENSOR), ("tc2_256x256x32_s3_e4", TENSOR),
+                ("tc2i_256x256x32_s3", TENSOR), ("tc2h_256x256x32_s3", TENSOR), ("tc_128x128x32_s3_ak", TENSOR), ("tc2_256x256x32_s3_e4", TENSOR),
                 ("tc2_256x256x32_s3", SKINNY), ("tc2_256x256x32_s3_tt", TENSOR), ("tc2_256x256x32_s3_tn", TENSOR)]
 
 
