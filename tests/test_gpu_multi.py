@@ -63,21 +63,26 @@ def test_one_rank_communicator_equals_the_single_gpu_calls(built):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("mnk,beta", [((2048, 4096 + 96, 2048), 0.0),      # pipelined host path, ragged last shard
-                                      ((1000, 700, 520), 0.75),            # small: single launch per rank, ragged slices of A
-                                      ((512, 256, 1024), 0.0)])            # fewer tiles than ranks at world 8: empty shards
-def test_sharded_host_call_and_allgather_over_several_gpus(built, world, mnk, beta):
+@pytest.mark.parametrize("mnk,beta,kernel", [
+    ((2048, 4096 + 96, 2048), 0.0, None),                    # pipelined host path, ragged last shard
+    ((1000, 700, 520), 0.75, None),                          # small: single launch per rank, ragged slices of A
+    ((512, 256, 1024), 0.0, None),                           # fewer tiles than ranks at world 8: empty shards
+    ((1024, 2048, 1000), 0.5, "tc2_256x256x32_s3_tn")])      # A stored transposed (K x M): its slices are cut along M
+def test_sharded_host_call_and_allgather_over_several_gpus(built, world, mnk, beta, kernel):
     from runner import api
     from runner.shard import shard_columns
     if api.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     m, n, k = mnk
     a, b, c = oracle.make_inputs(m, n, k, seed=29)
-    runners = open_runners(built, world)
+    logical_a, lda = a, 0
+    if kernel and kernel.endswith("_tn"):
+        a, lda = np.ascontiguousarray(a.reshape(k, m).T).reshape(-1), k      # K x M column-major storage, lda = K
+    runners = open_runners(built, world, kernel)
     try:
         tile_n = runners[0].info("tile_n")
         single = np.zeros(m * n, np.float32)
-        runners[0].run_host(a, b, c, single, m, n, k, alpha=1.0, beta=beta)
+        runners[0].run_host(a, b, c, single, m, n, k, alpha=1.0, beta=beta, lda=lda)
         # A shard is a smaller problem and would choose kernel and split-K by its own size; a caller that wants the
         # sharded result to equal the unsharded one bit for bit pins both to what the whole problem got
         variant, split_k = runners[0].info("last_variant"), runners[0].info("last_split_k")
@@ -98,7 +103,7 @@ def test_sharded_host_call_and_allgather_over_several_gpus(built, world, mnk, be
             w = n1 - n0
             try:
                 # the host call: this rank's slice of A goes up, the others' slices come over NVLink
-                r.run_host_sharded(a, b[n0 * k:], c[n0 * m:] if beta else None, outs[i], m, w, k, alpha=1.0, beta=beta)
+                r.run_host_sharded(a, b[n0 * k:], c[n0 * m:] if beta else None, outs[i], m, w, k, alpha=1.0, beta=beta, lda=lda)
                 # the device call into a full-size D ...
                 if w:
                     da, db, dc = r.dev_alloc(a.nbytes), r.dev_alloc(max(w * k, 1) * 4), r.dev_alloc(max(w * m, 1) * 4)
@@ -106,7 +111,7 @@ def test_sharded_host_call_and_allgather_over_several_gpus(built, world, mnk, be
                     r.upload(db, b[n0 * k:n1 * k])
                     r.upload(dc, c[n0 * m:n1 * m])
                     r.memset(full[i], 0xFF, m * n * 4)
-                    r.launch(da, db, dc if beta else None, full[i] + n0 * m * 4, m, w, k, alpha=1.0, beta=beta)
+                    r.launch(da, db, dc if beta else None, full[i] + n0 * m * 4, m, w, k, alpha=1.0, beta=beta, lda=lda)
                     r.sync()
                     for p in (da, db, dc):
                         r.dev_free(p)
@@ -134,8 +139,8 @@ def test_sharded_host_call_and_allgather_over_several_gpus(built, world, mnk, be
         assert assembled.tobytes() == single.tobytes()         # sharding changes no bit
         for g in gathered:
             assert g.tobytes() == single.tobytes()             # every rank holds all of D after the all-gather
-        ref = oracle.gemm(a, b, c, 1.0, beta, m, n, k)
-        bound = oracle.abs_bound(a, b, m, n, k) + abs(beta) * np.abs(c).astype(np.float64)
+        ref = oracle.gemm(logical_a, b, c, 1.0, beta, m, n, k)
+        bound = oracle.abs_bound(logical_a, b, m, n, k) + abs(beta) * np.abs(c).astype(np.float64)
         assert oracle.worst_ratio(single, ref, bound) <= 1.0
         for r, p in zip(runners, full):
             r.dev_free(p)
