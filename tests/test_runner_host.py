@@ -188,3 +188,14 @@ def test_bench_reports_ncu_traffic_only_for_the_source_it_was_captured_on(built,
     cubin_path, _ = built.ensure(built.DEFAULT_TENSOR)
     value, _ = importlib.reload(bench).ncu_traffic(built.DEFAULT_TENSOR, cubin_path, real[built.DEFAULT_TENSOR]["shape"])
     assert value in (None, real[built.DEFAULT_TENSOR]["dram_bytes_per_launch"])
+
+
+def test_header_is_plain_c(tmp_path):
+    """The drop-in boundary is a C ABI: include/sgemm_runner.h must compile as C99 (no C++ or torch types), so that
+    any language's FFI can bind it."""
+    import subprocess
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "sgemm_runner.h"\nint main(void) { sgemm_config c; (void)c; return SGEMM_ERR_COMM == -10 ? 0 : 1; }\n')
+    ret = subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", f"-I{ROOT / 'include'}", str(src)],
+                         capture_output=True, text=True)
+    assert ret.returncode == 0, ret.stderr
