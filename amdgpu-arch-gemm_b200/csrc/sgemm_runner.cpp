@@ -30,7 +30,7 @@ namespace {
 #define DRIVER_FUNCTIONS(X)                                                                              \
     X(cuInit) X(cuDeviceGet) X(cuDeviceGetCount) X(cuDeviceGetAttribute) X(cuDevicePrimaryCtxRetain)     \
     X(cuDevicePrimaryCtxRelease) X(cuCtxPushCurrent) X(cuCtxPopCurrent) X(cuModuleLoad) X(cuModuleUnload) \
-    X(cuModuleGetFunction) X(cuFuncSetAttribute) X(cuLaunchKernel) X(cuLaunchKernelEx) X(cuTensorMapEncodeTiled) \
+    X(cuModuleGetFunction) X(cuFuncSetAttribute) X(cuFuncGetAttribute) X(cuLaunchKernel) X(cuLaunchKernelEx) X(cuTensorMapEncodeTiled) \
     X(cuMemAlloc) X(cuMemFree) X(cuMemcpyHtoDAsync) X(cuMemcpyDtoHAsync) X(cuMemcpyHtoD) X(cuMemcpyDtoH) \
     X(cuMemsetD8) X(cuStreamSynchronize) X(cuCtxSynchronize) X(cuEventCreate)        \
     X(cuEventRecord) X(cuEventSynchronize) X(cuEventElapsedTime) X(cuEventDestroy) X(cuGetErrorString)   \
@@ -150,7 +150,7 @@ struct sgemm_handle {
     int64_t pipeline_chunks = 16;  // ... this many of them (fewer when N is small); 8192^3: 11.5 ms with 8, 11.1 with 16, 12.8 with 32
     bool pdl = true;            // launch with programmatic stream serialisation (see launch())
     int64_t acc_chain_opt = -1;   // -1: as generated, 0: whole K in one chain, else k per chain
-    int64_t last_variant = 0, last_split_k = 1, last_grid = 0, launches = 0, last_acc_chain = 0, last_tile_n = 0;
+    int64_t last_variant = 0, last_split_k = 1, last_grid = 0, launches = 0, last_acc_chain = 0, last_tile_n = 0, last_feed_tma = 0;
     CachedMap maps[4];
     // optional timing of the main GEMM kernel alone (events around it on the caller's stream)
     bool profile = false;
@@ -220,6 +220,7 @@ struct Plan {
     size_t rp_a_off = 0, rp_b_off = 0;
     uint32_t lda_eff = 0, ldb_eff = 0;  // leading dimensions the tensor kernel and its pre-pass see
     uint32_t acc_chain = 0;             // k per tensor-core accumulation chain (0: all of K in one chain)
+    bool ffma_tma = false;              // FFMA variant: the TMA-fed kernel serves this call (else the register-fed one)
 };
 
 // FP32: can TMA read this operand where it lies?  (a packed K-major copy of A gets its own pitch and alignment)
@@ -364,13 +365,17 @@ int make_plan(sgemm_handle *h, const void *a, const void *b, uint32_t m, uint32_
         if (p->repitch_b) { p->rp_b_off = off; off += round_up((size_t)ldb * (h->cfg.trans_b ? k : n) * 4, 256); }
         if (!tk->split_inkernel && h->elem_bytes == 4) { p->lo_b_off = off; off += round_up(p->span_b * 4, 256); }
     } else {
-        const bool own = h->cfg.variant == kVariantSimt;
+        // an FFMA cubin's own kernel, unless it is the TMA-fed one and TMA cannot describe these operands: then, as in
+        // a tensor-variant cubin, the register-fed fallback kernel
+        p->ffma_tma = h->cfg.variant == kVariantSimt && h->cfg.feed_tma && operand_tma_ok(a, lda) && operand_tma_ok(b, ldb);
+        const bool own = h->cfg.variant == kVariantSimt && (!h->cfg.feed_tma || p->ffma_tma);
         const uint32_t tm = own ? h->tile_m : (uint32_t)h->cfg.fallback_tile[0];
         const uint32_t tn = own ? h->tile_n : (uint32_t)h->cfg.fallback_tile[1];
         const uint32_t bk = own ? (uint32_t)h->cfg.depth_k : (uint32_t)h->cfg.fallback_tile[2];
         p->tiles_m = (m + tm - 1) / tm;
         p->tiles_n = (n + tn - 1) / tn;
-        p->split_k = pick_split_k(h, p->tiles_m * p->tiles_n, k, bk, 2u * (uint32_t)h->sm_count);
+        // blocks the device holds at a time: two per SM of the register-fed kernel, one of the TMA-fed one
+        p->split_k = pick_split_k(h, p->tiles_m * p->tiles_n, k, bk, (p->ffma_tma ? 1u : 2u) * (uint32_t)h->sm_count);
         p->grid_x = p->tiles_m * p->tiles_n;
     }
     if (p->split_k > 1) {
@@ -653,8 +658,25 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
                           const_cast<CUtensorMap *>(mb_hi), const_cast<CUtensorMap *>(mb_lo)};
         rc = launch_main(h, tk.fn, p.grid_x, 1, tk.threads, tk.smem, stream, params);
         if (rc) return rc;
+    } else if (p.ffma_tma) {
+        // TMA-fed FFMA kernel: one box per operand and k-step, no swizzle.  A tile: BK rows of BM floats (row = one k);
+        // B tile: BN rows of BK floats (row = one n), or, for a transposed B, BK rows of BN floats
+        const uint32_t bm = h->tile_m, bn = h->tile_n, bk = (uint32_t)h->cfg.depth_k;
+        const CUtensorMap *ma, *mb;
+        if ((rc = encode_map(h, 0, dA, m, k, (uint64_t)lda * 4, bm, bk, CU_TENSOR_MAP_SWIZZLE_NONE, &ma))) return rc;
+        if (h->cfg.trans_b) rc = encode_map(h, 2, dB, n, k, (uint64_t)ldb * 4, bn, bk, CU_TENSOR_MAP_SWIZZLE_NONE, &mb);
+        else rc = encode_map(h, 2, dB, k, n, (uint64_t)ldb * 4, bk, bn, CU_TENSOR_MAP_SWIZZLE_NONE, &mb);
+        if (rc) return rc;
+        uint32_t *wave_sync = nullptr;
+        uint32_t wave_base = 0;
+        void *params[] = {&dA, &dB, &dC, &dD, &m, &n, &k, &lda, &ldb, &ldc, &ldd, &alpha, &beta, &nwx, &nwy,
+                          &partial, &status_ptr, &split, &wave_sync, &wave_base,
+                          const_cast<CUtensorMap *>(ma), const_cast<CUtensorMap *>(mb)};
+        rc = launch_main(h, h->fn_main, p.grid_x, p.split_k, (uint32_t)h->cfg.num_threads, (uint32_t)h->cfg.dynamic_smem_bytes,
+                         stream, params);
+        if (rc) return rc;
     } else {
-        const bool own = h->cfg.variant == kVariantSimt;
+        const bool own = h->cfg.variant == kVariantSimt && !h->cfg.feed_tma;
         CUfunction f = own ? h->fn_main : h->fn_simt;
         const uint32_t threads = own ? (uint32_t)h->cfg.num_threads : (uint32_t)h->cfg.fallback_threads;
         uint32_t *wave_sync = nullptr;
@@ -676,6 +698,7 @@ int launch_device(sgemm_handle *h, const float *dA, const float *dB, const float
     h->last_variant = p.variant != kVariantTensor ? 2 : ((p.tk == &h->tk_skinny || p.tk == &h->tk_thin) ? 3 : 1);
     if (p.variant != kVariantTensor) h->last_acc_chain = 0;
     h->last_tile_n = p.variant == kVariantTensor ? p.tk->tile_n : 0;
+    h->last_feed_tma = p.variant == kVariantTensor || p.ffma_tma;
     h->last_split_k = p.split_k;
     h->last_grid = p.grid_x;
     return SGEMM_OK;
@@ -722,6 +745,7 @@ int config_from_toml(const char *path, sgemm_config *c, std::string *err) {
     c->stages = t.get_int("stages", &v) ? (int32_t)v : c->vmem_stage + 1;
     c->a_kmajor = (t.get_string("a_major", &s) && s == "k") ? 1 : 0;
     c->split_inkernel = !t.get_string("split", &s) ? 0 : s == "inkernel" ? 1 : s == "hybrid" ? 2 : 0;
+    c->feed_tma = (c->variant == kVariantSimt && t.get_string("feed", &s) && s == "tma") ? 1 : 0;
     std::vector<int64_t> fb;
     if (t.get_int_array("fallback_tile", &fb) && fb.size() == 3)
         for (int i = 0; i < 3; ++i) c->fallback_tile[i] = (int32_t)fb[i];
@@ -743,8 +767,8 @@ int config_from_toml(const char *path, sgemm_config *c, std::string *err) {
     std::snprintf(c->thin_entry, sizeof c->thin_entry, "%s", t.get_string("thin_entry", &s) ? s.c_str() : "");
     std::snprintf(c->entry, sizeof c->entry, "%s", t.get_string("entry", &s) ? s.c_str() : "generated_gemm");
     std::snprintf(c->fallback_entry, sizeof c->fallback_entry, "%s", t.get_string("fallback_entry", &s) ? s.c_str() : "");
-    if (c->variant == kVariantTensor && (c->fallback_threads <= 0 || c->fallback_tile[0] <= 0 || !c->fallback_entry[0])) {
-        *err = "tensor-variant config lacks the fallback_* keys";
+    if ((c->variant == kVariantTensor || c->feed_tma) && (c->fallback_threads <= 0 || c->fallback_tile[0] <= 0 || !c->fallback_entry[0])) {
+        *err = "a config whose main kernel is fed by TMA lacks the fallback_* keys";
         return SGEMM_ERR_TOML;
     }
     for (int i = 0; i < 2; ++i)
@@ -850,7 +874,7 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
     struct Want { CUfunction *f; const char *name; bool required; };
     const Want wants[] = {
         {&h->fn_main, cfg.entry, true},
-        {&h->fn_simt, cfg.fallback_entry, cfg.variant == kVariantTensor},
+        {&h->fn_simt, cfg.fallback_entry, cfg.variant == kVariantTensor || cfg.feed_tma != 0},
         {&h->fn_split_lo, "sgemm_split_lo", true},
         {&h->fn_pack_a, "sgemm_pack_a_kmajor", true},
         {&h->fn_pack16, "sgemm_pack16_kmajor", true},
@@ -913,6 +937,18 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
         (r = d.cuFuncSetAttribute_(h->fn_main, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, cfg.dynamic_smem_bytes)) != CUDA_SUCCESS) {
         fail(h, SGEMM_ERR_CUDA, "cannot opt in to %d bytes of dynamic shared memory: %s", cfg.dynamic_smem_bytes, cu_text(r).c_str());
         return bail(SGEMM_ERR_CUDA);
+    }
+    if (cfg.feed_tma && cfg.num_threads >= 384) {
+        // The TMA-fed FFMA kernel hands registers from its first warp group to the consumers, and a consumer waits
+        // without limit for registers the block was never given.  The kernel's budget assumes the launch allocation
+        // __launch_bounds__ allows; a cubin compiled to fewer must not be launched.
+        int regs = 0;
+        const int expect = (512 / (cfg.num_threads / 128)) / 8 * 8;
+        if ((r = d.cuFuncGetAttribute_(&regs, CU_FUNC_ATTRIBUTE_NUM_REGS, h->fn_main)) != CUDA_SUCCESS || regs != expect) {
+            fail(h, SGEMM_ERR_MODULE, "'%s' in '%s' uses %d registers per thread where its register hand-over assumes %d",
+                 cfg.entry, cubin_path, regs, expect);
+            return bail(SGEMM_ERR_MODULE);
+        }
     }
     if ((r = d.cuMemAlloc_(&h->status, kStatusAlloc * 4)) != CUDA_SUCCESS ||
         (r = d.cuMemsetD8_(h->status, 0, kStatusAlloc * 4)) != CUDA_SUCCESS ||
@@ -1229,6 +1265,7 @@ SGEMM_API int sgemm_get_info(sgemm_handle *h, const char *key, int64_t *value) {
     else if (k == "last_split_k") *value = h->last_split_k;
     else if (k == "last_acc_chain") *value = h->last_acc_chain;
     else if (k == "last_tile_n") *value = h->last_tile_n;
+    else if (k == "last_feed_tma") *value = h->last_feed_tma;
     else if (k == "acc_chain") *value = h->tk_main.acc_chain;
     else if (k == "skinny_acc_chain") *value = h->tk_skinny.acc_chain;
     else if (k == "last_grid") *value = h->last_grid;

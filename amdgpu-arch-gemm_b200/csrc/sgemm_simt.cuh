@@ -170,22 +170,93 @@ __device__ __forceinline__ void simt_read_frag(const SimtSmem &s, int buf, int k
 #ifndef SIMT_FMA2
 #define SIMT_FMA2 1   // accumulate with the packed FP32 FMA of sm_100 (fma.rn.f32x2): same results, half the FMA instructions
 #endif
-#if SIMT_FMA2
+#ifndef SGEMM_FFMA_SHARED
+#define SGEMM_FFMA_SHARED
+#ifndef FFMA_PACKED
+#define FFMA_PACKED 1   // 0: two scalar FMAs in place of each packed one (the same arithmetic; for comparison)
+#endif
+// (shared by the register-fed kernel below and the TMA-fed kernel of sgemm_ffma_tma.cuh; emitted once per translation unit)
 // acc2[j][i] (+)= {fa[2i], fa[2i+1]} * {fb[j], fb[j]}: one packed FMA per two rows of the thread tile
-__device__ __forceinline__ void simt_outer_product2(uint64_t (&acc2)[SIMT_TN][SIMT_TM / 2], const float (&fa)[SIMT_TM],
-                                                    const float (&fb)[SIMT_TN]) {
-    uint64_t a2[SIMT_TM / 2];
+template <int TM, int TN>
+__device__ __forceinline__ void ffma_outer_product2(uint64_t (&acc2)[TN][TM / 2], const float (&fa)[TM], const float (&fb)[TN]) {
+    uint64_t a2[TM / 2];
 #pragma unroll
-    for (int i = 0; i < SIMT_TM / 2; ++i) asm("mov.b64 %0, {%1, %2};" : "=l"(a2[i]) : "f"(fa[2 * i]), "f"(fa[2 * i + 1]));
+    for (int i = 0; i < TM / 2; ++i) asm("mov.b64 %0, {%1, %2};" : "=l"(a2[i]) : "f"(fa[2 * i]), "f"(fa[2 * i + 1]));
 #pragma unroll
-    for (int j = 0; j < SIMT_TN; ++j) {
+    for (int j = 0; j < TN; ++j) {
         uint64_t b2;
         asm("mov.b64 %0, {%1, %1};" : "=l"(b2) : "f"(fb[j]));
 #pragma unroll
-        for (int i = 0; i < SIMT_TM / 2; ++i) asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc2[j][i]) : "l"(a2[i]), "l"(b2));
+        for (int i = 0; i < TM / 2; ++i) {
+#if FFMA_PACKED
+            asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc2[j][i]) : "l"(a2[i]), "l"(b2));
+#else
+            float lo, hi;
+            asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc2[j][i]));
+            lo = fmaf(fa[2 * i], fb[j], lo);
+            hi = fmaf(fa[2 * i + 1], fb[j], hi);
+            asm("mov.b64 %0, {%1, %2};" : "=l"(acc2[j][i]) : "f"(lo), "f"(hi));
+#endif
+        }
     }
 }
-#endif
+
+// Epilogue of one thread: d = alpha*acc + beta*c (C is not read when beta == 0), or, with split_k > 1, the raw partial
+// product to this split's M x N slab of ws.  16-byte accesses where base and leading dimension allow, guarded scalars
+// at the edges.
+// The thread tile TM x TN is made of 4 x 4 blocks strided over the block tile: rows gi*TX*4 + tx*4 + (0..3), columns
+// gj*TY*4 + ty*4 + (0..3).
+template <int TM, int TN, int TX, int TY>
+__device__ __forceinline__ void ffma_epilogue(const float (&acc)[TN][TM], const float *c, float *d, float *ws,
+                                              uint32_t m, uint32_t n, uint32_t ldc, uint32_t ldd, float alpha, float beta,
+                                              uint32_t split_k, uint32_t m0, uint32_t n0, uint32_t tx, uint32_t ty) {
+    const bool partial = split_k > 1;
+    float *out = partial ? ws + (uint64_t)blockIdx.z * m * n : d;
+    const uint32_t ldo = partial ? m : ldd;
+    const bool o_vec = ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && (ldo % 4 == 0);
+    const bool c_vec = ((reinterpret_cast<uintptr_t>(c) & 15) == 0) && (ldc % 4 == 0);
+#pragma unroll
+    for (int gj = 0; gj < (TN / 4); ++gj) {
+#pragma unroll
+        for (int rj = 0; rj < 4; ++rj) {
+            const uint32_t col = n0 + gj * TY * 4 + ty * 4 + rj;
+            if (col >= n) continue;
+#pragma unroll
+            for (int gi = 0; gi < (TM / 4); ++gi) {
+                const uint32_t row = m0 + gi * TX * 4 + tx * 4;
+                if (row >= m) continue;
+                float r[4];
+#pragma unroll
+                for (int ri = 0; ri < 4; ++ri) r[ri] = acc[gj * 4 + rj][gi * 4 + ri];
+                if (!partial) {
+#pragma unroll
+                    for (int ri = 0; ri < 4; ++ri) r[ri] *= alpha;
+                    if (beta != 0.0f) {
+                        const float *cp = c + row + (uint64_t)col * ldc;
+                        if (c_vec && row + 3 < m) {
+                            const float4 cv = *reinterpret_cast<const float4 *>(cp);
+                            r[0] = fmaf(beta, cv.x, r[0]); r[1] = fmaf(beta, cv.y, r[1]);
+                            r[2] = fmaf(beta, cv.z, r[2]); r[3] = fmaf(beta, cv.w, r[3]);
+                        } else {
+#pragma unroll
+                            for (int ri = 0; ri < 4; ++ri)
+                                if (row + ri < m) r[ri] = fmaf(beta, cp[ri], r[ri]);
+                        }
+                    }
+                }
+                float *op = out + row + (uint64_t)col * ldo;
+                if (o_vec && row + 3 < m) {
+                    *reinterpret_cast<float4 *>(op) = make_float4(r[0], r[1], r[2], r[3]);
+                } else {
+#pragma unroll
+                    for (int ri = 0; ri < 4; ++ri)
+                        if (row + ri < m) op[ri] = r[ri];
+                }
+            }
+        }
+    }
+}
+#endif  // SGEMM_FFMA_SHARED
 
 extern "C" __global__ void __launch_bounds__(SIMT_THREADS)
 SIMT_ENTRY(const float *__restrict__ a, const float *__restrict__ b, const float *c, float *d,
@@ -252,7 +323,7 @@ SIMT_ENTRY(const float *__restrict__ a, const float *__restrict__ b, const float
         for (int kk = 0; kk < SIMT_BK; ++kk) {
             if (kk + 1 < SIMT_BK) simt_read_frag(s, buf, kk + 1, tx, ty, fa[(kk + 1) & 1], fb[(kk + 1) & 1]);
 #if SIMT_FMA2
-            simt_outer_product2(acc2, fa[kk & 1], fb[kk & 1]);
+            ffma_outer_product2<SIMT_TM, SIMT_TN>(acc2, fa[kk & 1], fb[kk & 1]);
 #else
 #pragma unroll
             for (int j = 0; j < SIMT_TN; ++j)
@@ -267,7 +338,7 @@ SIMT_ENTRY(const float *__restrict__ a, const float *__restrict__ b, const float
             float fa[SIMT_TM], fb[SIMT_TN];
             simt_read_frag(s, buf, kk, tx, ty, fa, fb);
 #if SIMT_FMA2
-            simt_outer_product2(acc2, fa, fb);
+            ffma_outer_product2<SIMT_TM, SIMT_TN>(acc2, fa, fb);
 #else
 #pragma unroll
             for (int j = 0; j < SIMT_TN; ++j)
@@ -288,50 +359,5 @@ SIMT_ENTRY(const float *__restrict__ a, const float *__restrict__ b, const float
         for (int i = 0; i < SIMT_TM / 2; ++i)
             asm("mov.b64 {%0, %1}, %2;" : "=f"(acc[j][2 * i]), "=f"(acc[j][2 * i + 1]) : "l"(acc2[j][i]));
 #endif
-    // epilogue: d = alpha*acc + beta*c (C is not read when beta == 0), or the raw partial to ws
-    const bool partial = split_k > 1;
-    float *out = partial ? ws + (uint64_t)blockIdx.z * m * n : d;
-    const uint32_t ldo = partial ? m : ldd;
-    const bool o_vec = ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && (ldo % 4 == 0);
-    const bool c_vec = ((reinterpret_cast<uintptr_t>(c) & 15) == 0) && (ldc % 4 == 0);
-#pragma unroll
-    for (int gj = 0; gj < SIMT_GN; ++gj) {
-#pragma unroll
-        for (int rj = 0; rj < 4; ++rj) {
-            const uint32_t col = n0 + gj * SIMT_TY * 4 + ty * 4 + rj;
-            if (col >= n) continue;
-#pragma unroll
-            for (int gi = 0; gi < SIMT_GM; ++gi) {
-                const uint32_t row = m0 + gi * SIMT_TX * 4 + tx * 4;
-                if (row >= m) continue;
-                float r[4];
-#pragma unroll
-                for (int ri = 0; ri < 4; ++ri) r[ri] = acc[gj * 4 + rj][gi * 4 + ri];
-                if (!partial) {
-#pragma unroll
-                    for (int ri = 0; ri < 4; ++ri) r[ri] *= alpha;
-                    if (beta != 0.0f) {
-                        const float *cp = c + row + (uint64_t)col * ldc;
-                        if (c_vec && row + 3 < m) {
-                            const float4 cv = *reinterpret_cast<const float4 *>(cp);
-                            r[0] = fmaf(beta, cv.x, r[0]); r[1] = fmaf(beta, cv.y, r[1]);
-                            r[2] = fmaf(beta, cv.z, r[2]); r[3] = fmaf(beta, cv.w, r[3]);
-                        } else {
-#pragma unroll
-                            for (int ri = 0; ri < 4; ++ri)
-                                if (row + ri < m) r[ri] = fmaf(beta, cp[ri], r[ri]);
-                        }
-                    }
-                }
-                float *op = out + row + (uint64_t)col * ldo;
-                if (o_vec && row + 3 < m) {
-                    *reinterpret_cast<float4 *>(op) = make_float4(r[0], r[1], r[2], r[3]);
-                } else {
-#pragma unroll
-                    for (int ri = 0; ri < 4; ++ri)
-                        if (row + ri < m) op[ri] = r[ri];
-                }
-            }
-        }
-    }
+    ffma_epilogue<SIMT_TM, SIMT_TN, SIMT_TX, SIMT_TY>(acc, c, d, ws, m, n, ldc, ldd, alpha, beta, split_k, m0, n0, tx, ty);
 }

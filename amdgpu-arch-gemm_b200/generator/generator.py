@@ -173,7 +173,8 @@ class GemmSolutionConfig:
                  mfma: Tuple[int, int, int, int], wave_group: Tuple[int, int], wave_tiling: Tuple[int, int],
                  depth_k: int, trans_a: bool, trans_b: bool, vmem_stage: int = 1, *,
                  a_major: str = "mn", terms: int = 3, split: str = "prepass",
-                 epilogue_warps: Optional[int] = None, companion: bool = True, acc_chain: Optional[int] = None):
+                 epilogue_warps: Optional[int] = None, companion: bool = True, acc_chain: Optional[int] = None,
+                 feed: str = "ldg"):
         self.a_type = a_type
         self.b_type = b_type
         self.cd_type = cd_type
@@ -207,6 +208,12 @@ class GemmSolutionConfig:
                                     # lo tiles in shared memory from the TMA-landed raw tiles) or "hybrid" (A_lo by the
                                     # pre-pass, B's lo tile by the transform warps)
 
+        # FFMA variant: how operand tiles reach shared memory.  "ldg": every thread loads 16-byte vectors into registers
+        # and stores them (two buffers, any base and leading dimension); "tma": a producer warp issues TMA box copies
+        # into a ring of vmem_stage + 1 stages and the other warps only multiply (operands TMA can describe; the
+        # register-fed fallback kernel of the tensor-variant cubins is emitted beside it for the rest)
+        self.feed = feed
+
         for t in (a_type, b_type, cd_type, scalar_type):
             datatype_size(t)
         if cd_type != DataType.FP32 or scalar_type != DataType.FP32:
@@ -234,7 +241,9 @@ class GemmSolutionConfig:
                                f"(128, N, 1, 16) for tcgen05 f16/bf16, "
                                f"(1, 1, 1, 1) for FFMA, or a legacy (16,16,1,4)/(32,32,1,2) shape")
 
-        limit = MAX_LDS_NUM_BYTES if self.variant == VARIANT_TENSOR else MAX_STATIC_LDS_NUM_BYTES
+        if self.variant == VARIANT_TENSOR and self.feed != "ldg":
+            raise RuntimeError("feed is a knob of the FFMA variant (the tensor variant is always fed by TMA)")
+        limit = MAX_LDS_NUM_BYTES if (self.variant == VARIANT_TENSOR or self.feed == "tma") else MAX_STATIC_LDS_NUM_BYTES
         if self.lds_usage_bytes > limit:
             raise RuntimeError(f"LDS usage exceeds {limit}: {self.lds_usage_bytes}")
 
@@ -325,6 +334,22 @@ class GemmSolutionConfig:
             raise RuntimeError("depth_k must be a multiple of 4 (16-byte loads along K)")
         if tm * tn > 128:
             raise RuntimeError(f"thread tile {tm}x{tn} does not fit the register file")
+        if self.feed not in ("ldg", "tma"):
+            raise RuntimeError("feed is 'ldg' or 'tma'")
+        if self.feed == "tma":
+            if self.trans_a:
+                raise RuntimeError("the TMA-fed FFMA kernel reads an untransposed A (a K-contiguous A tile would be read "
+                                   "with shared-memory bank conflicts): use feed='ldg'")
+            if threads % 128 or threads > 512:
+                raise RuntimeError(f"{threads} multiplying threads: registers are handed over in groups of four warps "
+                                   f"(128, 256, 384 or 512 threads)")
+            if max(bm, bn, self.depth_k) > 256:
+                raise RuntimeError("a TMA box has at most 256 elements per dimension")
+            if not self.trans_b and bm // tm < 8:
+                raise RuntimeError("the K-contiguous B tile is read without bank conflicts only when 8 neighbouring lanes "
+                                   "share their columns: tile M / thread tile M must be at least 8")
+            if self.stages < 2 or self.stages > 12:
+                raise RuntimeError(f"{self.stages} stages: the TMA ring has 2 to 12")
 
     # ------------------------------------------------------------------------------- geometry
     @property
@@ -354,7 +379,7 @@ class GemmSolutionConfig:
             return 128 + 32 * self.epilogue_warps + (128 if self.split != "prepass" else 0)
         bm, bn = self.tile_size
         tm, tn = self.simt_thread_tile
-        return (bm // tm) * (bn // tn)
+        return (bm // tm) * (bn // tn) + (128 if self.feed == "tma" else 0)   # + the producer's group of four warps
 
     @property
     def num_bytes_per_buffer_load(self) -> Tuple[int, int]:
@@ -384,6 +409,8 @@ class GemmSolutionConfig:
         bm, bn = self.tile_size
         if self.variant == VARIANT_TENSOR:
             return self._ring_bytes()
+        if self.feed == "tma":
+            return self.stages * self.depth_k * (bm + bn) * 4 + 128 + 256         # ring + alignment slack + barriers
         return 2 * self.depth_k * (bm + 4 + bn + 4) * 4                          # double-buffered, padded A and B
 
     @property
@@ -430,7 +457,7 @@ class GemmSolutionConfig:
             "cluster": list(self.wave_group) if self.variant == VARIANT_TENSOR else [1, 1],
             "stages": self.stages,
             "num_threads": self.num_workitems,
-            "dynamic_smem_bytes": self.lds_usage_bytes if self.variant == VARIANT_TENSOR else 0,
+            "dynamic_smem_bytes": self.lds_usage_bytes if (self.variant == VARIANT_TENSOR or self.feed == "tma") else 0,
             "tmem_columns": self.tmem_columns,
             "entry": KERNEL_ENTRY,
             # optimisation knobs of the reference that are accepted for compatibility and change nothing in these
@@ -469,6 +496,15 @@ class GemmSolutionConfig:
                     "thin_smem_bytes": th.lds_usage_bytes,
                     "thin_acc_chain": th.acc_chain,
                 })
+        elif self.feed == "tma":
+            # the register-fed kernel for operands TMA cannot describe
+            fb = simt_fallback_config(self.trans_a, self.trans_b)
+            d.update({
+                "feed": "tma",
+                "fallback_entry": SIMT_FALLBACK_ENTRY,
+                "fallback_tile": [fb.tile_size[0], fb.tile_size[1], fb.depth_k],
+                "fallback_threads": fb.num_workitems,
+            })
         return d
 
 
@@ -549,7 +585,16 @@ def gemm(context: GpuContext, name: str, arch: str, config: GemmSolutionConfig, 
               f"wgm {opt.wgm}, plr {opt.plr}, gw {opt.gw}\n")
     out.write(_defines([("OPT_WGM", opt.wgm)] + _trans_defines(config)))
     out.write(_read("sgemm_common.cuh"))
-    if config.variant == VARIANT_SIMT:
+    if config.variant == VARIANT_SIMT and config.feed == "tma":
+        # the register-fed kernel under the fallback name (as in a tensor-variant cubin), the TMA-fed one as the entry
+        out.write(_defines(_simt_defines(simt_fallback_config(config.trans_a, config.trans_b), opt, SIMT_FALLBACK_ENTRY)))
+        out.write(_read("sgemm_simt.cuh"))
+        bm, bn = config.tile_size
+        tm, tn = config.simt_thread_tile
+        out.write(_defines([("FT_ENTRY", KERNEL_ENTRY), ("FT_BM", bm), ("FT_BN", bn), ("FT_BK", config.depth_k),
+                            ("FT_TM", tm), ("FT_TN", tn), ("FT_STAGES", config.stages)]))
+        out.write(_read("sgemm_ffma_tma.cuh"))
+    elif config.variant == VARIANT_SIMT:
         out.write(_defines(_simt_defines(config, opt, KERNEL_ENTRY)))
         out.write(_read("sgemm_simt.cuh"))
     else:
@@ -645,9 +690,12 @@ def tensor_config(bn: int = 256, bk: int = 32, stages: int = 2, cluster: int = 1
 
 
 def simt_config(bm: int = 128, bn: int = 128, bk: int = 16, tm: int = 8, tn: int = 8, trans_a: bool = False,
-                trans_b: bool = False) -> GemmSolutionConfig:
+                trans_b: bool = False, feed: str = "ldg", stages: int = 2) -> GemmSolutionConfig:
+    """Shorthand for an FFMA configuration: block tile bm x bn x bk, thread tile tm x tn; ``feed="tma"`` selects the
+    TMA-fed, warp-specialised kernel with a ring of ``stages`` stages."""
     return GemmSolutionConfig(DataType.FP32, DataType.FP32, DataType.FP32, DataType.FP32,
-                              (1, 1, 1, 1), (bm // tm, bn // tn), (tm, tn), bk, trans_a, trans_b)
+                              (1, 1, 1, 1), (bm // tm, bn // tn), (tm, tn), bk, trans_a, trans_b,
+                              vmem_stage=stages - 1, feed=feed)
 
 
 def build_kernel(output_folder: str, config: GemmSolutionConfig, opt: Optional[GemmOptimizations] = None,

@@ -69,6 +69,12 @@ REGISTRY = {
     "simt_128x128x16": (lambda: simt_config(128, 128, 16, 8, 8), dict(wgm=8)),
     "simt_128x128x16_t16x8": (lambda: simt_config(128, 128, 16, 16, 8), dict(wgm=8)),   # best of the FFMA sweep at 4096^3
     "simt_64x64x16": (lambda: simt_config(64, 64, 16, 4, 4), dict(wgm=4)),
+    # FFMA kernels fed by TMA (a producer thread, mbarrier ring, consumers that only multiply)
+    "ffma_tma_256x128x16_s4": (lambda: simt_config(256, 128, 16, 16, 8, feed="tma", stages=4), dict(wgm=8)),
+    "ffma_tma_128x256x16_s4": (lambda: simt_config(128, 256, 16, 8, 16, feed="tma", stages=4), dict(wgm=8)),
+    "ffma_tma_128x128x16_s4": (lambda: simt_config(128, 128, 16, 8, 8, feed="tma", stages=4), dict(wgm=8)),
+    "ffma_tma_128x128x16_t16x8_s6": (lambda: simt_config(128, 128, 16, 16, 8, feed="tma", stages=6), dict(wgm=8)),
+    "ffma_tma_256x128x16_s4_nt": (lambda: simt_config(256, 128, 16, 16, 8, trans_b=True, feed="tma", stages=4), dict(wgm=8)),
     "simt_128x64x8_plr0": (lambda: simt_config(128, 64, 8, 8, 4), dict(wgm=1, plr=0)),
     # configurations written the reference's way (GCN MFMA shapes): served by the SIMT kernel
     "legacy_32x32x2_1wave": (lambda: _legacy((32, 32, 1, 2), (1, 1), (1, 1), 16), dict(wgm=1)),

@@ -41,6 +41,7 @@ class SgemmConfig(ctypes.Structure):
         ("wholek_entry", ctypes.c_char * 64),
         ("thin_tile", ctypes.c_int32 * 3), ("thin_threads", ctypes.c_int32), ("thin_smem_bytes", ctypes.c_int32),
         ("thin_acc_chain", ctypes.c_int32), ("thin_entry", ctypes.c_char * 64),
+        ("feed_tma", ctypes.c_int32),
     ]
 
 

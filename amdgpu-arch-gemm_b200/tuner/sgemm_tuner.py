@@ -57,6 +57,10 @@ SUPPORTED_SIMT = [((16, 16), (8, 8), 16), ((16, 16), (8, 8), 8), ((16, 8), (8, 8
                   ((16, 16), (8, 4), 16), ((16, 16), (4, 8), 16), ((32, 8), (4, 8), 16), ((16, 16), (4, 4), 16),
                   ((16, 8), (8, 8), 8), ((32, 16), (4, 8), 16), ((16, 16), (8, 16), 16), ((16, 16), (16, 8), 16),
                   ((8, 16), (16, 8), 16), ((16, 16), (8, 8), 32)]
+# FFMA variant fed by TMA (producer thread + mbarrier ring, one block per SM): (thread grid of the consumers,
+# per-thread tile, k per stage, stages)
+SUPPORTED_SIMT_TMA = [((16, 16), (16, 8), 16, 4), ((16, 16), (8, 16), 16, 4), ((16, 16), (8, 8), 16, 4),
+                      ((32, 16), (8, 8), 16, 4), ((16, 16), (16, 8), 32, 3), ((16, 8), (16, 8), 16, 6)]
 SUPPORTED_WGM = [1, 4, 8, 16]
 SUPPORTED_PLR = [0, 1]
 VERBOSE = False
@@ -93,6 +97,12 @@ def candidates(include_simt: bool = True, include_tensor: bool = True, ab_type: 
             yield (key,
                    lambda wg=wg, wt=wt, dk=dk: GemmSolutionConfig(F, F, F, F, (1, 1, 1, 1), wg, wt, dk, False, False),
                    lambda wgm=wgm, plr=plr: GemmOptimizations(1, wgm=wgm, plr=plr))
+        for (wg, wt, dk, stages), wgm in product(SUPPORTED_SIMT_TMA, SUPPORTED_WGM):
+            key = f"simt tma g{wg[0]}x{wg[1]} t{wt[0]}x{wt[1]} k{dk} s{stages} wgm{wgm}"
+            yield (key,
+                   lambda wg=wg, wt=wt, dk=dk, stages=stages: GemmSolutionConfig(
+                       F, F, F, F, (1, 1, 1, 1), wg, wt, dk, False, False, vmem_stage=stages - 1, feed="tma"),
+                   lambda wgm=wgm: GemmOptimizations(1, wgm=wgm))
 
 
 # ------------------------------------------------------------------------------------------ analytic pruning
@@ -122,7 +132,8 @@ def predict_time_us(config: GemmSolutionConfig, m: int, n: int, k: int, sm_count
     hbm_bytes_per_us = 6.5e6
     launch_us = 2.5
     if config.variant != "tcgen05_3xtf32":
-        slots = 2 * sm_count
+        tma_fed = getattr(config, "feed", "ldg") == "tma"                  # one block per SM on all of its lanes
+        slots = sm_count if tma_fed else 2 * sm_count
         kb_total = -(-k // config.depth_k)
         split = min(slots // tiles, kb_total // 8, 32) if tiles * 2 <= slots and kb_total >= 16 else 1
         split = max(split, 1)
@@ -130,9 +141,10 @@ def predict_time_us(config: GemmSolutionConfig, m: int, n: int, k: int, sm_count
         ttm, ttn = config.simt_thread_tile
         reuse = min(1.0, 0.4 + 0.6 * (ttm * ttn) / (ttm + ttn) / 4.0)      # FMAs per shared-memory word loaded, 8 x 8 -> 1
         depth = min(1.0, 0.7 + 0.3 * config.depth_k / 16.0)
-        # one block computes tm x tn x k_unit FMAs on half an SM's 128 lanes
         k_unit = -(-kb_total // split) * config.depth_k
-        clks = tm * tn * k_unit / 64.0 / (0.8 * reuse * depth)
+        # one block computes tm x tn x k_unit FMAs on half an SM's 128 lanes (all of them when fed by TMA, where the
+        # measured rate with a K-contiguous B tile is a tenth below the register-fed kernel's)
+        clks = tm * tn * k_unit / (128.0 if tma_fed else 64.0) / (0.8 * reuse * depth * (0.9 if tma_fed else 1.0))
         extra = (launch_us + (split + 1) * m * n * 4 / hbm_bytes_per_us) if split > 1 else 0.0
         return waves * clks / (ghz * 1e3) + launch_us + extra
     cluster = config.wave_group[0]
@@ -224,6 +236,12 @@ def structural_candidates(include_simt: bool = True, include_tensor: bool = True
             yield (key,
                    lambda wg=wg, wt=wt, dk=dk: GemmSolutionConfig(F, F, F, F, (1, 1, 1, 1), wg, wt, dk, False, False),
                    [(f" wgm{w}", lambda w=w, plr=plr: GemmOptimizations(1, wgm=w, plr=plr)) for w in wgms])
+        for wg, wt, dk, stages in SUPPORTED_SIMT_TMA:
+            key = f"simt tma g{wg[0]}x{wg[1]} t{wt[0]}x{wt[1]} k{dk} s{stages}"
+            yield (key,
+                   lambda wg=wg, wt=wt, dk=dk, stages=stages: GemmSolutionConfig(
+                       F, F, F, F, (1, 1, 1, 1), wg, wt, dk, False, False, vmem_stage=stages - 1, feed="tma"),
+                   [(f" wgm{w}", lambda w=w: GemmOptimizations(1, wgm=w)) for w in wgms])
 
 
 class Measurer:

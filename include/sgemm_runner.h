@@ -84,6 +84,9 @@ typedef struct sgemm_config {
     int32_t thin_smem_bytes;
     int32_t thin_acc_chain;
     char thin_entry[64];
+    /* FFMA variant: 1 = the main kernel is the TMA-fed, warp-specialised one (TOML feed = "tma"); operands TMA cannot
+     * describe go to the register-fed kernel named by fallback_entry, as in a tensor-variant cubin */
+    int32_t feed_tma;
 } sgemm_config;
 
 /* Replaces getAsmKernelConfig (runner/generator_runner.cpp:100-124).  Host only, needs no GPU. */
@@ -226,6 +229,8 @@ int sgemm_set_option(sgemm_handle *h, const char *key, int64_t value);
 
 /* Facts: "variant" (of the cubin), "last_variant" (1 tensor main / 2 simt / 3 tensor companion), "last_split_k", "last_grid",
  * "last_tile_n" (columns of the tile of the last launch: tells the companion, 128, from its narrow sibling, 32),
+ * "last_feed_tma" (1 when the main kernel of the last launch was fed by TMA: any tensor kernel, or the TMA-fed FFMA
+ * kernel; 0 for the register-fed FFMA kernel),
  * "last_acc_chain" (k per accumulation chain of the last tensor launch, 0 = whole K), "acc_chain" and
  * "skinny_acc_chain" (the chains the main and the companion tensor kernel were generated with),
  * "launches" (kernel launches issued so far), "tile_m", "tile_n", "sm_count", "workspace_bytes",

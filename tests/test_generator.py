@@ -232,3 +232,31 @@ def test_concurrent_ensure_builds_once(tmp_path):
     outs = [p.communicate()[0].split() for p in procs]
     assert all(p.returncode == 0 for p in procs)
     assert len({o[0] for o in outs}) == 1 and len({o[1] for o in outs}) == 1    # one build, seen by all
+
+
+def test_tma_fed_ffma_configuration():
+    """feed="tma": the FFMA variant as a producer / consumer kernel over a TMA ring; the register-fed fallback kernel
+    travels in the same cubin for operands TMA cannot describe."""
+    cfg = g.simt_config(256, 128, 16, 16, 8, feed="tma", stages=4)
+    assert cfg.variant == g.VARIANT_SIMT and cfg.tile_size == (256, 128) and cfg.stages == 4
+    assert cfg.num_workitems == 128 + 256                                   # the producer's warp group + 256 consumers
+    assert cfg.lds_usage_bytes == 4 * (256 + 128) * 16 * 4 + 128 + 256
+    d = cfg.to_dict()
+    assert d["variant"] == g.VARIANT_SIMT and d["feed"] == "tma" and d["dynamic_smem_bytes"] == cfg.lds_usage_bytes
+    assert d["fallback_entry"] == g.SIMT_FALLBACK_ENTRY and d["fallback_tile"] == [128, 128, 16] and d["fallback_threads"] == 256
+    src = g.gemm(None, "gemm", "sm_100a", cfg, g.GemmOptimizations(1, wgm=8), ARGS())
+    for needle in ("#define FT_ENTRY generated_gemm\n", "#define SIMT_ENTRY generated_gemm_simt\n", "#define FT_BM 256\n",
+                   "#define FT_TM 16\n", "#define FT_STAGES 4\n", "cp.async.bulk.tensor.2d", "setmaxnreg.inc"):
+        assert needle in src, needle
+    assert "multicast" not in src
+    plain = g.simt_config(128, 128, 16, 8, 8)
+    assert "feed" not in plain.to_dict() and plain.to_dict()["dynamic_smem_bytes"] == 0
+    assert "cp.async.bulk" not in g.gemm(None, "gemm", "sm_100a", plain, g.GemmOptimizations(1), ARGS())
+    with pytest.raises(RuntimeError, match="untransposed A"):
+        g.simt_config(256, 128, 16, 16, 8, trans_a=True, feed="tma", stages=4)
+    with pytest.raises(RuntimeError, match="groups of four warps"):
+        g.simt_config(64, 64, 16, 8, 8, feed="tma", stages=4)               # 64 consumers
+    with pytest.raises(RuntimeError, match="LDS usage"):
+        g.simt_config(256, 256, 64, 16, 8, feed="tma", stages=8)
+    with pytest.raises(RuntimeError, match="FFMA variant"):
+        g.tensor_config(256, 32, 3, cluster=2, feed="tma")
