@@ -4,7 +4,8 @@
 // ffma_epilogue are defined there), but the operand tiles are not carried through
 // registers: one producer thread issues two TMA box copies per k-step into a ring of FT_STAGES shared-memory stages
 // and the FT_CONSUMERS consumer threads only read fragments and multiply.  Stages are handed over with mbarriers
-// ("full": the copies' bytes have landed; "empty": every consumer warp has read the stage), so the block has no
+// ("full": the copies' bytes have landed; "ready": the B tile has been transposed, where that is needed; "empty":
+// every consumer warp has read the stage), so the block has no
 // block-wide barrier in its main loop, no global loads or shared stores in the multiplying warps, and copies run
 // FT_STAGES - 1 steps ahead of the arithmetic.
 //
@@ -13,18 +14,21 @@
 // same cubin for everything else.  M, N and K themselves are arbitrary: a box that reaches
 // past the matrix is zero-filled by TMA, and the epilogue guards rows and columns.
 //
-// Stage layout (floats):  A tile [FT_BK][FT_BM] (box {BM, BK} of the M x K matrix: row = one k), then the B tile:
-//   B untransposed (K contiguous): [FT_BN][FT_BK] (box {BK, BN} of the K x N matrix: row = one n); a thread reads
-//     16 bytes along k for each of its columns and keeps them for four k-slices.  The 8 lanes that share a
-//     shared-memory wavefront hold the same columns, so these reads are broadcasts.
-//   B transposed (N contiguous):   [FT_BK][FT_BN] (box {BN, BK} of the N x K matrix), read like A.
+// Stage layout (floats):  A tile [FT_BK][FT_BM] (box {BM, BK} of the M x K matrix: row = one k), then the B tile
+// [FT_BK][FT_BN] (row = one k) in which every thread finds the FT_TN values of a k-slice in 16-byte vectors:
+//   B transposed (N contiguous):   TMA writes it (box {BN, BK} of the N x K matrix).
+//   B untransposed (K contiguous): TMA cannot transpose.  It writes the box {BK, BN} of the K x N matrix (row = one n)
+//     into a third, raw buffer of the stage, and the three warps that share the producer's warp group copy it,
+//     transposed, into the B tile: 16-byte reads along k with the k-quad rotated over the lanes, 4-byte writes with
+//     32 consecutive n per warp, both free of bank conflicts.  (Reading a K-contiguous tile straight from the
+//     multiplying threads, eight rows per k-slice, measured 13 % slower than the register-fed kernel.)
 //
 // Every mbarrier wait is bounded: after FT_TIMEOUT_NS without progress the waiting thread records what it waited for
 // in the status words, raises a block-wide flag, every role leaves its loop, the block waits for copies that may still
 // be in flight and returns without writing D.
 //
-// Warps: the first group of four holds the producer (warp 0, one lane; warps 1 to 3 have no work), the consumers
-// follow.  Registers can be handed from one role to another only in groups of four warps (setmaxnreg), and every
+// Warps: the first group of four holds the producer (warp 0, one lane) and the transposing warps 1 to 3 (idle when B
+// needs no transposing), the consumers follow.  Registers can be handed from one role to another only in groups of four warps (setmaxnreg), and every
 // scheduler partition holds one warp of each group: the first group shrinks to FT_REGS_PRODUCER registers per thread and
 // the consumers grow to FT_REGS_CONSUMER, which is what lets 256 consumers hold 16 x 8 accumulators each.  One block per
 // SM (a tile lasts about a millisecond at K = 8192, its prologue and epilogue a few microseconds).
@@ -35,9 +39,6 @@
 // ---------------------------------------------------------------------------------------------
 #ifndef FT_STAGES
 #define FT_STAGES 4
-#endif
-#ifndef FT_KV
-#define FT_KV 4   // k-slices of a K-contiguous B tile a thread reads per shared-memory load (4: 16-byte, 2: 8-byte, 1: scalar)
 #endif
 #ifndef FT_TIMEOUT_NS
 #define FT_TIMEOUT_NS 2000000000ull
@@ -62,18 +63,22 @@
 #define FT_REGS_PRODUCER 40
 #define FT_REGS_CONSUMER_RAW ((FT_WARPS_PER_PARTITION * FT_REGS_LAUNCH - FT_REGS_PRODUCER) / (FT_WARPS_PER_PARTITION - 1) / 8 * 8)
 #define FT_REGS_CONSUMER (FT_REGS_CONSUMER_RAW > 232 ? 232 : FT_REGS_CONSUMER_RAW)
+#define FT_XFORM (!GEMM_TRANS_B)              // B arrives K-contiguous and is transposed in shared memory
+#define FT_XFORM_WARPS 3
 #define FT_A_FLOATS (FT_BK * FT_BM)
 #define FT_B_FLOATS (FT_BK * FT_BN)
-#define FT_STAGE_BYTES ((FT_A_FLOATS + FT_B_FLOATS) * 4)
-#define FT_SMEM_BYTES (FT_STAGES * FT_STAGE_BYTES + 128 + 256)   // ring + alignment slack + barriers and abort flag
+#define FT_RAW_FLOATS (FT_XFORM ? FT_BK * FT_BN : 0)
+#define FT_STAGE_FLOATS (FT_A_FLOATS + FT_B_FLOATS + FT_RAW_FLOATS)
+#define FT_TMA_BYTES ((FT_A_FLOATS + FT_B_FLOATS) * 4)           // what the two copies of a stage deliver
+#define FT_SMEM_BYTES (FT_STAGES * FT_STAGE_FLOATS * 4 + 128 + 512)   // ring + alignment slack + barriers and abort flag
+#define FT_KQ (FT_BK / 4)                     // 16-byte vectors along k in a row of the raw B tile
 
 static_assert(FT_TM % 4 == 0 && FT_TN % 4 == 0 && FT_BM % FT_TM == 0 && FT_BN % FT_TN == 0 && FT_BK % 4 == 0, "tile shapes");
 static_assert(FT_CONSUMERS % 128 == 0, "consumers are whole groups of four warps");
 static_assert(!GEMM_TRANS_A, "the TMA-fed FFMA kernel reads an untransposed A");
 static_assert(FT_BM <= 256 && FT_BN <= 256 && FT_BK <= 256, "a TMA box has at most 256 elements per dimension");
-static_assert(FT_TX >= 8 || GEMM_TRANS_B, "the K-contiguous B tile is read conflict-free when 8 neighbouring lanes share their columns");
+static_assert(!FT_XFORM || (FT_BN % 32 == 0 && (FT_KQ & (FT_KQ - 1)) == 0), "the transposing warps take 32 columns at a time and rotate a power-of-two number of k-quads");
 static_assert(FT_STAGES >= 2 && FT_STAGES <= 12, "ring depth");
-static_assert((FT_KV == 1 || FT_KV == 2 || FT_KV == 4) && FT_BK % FT_KV == 0, "B fragment vector");
 static_assert(!FT_REG_HANDOVER || ((FT_WARPS_PER_PARTITION - 1) * FT_REGS_CONSUMER + FT_REGS_PRODUCER <= FT_WARPS_PER_PARTITION * FT_REGS_LAUNCH &&
                                    FT_REGS_CONSUMER > FT_REGS_LAUNCH && FT_REGS_PRODUCER < FT_REGS_LAUNCH),
               "register hand-over: the consumers may only take what the first warp group releases");
@@ -119,6 +124,8 @@ struct FtWait {
 // tags of the status record: which role gave up
 #define FT_TAG_PRODUCER 0x46540001u   // producer waiting for a stage to be read ("empty")
 #define FT_TAG_CONSUMER 0x46540002u   // a consumer waiting for a stage's copies ("full")
+#define FT_TAG_XFORM 0x46540003u      // a transposing warp waiting for a stage's copies ("full")
+#define FT_TAG_READY 0x46540004u      // a consumer waiting for the transposed B tile ("ready")
 
 __device__ __forceinline__ bool ft_wait_slow(const FtWait &w, uint32_t bar, uint32_t parity, uint32_t tag, uint32_t step) {
     const uint64_t t0 = ft_globaltimer();
@@ -147,61 +154,55 @@ __device__ __forceinline__ bool ft_wait(const FtWait &w, uint32_t bar, uint32_t 
     return ft_wait_slow(w, bar, parity, tag, step);
 }
 
-// Fragments of k-slice kk of a stage.  as: this thread's first A element of the stage (tile + tx*4); bs: its first B
-// element.  A (and a transposed, N-contiguous B) is read in 16-byte vectors along M (N).  A K-contiguous B tile holds
-// the FT_TN values of one k-slice in FT_TN different rows: they are read FT_KV k-slices at a time (one vector along k
-// per column of the thread tile) into bq and handed out slice by slice.
-template <int KV>
+// Fragments of k-slice kk of a stage, 16-byte vectors along M and N.  as: this thread's first A element of the stage
+// (tile + tx*4); bs: its first B element (tile + ty*4).
 __device__ __forceinline__ void ft_load_fragments(int kk, const float *__restrict__ as, const float *__restrict__ bs,
-                                                  float (&fa)[FT_TM], float (&fb)[FT_TN], float (&bq)[FT_TN][KV]) {
+                                                  float (&fa)[FT_TM], float (&fb)[FT_TN]) {
 #pragma unroll
     for (int g = 0; g < FT_GM; ++g) {
         const float4 v = *reinterpret_cast<const float4 *>(as + kk * FT_BM + g * FT_TX * 4);
         fa[g * 4 + 0] = v.x; fa[g * 4 + 1] = v.y; fa[g * 4 + 2] = v.z; fa[g * 4 + 3] = v.w;
     }
-#if GEMM_TRANS_B
-    (void)bq;
 #pragma unroll
     for (int g = 0; g < FT_GN; ++g) {
         const float4 v = *reinterpret_cast<const float4 *>(bs + kk * FT_BN + g * FT_TY * 4);
         fb[g * 4 + 0] = v.x; fb[g * 4 + 1] = v.y; fb[g * 4 + 2] = v.z; fb[g * 4 + 3] = v.w;
     }
-#else
-    if (kk % KV == 0) {
-#pragma unroll
-        for (int g = 0; g < FT_GN; ++g)
-#pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                const float *p = bs + (g * FT_TY * 4 + r) * FT_BK + kk;
-                float (&dst)[KV] = bq[g * 4 + r];
-                if (KV == 4) {
-                    const float4 v = *reinterpret_cast<const float4 *>(p);
-                    dst[0] = v.x; dst[1 % KV] = v.y; dst[2 % KV] = v.z; dst[3 % KV] = v.w;
-                } else if (KV == 2) {
-                    const float2 v = *reinterpret_cast<const float2 *>(p);
-                    dst[0] = v.x; dst[1 % KV] = v.y;
-                } else {
-                    dst[0] = *p;
-                }
-            }
-    }
-#pragma unroll
-    for (int jj = 0; jj < FT_TN; ++jj) fb[jj] = bq[jj][kk % KV];
-#endif
 }
 
 // One stage: FT_BK k-slices, the fragments of slice kk + 1 requested before the multiplications of slice kk are issued.
-template <int KV>
 __device__ __forceinline__ void ft_stage(uint64_t (&acc2)[FT_TN][FT_TM / 2], const float *__restrict__ as,
                                          const float *__restrict__ bs) {
-    float fa[2][FT_TM], fb[2][FT_TN], bq[FT_TN][KV];
-    ft_load_fragments<KV>(0, as, bs, fa[0], fb[0], bq);
+    float fa[2][FT_TM], fb[2][FT_TN];
+    ft_load_fragments(0, as, bs, fa[0], fb[0]);
 #pragma unroll
     for (int kk = 0; kk < FT_BK; ++kk) {
-        if (kk + 1 < FT_BK) ft_load_fragments<KV>(kk + 1, as, bs, fa[(kk + 1) & 1], fb[(kk + 1) & 1], bq);
+        if (kk + 1 < FT_BK) ft_load_fragments(kk + 1, as, bs, fa[(kk + 1) & 1], fb[(kk + 1) & 1]);
         ffma_outer_product2<FT_TM, FT_TN>(acc2, fa[kk & 1], fb[kk & 1]);
     }
 }
+
+#if FT_XFORM
+// raw [FT_BN][FT_BK] (row = one n) -> tile [FT_BK][FT_BN] (row = one k), by one of the FT_XFORM_WARPS transposing warps.
+// A work item is 32 columns x one k-quad per lane: lane l reads the 16 bytes of column n0 + l at k-quad
+// (l * min(KQ, 8) / 8 + c) mod KQ — within the 8 lanes of a shared-memory wavefront the rows are 4*FT_BK bytes apart,
+// and rotating the k-quad spreads them over the banks — and writes its four values to four rows of the tile, where the
+// 32 lanes of the warp hit 32 consecutive words.
+__device__ __forceinline__ void ft_transpose_b(const float *__restrict__ raw, float *__restrict__ tile, uint32_t xwarp, uint32_t lane) {
+    constexpr uint32_t kItems = (FT_BN / 32) * FT_KQ;
+    constexpr uint32_t kSpread = FT_KQ < 8 ? FT_KQ : 8;
+    for (uint32_t item = xwarp; item < kItems; item += FT_XFORM_WARPS) {
+        const uint32_t n = (item / FT_KQ) * 32 + lane;
+        const uint32_t kq = ((lane % 8) * kSpread / 8 + item % FT_KQ) % FT_KQ;
+        const float4 v = *reinterpret_cast<const float4 *>(raw + n * FT_BK + kq * 4);
+        float *dst = tile + (kq * 4) * FT_BN + n;
+        dst[0] = v.x;
+        dst[FT_BN] = v.y;
+        dst[2 * FT_BN] = v.z;
+        dst[3 * FT_BN] = v.w;
+    }
+}
+#endif
 
 extern "C" __global__ void __launch_bounds__(FT_THREADS, 1)
 FT_ENTRY(const float *__restrict__ a, const float *__restrict__ b, const float *c, float *d,
@@ -216,9 +217,9 @@ FT_ENTRY(const float *__restrict__ a, const float *__restrict__ b, const float *
 
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(ft_smem_raw) + 127) & ~(uintptr_t)127);
     float *ring = reinterpret_cast<float *>(base);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(base + FT_STAGES * FT_STAGE_BYTES);   // full[S] | empty[S]
-    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(bars + 2 * FT_STAGES);
-    const uint32_t full0 = ft_smem_u32(bars), empty0 = ft_smem_u32(bars + FT_STAGES);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(base + FT_STAGES * FT_STAGE_FLOATS * 4);   // full[S] | empty[S] | ready[S]
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(bars + 3 * FT_STAGES);
+    const uint32_t full0 = ft_smem_u32(bars), empty0 = ft_smem_u32(bars + FT_STAGES), ready0 = ft_smem_u32(bars + 2 * FT_STAGES);
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
 
     if (threadIdx.x == 0) {
@@ -226,6 +227,7 @@ FT_ENTRY(const float *__restrict__ a, const float *__restrict__ b, const float *
         for (int s = 0; s < FT_STAGES; ++s) {
             ft_mbar_init(full0 + 8 * s, 1);
             ft_mbar_init(empty0 + 8 * s, FT_CONSUMER_WARPS);
+            ft_mbar_init(ready0 + 8 * s, FT_XFORM_WARPS);
         }
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -259,17 +261,32 @@ FT_ENTRY(const float *__restrict__ a, const float *__restrict__ b, const float *
                 // a stage is free once the consumers have read its previous contents (first round: free from the start)
                 if (!ft_wait(waiter, empty0 + 8 * s, (round & 1u) ^ 1u, FT_TAG_PRODUCER, t)) break;
                 const uint32_t full = full0 + 8 * s;
-                const uint32_t dst_a = ft_smem_u32(ring + (size_t)s * (FT_A_FLOATS + FT_B_FLOATS));
+                const uint32_t dst_a = ft_smem_u32(ring + (size_t)s * FT_STAGE_FLOATS);
                 const int32_t k0 = (int32_t)(k_begin + t * FT_BK);
-                ft_mbar_expect_tx(full, FT_STAGE_BYTES);
+                ft_mbar_expect_tx(full, FT_TMA_BYTES);
                 ft_tma_load_2d(dst_a, &map_a, full, (int32_t)m0, k0);
-#if GEMM_TRANS_B
-                ft_tma_load_2d(dst_a + FT_A_FLOATS * 4, &map_b, full, (int32_t)n0, k0);
+#if FT_XFORM
+                ft_tma_load_2d(dst_a + (FT_A_FLOATS + FT_B_FLOATS) * 4, &map_b, full, k0, (int32_t)n0);   // the raw buffer
 #else
-                ft_tma_load_2d(dst_a + FT_A_FLOATS * 4, &map_b, full, k0, (int32_t)n0);
+                ft_tma_load_2d(dst_a + FT_A_FLOATS * 4, &map_b, full, (int32_t)n0, k0);
 #endif
             }
         }
+#if FT_XFORM
+        // -------------------------------------------------------------- warps 1 to 3: transpose the B tile of every stage
+        // (the raw buffer and the tile of a stage are free when its copies land: the producer issued them only after
+        // the consumers had released the stage, and these warps finished with its raw buffer before the consumers began)
+        if (warp >= 1) {
+            for (uint32_t t = 0; t < steps; ++t) {
+                const uint32_t s = t % FT_STAGES, round = t / FT_STAGES;
+                if (!ft_wait(waiter, full0 + 8 * s, round & 1u, FT_TAG_XFORM, t)) break;
+                float *stage = ring + (size_t)s * FT_STAGE_FLOATS;
+                ft_transpose_b(stage + FT_A_FLOATS + FT_B_FLOATS, stage + FT_A_FLOATS, warp - 1, lane);
+                __syncwarp();
+                if (lane == 0) ft_mbar_arrive(ready0 + 8 * s);
+            }
+        }
+#endif
     } else {
 #if FT_REG_HANDOVER
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FT_REGS_CONSUMER));
@@ -283,18 +300,17 @@ FT_ENTRY(const float *__restrict__ a, const float *__restrict__ b, const float *
 #pragma unroll
             for (int i = 0; i < FT_TM / 2; ++i) acc2[j][i] = 0ull;
 
-        const uint32_t a_off = tx * 4;
-#if GEMM_TRANS_B
-        const uint32_t b_off = FT_A_FLOATS + ty * 4;
-#else
-        const uint32_t b_off = FT_A_FLOATS + ty * 4 * FT_BK;
-#endif
+        const uint32_t a_off = tx * 4, b_off = FT_A_FLOATS + ty * 4;
         bool ok = true;
         for (uint32_t t = 0; t < steps; ++t) {
             const uint32_t s = t % FT_STAGES, round = t / FT_STAGES;
+            // the A tile is TMA's: wait for the copies themselves, then (where B is transposed here) for the B tile
             if (!ft_wait(waiter, full0 + 8 * s, round & 1u, FT_TAG_CONSUMER, t)) { ok = false; break; }
-            const float *stage = ring + (size_t)s * (FT_A_FLOATS + FT_B_FLOATS);
-            ft_stage<FT_KV>(acc2, stage + a_off, stage + b_off);
+#if FT_XFORM
+            if (!ft_wait(waiter, ready0 + 8 * s, round & 1u, FT_TAG_READY, t)) { ok = false; break; }
+#endif
+            const float *stage = ring + (size_t)s * FT_STAGE_FLOATS;
+            ft_stage(acc2, stage + a_off, stage + b_off);
             __syncwarp();
             if (lane == 0) ft_mbar_arrive(empty0 + 8 * s);
         }

@@ -345,9 +345,9 @@ class GemmSolutionConfig:
                                    f"(128, 256, 384 or 512 threads)")
             if max(bm, bn, self.depth_k) > 256:
                 raise RuntimeError("a TMA box has at most 256 elements per dimension")
-            if not self.trans_b and bm // tm < 8:
-                raise RuntimeError("the K-contiguous B tile is read without bank conflicts only when 8 neighbouring lanes "
-                                   "share their columns: tile M / thread tile M must be at least 8")
+            if not self.trans_b and (bn % 32 or (self.depth_k // 4) & (self.depth_k // 4 - 1)):
+                raise RuntimeError("an untransposed B is transposed in shared memory 32 columns and a power-of-two number "
+                                   "of k-quads at a time: tile N must be a multiple of 32, depth_k / 4 a power of two")
             if self.stages < 2 or self.stages > 12:
                 raise RuntimeError(f"{self.stages} stages: the TMA ring has 2 to 12")
 
@@ -410,7 +410,9 @@ class GemmSolutionConfig:
         if self.variant == VARIANT_TENSOR:
             return self._ring_bytes()
         if self.feed == "tma":
-            return self.stages * self.depth_k * (bm + bn) * 4 + 128 + 256         # ring + alignment slack + barriers
+            # A tile, B tile and, for an untransposed B, the raw buffer TMA fills before the tile is transposed
+            raw = 0 if self.trans_b else bn
+            return self.stages * self.depth_k * (bm + bn + raw) * 4 + 128 + 512   # ring + alignment slack + barriers
         return 2 * self.depth_k * (bm + 4 + bn + 4) * 4                          # double-buffered, padded A and B
 
     @property

@@ -70,6 +70,7 @@ REGISTRY = {
     "simt_128x128x16_t16x8": (lambda: simt_config(128, 128, 16, 16, 8), dict(wgm=8)),   # best of the FFMA sweep at 4096^3
     "simt_64x64x16": (lambda: simt_config(64, 64, 16, 4, 4), dict(wgm=4)),
     # FFMA kernels fed by TMA (a producer thread, mbarrier ring, consumers that only multiply)
+    "ffma_tma_256x128x32_s3": (lambda: simt_config(256, 128, 32, 16, 8, feed="tma", stages=3), dict(wgm=8)),   # best of the staged FFMA search at 8192^3
     "ffma_tma_256x128x16_s4": (lambda: simt_config(256, 128, 16, 16, 8, feed="tma", stages=4), dict(wgm=8)),
     "ffma_tma_128x256x16_s4": (lambda: simt_config(128, 256, 16, 8, 16, feed="tma", stages=4), dict(wgm=8)),
     "ffma_tma_128x128x16_s4": (lambda: simt_config(128, 128, 16, 8, 8, feed="tma", stages=4), dict(wgm=8)),
@@ -154,6 +155,9 @@ def _registered_like(entry) -> str | None:
             continue
         if (list(cfg.tile_size), cfg.depth_k, list(cfg.wave_group)) != (entry["tile"], entry["depth_k"], entry["cluster"]):
             continue
+        if cfg.variant == "simt_ffma" and (getattr(cfg, "feed", "ldg") != entry.get("feed", "ldg")
+                                           or (cfg.feed == "tma" and cfg.stages != entry["stages"])):
+            continue
         if cfg.variant == "tcgen05_3xtf32" and (cfg.stages != entry["stages"] or getattr(cfg, "split", "prepass") != entry["split"]
                                                 or getattr(cfg, "a_major", "mn") == "k" or getattr(cfg, "terms", 3) != (3 if want_type == DataType.FP32 else 1)
                                                 or getattr(cfg, "epilogue_warps", 8) != 8):
@@ -162,8 +166,15 @@ def _registered_like(entry) -> str | None:
     return None
 
 
-def recommend(m: int, n: int, k: int, operands: str = "fp32") -> str:
+DEFAULT_SIMT_LARGE = "ffma_tma_256x128x32_s3"   # strict FP32 on problems of many 256 x 128 tiles
+
+
+def recommend(m: int, n: int, k: int, operands: str = "fp32", strict_fp32: bool = False) -> str:
     """Registered kernel to use for a problem of this shape on a B200 (NN layout).
+
+    ``strict_fp32`` asks for the FFMA variant (every product and sum in IEEE FP32, what ``force_variant`` 2 runs): the
+    tuner table's FFMA entry nearest to the problem if a registered kernel has its structure, else the TMA-fed kernel
+    when the problem has at least two waves of its 256 x 128 tiles, else the register-fed default.
 
     A handle serves one cubin, so choosing between configurations is the caller's (or the tuner's) job, as in the
     reference where the tuner picks one configuration per problem size.  Two sources, in this order:
@@ -180,6 +191,24 @@ def recommend(m: int, n: int, k: int, operands: str = "fp32") -> str:
     import math
 
     flops = 2.0 * m * n * k
+    if strict_fp32:
+        if operands != "fp32":
+            raise ValueError("the FFMA variant computes on FP32 operands only")
+        try:
+            entries = json.loads(TUNED_TABLE.read_text())["entries"]
+        except (OSError, ValueError, KeyError):
+            entries = []
+        near = None
+        for e in entries:
+            if e["operands"] != "fp32" or e["variant"] != "simt_ffma":
+                continue
+            steps = [abs(math.log2(x / y)) for x, y in ((m, e["m"]), (n, e["n"]), (k, e["k"]))]
+            if max(steps) <= 1.0 and (near is None or sum(steps) < near[0]):
+                near = (sum(steps), e)
+        name = _registered_like(near[1]) if near is not None else None
+        if name is not None:
+            return name
+        return DEFAULT_SIMT_LARGE if -(-m // 256) * -(-n // 128) >= 2 * 148 else DEFAULT_SIMT
     if operands == "fp32":
         if flops < 2 ** 27:
             return DEFAULT_SIMT

@@ -59,8 +59,9 @@ SUPPORTED_SIMT = [((16, 16), (8, 8), 16), ((16, 16), (8, 8), 8), ((16, 8), (8, 8
                   ((8, 16), (16, 8), 16), ((16, 16), (8, 8), 32)]
 # FFMA variant fed by TMA (producer thread + mbarrier ring, one block per SM): (thread grid of the consumers,
 # per-thread tile, k per stage, stages)
-SUPPORTED_SIMT_TMA = [((16, 16), (16, 8), 16, 4), ((16, 16), (8, 16), 16, 4), ((16, 16), (8, 8), 16, 4),
-                      ((32, 16), (8, 8), 16, 4), ((16, 16), (16, 8), 32, 3), ((16, 8), (16, 8), 16, 6)]
+SUPPORTED_SIMT_TMA = [((16, 16), (16, 8), 16, 4), ((16, 16), (16, 8), 16, 3), ((16, 16), (16, 8), 16, 6),
+                      ((16, 16), (16, 8), 8, 6), ((16, 16), (16, 8), 32, 3), ((16, 16), (8, 16), 16, 4),
+                      ((16, 16), (8, 8), 16, 4), ((32, 16), (8, 8), 16, 4), ((16, 8), (16, 8), 16, 6)]
 SUPPORTED_WGM = [1, 4, 8, 16]
 SUPPORTED_PLR = [0, 1]
 VERBOSE = False
@@ -142,9 +143,9 @@ def predict_time_us(config: GemmSolutionConfig, m: int, n: int, k: int, sm_count
         reuse = min(1.0, 0.4 + 0.6 * (ttm * ttn) / (ttm + ttn) / 4.0)      # FMAs per shared-memory word loaded, 8 x 8 -> 1
         depth = min(1.0, 0.7 + 0.3 * config.depth_k / 16.0)
         k_unit = -(-kb_total // split) * config.depth_k
-        # one block computes tm x tn x k_unit FMAs on half an SM's 128 lanes (all of them when fed by TMA, where the
-        # measured rate with a K-contiguous B tile is a tenth below the register-fed kernel's)
-        clks = tm * tn * k_unit / (128.0 if tma_fed else 64.0) / (0.8 * reuse * depth * (0.9 if tma_fed else 1.0))
+        # one block computes tm x tn x k_unit FMAs on half an SM's 128 lanes (all of them when fed by TMA, whose
+        # multiplying warps issue nothing but fragment loads and FMAs: measured 5 % above the register-fed kernel)
+        clks = tm * tn * k_unit / (128.0 if tma_fed else 64.0) / (0.8 * reuse * depth * (1.05 if tma_fed else 1.0))
         extra = (launch_us + (split + 1) * m * n * 4 / hbm_bytes_per_us) if split > 1 else 0.0
         return waves * clks / (ghz * 1e3) + launch_us + extra
     cluster = config.wave_group[0]
@@ -285,7 +286,7 @@ class Measurer:
         self.measured += 1
         rec = {"key": problem_key, "returncode": ret.returncode, "tile": list(config.tile_size), "depth_k": config.depth_k,
                "stages": config.stages, "cluster": list(config.wave_group), "variant": config.variant, "wgm": opt.wgm,
-               "plr": opt.plr, "split": getattr(config, "split", ""), "runs": runs}
+               "plr": opt.plr, "split": getattr(config, "split", ""), "feed": getattr(config, "feed", "ldg"), "runs": runs}
         if not ret.returncode:
             rec["gflops"] = parse_gflops(ret.stdout.decode())
         else:
@@ -296,9 +297,17 @@ class Measurer:
         return rec
 
 
+def describe(rec) -> str:
+    """The variant of a record and what distinguishes kernels within it: where the lo terms are made (tensor variant),
+    how the tiles reach shared memory (FFMA variant)."""
+    if rec["variant"] == "simt_ffma":
+        return f"simt_ffma {'tma' if rec.get('feed') == 'tma' or ' tma ' in rec.get('key', '') else 'ldg'}-fed"
+    return f"{rec['variant']} {rec.get('split', '')}"
+
+
 def report(rec) -> None:
     print(f"Gflops: {rec['gflops']}, MT: {tuple(rec['tile'])}, DK: {rec['depth_k']}, wgm: {rec['wgm']}, plr: {rec['plr']}, "
-          f"stages: {rec['stages']}, cluster: {tuple(rec['cluster'])}, variant: {rec['variant']} {rec.get('split', '')}")
+          f"stages: {rec['stages']}, cluster: {tuple(rec['cluster'])}, variant: {describe(rec)}")
 
 
 def staged_search(points, measure, m: int, n: int, k: int, shortlist: int = 40, short_runs: int = 5, long_runs: int = 50,
@@ -375,17 +384,23 @@ def tune(m: int, n: int, k: int, bench: str, output_folder: str, include_simt: b
         print(f"staged search: {calls} measurements asked for ({measure.measured} new) of {total} points in the full product")
     if best is not None:
         print(f"Best: {best['gflops']} Gflops, MT: {tuple(best['tile'])}, DK: {best['depth_k']}, wgm: {best['wgm']}, "
-              f"plr: {best['plr']}, stages: {best['stages']}, cluster: {tuple(best['cluster'])}, variant: {best['variant']} "
-              f"{best.get('split', '')}")
+              f"plr: {best['plr']}, stages: {best['stages']}, cluster: {tuple(best['cluster'])}, variant: {describe(best)}")
     else:
         print("No valid configurations found.")
     return best
 
 
-def summarise(paths, table_path: str) -> dict:
+def summarise(paths, table_path: str, merge: bool = True) -> dict:
     """Best measured configuration per (problem, variant, operand type) over result files -> the JSON table
-    ``kernels.recommend`` consults (``tuner/tuned.json``)."""
+    ``kernels.recommend`` consults (``tuner/tuned.json``).  With ``merge`` the entries of an existing table are kept
+    unless a result file holds a faster configuration for the same slot (sweeps come from different sessions)."""
     best = {}
+    if merge and Path(table_path).exists():
+        try:
+            for e in json.loads(Path(table_path).read_text())["entries"]:
+                best[f"{e['m']}x{e['n']}x{e['k']} {e['variant']} {e['operands']}"] = e
+        except (ValueError, KeyError):
+            best = {}
     for path in paths:
         for rec in load_done(Path(path)).values():
             if rec.get("returncode") or "gflops" not in rec:
@@ -400,7 +415,8 @@ def summarise(paths, table_path: str) -> dict:
                 m, n, k = (int(x) for x in problem.split("x"))
                 best[slot] = {"m": m, "n": n, "k": k, "operands": operand, "variant": rec["variant"], "gflops": rec["gflops"],
                               "tile": rec["tile"], "depth_k": rec["depth_k"], "stages": rec["stages"], "cluster": rec["cluster"],
-                              "wgm": rec["wgm"], "plr": rec["plr"], "split": rec.get("split") or "prepass", "key": rec["key"]}
+                              "wgm": rec["wgm"], "plr": rec["plr"], "split": rec.get("split") or "prepass",
+                              "feed": "tma" if rec.get("feed") == "tma" or " tma " in rec["key"] else "ldg", "key": rec["key"]}
     table = {"entries": sorted(best.values(), key=lambda e: (e["operands"], e["variant"], e["m"] * e["n"] * e["k"]))}
     Path(table_path).write_text(json.dumps(table, indent=1) + "\n")
     return table

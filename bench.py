@@ -24,6 +24,7 @@ What one JSON line carries:
   e2e                   the measurement through the host-buffer entry points with pinned HOST buffers, uploads and
                         downloads inside the timed region; with N ranks every rank uploads 1/N of the replicated A and
                         the ranks complete it with an all-gather over NVLink (sgemm_run_host_sharded).
+  ffma_path             the same problem on the FFMA kernel (strict FP32), with the FP32 FMA peak at the sampled clock.
   cpu_baseline          the reference's CPU GEMM (oracle restatement) on the box's host cores, N = 1 only.
 
 --impl reference times the reference's CPU GEMM (restated in oracle/, its native runner needs HIP and cannot be
@@ -361,6 +362,7 @@ def main():
     ap.add_argument("--c5-seconds", type=float, default=2.5, help="timed length of the 32768 x 32768 x 8192 record (0: skip)")
     ap.add_argument("--parity-columns", type=int, default=16, help="columns of D every rank checks against the oracle (0: skip)")
     ap.add_argument("--no-tf32-probe", dest="tf32_probe", action="store_false", help="skip the plain-TF32 probe of the tensor rate")
+    ap.add_argument("--no-ffma", dest="ffma", action="store_false", help="skip the FFMA-path record of the same problem")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -475,6 +477,41 @@ def main():
             torch.cuda.synchronize()
         except Exception as exc:   # noqa: BLE001 - the probe is informational
             probe = {"error": str(exc)[:200]}
+
+    # The FFMA path on the same problem (strict FP32: the other arm of the 8192^3 comparison), on the kernel
+    # kernels.recommend names for it; outside every other figure.  Its roof is the FP32 FMA pipe, 128 lanes per SM and
+    # clock, at the clock NVML samples during the launches.
+    ffma = None
+    if args.ffma and args.workload == "c3" and args.kernel is None and args.size == 8192:   # (the headline run only)
+        try:
+            fname = kernels.recommend(job.m, n_local, job.k, strict_fp32=True)
+            fr = api.SgemmRunner(*kernels.ensure(fname), local_rank)
+            fr.set_option("force_variant", 2)
+            fr.set_workspace(job.ws, job.ws.numel())
+            for _ in range(3):
+                fr.launch(job.a, job.b, None, job.d, job.m, n_local, job.k, alpha=1.0, beta=0.0, stream=stream)
+            job.barrier()
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            runs = 10
+            sampler.start()
+            f0.record()
+            for _ in range(runs):
+                fr.launch(job.a, job.b, None, job.d, job.m, n_local, job.k, alpha=1.0, beta=0.0, stream=stream)
+            f1.record()
+            torch.cuda.synchronize()
+            fclk = sampler.stop()
+            fms = f0.elapsed_time(f1) / runs
+            frate = 2.0 * job.m * n_local * job.k / (fms * 1e-3) * 1e-12
+            fmhz = fclk.get("sm_mhz") if fclk and fclk.get("valid") else None
+            fpeak = sm_count * 128 * 2 * fmhz * 1e6 * 1e-12 if fmhz else None
+            ffma = {"kernel": fname, "fed_by_tma": bool(fr.info("last_feed_tma")), "launches": runs, "ms_per_launch": fms,
+                    "tflops": frate, "sm_mhz": fmhz, "fp32_peak_tflops_at_that_clock": fpeak,
+                    "frac": frate / fpeak if fpeak else None, "device_status": fr.last_status()[0]}
+            fr.close()
+            job.step()          # D holds the FFMA product: recompute the tensor-path one before anything reads it
+            torch.cuda.synchronize()
+        except Exception as exc:   # noqa: BLE001 - informational
+            ffma = {"error": str(exc)[:200]}
 
     # sustained: the same step for a few seconds, clock-sampled, so that the power-capped rate is on record
     sustained = None
@@ -634,7 +671,7 @@ def main():
             "roofline": roofline, "e2e": e2e, "gpu_launches": head["launches"], "clocks": head["clocks"],
             "main_kernel_ms_per_rank": head["main_kernel_ms_per_rank"],
             "sustained": sustained, "parity": parity, "c5": c5,
-            "device_status": max(status[0], status2[0]), "allgather": allgather,
+            "device_status": max(status[0], status2[0]), "allgather": allgather, "ffma_path": ffma,
         }
         if world == 1 and not args.no_cpu_baseline:
             from oracle import oracle

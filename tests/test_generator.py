@@ -240,7 +240,8 @@ def test_tma_fed_ffma_configuration():
     cfg = g.simt_config(256, 128, 16, 16, 8, feed="tma", stages=4)
     assert cfg.variant == g.VARIANT_SIMT and cfg.tile_size == (256, 128) and cfg.stages == 4
     assert cfg.num_workitems == 128 + 256                                   # the producer's warp group + 256 consumers
-    assert cfg.lds_usage_bytes == 4 * (256 + 128) * 16 * 4 + 128 + 256
+    assert cfg.lds_usage_bytes == 4 * (256 + 128 + 128) * 16 * 4 + 128 + 512  # A, B and the raw B that is transposed into it
+    assert g.simt_config(256, 128, 16, 16, 8, trans_b=True, feed="tma", stages=4).lds_usage_bytes == 4 * (256 + 128) * 16 * 4 + 128 + 512
     d = cfg.to_dict()
     assert d["variant"] == g.VARIANT_SIMT and d["feed"] == "tma" and d["dynamic_smem_bytes"] == cfg.lds_usage_bytes
     assert d["fallback_entry"] == g.SIMT_FALLBACK_ENTRY and d["fallback_tile"] == [128, 128, 16] and d["fallback_threads"] == 256

@@ -12,7 +12,7 @@ from test_gpu_parity import check, run, runner_of, stored  # noqa: F401  (runner
 pytestmark = pytest.mark.gpu
 
 SIMT = 2
-KERNELS = ["ffma_tma_256x128x16_s4", "ffma_tma_128x256x16_s4", "ffma_tma_128x128x16_s4", "ffma_tma_128x128x16_t16x8_s6"]
+KERNELS = ["ffma_tma_256x128x32_s3", "ffma_tma_256x128x16_s4", "ffma_tma_128x256x16_s4", "ffma_tma_128x128x16_s4", "ffma_tma_128x128x16_t16x8_s6"]
 SHAPES = [(1, 1, 1), (8, 8, 8), (32, 32, 32), (33, 65, 129), (127, 257, 513), (256, 128, 16), (257, 129, 17),
           (512, 384, 96), (1000, 1000, 1000), (1024, 1024, 1024), (130, 4, 2048), (4, 300, 77)]
 

@@ -166,3 +166,32 @@ def test_summarise_writes_the_table_recommend_reads(golden_dir, tmp_path):
     assert entries[(8192, "tcgen05_3xtf32")]["tile"] == [256, 256] and entries[(8192, "tcgen05_3xtf32")]["cluster"] == [2, 1]
     assert entries[(4096, "simt_ffma")]["tile"] == [128, 128]
     assert json.loads((tmp_path / "tuned.json").read_text()) == table
+
+
+def test_tma_fed_ffma_structures_are_searched_and_recorded(tmp_path):
+    """The FFMA space has a feed dimension; records and the table say which feed a measurement was of, and an existing
+    table keeps its entries unless a result file holds a faster one for the same slot."""
+    keys = [k for k, _, _ in t.structural_candidates(True, False)]
+    tma = [k for k in keys if k.startswith("simt tma ")]
+    assert len(tma) == len(t.SUPPORTED_SIMT_TMA) and len(set(keys)) == len(keys)
+    for key, make_config, variations in t.structural_candidates(True, False):
+        if key.startswith("simt tma "):
+            cfg = make_config()
+            assert cfg.feed == "tma" and cfg.num_workitems % 128 == 0 and len(variations) == len(t.SUPPORTED_WGM)
+            assert t.predict_time_us(cfg, 8192, 8192, 8192) > 0
+    fed = {"key": "8192x8192x8192 simt tma g16x16 t16x8 k32 s3 wgm4", "returncode": 0, "tile": [256, 128], "depth_k": 32,
+           "stages": 3, "cluster": [16, 16], "variant": "simt_ffma", "wgm": 4, "plr": 1, "split": "prepass", "feed": "tma",
+           "runs": 50, "gflops": 60825.0}
+    slow = dict(fed, key="8192x8192x8192 simt g16x16 t8x8 k16 wgm8 plr1", tile=[128, 128], depth_k=16, stages=2, feed="ldg", gflops=54000.0)
+    assert t.describe(fed) == "simt_ffma tma-fed" and t.describe(slow) == "simt_ffma ldg-fed"
+    log = tmp_path / "a.jsonl"
+    log.write_text(json.dumps(slow) + "\n")
+    table = t.summarise([log], str(tmp_path / "tuned.json"))
+    assert [e["feed"] for e in table["entries"]] == ["ldg"]
+    log2 = tmp_path / "b.jsonl"
+    log2.write_text(json.dumps(fed) + "\n" + json.dumps(dict(fed, key="1024x1024x1024 simt tma g16x16 t16x8 k32 s3 wgm4", gflops=20000.0)) + "\n")
+    table = t.summarise([log2], str(tmp_path / "tuned.json"))          # merged into the table written above
+    got = {(e["m"], e["feed"]): e["gflops"] for e in table["entries"]}
+    assert got == {(8192, "tma"): 60825.0, (1024, "tma"): 20000.0}
+    table = t.summarise([log], str(tmp_path / "tuned.json"))           # a slower measurement does not displace the entry
+    assert {(e["m"], e["feed"]) for e in table["entries"]} == {(8192, "tma"), (1024, "tma")}
