@@ -286,15 +286,18 @@ int main(int argc, char **argv) {
         if ((rc = sgemm_last_status(r.h, status))) return die(r.h, "device status check", rc);
         if (sgemm_get_info(r.h, "sm_khz_effective", &khz) == 0) r.sm_mhz = (double)khz * 1e-3;
     }
-    int64_t variant = 0, split = 0;
+    int64_t variant = 0, split = 0, fed_by_tma = 0;
     sgemm_get_info(h, "last_variant", &variant);
+    sgemm_get_info(h, "last_feed_tma", &fed_by_tma);
     sgemm_get_info(h, "last_split_k", &split);
     sgemm_get_info(h, "launches", &info);
     // 1 = the cubin's main tensor kernel, 3 = its companion for problems with few flops per input byte, 2 = SIMT
     const char *variant_text = half ? (parsed.a_type == 2 ? "tcgen05 BF16" : "tcgen05 FP16")
-                               : variant == 1 ? "tcgen05 3xTF32" : variant == 3 ? "tcgen05 3xTF32 (companion)" : "SIMT FFMA";
+                               : variant == 1 ? "tcgen05 3xTF32" : variant == 3 ? "tcgen05 3xTF32 (companion)"
+                               : fed_by_tma ? "SIMT FFMA (fed by TMA)" : "SIMT FFMA";
     const char *variant_key = half ? (parsed.a_type == 2 ? "tcgen05_bf16" : "tcgen05_fp16")
-                              : variant == 1 ? "tcgen05_3xtf32" : variant == 3 ? "tcgen05_3xtf32_companion" : "simt_ffma";
+                              : variant == 1 ? "tcgen05_3xtf32" : variant == 3 ? "tcgen05_3xtf32_companion"
+                              : fed_by_tma ? "simt_ffma_tma" : "simt_ffma";
     std::fprintf(stderr, "measured kernel: %s, split_k %lld, %.3f TFLOPS, %lld launches in total, SM clock counted on the device %.0f MHz\n",
                  variant_text, (long long)split, gflops(m, n, k, ms) * 1e-3, (long long)info, g_ranks[0].sm_mhz);
     std::string per_gpu_json = "[";

@@ -29,7 +29,7 @@ def test_cli_on_the_1024_cubed_configuration_as_worded(built):
     assert float(lines[-3].split(":")[-1]) > 0 and "tcgen05 3xTF32" in ret.stderr
 
 
-@pytest.mark.parametrize("kernel", ["tc_128x256x32_s2", "simt_128x128x16"])
+@pytest.mark.parametrize("kernel", ["tc_128x256x32_s2", "simt_128x128x16", "ffma_tma_256x128x16_s4"])
 def test_cli_stdout_contract_and_validation(built, kernel):
     ret = run_cli(built, kernel, 512, 768, 640, 1)
     assert ret.returncode == 0, ret.stdout + ret.stderr
@@ -43,7 +43,7 @@ def test_cli_stdout_contract_and_validation(built, kernel):
         ret = run_cli(built, kernel, 512, 768, 640, 0, env={"SGEMM_JSON": f"{tmp}/r.json", "SGEMM_BETA": "0", "SGEMM_SEED": "7"})
         rec = json.load(open(f"{tmp}/r.json"))
     assert (rec["m"], rec["n"], rec["k"], rec["beta"], rec["seed"], rec["validated"]) == (512, 768, 640, 0, 7, False)
-    assert rec["tflops"] > 0 and rec["variant"].startswith("tcgen05_3xtf32" if kernel.startswith("tc") else "simt_ffma")
+    assert rec["tflops"] > 0 and rec["variant"] == {"tc": "tcgen05_3xtf32", "si": "simt_ffma", "ff": "simt_ffma_tma"}[kernel[:2]]
     assert ret.returncode == 0
     gflops = float(ret.stdout.split("\n")[-3].split(":")[-1])   # tuner/sgemm_tuner.py:115
     assert gflops > 0
