@@ -43,7 +43,8 @@ def test_cli_stdout_contract_and_validation(built, kernel):
         ret = run_cli(built, kernel, 512, 768, 640, 0, env={"SGEMM_JSON": f"{tmp}/r.json", "SGEMM_BETA": "0", "SGEMM_SEED": "7"})
         rec = json.load(open(f"{tmp}/r.json"))
     assert (rec["m"], rec["n"], rec["k"], rec["beta"], rec["seed"], rec["validated"]) == (512, 768, 640, 0, 7, False)
-    assert rec["tflops"] > 0 and rec["variant"] == {"tc": "tcgen05_3xtf32", "si": "simt_ffma", "ff": "simt_ffma_tma"}[kernel[:2]]
+    want = {"tc": "tcgen05_3xtf32", "si": "simt_ffma", "ff": "simt_ffma_tma"}[kernel[:2]]   # (a small problem runs on the tensor cubin's companion)
+    assert rec["tflops"] > 0 and (rec["variant"].startswith(want) if kernel.startswith("tc") else rec["variant"] == want)
     assert ret.returncode == 0
     gflops = float(ret.stdout.split("\n")[-3].split(":")[-1])   # tuner/sgemm_tuner.py:115
     assert gflops > 0
