@@ -120,6 +120,7 @@ __device__ __forceinline__ void ft_tma_load_2d(uint32_t dst, const FtTensorMap *
 struct FtWait {
     volatile uint32_t *abort_flag;  // shared memory, block-wide
     uint32_t *status;               // global memory, SGEMM_STATUS_WORDS words
+    uint64_t timeout_ns;            // how long one wait may go without the barrier completing
 };
 // tags of the status record: which role gave up
 #define FT_TAG_PRODUCER 0x46540001u   // producer waiting for a stage to be read ("empty")
@@ -134,7 +135,7 @@ __device__ __forceinline__ bool ft_wait_slow(const FtWait &w, uint32_t bar, uint
         if (ft_mbar_try_wait(bar, parity)) return true;
         if ((++spins & 31u) == 0u) {
             if (*w.abort_flag) return false;
-            if (ft_globaltimer() - t0 > FT_TIMEOUT_NS) {
+            if (ft_globaltimer() - t0 > w.timeout_ns) {
                 *w.abort_flag = 1u;
                 if (atomicCAS(w.status, SGEMM_STATUS_OK, SGEMM_STATUS_TIMEOUT) == SGEMM_STATUS_OK) {
                     w.status[1] = tag;
@@ -233,7 +234,7 @@ FT_ENTRY(const float *__restrict__ a, const float *__restrict__ b, const float *
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    const FtWait waiter{abort_flag, status};
+    const FtWait waiter{abort_flag, status, FT_TIMEOUT_NS};
 
     sgemm_launch_dependents();
     sgemm_grid_dependency_wait();
@@ -333,4 +334,27 @@ FT_ENTRY(const float *__restrict__ a, const float *__restrict__ b, const float *
         const uint64_t t0 = ft_globaltimer();
         while (ft_globaltimer() - t0 < 2000000ull) __nanosleep(1000);
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Self-test of the bounded wait (same entry name and arguments as the tensor kernels' self-test, of which a cubin
+// holds one or the other): one block initialises an mbarrier that nothing will ever arrive on and waits on it with this
+// kernel's own wait routine and a short limit.  The wait must run out, record the status words and return, the kernel
+// must end normally and the context must stay usable.
+// ---------------------------------------------------------------------------------------------
+extern "C" __global__ void sgemm_wait_selftest(uint32_t *status, uint64_t timeout_ns, uint32_t tag) {
+    __shared__ __align__(8) uint64_t barrier_storage;
+    __shared__ uint32_t abort_flag;
+    sgemm_grid_dependency_wait();
+    if (threadIdx.x == 0) {
+        ft_mbar_init(ft_smem_u32(&barrier_storage), 1);
+        abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const FtWait waiter{&abort_flag, status, timeout_ns};
+    // every thread waits; the first whose limit runs out reports, the others leave through the abort flag
+    const bool completed = ft_wait(waiter, ft_smem_u32(&barrier_storage), 0u, tag, threadIdx.x);
+    if (completed && threadIdx.x == 0) status[6] = 0xBAD0BAD0u;   // cannot happen: nobody arrives
+    __syncthreads();
 }

@@ -883,7 +883,7 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
         {&h->fn_reduce, "sgemm_splitk_reduce", true},
         {&h->fn_fill, "sgemm_fill_uniform", true},
         {&h->fn_tile_map, "sgemm_tile_map", true},
-        {&h->fn_wait_selftest, "sgemm_wait_selftest", cfg.variant == kVariantTensor},
+        {&h->fn_wait_selftest, "sgemm_wait_selftest", cfg.variant == kVariantTensor || cfg.feed_tma != 0},
     };
     for (const Want &w : wants) {
         if (!w.required) continue;   // entry points that only one variant's cubin contains stay NULL in the other's handle
@@ -1229,7 +1229,7 @@ SGEMM_API int sgemm_last_status(sgemm_handle *h, uint32_t status[8]) {
 SGEMM_API int sgemm_wait_selftest(sgemm_handle *h, uint32_t timeout_ms, uint32_t tag) {
     if (!h || timeout_ms == 0 || timeout_ms > 1000) return SGEMM_ERR_INVALID_ARGUMENT;
     if (!h->fn_wait_selftest)
-        return fail(h, SGEMM_ERR_UNSUPPORTED, "the loaded cubin has no tensor-core kernel, hence no bounded waits to test");
+        return fail(h, SGEMM_ERR_UNSUPPORTED, "the loaded cubin has no kernel fed by TMA, hence no bounded waits to test");
     CtxGuard guard(h);
     uint32_t *status_ptr = reinterpret_cast<uint32_t *>(h->status);
     uint64_t timeout_ns = (uint64_t)timeout_ms * 1000000ull;

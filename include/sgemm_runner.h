@@ -199,7 +199,8 @@ int sgemm_last_status(sgemm_handle *h, uint32_t status[8]);
  * one-block kernel that waits, with the GEMM kernel's own bounded-wait routine and a limit of `timeout_ms`
  * (1..1000), on a barrier nothing arrives on.  The wait runs out, the kernel records the status words and ends
  * normally; the following sgemm_last_status must return SGEMM_ERR_DEVICE_STATUS with status[1] == tag, and the
- * handle must keep working.  Tensor-variant cubins only. */
+ * handle must keep working.  Cubins whose main kernel is fed by TMA (tensor variant, TMA-fed FFMA) only: the
+ * register-fed FFMA kernel waits on nothing. */
 int sgemm_wait_selftest(sgemm_handle *h, uint32_t timeout_ms, uint32_t tag);
 
 /* Options: "force_variant" 0 auto, 1 tensor (main kernel), 2 simt, 3 tensor (companion kernel for skinny shapes);

@@ -482,8 +482,21 @@ def test_bounded_wait_runs_out_reports_and_leaves_the_context_usable(built):
         d = run(r, a, b, c, m, n, k, 1.0, 1.0, force=TENSOR, split_k=2)
         check(d, a, b, c, m, n, k, 1.0, 1.0)
         assert r.last_status()[0] == 0
+    cubin, toml = built.ensure("ffma_tma_256x128x16_s4")     # the TMA-fed FFMA kernel has its own copy of the wait routine
+    with api.SgemmRunner(cubin, toml, 0) as r:
+        r.wait_selftest(timeout_ms=20, tag=0x51DF)
+        with pytest.raises(api.SgemmError) as e:
+            r.last_status()
+        assert e.value.code == -8 and "0x51df" in str(e.value)
+        assert r.last_status()[0] == 0
+        m, n, k = 300, 260, 520
+        a, b, c = oracle.make_inputs(m, n, k, seed=5, lda=300, ldb=520)
+        d = run(r, a, b, c, m, n, k, 1.0, 1.0, force=SIMT, split_k=2)
+        assert r.info("last_feed_tma") == 1
+        check(d, a, b, c, m, n, k, 1.0, 1.0, lda=300, ldb=520)
+        assert r.last_status()[0] == 0
     cubin, toml = built.ensure("simt_128x128x16")
-    with api.SgemmRunner(cubin, toml, 0) as r:               # an FFMA-only cubin has no bounded waits
+    with api.SgemmRunner(cubin, toml, 0) as r:               # a register-fed FFMA cubin has no bounded waits
         with pytest.raises(api.SgemmError) as e:
             r.wait_selftest()
         assert e.value.code == -6
