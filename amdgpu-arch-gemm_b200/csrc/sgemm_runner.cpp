@@ -938,15 +938,28 @@ SGEMM_API int sgemm_open(const char *cubin_path, const char *toml_path, int devi
         fail(h, SGEMM_ERR_CUDA, "cannot opt in to %d bytes of dynamic shared memory: %s", cfg.dynamic_smem_bytes, cu_text(r).c_str());
         return bail(SGEMM_ERR_CUDA);
     }
-    if (cfg.feed_tma && cfg.num_threads >= 384) {
-        // The TMA-fed FFMA kernel hands registers from its first warp group to the consumers, and a consumer waits
-        // without limit for registers the block was never given.  The kernel's budget assumes the launch allocation
-        // __launch_bounds__ allows; a cubin compiled to fewer must not be launched.
+    // Kernels that hand registers from one warp group to another (setmaxnreg) size the shares from the launch
+    // allocation __launch_bounds__ allows, and a growing warp waits without limit for registers the block was never
+    // given: a cubin whose entry was compiled to a different register count must not be launched.  That is the TMA-fed
+    // FFMA kernel with 256 or more consumers, and a tensor kernel with chunked accumulation and 8 epilogue warps.
+    auto hands_over = [&](uint32_t threads, bool inkernel, uint32_t acc_chain) {
+        if (cfg.variant != kVariantTensor) return cfg.feed_tma != 0 && threads >= 384;
+        const uint32_t epilogue_warps = (threads - 128 - (inkernel ? 128 : 0)) / 32;
+        return acc_chain > 0 && epilogue_warps == 8;
+    };
+    struct Entry { CUfunction fn; const char *name; uint32_t threads; bool inkernel; uint32_t acc_chain; };
+    const Entry entries[] = {
+        {h->tk_main.fn, cfg.entry, h->tk_main.threads, h->tk_main.split_inkernel, h->tk_main.acc_chain},
+        {h->tk_skinny.fn, cfg.skinny_entry, h->tk_skinny.threads, true, h->tk_skinny.acc_chain},
+        {h->tk_thin.fn, cfg.thin_entry, h->tk_thin.threads, true, h->tk_thin.acc_chain},
+    };
+    for (const Entry &e : entries) {
+        if (!e.fn || e.threads < 256 || !hands_over(e.threads, e.inkernel, e.acc_chain)) continue;
         int regs = 0;
-        const int expect = (512 / (cfg.num_threads / 128)) / 8 * 8;
-        if ((r = d.cuFuncGetAttribute_(&regs, CU_FUNC_ATTRIBUTE_NUM_REGS, h->fn_main)) != CUDA_SUCCESS || regs != expect) {
+        const int expect = (512 / (int)(e.threads / 128)) / 8 * 8;
+        if ((r = d.cuFuncGetAttribute_(&regs, CU_FUNC_ATTRIBUTE_NUM_REGS, e.fn)) != CUDA_SUCCESS || regs != expect) {
             fail(h, SGEMM_ERR_MODULE, "'%s' in '%s' uses %d registers per thread where its register hand-over assumes %d",
-                 cfg.entry, cubin_path, regs, expect);
+                 e.name, cubin_path, regs, expect);
             return bail(SGEMM_ERR_MODULE);
         }
     }
