@@ -272,3 +272,147 @@ class Model:
                 tuple((b.phase, b.pending, b.tx) for cl in self.clusters for c in cl
                       for b in c.full + c.empty + c.ready + c.tfull + c.tempty),
                 len(self.output), tuple(tuple(c.reads_left) + tuple(c.tmem_readers) for cl in self.clusters for c in cl))
+
+
+# =====================================================================================================================
+# The TMA-fed FFMA kernel (csrc/sgemm_ffma_tma.cuh): one block, one tile.
+#
+# * producer        waits ``empty[s]``, arms ``full[s]``, its two copies land later and asynchronously (A tile; raw B);
+# * transposing warps (an untransposed B only) wait ``full[s]``, read the raw buffer, write the B tile, arrive on ``ready[s]``;
+# * consumer warps  wait ``full[s]`` (and ``ready[s]``), read the A and B tiles, arrive on ``empty[s]``.
+#
+# Register hand-over: every scheduler partition holds one warp of the first group and ``consumer_groups`` consumer
+# warps, all launched with ``regs_launch`` registers per lane.  ``setmaxnreg.dec`` returns registers to the partition's
+# share of the block's allocation, ``setmaxnreg.inc`` waits until that share holds enough — without limit, which is why a
+# budget that asks for more than the launch allocation must show up here as a deadlock and not on a GPU.
+# =====================================================================================================================
+class FfmaModel:
+    def __init__(self, steps: int, stages: int, consumer_warps: int = 8, transpose: bool = True, seed: int = 0,
+                 bug: str = "", regs_launch: int = 168, regs_small: int = 40, regs_consumer: int = 232, handover: bool = True):
+        self.steps, self.stages, self.consumer_warps, self.transpose, self.bug = steps, stages, consumer_warps, transpose, bug
+        self.rng = random.Random(seed)
+        self.full = [Mbarrier(1, f"full{s}") for s in range(stages)]
+        self.ready = [Mbarrier(3, f"ready{s}") for s in range(stages)]
+        self.empty = [Mbarrier(consumer_warps - (1 if bug == "empty_count_short" else 0), f"empty{s}") for s in range(stages)]
+        self.a_tile: List[Optional[int]] = [None] * stages      # step whose data the buffer holds
+        self.raw: List[Optional[int]] = [None] * stages
+        self.b_tile: List[Optional[int]] = [None] * stages
+        self.xform_parts: List[int] = [0] * stages               # transposing warps that have written their part
+        self.readers: List[int] = [0] * stages                   # consumer warps inside the stage
+        self.xform_readers: List[int] = [0] * stages
+        self.pending_async: List = []
+        self.consumed = [0] * consumer_warps
+        # registers per lane in one scheduler partition: one warp of the first group + consumer_warps / 4 consumer warps
+        self.handover = handover
+        self.regs_launch, self.regs_small, self.regs_consumer = regs_launch, regs_small, regs_consumer
+        self.free_regs = 0                                        # released and not yet taken (the launch allocation is all in use)
+
+    # ------------------------------------------------------------------------------------------------ roles
+    def first_group_warp(self, role):
+        """A warp of the first group: shrink, then its role."""
+        if self.handover:
+            self.free_regs += self.regs_launch - self.regs_small
+            yield
+        yield from role
+
+    def consumer_warp(self, w):
+        if self.handover:
+            need = self.regs_consumer - self.regs_launch
+            while self.free_regs < need:                          # setmaxnreg.inc: no limit on this wait
+                yield
+            self.free_regs -= need
+            yield
+        yield from self.consumer(w)
+
+    def producer(self):
+        for t in range(self.steps):
+            s, rnd = t % self.stages, t // self.stages
+            while not self.empty[s].try_wait((rnd & 1) ^ 1):
+                yield
+            if self.readers[s] or self.xform_readers[s]:
+                raise ProtocolError(f"producer refills stage {s} while it is being read")
+            self.full[s].arrive(tx=2)
+
+            def land_a(s=s, t=t):
+                self.a_tile[s] = t
+                self.full[s].complete_tx(1)
+
+            def land_b(s=s, t=t):
+                if self.transpose:
+                    self.raw[s] = t
+                else:
+                    self.b_tile[s] = t
+                self.full[s].complete_tx(1)
+            self.pending_async += [land_a, land_b]
+            yield
+
+    def transposer(self, w):
+        for t in range(self.steps):
+            s, rnd = t % self.stages, t // self.stages
+            while not self.full[s].try_wait(rnd & 1):
+                yield
+            if self.raw[s] != t:
+                raise ProtocolError(f"transposing warp {w} finds step {self.raw[s]} in the raw buffer of stage {s}, wants {t}")
+            if self.readers[s]:
+                raise ProtocolError(f"transposing warp {w} rewrites the B tile of stage {s} while consumers read it")
+            self.xform_readers[s] += 1
+            yield
+            self.xform_readers[s] -= 1
+            self.xform_parts[s] += 1
+            if self.xform_parts[s] == 3:
+                self.b_tile[s], self.xform_parts[s] = t, 0
+            self.ready[s].arrive()
+            yield
+
+    def consumer(self, w):
+        for t in range(self.steps):
+            s, rnd = t % self.stages, t // self.stages
+            while not self.full[s].try_wait(rnd & 1):
+                yield
+            if self.transpose and self.bug != "ready_not_waited":
+                while not self.ready[s].try_wait(rnd & 1):
+                    yield
+            if self.a_tile[s] != t or self.b_tile[s] != t:
+                raise ProtocolError(f"consumer warp {w}, step {t}: stage {s} holds A of {self.a_tile[s]}, B of {self.b_tile[s]}")
+            self.readers[s] += 1
+            yield
+            self.readers[s] -= 1
+            self.consumed[w] += 1
+            self.empty[s].arrive()
+            yield
+
+    # -------------------------------------------------------------------------------------------- scheduler
+    def run(self, max_steps: int = 1_000_000):
+        roles = [self.first_group_warp(self.producer())]
+        roles += [self.first_group_warp(self.transposer(w) if self.transpose else iter(())) for w in range(3)]
+        # (registers are pooled over the four scheduler partitions here: each holds one warp of the first group and
+        # consumer_warps / 4 consumer warps, so the sums scale alike and the block-wide balance is the partition's)
+        roles += [self.consumer_warp(w) for w in range(self.consumer_warps)]
+        idle = 0
+        for _ in range(max_steps):
+            if not roles and not self.pending_async:
+                break
+            progressed = False
+            if self.pending_async and (not roles or self.rng.random() < 0.4):
+                self.pending_async.pop(self.rng.randrange(len(self.pending_async)))()
+                progressed = True
+            elif roles:
+                r = self.rng.choice(roles)
+                before = self._state()
+                try:
+                    next(r)
+                except StopIteration:
+                    roles.remove(r)
+                progressed = self._state() != before or r not in roles
+            idle = 0 if progressed else idle + 1
+            if idle > 20000:
+                raise ProtocolError("deadlock: no role makes progress")
+        else:
+            raise ProtocolError("did not finish")
+        if self.consumed != [self.steps] * self.consumer_warps:
+            raise ProtocolError("not every consumer warp multiplied every step exactly once")
+        return True
+
+    def _state(self):
+        return (len(self.pending_async), self.free_regs, tuple(self.consumed), tuple(self.readers), tuple(self.xform_readers),
+                tuple((b.phase, b.pending, b.tx) for b in self.full + self.ready + self.empty))
