@@ -111,7 +111,7 @@ def test_kernel_recommendation_names_registered_kernels(built):
         assert built.recommend(*shape) in built.REGISTRY
     # strict FP32: the FFMA variant; the TMA-fed kernel where the tuner measured it fastest or the problem has many tiles
     strict = {(8192, 8192, 8192): "ffma_tma_256x128x32_s3", (32768, 32768, 8192): "ffma_tma_256x128x32_s3",
-              (4096, 4096, 4096): "simt_128x128x16", (100, 100, 100): "simt_128x128x16"}
+              (4096, 4096, 4096): "simt_128x128x16_t16x8", (100, 100, 100): "simt_128x128x16"}
     for shape, want in strict.items():
         assert built.recommend(*shape, strict_fp32=True) == want, shape
     with pytest.raises(ValueError):
