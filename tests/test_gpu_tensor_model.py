@@ -87,7 +87,8 @@ def test_tensor_kernels_equal_the_model_bit_for_bit(runner_of, kernel, force, mn
 
 
 @pytest.mark.parametrize("kernel,bk", [("simt_128x128x16", 16), ("simt_64x64x16", 16), ("simt_128x64x8_plr0", 8),
-                                       ("legacy_32x32x2_1wave", None), ("simt_64x64x16_tt", 16)])
+                                       ("legacy_32x32x2_1wave", None), ("simt_64x64x16_tt", 16),
+                                       ("ffma_tma_128x128x16_s4", 16), ("ffma_tma_256x128x32_s3", 32)])   # (TMA-fed where lda, ldb allow)
 @pytest.mark.parametrize("mnk", [(96, 80, 72), (33, 65, 129), (130, 4, 300)])
 @pytest.mark.parametrize("alpha,beta,split_k", [(1.0, 0.0, 1), (0.75, -1.25, 1), (-2.5, 0.3, 3)])
 def test_simt_kernels_equal_the_fma_chain_bit_for_bit(runner_of, built, kernel, bk, mnk, alpha, beta, split_k):
