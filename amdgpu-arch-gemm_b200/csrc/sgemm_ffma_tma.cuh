@@ -1,18 +1,17 @@
 // ---------------------------------------------------------------------------------------------
-// TMA-fed, warp-specialised pure-FFMA SGEMM (strict FP32).  Same arithmetic, thread tiles and epilogue as the
-// FFMA kernel of sgemm_simt.cuh (which must precede this file in the translation unit: ffma_outer_product2 and
-// ffma_epilogue are defined there), but the operand tiles are not carried through
-// registers: one producer thread issues two TMA box copies per k-step into a ring of FT_STAGES shared-memory stages
-// and the FT_CONSUMERS consumer threads only read fragments and multiply.  Stages are handed over with mbarriers
-// ("full": the copies' bytes have landed; "ready": the B tile has been transposed, where that is needed; "empty":
-// every consumer warp has read the stage), so the block has no
-// block-wide barrier in its main loop, no global loads or shared stores in the multiplying warps, and copies run
+// TMA-fed, warp-specialised pure-FFMA SGEMM (strict FP32).  Same arithmetic, thread tiles and epilogue as the FFMA kernel
+// of sgemm_simt.cuh (which must precede this file in the translation unit: ffma_outer_product2 and ffma_epilogue are
+// defined there), but the operand tiles are not carried through registers: one producer thread issues two TMA box
+// copies per k-step into a ring of FT_STAGES shared-memory stages and the FT_CONSUMERS consumer threads only read
+// fragments and multiply.  Stages are handed over with mbarriers ("full": the copies' bytes have landed; "ready": the
+// B tile has been transposed, where that is needed; "empty": every consumer warp has read the stage), so the block has
+// no block-wide barrier in its main loop, no global loads or shared stores in the multiplying warps, and copies run
 // FT_STAGES - 1 steps ahead of the arithmetic.
 //
 // What TMA can describe decides who may use this kernel: FP32 operands with 16-byte aligned bases and leading
-// dimensions that are multiples of 4; A stored untransposed.  The runner launches the register-fed kernel of the
-// same cubin for everything else.  M, N and K themselves are arbitrary: a box that reaches
-// past the matrix is zero-filled by TMA, and the epilogue guards rows and columns.
+// dimensions that are multiples of 4; A stored untransposed.  The runner launches the register-fed kernel of the same
+// cubin for everything else.  M, N and K themselves are arbitrary: a box that reaches past the matrix is zero-filled by
+// TMA, and the epilogue guards rows and columns.
 //
 // Stage layout (floats):  A tile [FT_BK][FT_BM] (box {BM, BK} of the M x K matrix: row = one k), then the B tile
 // [FT_BK][FT_BN] (row = one k) in which every thread finds the FT_TN values of a k-slice in 16-byte vectors:
@@ -28,13 +27,14 @@
 // be in flight and returns without writing D.
 //
 // Warps: the first group of four holds the producer (warp 0, one lane) and the transposing warps 1 to 3 (idle when B
-// needs no transposing), the consumers follow.  Registers can be handed from one role to another only in groups of four warps (setmaxnreg), and every
-// scheduler partition holds one warp of each group: the first group shrinks to FT_REGS_PRODUCER registers per thread and
-// the consumers grow to FT_REGS_CONSUMER, which is what lets 256 consumers hold 16 x 8 accumulators each.  One block per
-// SM (a tile lasts about a millisecond at K = 8192, its prologue and epilogue a few microseconds).
+// needs no transposing), the consumers follow.  Registers can be handed from one role to another only in groups of
+// four warps (setmaxnreg), and every scheduler partition holds one warp of each group: the first group shrinks to
+// FT_REGS_PRODUCER registers per thread and the consumers grow to FT_REGS_CONSUMER, which is what lets 256 consumers hold
+// 16 x 8 accumulators each.  One block per SM (a tile lasts about a millisecond at K = 8192, its prologue and epilogue
+// a few microseconds).
 //
-// Generator-supplied macros: FT_ENTRY, FT_BM, FT_BN, FT_BK (block tile), FT_TM, FT_TN (thread tile: 4 x 4 blocks strided over
-// the block tile, as in the register-fed kernel), FT_STAGES.
+// Generator-supplied macros: FT_ENTRY, FT_BM, FT_BN, FT_BK (block tile), FT_TM, FT_TN (thread tile: 4 x 4 blocks strided
+// over the block tile, as in the register-fed kernel), FT_STAGES.
 // Launch: grid (tiles_m * tiles_n, 1, split_k), block FT_THREADS, FT_SMEM_BYTES of dynamic shared memory.
 // ---------------------------------------------------------------------------------------------
 #ifndef FT_STAGES
@@ -49,7 +49,7 @@
 #define FT_GN (FT_TN / 4)
 #define FT_CONSUMERS (FT_TX * FT_TY)
 #define FT_CONSUMER_WARPS (FT_CONSUMERS / 32)
-#define FT_FIRST_CONSUMER 128                 // threads of the first warp group (producer + three idle warps)
+#define FT_FIRST_CONSUMER 128                 // threads of the first warp group (producer + three transposing warps)
 #define FT_THREADS (FT_FIRST_CONSUMER + FT_CONSUMERS)
 // Register hand-over.  Every scheduler partition holds one warp of the first group and FT_CONSUMERS / 128 consumer warps,
 // and owns 512 registers per lane; __launch_bounds__ lets ptxas give every thread FT_REGS_LAUNCH of them, which is what
