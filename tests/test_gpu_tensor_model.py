@@ -104,6 +104,8 @@ def test_simt_kernels_equal_the_fma_chain_bit_for_bit(runner_of, built, kernel, 
     b, ldb = stored(colmajor(b_mat), k, n, t)
     r = runner_of(kernel)
     d = run(r, a, b, colmajor(c_mat), m, n, k, alpha, beta, force=SIMT, split_k=split_k, lda=lda, ldb=ldb)
+    if kernel.startswith("ffma_tma") and not r.info("last_feed_tma"):
+        bk = 16   # operands TMA cannot describe ran on the cubin's register-fed kernel, whose k per stage cuts the splits
     want = tensor_model.simt_gemm(a_mat, b_mat, c_mat, alpha, beta, split_k=r.info("last_split_k"), bk=bk)
     assert np.array_equal(as_matrix(d, m, n), want)
 
